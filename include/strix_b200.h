@@ -1,0 +1,232 @@
+/* strix_b200.h - C ABI of the B200 (sm_100a) implementation of strixite's quantized MoE FFN path.
+ *
+ * Every entry point is the `extern "C"` twin of one launcher in the reference's namespace
+ * strix::kernels (the reference file:line is cited at each declaration).  Arguments keep the
+ * reference's order and meaning; what changes is only what a C ABI forces:
+ *   - `const Q4DeviceView &` / `const Q8DeviceView &` become `const SxbQView *` (same fields, same order:
+ *     runtime/q4_device.hpp:14-19, runtime/q8_device.hpp:13-18);
+ *   - `Act`, `MoeMath` become int (SXB_ACT_*, SXB_MATH_*; kernels/norm.hpp:20, kernels/moe_grouped.hpp:39);
+ *   - `hipStream_t` becomes `sxb_stream_t`, a `cudaStream_t` passed as void *;
+ *   - a thrown strix::Error becomes a non-zero return code; sxb_last_error() returns the message
+ *     ("function (file:line): check `cond` failed: what was expected, what was found", common/check.hpp:59-62).
+ *
+ * Ownership, as in the reference (kernels/moe_grouped.hpp:84-87, runtime/qwen4exp.cpp:1092-1101): the caller owns
+ * every buffer - weights, activations, ids / coef, the grouping workspace, the combine's `partial`, the error
+ * words.  Unless a declaration says otherwise, no entry point allocates, frees or synchronizes; all work is enqueued
+ * on the caller's stream.  Exceptions: sxb_check_*_error (a blocking 12-byte copy, as the reference's).
+ *
+ * Error words (`err`): >= 3 zeroed uint32 on the device, zeroed by the caller at session start.  A data error on the
+ * device sets err[0] = 1, err[1], err[2] (first writer wins), poisons the affected outputs with NaN and never reads
+ * out of bounds (kernels/moe_router.hpp:19-23, kernels/linear_q4.hpp:39-41, kernels/moe_grouped.hpp:13-15).
+ *
+ * Threading: one host thread at a time per stream, as the reference's session (serve/seq_backend.hpp:7-9).  The
+ * library keeps no per-device state except lazily cached function attributes, so several devices may be driven
+ * from one process (one current device per call).
+ */
+#ifndef STRIX_B200_H
+#define STRIX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default) /* the library itself is built with -fvisibility=hidden */
+#endif
+
+typedef void *sxb_stream_t; /* cudaStream_t */
+
+/* Return codes. */
+enum {
+    SXB_OK = 0,
+    SXB_ERR_CHECK = 1, /* a precondition failed before any launch (the reference throws strix::Error) */
+    SXB_ERR_CUDA = 2,  /* a CUDA call or launch failed (the reference's STRIX_HIP_CHECK_LAUNCH) */
+    SXB_ERR_FATAL = 3, /* a sticky CUDA error: the context is gone (the reference's GpuFatalError) */
+    SXB_ERR_DATA = 4   /* sxb_check_* / sxb_report_*: the device error words are set */
+};
+
+/* kernels/norm.hpp:20  enum class Act { F32, BF16 }.  BF16 buffers hold raw uint16_t bits. */
+enum { SXB_ACT_F32 = 0, SXB_ACT_BF16 = 1 };
+
+/* kernels/moe_grouped.hpp:39  enum class MoeMath.  Here:
+ *   F32, WMMA_BF16            exact products: BF16 activations times the integer codes on mma.sync tensor cores,
+ *                             scale / min applied per group in FP32, FP32 accumulation (the reference's
+ *                             "exact weights" semantics; only the summation order differs from its FP32 kernels);
+ *   WMMA_F16 and its kinds    activations as F16, weights dequantized to F16 (code * scale + min, one rounding),
+ *                             FP32 accumulation in tensor memory on tcgen05 tensor cores.  Narrow / Wide / Wide256
+ *                             are accepted for source compatibility and select the same kernel. */
+enum {
+    SXB_MATH_F32 = 0,
+    SXB_MATH_WMMA_BF16 = 1,
+    SXB_MATH_WMMA_F16 = 2,
+    SXB_MATH_WMMA_F16_NARROW = 3,
+    SXB_MATH_WMMA_F16_WIDE = 4,
+    SXB_MATH_WMMA_F16_WIDE256 = 5
+};
+
+/* runtime/q4_device.hpp:14-19 (Q4DeviceView) and runtime/q8_device.hpp:13-18 (Q8DeviceView): a non-owning view of
+ * a row-major quantized matrix W [N, K] with groups of G codes along K (formats/q4.hpp:3-8, formats/q8.hpp:3-11):
+ *   Q4: q [N, K/2] bytes, low nibble = even k;   Q8: q [N, K] bytes;
+ *   scale, minv [N, K/G] BF16 bits;   w[n, k] = code * scale[n, k/G] + minv[n, k/G].
+ * Experts are stacked along N: expert e = rows e*N/E .. (e+1)*N/E - 1 (kernels/linear_q4.hpp:32-35). */
+typedef struct SxbQView {
+    const uint8_t *q;
+    const uint16_t *scale;
+    const uint16_t *minv;
+    int64_t N, K, G;
+} SxbQView;
+
+/* kernels/moe_grouped.hpp:75-81  struct MoeSharedAdd. */
+typedef struct SxbMoeSharedAdd {
+    const void *s;           /* the shared expert's output [M, N], activation dtype, not overlapping y */
+    const float *gate_logit; /* token m's gate logit at gate_logit[m * gate_ld] */
+    int64_t gate_ld;
+    uint32_t gate_index;
+    uint32_t *err;
+} SxbMoeSharedAdd;
+
+/* The message of the calling thread's last failed call ("" if none).  Valid until that thread's next failure. */
+const char *sxb_last_error(void);
+/* "strix_b200 <version> sm_100a" */
+const char *sxb_version(void);
+
+/* ---- Router ------------------------------------------------------------------------------------------------ */
+
+/* kernels/moe_router.hpp:38-40  moe_router.  Top-k on the logits (larger first, a tie to the lower index), coef =
+ * softmax over the k picks; optional shared slot k (id = shared_id, coef = sigmoid(gate logit)).  ids [M, A] int32,
+ * coef [M, A] F32, A = k + (shared_logit != NULL).  1 <= E <= 1024, 1 <= k <= min(E, 32), ld >= E.  A non-finite
+ * logit: that token's ids -1, coef NaN, err = {1, token, expert index (E = the shared logit)}. */
+int sxb_moe_router(const void *logits, int64_t ld, int64_t M, int64_t E, int64_t k, const void *shared_logit,
+                   int64_t shared_ld, int32_t shared_id, int32_t *ids, float *coef, int act, uint32_t *err,
+                   sxb_stream_t stream);
+/* kernels/moe_router.hpp:41-43  check_router_error (synchronizes: copies the 3 words) / report_router_error (the 3
+ * words already on the host).  Return SXB_ERR_DATA with the reference's message when err[0] != 0. */
+int sxb_check_router_error(const uint32_t *err, const char *what);
+int sxb_report_router_error(const uint32_t e[3], const char *what);
+
+/* kernels/moe_router.hpp:53-54  moe_shared_add:  y[m, :] += sigmoid(gate_logit[m * gate_ld]) * s[m, :]. */
+int sxb_moe_shared_add(void *y, const void *s, const float *gate_logit, int64_t gate_ld, int64_t M, int64_t N,
+                       uint32_t gate_index, int act, uint32_t *err, sxb_stream_t stream);
+/* kernels/moe_router.hpp:61-63  moe_shared_add_inject: the add, then x[m, st*N + n] = fma(w_in[m, st], y, x) for the
+ * H = 4 residual streams of x [M, H*N]. */
+int sxb_moe_shared_add_inject(void *y, const void *s, const float *gate_logit, int64_t gate_ld, int64_t M, int64_t N,
+                              uint32_t gate_index, void *x, const float *w_in, int64_t H, int act, uint32_t *err,
+                              sxb_stream_t stream);
+
+/* ---- Pack (grouping of slots by expert) --------------------------------------------------------------------- */
+
+/* kernels/moe_grouped.hpp:48  moe_route_workspace_bytes.  Returns 0 and sets the error message on bad arguments.
+ * The workspace layout is this library's own (see sxb_route_layout). */
+size_t sxb_moe_route_workspace_bytes(int64_t M, int64_t A, int64_t E);
+/* kernels/moe_grouped.hpp:53-54  moe_group_routes: counting sort of the S = M*A slots of ids [M, A] by expert into
+ * ws.  Bucket E collects ids outside [0, E) and raises err = {1, id, slot} for the first such slot in slot order.
+ * Unlike the reference (whose order inside a bucket is left to its atomics), slots inside a bucket are in ascending
+ * slot order, so the whole workspace is reproducible.  1 <= A <= 64, 1 <= E <= 1023, M*A <= 2^20. */
+int sxb_moe_group_routes(const int32_t *ids, int64_t M, int64_t A, int64_t E, void *ws, size_t ws_bytes, uint32_t *err,
+                         sxb_stream_t stream);
+/* No counterpart in the reference (which has one GPU).  The expert-parallel form: this rank owns experts
+ * [e_lo, e_lo + E_local) of E_total; bucket b = expert e_lo + b; slots of other ranks' experts and invalid ids go to
+ * bucket E_local.  err is raised only for ids outside [0, E_total). */
+int sxb_moe_group_routes_ep(const int32_t *ids, int64_t M, int64_t A, int64_t E_total, int64_t e_lo, int64_t E_local,
+                            void *ws, size_t ws_bytes, uint32_t *err, sxb_stream_t stream);
+/* Word offsets (int32 units) of the parts of a workspace for (M, A, E), for hosts that read it back:
+ * out[0] = header (8 words: n_tiles8, S, E, n_tiles128, ...), out[1] = offsets [E + 2], out[2] = slots [S],
+ * out[3] = tile8_bucket, out[4] = tile8_start, out[5] = tile128_bucket, out[6] = tile128_start, out[7] = total words. */
+int sxb_route_layout(int64_t M, int64_t A, int64_t E, int64_t out[8]);
+
+/* ---- Dense quantized linear --------------------------------------------------------------------------------- */
+
+/* kernels/linear_q4.hpp:26,30  linear_q4:  y [M, N] = x [M, K] * dequant(W)^T.  out_act == act, or BF16 x -> F32 y. */
+int sxb_linear_q4(const void *x, const SxbQView *w, void *y, int64_t M, int act, int out_act, sxb_stream_t stream);
+/* kernels/linear_q8.hpp:13-14  linear_q8. */
+int sxb_linear_q8(const void *x, const SxbQView *w, void *y, int64_t M, int act, int out_act, sxb_stream_t stream);
+
+/* kernels/swiglu.hpp:21  swiglu: gu [rows, 2I] = [gate | up] -> h [rows, I]; BF16: h = bf16(bf16(silu(g)) * u). */
+int sxb_swiglu(const void *gu, void *h, int64_t rows, int64_t I, int act, sxb_stream_t stream);
+
+/* ---- Experts, per-slot form (decode) ------------------------------------------------------------------------ */
+
+/* kernels/linear_q4.hpp:42-43  linear_q4_experts_gather:  y[m, a, :] = x[m, :] * W[ids[m, a]]^T. */
+int sxb_linear_q4_experts_gather(const void *x, const SxbQView *w, int64_t E, const int32_t *ids, int64_t M, int64_t A,
+                                 void *y, int act, uint32_t *err, sxb_stream_t stream);
+/* kernels/linear_q4.hpp:55-56  linear_q4_experts_gather_swiglu:  h [M, A, N/2] = silu(gate) * up of the merged
+ * [gate | up] expert rows, g and u rounded as stored, then h = stored(stored(silu(g)) * u). */
+int sxb_linear_q4_experts_gather_swiglu(const void *x, const SxbQView *w, int64_t E, const int32_t *ids, int64_t M,
+                                        int64_t A, void *h, int act, uint32_t *err, sxb_stream_t stream);
+/* kernels/linear_q4.hpp:44-46  linear_q4_experts_combine:  y[m, :] = sum_a coef[m, a] * h[m, a, :] * W[ids[m, a]]^T.
+ * out_act (not in the reference, which stores y in `act`): SXB_ACT_F32 keeps the FP32 sum unrounded. */
+int sxb_linear_q4_experts_combine(const void *h, const SxbQView *w, int64_t E, const int32_t *ids, const float *coef,
+                                  int64_t M, int64_t A, void *y, int act, int out_act, uint32_t *err,
+                                  sxb_stream_t stream);
+/* The same three for Q8 experts.  No counterpart in the reference (its experts are Q4 / Q5 only:
+ * runtime/qweight.hpp:80-100); same semantics with codes 0..255. */
+int sxb_linear_q8_experts_gather(const void *x, const SxbQView *w, int64_t E, const int32_t *ids, int64_t M, int64_t A,
+                                 void *y, int act, uint32_t *err, sxb_stream_t stream);
+int sxb_linear_q8_experts_gather_swiglu(const void *x, const SxbQView *w, int64_t E, const int32_t *ids, int64_t M,
+                                        int64_t A, void *h, int act, uint32_t *err, sxb_stream_t stream);
+int sxb_linear_q8_experts_combine(const void *h, const SxbQView *w, int64_t E, const int32_t *ids, const float *coef,
+                                  int64_t M, int64_t A, void *y, int act, int out_act, uint32_t *err,
+                                  sxb_stream_t stream);
+/* kernels/linear_q4.hpp:59-61  check_expert_error / report_expert_error. */
+int sxb_check_expert_error(const uint32_t *err, const char *what);
+int sxb_report_expert_error(const uint32_t e[3], const char *what);
+
+/* ---- Experts, grouped form (multi-token forwards) ----------------------------------------------------------- */
+
+/* kernels/moe_grouped.hpp:58-60  linear_q4_experts_gather_grouped (ws from sxb_moe_group_routes, same ids/M/A/E). */
+int sxb_linear_q4_experts_gather_grouped(const void *x, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes,
+                                         int64_t M, int64_t A, void *y, int act, int math, sxb_stream_t stream);
+/* kernels/moe_grouped.hpp:67-69  linear_q4_experts_gather_grouped_swiglu.  With a WMMA_F16 math: h = silu(g) * u from
+ * the FP32 accumulators, rounded once; h_f16: h stored as F16 bits of its BF16 rounding.  With SXB_MATH_F32 /
+ * WMMA_BF16 (an extension: the reference refuses them here) the decode form's rounding points are kept. */
+int sxb_linear_q4_experts_gather_grouped_swiglu(const void *x, const SxbQView *w, int64_t E, const void *ws,
+                                                size_t ws_bytes, int64_t M, int64_t A, void *h, int act, int math,
+                                                sxb_stream_t stream, int h_f16);
+/* kernels/moe_grouped.hpp:88-91  linear_q4_experts_combine_grouped.  partial: M*A*N FP32 scratch owned by the caller
+ * (the per-slot dots); y[m, :] = sum_a fma(coef[m, a], partial[m*A + a, :]) in slot order, one rounding, optionally
+ * + sigmoid(gate) * s (shared).  out_act as for sxb_linear_q4_experts_combine. */
+int sxb_linear_q4_experts_combine_grouped(const void *h, const SxbQView *w, int64_t E, const int32_t *ids,
+                                          const float *coef, const void *ws, size_t ws_bytes, float *partial,
+                                          int64_t M, int64_t A, void *y, int act, int out_act, int math,
+                                          sxb_stream_t stream, const SxbMoeSharedAdd *shared, int h_f16);
+/* The same three for Q8 experts (no counterpart in the reference, see above). */
+int sxb_linear_q8_experts_gather_grouped(const void *x, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes,
+                                         int64_t M, int64_t A, void *y, int act, int math, sxb_stream_t stream);
+int sxb_linear_q8_experts_gather_grouped_swiglu(const void *x, const SxbQView *w, int64_t E, const void *ws,
+                                                size_t ws_bytes, int64_t M, int64_t A, void *h, int act, int math,
+                                                sxb_stream_t stream, int h_f16);
+int sxb_linear_q8_experts_combine_grouped(const void *h, const SxbQView *w, int64_t E, const int32_t *ids,
+                                          const float *coef, const void *ws, size_t ws_bytes, float *partial,
+                                          int64_t M, int64_t A, void *y, int act, int out_act, int math,
+                                          sxb_stream_t stream, const SxbMoeSharedAdd *shared, int h_f16);
+
+/* No counterpart in the reference (one GPU).  The combine for an expert-parallel rank that holds experts
+ * [e_lo, e_lo + E_local) of E_total in w (ws from sxb_moe_group_routes_ep): slots routed to other ranks' experts add
+ * nothing, so y is this rank's partial sum of every token's row (zeros for tokens it serves no expert of); an id
+ * outside [0, E_total) still makes the row NaN. */
+int sxb_linear_q4_experts_combine_grouped_ep(const void *h, const SxbQView *w, int64_t E_local, int64_t E_total,
+                                             int64_t e_lo, const int32_t *ids, const float *coef, const void *ws,
+                                             size_t ws_bytes, float *partial, int64_t M, int64_t A, void *y, int act,
+                                             int out_act, int math, sxb_stream_t stream, int h_f16);
+int sxb_linear_q8_experts_combine_grouped_ep(const void *h, const SxbQView *w, int64_t E_local, int64_t E_total,
+                                             int64_t e_lo, const int32_t *ids, const float *coef, const void *ws,
+                                             size_t ws_bytes, float *partial, int64_t M, int64_t A, void *y, int act,
+                                             int out_act, int math, sxb_stream_t stream, int h_f16);
+
+/* ---- Quantizers on the device ------------------------------------------------------------------------------- */
+
+/* formats/q4.hpp:32 quantize_q4 / formats/q8.hpp:32 quantize_q8, for weights already on the device: w [N, K] FP32 ->
+ * codes, scales, mins, bit-identical to the reference's host quantizers (IEEE division, round half to even).
+ * bits = 4 or 8; G = 32, 64 or 128; K % G == 0.  Non-finite input sets err = {1, row, column}. */
+int sxb_quantize(const float *w, int64_t N, int64_t K, int64_t G, int bits, uint8_t *q, uint16_t *scale,
+                 uint16_t *minv, uint32_t *err, sxb_stream_t stream);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* STRIX_B200_H */

@@ -1,0 +1,82 @@
+"""ctypes binding of libstrix_b200.so, the C ABI declared in include/strix_b200.h.
+
+The library is the product: there is no fallback.  Importing this module without the built library raises, and so
+does any call when the loaded library reports an error.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import pathlib
+
+_PKG = pathlib.Path(__file__).resolve().parent
+LIB_PATH = _PKG / "libstrix_b200.so"
+
+i64, i32, u32, sz, vp, cp = C.c_int64, C.c_int32, C.c_uint32, C.c_size_t, C.c_void_p, C.c_char_p
+
+
+class SxbQView(C.Structure):
+    """runtime/q4_device.hpp:14-19 Q4DeviceView / runtime/q8_device.hpp:13-18 Q8DeviceView."""
+
+    _fields_ = [("q", vp), ("scale", vp), ("minv", vp), ("N", i64), ("K", i64), ("G", i64)]
+
+
+class SxbMoeSharedAdd(C.Structure):
+    """kernels/moe_grouped.hpp:75-81 MoeSharedAdd."""
+
+    _fields_ = [("s", vp), ("gate_logit", vp), ("gate_ld", i64), ("gate_index", u32), ("err", vp)]
+
+
+QV = C.POINTER(SxbQView)
+SA = C.POINTER(SxbMoeSharedAdd)
+
+# name -> (restype, argtypes); mirrors include/strix_b200.h declaration by declaration.
+SIGNATURES = {
+    "sxb_last_error": (cp, []),
+    "sxb_version": (cp, []),
+    "sxb_moe_router": (C.c_int, [vp, i64, i64, i64, i64, vp, i64, i32, vp, vp, C.c_int, vp, vp]),
+    "sxb_check_router_error": (C.c_int, [vp, cp]),
+    "sxb_report_router_error": (C.c_int, [C.POINTER(u32), cp]),
+    "sxb_moe_shared_add": (C.c_int, [vp, vp, vp, i64, i64, i64, u32, C.c_int, vp, vp]),
+    "sxb_moe_shared_add_inject": (C.c_int, [vp, vp, vp, i64, i64, i64, u32, vp, vp, i64, C.c_int, vp, vp]),
+    "sxb_moe_route_workspace_bytes": (sz, [i64, i64, i64]),
+    "sxb_moe_group_routes": (C.c_int, [vp, i64, i64, i64, vp, sz, vp, vp]),
+    "sxb_moe_group_routes_ep": (C.c_int, [vp, i64, i64, i64, i64, i64, vp, sz, vp, vp]),
+    "sxb_route_layout": (C.c_int, [i64, i64, i64, C.POINTER(i64)]),
+    "sxb_linear_q4": (C.c_int, [vp, QV, vp, i64, C.c_int, C.c_int, vp]),
+    "sxb_linear_q8": (C.c_int, [vp, QV, vp, i64, C.c_int, C.c_int, vp]),
+    "sxb_swiglu": (C.c_int, [vp, vp, i64, i64, C.c_int, vp]),
+    "sxb_check_expert_error": (C.c_int, [vp, cp]),
+    "sxb_report_expert_error": (C.c_int, [C.POINTER(u32), cp]),
+    "sxb_quantize": (C.c_int, [vp, i64, i64, i64, C.c_int, vp, vp, vp, vp, vp]),
+}
+for _b in ("q4", "q8"):
+    SIGNATURES[f"sxb_linear_{_b}_experts_gather"] = (C.c_int, [vp, QV, i64, vp, i64, i64, vp, C.c_int, vp, vp])
+    SIGNATURES[f"sxb_linear_{_b}_experts_gather_swiglu"] = (C.c_int, [vp, QV, i64, vp, i64, i64, vp, C.c_int, vp, vp])
+    SIGNATURES[f"sxb_linear_{_b}_experts_combine"] = (
+        C.c_int, [vp, QV, i64, vp, vp, i64, i64, vp, C.c_int, C.c_int, vp, vp])
+    SIGNATURES[f"sxb_linear_{_b}_experts_gather_grouped"] = (
+        C.c_int, [vp, QV, i64, vp, sz, i64, i64, vp, C.c_int, C.c_int, vp])
+    SIGNATURES[f"sxb_linear_{_b}_experts_gather_grouped_swiglu"] = (
+        C.c_int, [vp, QV, i64, vp, sz, i64, i64, vp, C.c_int, C.c_int, vp, C.c_int])
+    SIGNATURES[f"sxb_linear_{_b}_experts_combine_grouped"] = (
+        C.c_int, [vp, QV, i64, vp, vp, vp, sz, vp, i64, i64, vp, C.c_int, C.c_int, C.c_int, vp, SA, C.c_int])
+    SIGNATURES[f"sxb_linear_{_b}_experts_combine_grouped_ep"] = (
+        C.c_int, [vp, QV, i64, i64, i64, vp, vp, vp, sz, vp, i64, i64, vp, C.c_int, C.c_int, C.c_int, vp, C.c_int])
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads the library once; raises if it has not been built (python -m strixite_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m strixite_b200.build` "
+                "(there is no CPU or PyTorch fallback for these kernels)")
+        lib = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)  # AttributeError here = header and library disagree
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib

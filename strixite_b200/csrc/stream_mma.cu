@@ -1,0 +1,670 @@
+// Streaming expert / dense kernels for the HBM-bound regime (decode and small ragged batches; also the exact-product
+// path at any size).  C ABI twins of the launchers in kernels/linear_q4.hpp, kernels/linear_q8.hpp and of the
+// MoeMath::F32 / WmmaBf16 forms of kernels/moe_grouped.hpp.
+//
+// What the reference does (kernels/linear_q4.hip:175-199): a wave walks one weight row, every lane takes 32 codes per
+// 16-byte load and forms s * sum(x*q) + m * sum(x) per chunk with one FMA per weight, then a wave-shuffle reduction.
+// On B200 that form is issue-bound long before HBM is: at 6.5 TB/s an SM receives ~46 codes per clock, and one FMA plus
+// the nibble -> float conversion per code and per token already exceeds the 128 FP32 lanes.
+//
+// This kernel keeps the same arithmetic - exact products of BF16 activations with the integer codes, FP32 sums, scale
+// and min applied per group in FP32 - but lets the tensor cores form the products:
+//   * a warp owns 16 weight rows; lane (g = lane / 4, c = lane % 4) streams rows g and g + 8 with one 16-byte
+//     `ld.global.nc` each per step, the four lanes of a quad covering 64 contiguous bytes of a row, which for the
+//     served formats (Q4 G = 128, Q8 G = 64) is exactly one quantization group;
+//   * nibbles become BF16 pairs in registers with one shift + one `lop3` per pair: (w >> 4s) & 0x000F000F | 0x43004300
+//     is the pair (128 + code, 128 + code') exactly; the 128 offset is removed in FP32 with the group's sum(x);
+//     a Q8 byte is split into its two nibbles and the high one meets 16 * x;
+//   * the activations of the tile's <= 8 tokens sit in shared memory already permuted into `mma.m16n8k16` B-fragment
+//     order, so a lane fetches its fragments with conflict-free 16-byte loads; k is permuted consistently on both
+//     operands, which a dot product does not notice;
+//   * per step: D = sum over the quad's codes of (128 + q) * x on the tensor cores, then
+//     acc += s * D + (m - 128 s) * sum(x) in FP32.
+// Work is cut into units of 16 rows x one tile of <= 8 tokens of one expert; CTAs take contiguous ranges of units so
+// a CTA restages activations only when it crosses into another tile, and every touched expert's weights are read
+// once per tile (once in total when an expert has <= 8 tokens, the decode case).
+
+#include "experts.cuh"
+
+#include <cuda_bf16.h>
+
+namespace sxb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kTileTokens = 8;
+constexpr int kPrefetch = 4;  // steps of weights in flight per warp beyond the one being consumed
+constexpr int64_t kMaxK = 1 << 24;
+constexpr int64_t kMaxN = 0x7fffffff;
+constexpr size_t kMaxDynSmem = 200 * 1024;
+
+enum Mode { kGather = 0, kSwiglu = 1, kPartial = 2 };
+enum Src { kFromWs = 0, kFromSlots = 1, kDense = 2, kPerToken = 3 };
+
+template <int BITS, int G>
+struct Geo {
+    static constexpr int kCodesPerLane = (BITS == 4 ? 32 : 16) < G / 4 ? (BITS == 4 ? 32 : 16) : G / 4;
+    static constexpr int kLoadBytes = kCodesPerLane * BITS / 8;  // 16, 8 or 4
+    static constexpr int kWords = kLoadBytes / 4;
+    static constexpr int kStepCodes = 4 * kCodesPerLane;  // codes of one row a quad consumes per step (<= G)
+    static constexpr int kUnits = kCodesPerLane / 8;      // 16-byte activation units per lane per step
+    static constexpr int kStepsPerGroup = G / kStepCodes;
+    static constexpr float kOffset = BITS == 4 ? 128.f : 128.f * 17.f;
+};
+
+template <int WORDS> __device__ inline void load_codes(uint32_t (&w)[WORDS], const uint8_t *p, bool pred);
+template <> __device__ inline void load_codes<4>(uint32_t (&w)[4], const uint8_t *p, bool pred) {
+    w[0] = w[1] = w[2] = w[3] = 0u;
+    if (pred)
+        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                     : "l"(p));
+}
+template <> __device__ inline void load_codes<2>(uint32_t (&w)[2], const uint8_t *p, bool pred) {
+    w[0] = w[1] = 0u;
+    if (pred) asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(w[0]), "=r"(w[1]) : "l"(p));
+}
+template <> __device__ inline void load_codes<1>(uint32_t (&w)[1], const uint8_t *p, bool pred) {
+    w[0] = 0u;
+    if (pred) asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(w[0]) : "l"(p));
+}
+
+__device__ inline void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Nibbles s and s + 4 of w as the BF16 pair (128 + n_s, 128 + n_{s+4}).
+template <int S> __device__ inline uint32_t nibble_pair(uint32_t w) { return ((w >> (4 * S)) & 0x000F000Fu) | 0x43004300u; }
+
+__device__ inline uint32_t times16(uint32_t bf16x2) {
+    __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162 *>(&bf16x2);
+    v = __hmul2(v, __float2bfloat162_rn(16.f));
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+struct StreamArgs {
+    const uint16_t *x;  // BF16 activations: x [M, K] (gather / dense) or h [M*A, K] (partial)
+    const uint8_t *q;
+    const uint16_t *scale, *minv;
+    int64_t N, K;        // rows per expert, codes per row
+    int64_t M, A, E;     // tokens, slots per token, experts in the view
+    const int32_t *ws;   // kFromWs
+    RouteWords L;
+    const int32_t *ids;  // kFromSlots, kPerToken
+    const float *coef;   // kPerToken
+    void *out;
+    uint32_t *err;
+};
+
+template <typename T> __device__ inline void store_out(T *p, int64_t i, float v) { store_from_f32(p, i, v); }
+
+// Stages up to 8 activation rows (rows[n] < 0 = none, zeros) into fragment order at xs / xsum.  All threads of the CTA.
+template <int BITS, int G>
+__device__ inline void stage_tile(const uint16_t *__restrict__ x, int K, const int64_t *rows, uint4 *xs, float *xsum) {
+    using geo = Geo<BITS, G>;
+    constexpr int UNITS = geo::kUnits, KI = geo::kStepCodes, CPL = geo::kCodesPerLane;
+    const int units_per_row = K / 8, steps = K / KI;
+    // 8 consecutive k of token n (16 bytes) -> one unit, permuted to match the nibble pairs of the weights.
+    for (int idx = threadIdx.x; idx < kTileTokens * units_per_row; idx += kThreads) {
+        const int n = idx / units_per_row, k8 = idx % units_per_row;
+        const int k = k8 * 8, step = k / KI, rem = k % KI, cc = rem / CPL, v = (rem % CPL) / 8;
+        uint4 src = make_uint4(0u, 0u, 0u, 0u);
+        const int64_t row = rows[n];
+        if (row >= 0) src = *reinterpret_cast<const uint4 *>(x + row * K + k);
+        uint4 dst;
+        if (BITS == 4) {  // [x0 x4 | x1 x5 | x2 x6 | x3 x7]
+            dst.x = __byte_perm(src.x, src.z, 0x5410), dst.y = __byte_perm(src.x, src.z, 0x7632);
+            dst.z = __byte_perm(src.y, src.w, 0x5410), dst.w = __byte_perm(src.y, src.w, 0x7632);
+        } else {  // [x0 x2 | x1 x3 | x4 x6 | x5 x7]
+            dst.x = __byte_perm(src.x, src.y, 0x5410), dst.y = __byte_perm(src.x, src.y, 0x7632);
+            dst.z = __byte_perm(src.z, src.w, 0x5410), dst.w = __byte_perm(src.z, src.w, 0x7632);
+        }
+        xs[(step * UNITS + v) * 32 + n * 4 + cc] = dst;
+    }
+    // sum(x) of every (step, token), in a fixed order.
+    for (int idx = threadIdx.x; idx < steps * kTileTokens; idx += kThreads) {
+        const int step = idx / kTileTokens, n = idx % kTileTokens;
+        const int64_t row = rows[n];
+        float sum = 0.f;
+        if (row >= 0) {
+            const uint4 *p = reinterpret_cast<const uint4 *>(x + row * K + (int64_t)step * KI);
+            for (int i = 0; i < KI / 8; ++i) {
+                const uint4 u = p[i];
+                const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) sum += __uint_as_float(w4[j] << 16), sum += __uint_as_float(w4[j] & 0xffff0000u);
+            }
+        }
+        xsum[idx] = sum;
+    }
+}
+
+// One warp: the dots of weight rows rowa / rowb (lane quad g streams both) with the staged tokens.
+// acc[0], acc[1] = row a x tokens 2c, 2c+1;  acc[2], acc[3] = row b x the same tokens.
+template <int BITS, int G>
+__device__ inline void rows_dot(float (&acc)[4], const StreamArgs &a, int64_t rowa, int64_t rowb, bool va, bool vb,
+                                const uint4 *xs, const float *xsum, int lane) {
+    using geo = Geo<BITS, G>;
+    constexpr int W = geo::kWords, UNITS = geo::kUnits, KI = geo::kStepCodes;
+    const int K = (int)a.K, steps = K / KI, groups = K / G, c = lane & 3;
+    const int64_t row_bytes = BITS == 4 ? a.K / 2 : a.K;
+    const uint8_t *pa = a.q + rowa * row_bytes + c * geo::kLoadBytes;
+    const uint8_t *pb = a.q + rowb * row_bytes + c * geo::kLoadBytes;
+    const uint16_t *sa = a.scale + rowa * groups, *ma = a.minv + rowa * groups;
+    const uint16_t *sb = a.scale + rowb * groups, *mb = a.minv + rowb * groups;
+
+    uint32_t wa[kPrefetch][W], wb[kPrefetch][W];
+    uint16_t qs[kPrefetch][4];
+    auto fetch = [&](int slot, int step) {
+        const bool in = step < steps;
+        load_codes<W>(wa[slot], pa + (int64_t)step * 4 * geo::kLoadBytes, in && va);
+        load_codes<W>(wb[slot], pb + (int64_t)step * 4 * geo::kLoadBytes, in && vb);
+        const int grp = step / geo::kStepsPerGroup;
+        qs[slot][0] = in && va ? __ldg(sa + grp) : (uint16_t)0;
+        qs[slot][1] = in && va ? __ldg(ma + grp) : (uint16_t)0;
+        qs[slot][2] = in && vb ? __ldg(sb + grp) : (uint16_t)0;
+        qs[slot][3] = in && vb ? __ldg(mb + grp) : (uint16_t)0;
+    };
+#pragma unroll
+    for (int p = 0; p < kPrefetch; ++p) fetch(p, p);
+    for (int step0 = 0; step0 < steps; step0 += kPrefetch) {
+#pragma unroll
+        for (int p = 0; p < kPrefetch; ++p) {
+            const int step = step0 + p;
+            if (step < steps) {
+                float d[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint4 *xu = xs + (size_t)step * UNITS * 32 + lane;
+#pragma unroll
+                for (int v = 0; v < UNITS; ++v) {
+                    const uint4 bx = xu[v * 32];
+                    if (BITS == 4) {
+                        const uint32_t x0 = wa[p][v], x1 = wb[p][v];
+                        mma_bf16(d, nibble_pair<0>(x0), nibble_pair<0>(x1), nibble_pair<1>(x0), nibble_pair<1>(x1), bx.x, bx.y);
+                        mma_bf16(d, nibble_pair<2>(x0), nibble_pair<2>(x1), nibble_pair<3>(x0), nibble_pair<3>(x1), bx.z, bx.w);
+                    } else {
+                        const uint32_t bw[4] = {bx.x, bx.y, bx.z, bx.w};
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const uint32_t x0 = wa[p][2 * v + h], x1 = wb[p][2 * v + h];
+                            mma_bf16(d, nibble_pair<0>(x0), nibble_pair<0>(x1), nibble_pair<1>(x0), nibble_pair<1>(x1),
+                                     bw[2 * h], times16(bw[2 * h]));
+                            mma_bf16(d, nibble_pair<2>(x0), nibble_pair<2>(x1), nibble_pair<3>(x0), nibble_pair<3>(x1),
+                                     bw[2 * h + 1], times16(bw[2 * h + 1]));
+                        }
+                    }
+                }
+                const float2 xs2 = *reinterpret_cast<const float2 *>(xsum + step * kTileTokens + 2 * c);
+                const float s_a = bf16_bits_to_f32(qs[p][0]), m_a = bf16_bits_to_f32(qs[p][1]);
+                const float s_b = bf16_bits_to_f32(qs[p][2]), m_b = bf16_bits_to_f32(qs[p][3]);
+                const float off_a = fmaf(-geo::kOffset, s_a, m_a), off_b = fmaf(-geo::kOffset, s_b, m_b);
+                acc[0] = fmaf(s_a, d[0], fmaf(off_a, xs2.x, acc[0]));
+                acc[1] = fmaf(s_a, d[1], fmaf(off_a, xs2.y, acc[1]));
+                acc[2] = fmaf(s_b, d[2], fmaf(off_b, xs2.x, acc[2]));
+                acc[3] = fmaf(s_b, d[3], fmaf(off_b, xs2.y, acc[3]));
+            }
+            fetch(p, step + kPrefetch);  // refill the slot just consumed
+        }
+    }
+}
+
+template <int BITS, int G, int MODE, int SRC, typename TOUT>
+__global__ void __launch_bounds__(kThreads, 2) stream_kernel(const StreamArgs a) {
+    using geo = Geo<BITS, G>;
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int K = (int)a.K, steps = K / geo::kStepCodes;
+    const size_t pass_bytes = (size_t)steps * geo::kUnits * 512 + (size_t)steps * kTileTokens * 4;
+    __shared__ int64_t s_row[kTileTokens];  // activation row of each token of the tile, -1 = none
+    __shared__ int64_t s_out[kTileTokens];  // output row (slot, or token for dense)
+    __shared__ int s_bucket, s_cnt;
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c = lane & 3;
+    const int64_t I = a.N / 2;
+    const int64_t units_per_tile = MODE == kSwiglu ? (I + 7) / 8 : (a.N + 15) / 16;
+    const int64_t n_tiles = SRC == kFromWs      ? a.ws[0]
+                            : SRC == kFromSlots ? a.M * a.A
+                            : SRC == kDense     ? (a.M + kTileTokens - 1) / kTileTokens
+                                                : a.M;
+    const int64_t total = n_tiles * units_per_tile;
+    const int64_t u_begin = total * blockIdx.x / gridDim.x, u_end = total * (blockIdx.x + 1) / gridDim.x;
+    TOUT *out = static_cast<TOUT *>(a.out);
+
+    for (int64_t tile = u_begin / units_per_tile; tile * units_per_tile < u_end; ++tile) {
+        const int64_t lo = max(u_begin, tile * units_per_tile), hi = min(u_end, (tile + 1) * units_per_tile);
+
+        if (SRC == kPerToken) {
+            // Per-slot combine (kernels/linear_q4.hip:281-322): the tile is token `tile`; its A slots' h rows are
+            // staged eight to a pass, every slot meets its own expert's rows, and y = sum_a coef * dot in slot order.
+            const int64_t m = tile;
+            const int passes = (int)((a.A + kTileTokens - 1) / kTileTokens);
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                int bad = -1;
+                for (int k = 0; k < a.A && bad < 0; ++k)
+                    if (a.ids[m * a.A + k] < 0 || a.ids[m * a.A + k] >= a.E) bad = k;
+                if (bad >= 0) raise_error(a.err, (uint32_t)a.ids[m * a.A + bad], (uint32_t)(m * a.A + bad));
+                s_cnt = bad < 0;
+            }
+            __syncthreads();
+            const bool valid = s_cnt != 0;
+            for (int p = 0; valid && p < passes; ++p) {
+                __syncthreads();
+                if (threadIdx.x < kTileTokens) {
+                    const int k = p * kTileTokens + threadIdx.x;
+                    s_row[threadIdx.x] = k < a.A ? m * a.A + k : -1;
+                }
+                __syncthreads();
+                stage_tile<BITS, G>(a.x, K, s_row, reinterpret_cast<uint4 *>(smem + p * pass_bytes),
+                                    reinterpret_cast<float *>(smem + p * pass_bytes + (size_t)steps * geo::kUnits * 512));
+            }
+            __syncthreads();
+            for (int64_t unit = lo + warp; unit < hi; unit += kWarps) {
+                const int64_t u = unit - tile * units_per_tile;
+                const int64_t ra = u * 16 + g, rb = ra + 8;
+                const bool va = ra < a.N, vb = rb < a.N;
+                float ta = 0.f, tb = 0.f;
+                for (int k = 0; valid && k < a.A; ++k) {
+                    const int p = k / kTileTokens, col = k % kTileTokens;
+                    const int64_t base = (int64_t)a.ids[m * a.A + k] * a.N;
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                    rows_dot<BITS, G>(acc, a, base + ra, base + rb, va, vb, reinterpret_cast<const uint4 *>(smem + p * pass_bytes),
+                                      reinterpret_cast<const float *>(smem + p * pass_bytes + (size_t)steps * geo::kUnits * 512),
+                                      lane);
+                    if (c == col / 2) {  // the lane of the quad that holds this slot's column
+                        const float cf = a.coef[m * a.A + k];
+                        ta = fmaf(cf, col & 1 ? acc[1] : acc[0], ta);
+                        tb = fmaf(cf, col & 1 ? acc[3] : acc[2], tb);
+                    }
+                }
+                // the four lanes of a quad hold the partial sums of slots {0,1}, {2,3}, {4,5}, {6,7} (mod 8)
+                ta += __shfl_xor_sync(0xffffffffu, ta, 1), tb += __shfl_xor_sync(0xffffffffu, tb, 1);
+                ta += __shfl_xor_sync(0xffffffffu, ta, 2), tb += __shfl_xor_sync(0xffffffffu, tb, 2);
+                if (c == 0) {
+                    if (va) store_out(out, m * a.N + ra, valid ? ta : qnan_f32());
+                    if (vb) store_out(out, m * a.N + rb, valid ? tb : qnan_f32());
+                }
+            }
+            continue;
+        }
+
+        __syncthreads();  // every warp is done with the previous tile's shared memory
+        if (threadIdx.x < kTileTokens) {
+            const int n = threadIdx.x;
+            int64_t row = -1, orow = -1;
+            if (SRC == kFromWs) {
+                const int bucket = a.ws[a.L.t8_bucket + tile], start = a.ws[a.L.t8_start + tile];
+                const int cnt = min(kTileTokens, a.ws[a.L.offsets + bucket + 1] - start);
+                if (n == 0) s_bucket = bucket, s_cnt = cnt;
+                if (n < cnt) {
+                    orow = a.ws[a.L.slots + start + n];
+                    row = MODE == kPartial ? orow : orow / a.A;
+                }
+            } else if (SRC == kFromSlots) {
+                if (n == 0) {
+                    const int32_t id = a.ids[tile];
+                    const bool ok = id >= 0 && id < a.E;
+                    if (!ok) raise_error(a.err, (uint32_t)id, (uint32_t)tile);
+                    s_bucket = ok ? id : (int)a.E, s_cnt = 1;
+                    orow = tile;
+                    row = MODE == kPartial ? tile : tile / a.A;
+                }
+            } else {
+                const int64_t m = tile * kTileTokens + n;
+                if (n == 0) s_bucket = 0, s_cnt = (int)min((int64_t)kTileTokens, a.M - tile * kTileTokens);
+                if (m < a.M) row = orow = m;
+            }
+            s_row[n] = row, s_out[n] = orow;
+        }
+        __syncthreads();
+        const int bucket = s_bucket, cnt = s_cnt;
+        const bool valid = bucket < a.E;  // bucket E: slots with an id outside [0, E) - their outputs become NaN
+        uint4 *xs = reinterpret_cast<uint4 *>(smem);
+        float *xsum = reinterpret_cast<float *>(smem + (size_t)steps * geo::kUnits * 512);
+        if (valid) stage_tile<BITS, G>(a.x, K, s_row, xs, xsum);
+        __syncthreads();
+
+        for (int64_t unit = lo + warp; unit < hi; unit += kWarps) {
+            const int64_t u = unit - tile * units_per_tile;
+            // The two weight rows this lane streams, as rows inside the expert, and where their results go.
+            int64_t ra, rb;
+            bool va, vb;
+            if (MODE == kSwiglu) {
+                ra = u * 8 + g, rb = I + u * 8 + g;
+                va = vb = u * 8 + g < I;
+            } else {
+                ra = u * 16 + g, rb = ra + 8;
+                va = ra < a.N, vb = rb < a.N;
+            }
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            if (valid) rows_dot<BITS, G>(acc, a, (int64_t)bucket * a.N + ra, (int64_t)bucket * a.N + rb, va, vb, xs, xsum, lane);
+            // Epilogue.  Lane (g, c) holds rows ra / rb for tokens 2c and 2c + 1.
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                const int n = 2 * c + t;
+                if (n >= cnt) continue;
+                const int64_t orow = s_out[n];
+                if (MODE == kSwiglu) {
+                    if (!va) continue;
+                    // kernels/linear_q4.hip:272-274: g, u as stored, h = stored(stored(silu(g)) * u)
+                    const float gg = as_stored_bf16(acc[t]), uu = as_stored_bf16(acc[2 + t]);
+                    const float hv = as_stored_bf16(silu_f32(gg)) * uu;
+                    store_out(out, orow * I + ra, valid ? hv : qnan_f32());
+                } else {
+                    if (va) store_out(out, orow * a.N + ra, valid ? acc[t] : qnan_f32());
+                    if (vb) store_out(out, orow * a.N + rb, valid ? acc[2 + t] : qnan_f32());
+                }
+            }
+        }
+    }
+}
+
+// y[m, n] = sum_a fma(coef[m, a], partial[m*A + a, n]) in slot order, one rounding (kernels/moe_grouped.hip:948-984).
+// Four columns a thread.  A token with an id outside [0, E_total) gets a NaN row.  Slots of experts outside
+// [e_lo, e_lo + E_local) - other ranks' in expert-parallel runs - are skipped.  SH folds the shared expert's gated add:
+// y = stored(sum) + sigmoid(gate) * s, the arithmetic of moe_shared_add on the stored y.
+template <typename TOUT, typename TS, bool SH>
+__global__ void __launch_bounds__(256)
+    combine_reduce_kernel(const float *__restrict__ partial, const int32_t *__restrict__ ids, const float *__restrict__ coef,
+                          int64_t M, int64_t A, int64_t E_total, int64_t e_lo, int64_t E_local, int64_t N,
+                          TOUT *__restrict__ y, const TS *__restrict__ s, const float *__restrict__ gate_logit,
+                          int64_t gate_ld, uint32_t gate_index, uint32_t *err) {
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= M * N) return;
+    const int64_t m = i / N, n = i % N;  // N % 4 == 0: the four columns lie in one row
+    bool ok = true;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int64_t k = 0; k < A; ++k) {
+        const int32_t id = ids[m * A + k];
+        ok = ok && id >= 0 && id < E_total;
+        if (id < e_lo || id >= e_lo + E_local) continue;
+        const float cf = coef[m * A + k];
+        const float4 p = *reinterpret_cast<const float4 *>(partial + (m * A + k) * N + n);
+        v[0] = fmaf(cf, p.x, v[0]), v[1] = fmaf(cf, p.y, v[1]), v[2] = fmaf(cf, p.z, v[2]), v[3] = fmaf(cf, p.w, v[3]);
+    }
+    if (!ok) v[0] = v[1] = v[2] = v[3] = qnan_f32();
+    if constexpr (SH) {
+        const float gl = gate_logit[m * gate_ld];
+        const bool gok = isfinite(gl);
+        if (!gok && n == 0) raise_error(err, (uint32_t)m, gate_index);
+        const float gt = gok ? 1.f / (1.f + expf(-gl)) : qnan_f32();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = fmaf(gt, load_as_f32(s, i + j), as_stored<TOUT>(v[j]));
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) store_from_f32(y, i + j, v[j]);
+}
+
+int check_view(const char *fn, const SxbQView *w) {
+    SXB_CHECK(w != nullptr, fn, ": null weight view");
+    SXB_CHECK(w->q != nullptr && w->scale != nullptr && w->minv != nullptr, fn, ": null weight pointer (q=",
+              (const void *)w->q, ", scale=", (const void *)w->scale, ", min=", (const void *)w->minv, ")");
+    SXB_CHECK(w->G == 32 || w->G == 64 || w->G == 128, fn, ": group size ", w->G, " unsupported (32, 64 or 128)");
+    SXB_CHECK(w->N >= 1 && w->N <= kMaxN, fn, ": N = ", w->N, ", expected 1..", kMaxN);
+    SXB_CHECK(w->K >= w->G && w->K <= kMaxK && w->K % w->G == 0, fn, ": K = ", w->K,
+              " must be a positive multiple of group size ", w->G, " and <= ", kMaxK);
+    SXB_CHECK(aligned16(w->q), fn, ": code array ", (const void *)w->q, " must be 16-byte aligned for vector loads");
+    SXB_CHECK(reinterpret_cast<uintptr_t>(w->scale) % 2 == 0 && reinterpret_cast<uintptr_t>(w->minv) % 2 == 0, fn,
+              ": scale / min arrays must be 2-byte aligned");
+    return SXB_OK;
+}
+
+template <int BITS, int G, int MODE, int SRC, typename TOUT>
+int launch_stream(const char *fn, const StreamArgs &a, int64_t est_units, cudaStream_t st) {
+    using geo = Geo<BITS, G>;
+    const int64_t steps = a.K / geo::kStepCodes;
+    const int64_t passes = SRC == kPerToken ? (a.A + kTileTokens - 1) / kTileTokens : 1;
+    const size_t smem = (size_t)passes * ((size_t)steps * geo::kUnits * 512 + (size_t)steps * kTileTokens * 4);
+    SXB_CHECK(smem <= kMaxDynSmem, fn, ": K = ", a.K, SRC == kPerToken ? " x A = " : "", SRC == kPerToken ? a.A : 0, " needs ", smem,
+              " bytes of shared memory for one tile's activations, more than ", kMaxDynSmem,
+              " (K * 16 * ceil(A / 8) bytes for the per-slot combine, K * 16 otherwise; use the grouped form)");
+    auto kern = stream_kernel<BITS, G, MODE, SRC, TOUT>;
+    SXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn,
+             ": reserving shared memory");
+    const int per_sm = smem > 100 * 1024 ? 1 : 2;
+    // Enough CTAs to fill the machine, never more than one per 8 units (a CTA's warps each want a unit).
+    int64_t grid = (int64_t)sm_count() * per_sm;
+    grid = std::max<int64_t>(1, std::min<int64_t>(grid, (est_units + kWarps - 1) / kWarps));
+    kern<<<(unsigned)grid, kThreads, smem, st>>>(a);
+    return SXB_OK;
+}
+
+template <int BITS, int MODE, int SRC, typename TOUT>
+int launch_by_group(const char *fn, const StreamArgs &a, int64_t G, int64_t est_units, cudaStream_t st) {
+    switch (G) {
+        case 32: return launch_stream<BITS, 32, MODE, SRC, TOUT>(fn, a, est_units, st);
+        case 64: return launch_stream<BITS, 64, MODE, SRC, TOUT>(fn, a, est_units, st);
+        default: return launch_stream<BITS, 128, MODE, SRC, TOUT>(fn, a, est_units, st);
+    }
+}
+
+int need_bf16(const char *fn, int act) {
+    SXB_CHECK(act_ok(act), fn, ": unsupported activation dtype ", act);
+    SXB_CHECK(act == SXB_ACT_BF16, fn,
+              ": FP32 activations are not implemented by the sm_100a expert kernels (BF16 activations only)");
+    return SXB_OK;
+}
+
+// Dense y = x W^T.
+template <int BITS>
+int linear_impl(const char *fn, const void *x, const SxbQView *w, void *y, int64_t M, int act, int out_act,
+                sxb_stream_t stream) {
+    SXB_CHECK(x != nullptr && y != nullptr, fn, ": null pointer (x=", x, ", y=", y, ")");
+    if (int rc = check_view(fn, w)) return rc;
+    SXB_CHECK(M >= 1 && M <= 65535ll * 8, fn, ": M (rows of x) = ", M, ", expected 1..", 65535ll * 8);
+    SXB_CHECK(aligned16(x), fn, ": x ", x, " must be 16-byte aligned for vector loads");
+    if (int rc = need_bf16(fn, act)) return rc;
+    SXB_CHECK(out_act == act || out_act == SXB_ACT_F32, fn, ": output dtype ", act_name(out_act), " with input ",
+              act_name(act), " unsupported (same dtype, or BF16 -> F32)");
+    SXB_CHECK(apart(x, M * w->K * 2, y, M * w->N * act_bytes(out_act)), fn, ": output y [", y, ", +",
+              M * w->N * act_bytes(out_act), " B) overlaps input x [", x, ", +", M * w->K * 2, " B)");
+    StreamArgs a{};
+    a.x = static_cast<const uint16_t *>(x), a.q = w->q, a.scale = w->scale, a.minv = w->minv;
+    a.N = w->N, a.K = w->K, a.M = M, a.A = 1, a.E = 1, a.out = y;
+    const int64_t units = ((M + 7) / 8) * ((w->N + 15) / 16);
+    auto st = static_cast<cudaStream_t>(stream);
+    int rc = out_act == SXB_ACT_F32 ? launch_by_group<BITS, kGather, kDense, float>(fn, a, w->G, units, st)
+                                    : launch_by_group<BITS, kGather, kDense, uint16_t>(fn, a, w->G, units, st);
+    if (rc) return rc;
+    SXB_CHECK_LAUNCH(fn, " ", act_name(act), "->", act_name(out_act), " M=", M, " N=", w->N, " K=", w->K, " G=", w->G);
+    return SXB_OK;
+}
+
+int check_experts(const char *fn, const void *x, const SxbQView *w, int64_t E, int64_t M, int64_t A, const void *y) {
+    SXB_CHECK(x != nullptr && y != nullptr, fn, ": null pointer (x=", x, ", y=", y, ")");
+    if (int rc = check_view(fn, w)) return rc;
+    SXB_CHECK(E >= 1 && w->N % E == 0, fn, ": weight has ", w->N, " rows, not a multiple of E = ", E, " experts");
+    SXB_CHECK(A >= 1 && A <= 64 && A <= E, fn, ": A (active experts per token) = ", A, ", expected 1..min(64, E=", E, ")");
+    SXB_CHECK(aligned16(x), fn, ": input ", x, " must be 16-byte aligned");
+    return SXB_OK;
+}
+
+// Per-slot gather (optionally with SwiGLU): kernels/linear_q4.hip:420-453.
+template <int BITS>
+int experts_slots_impl(const char *fn, const void *x, const SxbQView *w, int64_t E, const int32_t *ids, int64_t M,
+                       int64_t A, void *y, int act, uint32_t *err, sxb_stream_t stream, bool swiglu) {
+    if (int rc = check_experts(fn, x, w, E, M, A, y)) return rc;
+    SXB_CHECK(ids != nullptr && err != nullptr, fn, ": null pointer (ids=", (const void *)ids, ", err=", (const void *)err, ")");
+    SXB_CHECK(M >= 1 && M <= 65535, fn, ": M (tokens) = ", M, ", expected 1..65535");
+    if (int rc = need_bf16(fn, act)) return rc;
+    const int64_t N = w->N / E;
+    SXB_CHECK(!swiglu || N % 2 == 0, fn, ": SwiGLU gather needs an even row count per expert ([gate | up]), got ", N);
+    SXB_CHECK(apart(x, M * w->K * 2, y, M * A * (swiglu ? N / 2 : N) * 2), fn, ": output overlaps input");
+    StreamArgs a{};
+    a.x = static_cast<const uint16_t *>(x), a.q = w->q, a.scale = w->scale, a.minv = w->minv;
+    a.N = N, a.K = w->K, a.M = M, a.A = A, a.E = E, a.ids = ids, a.out = y, a.err = err;
+    auto st = static_cast<cudaStream_t>(stream);
+    const int64_t units = M * A * (swiglu ? (N / 2 + 7) / 8 : (N + 15) / 16);
+    int rc = swiglu ? launch_by_group<BITS, kSwiglu, kFromSlots, uint16_t>(fn, a, w->G, units, st)
+                    : launch_by_group<BITS, kGather, kFromSlots, uint16_t>(fn, a, w->G, units, st);
+    if (rc) return rc;
+    SXB_CHECK_LAUNCH(fn, " ", act_name(act), " M=", M, " A=", A, " E=", E, " N=", N, " K=", w->K, " G=", w->G,
+                     swiglu ? " swiglu" : "");
+    return SXB_OK;
+}
+
+int check_grouped(const char *fn, const void *x, const SxbQView *w, int64_t E, int64_t M, int64_t A, const void *ws,
+                  size_t ws_bytes, const void *y) {
+    if (int rc = check_experts(fn, x, w, E, M, A, y)) return rc;
+    SXB_CHECK(ws != nullptr, fn, ": null workspace");
+    SXB_CHECK(E <= kMoeMaxExperts && M * A <= kMoeMaxSlots, fn, ": M = ", M, " tokens x A = ", A, " slots over E = ", E,
+              " experts (E <= ", kMoeMaxExperts, ", M*A <= ", kMoeMaxSlots, ")");
+    SXB_CHECK(ws_bytes >= (size_t)route_words(M, A, E).total * 4, fn, ": workspace of ", ws_bytes, " bytes, needs ",
+              route_words(M, A, E).total * 4, " for M = ", M, ", A = ", A, ", E = ", E);
+    return SXB_OK;
+}
+
+}  // namespace
+
+// The exact-product grouped forms (MoeMath::F32 / WmmaBf16), shared with grouped.cu's dispatch.
+template <int BITS>
+int stream_gather_grouped(const char *fn, const void *x, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes,
+                          int64_t M, int64_t A, void *y, int act, bool swiglu, sxb_stream_t stream) {
+    if (int rc = check_grouped(fn, x, w, E, M, A, ws, ws_bytes, y)) return rc;
+    if (int rc = need_bf16(fn, act)) return rc;
+    const int64_t N = w->N / E;
+    SXB_CHECK(!swiglu || N % 2 == 0, fn, ": gate_up has ", N, " rows an expert, expected an even count (gate rows then up rows)");
+    SXB_CHECK(apart(x, M * w->K * 2, y, M * A * (swiglu ? N / 2 : N) * 2), fn, ": output overlaps input x");
+    StreamArgs a{};
+    a.x = static_cast<const uint16_t *>(x), a.q = w->q, a.scale = w->scale, a.minv = w->minv;
+    a.N = N, a.K = w->K, a.M = M, a.A = A, a.E = E, a.ws = static_cast<const int32_t *>(ws), a.L = route_words(M, A, E);
+    a.out = y;
+    auto st = static_cast<cudaStream_t>(stream);
+    const int64_t units = (M * A / 8 + std::min<int64_t>(E, M * A)) * (swiglu ? (N / 2 + 7) / 8 : (N + 15) / 16);
+    int rc = swiglu ? launch_by_group<BITS, kSwiglu, kFromWs, uint16_t>(fn, a, w->G, units, st)
+                    : launch_by_group<BITS, kGather, kFromWs, uint16_t>(fn, a, w->G, units, st);
+    if (rc) return rc;
+    SXB_CHECK_LAUNCH(fn, " ", act_name(act), " M=", M, " A=", A, " E=", E, " N=", N, " K=", w->K, " G=", w->G);
+    return SXB_OK;
+}
+
+template <int BITS>
+int stream_partial_grouped(const char *fn, const void *h, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes,
+                           int64_t M, int64_t A, float *partial, int act, sxb_stream_t stream) {
+    if (int rc = check_grouped(fn, h, w, E, M, A, ws, ws_bytes, partial)) return rc;
+    if (int rc = need_bf16(fn, act)) return rc;
+    const int64_t N = w->N / E;
+    StreamArgs a{};
+    a.x = static_cast<const uint16_t *>(h), a.q = w->q, a.scale = w->scale, a.minv = w->minv;
+    a.N = N, a.K = w->K, a.M = M, a.A = A, a.E = E, a.ws = static_cast<const int32_t *>(ws), a.L = route_words(M, A, E);
+    a.out = partial;
+    auto st = static_cast<cudaStream_t>(stream);
+    const int64_t units = (M * A / 8 + std::min<int64_t>(E, M * A)) * ((N + 15) / 16);
+    if (int rc = launch_by_group<BITS, kPartial, kFromWs, float>(fn, a, w->G, units, st)) return rc;
+    SXB_CHECK_LAUNCH(fn, " partial M=", M, " A=", A, " E=", E, " N=", N, " K=", w->K, " G=", w->G);
+    return SXB_OK;
+}
+
+// Per-slot combine without scratch (kernels/linear_q4.hpp:44-46).
+template <int BITS>
+int stream_combine_slots(const char *fn, const void *h, const SxbQView *w, int64_t E, const int32_t *ids,
+                         const float *coef, int64_t M, int64_t A, void *y, int act, int out_act, uint32_t *err,
+                         sxb_stream_t stream) {
+    SXB_CHECK(coef != nullptr, fn, ": null coef");
+    if (int rc = check_experts(fn, h, w, E, M, A, y)) return rc;
+    SXB_CHECK(ids != nullptr && err != nullptr, fn, ": null pointer (ids=", (const void *)ids, ", err=", (const void *)err, ")");
+    SXB_CHECK(M >= 1 && M <= 65535, fn, ": M (tokens) = ", M, ", expected 1..65535");
+    if (int rc = need_bf16(fn, act)) return rc;
+    SXB_CHECK(out_act == act || out_act == SXB_ACT_F32, fn, ": output dtype ", act_name(out_act), " with activations ",
+              act_name(act), " unsupported (same dtype, or F32)");
+    const int64_t N = w->N / E;
+    SXB_CHECK(apart(h, M * A * w->K * 2, y, M * N * act_bytes(out_act)), fn, ": output y overlaps input h");
+    StreamArgs a{};
+    a.x = static_cast<const uint16_t *>(h), a.q = w->q, a.scale = w->scale, a.minv = w->minv;
+    a.N = N, a.K = w->K, a.M = M, a.A = A, a.E = E, a.ids = ids, a.coef = coef, a.out = y, a.err = err;
+    auto st = static_cast<cudaStream_t>(stream);
+    const int64_t units = M * ((N + 15) / 16);
+    int rc = out_act == SXB_ACT_F32 ? launch_by_group<BITS, kGather, kPerToken, float>(fn, a, w->G, units, st)
+                                    : launch_by_group<BITS, kGather, kPerToken, uint16_t>(fn, a, w->G, units, st);
+    if (rc) return rc;
+    SXB_CHECK_LAUNCH(fn, " ", act_name(act), " M=", M, " A=", A, " E=", E, " N=", N, " K=", w->K, " G=", w->G);
+    return SXB_OK;
+}
+
+template int stream_combine_slots<4>(const char *, const void *, const SxbQView *, int64_t, const int32_t *, const float *,
+                                     int64_t, int64_t, void *, int, int, uint32_t *, sxb_stream_t);
+template int stream_combine_slots<8>(const char *, const void *, const SxbQView *, int64_t, const int32_t *, const float *,
+                                     int64_t, int64_t, void *, int, int, uint32_t *, sxb_stream_t);
+
+template int stream_gather_grouped<4>(const char *, const void *, const SxbQView *, int64_t, const void *, size_t, int64_t,
+                                      int64_t, void *, int, bool, sxb_stream_t);
+template int stream_gather_grouped<8>(const char *, const void *, const SxbQView *, int64_t, const void *, size_t, int64_t,
+                                      int64_t, void *, int, bool, sxb_stream_t);
+template int stream_partial_grouped<4>(const char *, const void *, const SxbQView *, int64_t, const void *, size_t, int64_t,
+                                       int64_t, float *, int, sxb_stream_t);
+template int stream_partial_grouped<8>(const char *, const void *, const SxbQView *, int64_t, const void *, size_t, int64_t,
+                                       int64_t, float *, int, sxb_stream_t);
+
+int combine_reduce(const char *fn, const float *partial, const int32_t *ids, const float *coef, int64_t M, int64_t A,
+                   int64_t E_total, int64_t e_lo, int64_t E_local, int64_t N, void *y, int out_act,
+                   const SxbMoeSharedAdd *shared, int s_act, sxb_stream_t stream) {
+    SXB_CHECK(partial != nullptr && ids != nullptr && coef != nullptr && y != nullptr, fn, ": null pointer (partial=",
+              (const void *)partial, ", ids=", (const void *)ids, ", coef=", (const void *)coef, ", y=", y, ")");
+    SXB_CHECK(N % 4 == 0 && aligned16(partial), fn, ": N = ", N, " must be a multiple of 4 and partial 16-byte aligned");
+    SXB_CHECK(act_ok(out_act), fn, ": unsupported output dtype ", out_act);
+    if (shared != nullptr) {
+        SXB_CHECK(shared->s != nullptr && shared->gate_logit != nullptr && shared->err != nullptr, fn,
+                  ": shared add with a null pointer (s=", shared->s, ", gate_logit=", (const void *)shared->gate_logit,
+                  ", err=", (const void *)shared->err, ")");
+        SXB_CHECK(shared->gate_ld >= 1, fn, ": shared add gate_ld = ", shared->gate_ld, ", expected >= 1");
+        SXB_CHECK(apart(y, M * N * act_bytes(out_act), shared->s, M * N * act_bytes(s_act)), fn, ": y overlaps shared s");
+    }
+    SXB_CHECK(apart(y, M * N * act_bytes(out_act), partial, M * A * N * 4), fn, ": y overlaps partial");
+    const unsigned blocks = (unsigned)((M * N / 4 + 255) / 256);
+    auto st = static_cast<cudaStream_t>(stream);
+    const float *gl = shared ? shared->gate_logit : nullptr;
+    const int64_t gld = shared ? shared->gate_ld : 0;
+    const uint32_t gi = shared ? shared->gate_index : 0;
+    uint32_t *err = shared ? shared->err : nullptr;
+#define SXB_REDUCE(TOUT, TS, SH)                                                                                        \
+    combine_reduce_kernel<TOUT, TS, SH><<<blocks, 256, 0, st>>>(partial, ids, coef, M, A, E_total, e_lo, E_local, N,   \
+                                                                static_cast<TOUT *>(y),                                \
+                                                                static_cast<const TS *>(shared ? shared->s : nullptr), \
+                                                                gl, gld, gi, err)
+    if (out_act == SXB_ACT_F32) {
+        if (!shared) SXB_REDUCE(float, float, false);
+        else if (s_act == SXB_ACT_F32) SXB_REDUCE(float, float, true);
+        else SXB_REDUCE(float, uint16_t, true);
+    } else {
+        if (!shared) SXB_REDUCE(uint16_t, uint16_t, false);
+        else if (s_act == SXB_ACT_F32) SXB_REDUCE(uint16_t, float, true);
+        else SXB_REDUCE(uint16_t, uint16_t, true);
+    }
+#undef SXB_REDUCE
+    SXB_CHECK_LAUNCH(fn, " reduce M=", M, " A=", A, " N=", N, shared ? " +shared" : "");
+    return SXB_OK;
+}
+
+}  // namespace sxb
+
+using namespace sxb;
+
+extern "C" {
+
+int sxb_linear_q4(const void *x, const SxbQView *w, void *y, int64_t M, int act, int out_act, sxb_stream_t stream) {
+    return linear_impl<4>("linear_q4", x, w, y, M, act, out_act, stream);
+}
+int sxb_linear_q8(const void *x, const SxbQView *w, void *y, int64_t M, int act, int out_act, sxb_stream_t stream) {
+    return linear_impl<8>("linear_q8", x, w, y, M, act, out_act, stream);
+}
+
+int sxb_linear_q4_experts_gather(const void *x, const SxbQView *w, int64_t E, const int32_t *ids, int64_t M, int64_t A,
+                                 void *y, int act, uint32_t *err, sxb_stream_t stream) {
+    return experts_slots_impl<4>("linear_q4_experts_gather", x, w, E, ids, M, A, y, act, err, stream, false);
+}
+int sxb_linear_q4_experts_gather_swiglu(const void *x, const SxbQView *w, int64_t E, const int32_t *ids, int64_t M,
+                                        int64_t A, void *h, int act, uint32_t *err, sxb_stream_t stream) {
+    return experts_slots_impl<4>("linear_q4_experts_gather_swiglu", x, w, E, ids, M, A, h, act, err, stream, true);
+}
+int sxb_linear_q8_experts_gather(const void *x, const SxbQView *w, int64_t E, const int32_t *ids, int64_t M, int64_t A,
+                                 void *y, int act, uint32_t *err, sxb_stream_t stream) {
+    return experts_slots_impl<8>("linear_q8_experts_gather", x, w, E, ids, M, A, y, act, err, stream, false);
+}
+int sxb_linear_q8_experts_gather_swiglu(const void *x, const SxbQView *w, int64_t E, const int32_t *ids, int64_t M,
+                                        int64_t A, void *h, int act, uint32_t *err, sxb_stream_t stream) {
+    return experts_slots_impl<8>("linear_q8_experts_gather_swiglu", x, w, E, ids, M, A, h, act, err, stream, true);
+}
+
+}  // extern "C"

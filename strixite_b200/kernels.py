@@ -1,0 +1,248 @@
+"""Host-side mirror of the reference's `strix::kernels` launchers for the MoE path, over the C ABI.
+
+Same function names, argument order and meaning as kernels/moe_router.hpp, kernels/moe_grouped.hpp,
+kernels/linear_q4.hpp, kernels/linear_q8.hpp and kernels/swiglu.hpp; a failed precondition raises `Error` (the
+reference throws strix::Error) carrying the library's message.  Tensors are torch CUDA tensors used purely as device
+memory: BF16 activations may be passed as torch.bfloat16 or as raw uint16/int16 bit tensors.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+
+class Error(RuntimeError):
+    """A failed precondition or launch; the reference's strix::Error (common/check.hpp:29-32)."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(message)
+        self.code = code
+
+
+class GpuFatalError(Error):
+    """A sticky CUDA error: the context is gone (common/check.hpp:36-39)."""
+
+
+class Act(enum.IntEnum):  # kernels/norm.hpp:20
+    F32 = 0
+    BF16 = 1
+
+
+class MoeMath(enum.IntEnum):  # kernels/moe_grouped.hpp:39
+    F32 = 0
+    WmmaBf16 = 1
+    WmmaF16 = 2
+    WmmaF16Narrow = 3
+    WmmaF16Wide = 4
+    WmmaF16Wide256 = 5
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        msg = _lib.load().sxb_last_error().decode()
+        raise (GpuFatalError if rc == 3 else Error)(rc, msg)
+
+
+def _ptr(t) -> Optional[int]:
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    if not t.is_cuda:
+        raise Error(1, "strixite_b200.kernels: tensors must live on a CUDA device (no CPU path exists)")
+    return t.data_ptr()
+
+
+def _stream(stream) -> int:
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    return stream if isinstance(stream, int) else stream.cuda_stream
+
+
+@dataclass
+class QDeviceView:
+    """A quantized matrix on the device: Q4DeviceView / Q8DeviceView (runtime/q4_device.hpp:14-19) plus its bit width."""
+
+    q: torch.Tensor       # uint8 [N, K/2] (Q4) or [N, K] (Q8)
+    scale: torch.Tensor   # BF16 bits [N, K/G]
+    minv: torch.Tensor    # BF16 bits [N, K/G]
+    N: int
+    K: int
+    G: int
+    bits: int = 4
+
+    def c(self) -> _lib.SxbQView:
+        return _lib.SxbQView(self.q.data_ptr(), self.scale.data_ptr(), self.minv.data_ptr(), self.N, self.K, self.G)
+
+    def bytes(self) -> int:
+        return self.q.numel() + 2 * self.scale.numel() + 2 * self.minv.numel()
+
+    def rows(self, lo: int, hi: int) -> "QDeviceView":
+        """The view of rows [lo, hi) (e.g. one rank's experts of a stacked matrix)."""
+        return QDeviceView(self.q[lo:hi], self.scale[lo:hi], self.minv[lo:hi], hi - lo, self.K, self.G, self.bits)
+
+
+def _b(w: QDeviceView) -> str:
+    if w.bits not in (4, 8):
+        raise Error(1, f"experts have {w.bits} bits, expected 4 or 8")
+    return f"q{w.bits}"
+
+
+# ---- kernels/moe_router.hpp -----------------------------------------------------------------------------------
+
+def moe_router(logits, ld, M, E, k, shared_logit, shared_ld, shared_id, ids, coef, act, err, stream=None):
+    _check(_lib.load().sxb_moe_router(_ptr(logits), ld, M, E, k, _ptr(shared_logit), shared_ld, shared_id, _ptr(ids),
+                                      _ptr(coef), int(act), _ptr(err), _stream(stream)))
+
+
+def check_router_error(err, what: str):
+    _check(_lib.load().sxb_check_router_error(_ptr(err), what.encode()))
+
+
+def report_router_error(e, what: str):
+    _check(_lib.load().sxb_report_router_error((C.c_uint32 * 3)(*[int(v) for v in e]), what.encode()))
+
+
+def moe_shared_add(y, s, gate_logit, gate_ld, M, N, gate_index, act, err, stream=None):
+    _check(_lib.load().sxb_moe_shared_add(_ptr(y), _ptr(s), _ptr(gate_logit), gate_ld, M, N, gate_index, int(act),
+                                          _ptr(err), _stream(stream)))
+
+
+def moe_shared_add_inject(y, s, gate_logit, gate_ld, M, N, gate_index, x, w_in, H, act, err, stream=None):
+    _check(_lib.load().sxb_moe_shared_add_inject(_ptr(y), _ptr(s), _ptr(gate_logit), gate_ld, M, N, gate_index, _ptr(x),
+                                                 _ptr(w_in), H, int(act), _ptr(err), _stream(stream)))
+
+
+# ---- kernels/moe_grouped.hpp ----------------------------------------------------------------------------------
+
+def moe_route_workspace_bytes(M, A, E) -> int:
+    n = _lib.load().sxb_moe_route_workspace_bytes(M, A, E)
+    if n == 0:
+        _check(1)
+    return n
+
+
+def route_layout(M, A, E) -> dict:
+    out = (C.c_int64 * 8)()
+    _check(_lib.load().sxb_route_layout(M, A, E, out))
+    keys = ["header", "offsets", "slots", "tile8_bucket", "tile8_start", "tile128_bucket", "tile128_start", "total"]
+    return dict(zip(keys, list(out)))
+
+
+def moe_group_routes(ids, M, A, E, ws, ws_bytes, err, stream=None):
+    _check(_lib.load().sxb_moe_group_routes(_ptr(ids), M, A, E, _ptr(ws), ws_bytes, _ptr(err), _stream(stream)))
+
+
+def moe_group_routes_ep(ids, M, A, E_total, e_lo, E_local, ws, ws_bytes, err, stream=None):
+    _check(_lib.load().sxb_moe_group_routes_ep(_ptr(ids), M, A, E_total, e_lo, E_local, _ptr(ws), ws_bytes, _ptr(err),
+                                               _stream(stream)))
+
+
+def linear_qw_experts_gather_grouped(x, w: QDeviceView, E, ws, ws_bytes, M, A, y, act, math, stream=None):
+    fn = getattr(_lib.load(), f"sxb_linear_{_b(w)}_experts_gather_grouped")
+    _check(fn(_ptr(x), C.byref(w.c()), E, _ptr(ws), ws_bytes, M, A, _ptr(y), int(act), int(math), _stream(stream)))
+
+
+def linear_qw_experts_gather_grouped_swiglu(x, w: QDeviceView, E, ws, ws_bytes, M, A, h, act, math, stream=None,
+                                            h_f16=False):
+    fn = getattr(_lib.load(), f"sxb_linear_{_b(w)}_experts_gather_grouped_swiglu")
+    _check(fn(_ptr(x), C.byref(w.c()), E, _ptr(ws), ws_bytes, M, A, _ptr(h), int(act), int(math), _stream(stream),
+              int(h_f16)))
+
+
+@dataclass
+class MoeSharedAdd:  # kernels/moe_grouped.hpp:75-81
+    s: torch.Tensor
+    gate_logit: object  # tensor or raw pointer to token 0's gate logit
+    gate_ld: int
+    gate_index: int
+    err: torch.Tensor
+
+    def c(self) -> _lib.SxbMoeSharedAdd:
+        return _lib.SxbMoeSharedAdd(_ptr(self.s), _ptr(self.gate_logit), self.gate_ld, self.gate_index, _ptr(self.err))
+
+
+def linear_qw_experts_combine_grouped(h, w: QDeviceView, E, ids, coef, ws, ws_bytes, partial, M, A, y, act, math,
+                                      stream=None, shared: Optional[MoeSharedAdd] = None, h_f16=False, out_act=None):
+    fn = getattr(_lib.load(), f"sxb_linear_{_b(w)}_experts_combine_grouped")
+    sh = C.byref(shared.c()) if shared is not None else None
+    _check(fn(_ptr(h), C.byref(w.c()), E, _ptr(ids), _ptr(coef), _ptr(ws), ws_bytes, _ptr(partial), M, A, _ptr(y),
+              int(act), int(act if out_act is None else out_act), int(math), _stream(stream), sh, int(h_f16)))
+
+
+def linear_qw_experts_combine_grouped_ep(h, w: QDeviceView, E_local, E_total, e_lo, ids, coef, ws, ws_bytes, partial, M,
+                                         A, y, act, math, stream=None, h_f16=False, out_act=None):
+    fn = getattr(_lib.load(), f"sxb_linear_{_b(w)}_experts_combine_grouped_ep")
+    _check(fn(_ptr(h), C.byref(w.c()), E_local, E_total, e_lo, _ptr(ids), _ptr(coef), _ptr(ws), ws_bytes, _ptr(partial),
+              M, A, _ptr(y), int(act), int(act if out_act is None else out_act), int(math), _stream(stream), int(h_f16)))
+
+
+# ---- kernels/linear_q4.hpp, kernels/linear_q8.hpp, runtime/qweight.hpp -----------------------------------------
+
+def linear_qw(x, w: QDeviceView, y, M, act, out_act=None, stream=None):
+    fn = getattr(_lib.load(), f"sxb_linear_{_b(w)}")
+    _check(fn(_ptr(x), C.byref(w.c()), _ptr(y), M, int(act), int(act if out_act is None else out_act), _stream(stream)))
+
+
+def linear_q4(x, w, y, M, act, out_act=None, stream=None):
+    linear_qw(x, w, y, M, act, out_act, stream)
+
+
+linear_q8 = linear_q4
+
+
+def linear_qw_experts_gather(x, w: QDeviceView, E, ids, M, A, y, act, err, stream=None):
+    fn = getattr(_lib.load(), f"sxb_linear_{_b(w)}_experts_gather")
+    _check(fn(_ptr(x), C.byref(w.c()), E, _ptr(ids), M, A, _ptr(y), int(act), _ptr(err), _stream(stream)))
+
+
+def linear_qw_experts_gather_swiglu(x, w: QDeviceView, E, ids, M, A, h, act, err, stream=None):
+    fn = getattr(_lib.load(), f"sxb_linear_{_b(w)}_experts_gather_swiglu")
+    _check(fn(_ptr(x), C.byref(w.c()), E, _ptr(ids), M, A, _ptr(h), int(act), _ptr(err), _stream(stream)))
+
+
+def linear_qw_experts_combine(h, w: QDeviceView, E, ids, coef, M, A, y, act, err, stream=None, out_act=None):
+    fn = getattr(_lib.load(), f"sxb_linear_{_b(w)}_experts_combine")
+    _check(fn(_ptr(h), C.byref(w.c()), E, _ptr(ids), _ptr(coef), M, A, _ptr(y), int(act),
+              int(act if out_act is None else out_act), _ptr(err), _stream(stream)))
+
+
+def check_expert_error(err, what: str):
+    _check(_lib.load().sxb_check_expert_error(_ptr(err), what.encode()))
+
+
+def report_expert_error(e, what: str):
+    _check(_lib.load().sxb_report_expert_error((C.c_uint32 * 3)(*[int(v) for v in e]), what.encode()))
+
+
+# ---- kernels/swiglu.hpp ---------------------------------------------------------------------------------------
+
+def swiglu(gu, h, rows, I, act, stream=None):
+    _check(_lib.load().sxb_swiglu(_ptr(gu), _ptr(h), rows, I, int(act), _stream(stream)))
+
+
+# ---- formats/q4.hpp, formats/q8.hpp (on the device) -----------------------------------------------------------
+
+def quantize(w: torch.Tensor, G: int, bits: int, err: Optional[torch.Tensor] = None, stream=None) -> QDeviceView:
+    """quantize_q4 / quantize_q8 (formats/q4.hpp:32, formats/q8.hpp:32) of an FP32 [N, K] tensor on the device."""
+    if w.dtype != torch.float32 or w.dim() != 2 or not w.is_contiguous():
+        raise Error(1, "quantize: w must be a contiguous FP32 [N, K] tensor")
+    N, K = w.shape
+    if bits not in (4, 8) or G not in (32, 64, 128) or K % G:
+        raise Error(1, f"quantize: bits = {bits}, G = {G}, K = {K} unsupported")
+    q = torch.empty((N, K // 2 if bits == 4 else K), dtype=torch.uint8, device=w.device)
+    scale = torch.empty((N, K // G), dtype=torch.int16, device=w.device)
+    minv = torch.empty((N, K // G), dtype=torch.int16, device=w.device)
+    own = err is None
+    if own:
+        err = torch.zeros(4, dtype=torch.int32, device=w.device)
+    _check(_lib.load().sxb_quantize(_ptr(w), N, K, G, bits, _ptr(q), _ptr(scale), _ptr(minv), _ptr(err), _stream(stream)))
+    if own and int(err[0].item()) != 0:
+        raise Error(1, f"quantize: non-finite weight at [{int(err[1])}, {int(err[2])}]")
+    return QDeviceView(q, scale, minv, N, K, G, bits)

@@ -1,0 +1,154 @@
+"""The MoE sublayer as the reference's forward composes it (runtime/qwen4exp.cpp:3143-3217), over the C ABI.
+
+    router top-k  ->  shared expert (dense Q8 gate_up, SwiGLU, down)  ->  pack slots by expert
+                  ->  grouped gate/up + SwiGLU  ->  grouped down, combine, + sigmoid(gate) * shared
+
+`MoeLayer` owns what the reference's session owns for this block (runtime/qwen4exp.cpp:1018-1027,1092-1101): ids,
+coef, the grouping workspace, h, the combine's partial, the shared expert's buffers and the two error buffers.
+Everything is enqueued on the current CUDA stream; nothing synchronizes except `check_errors`.
+
+Path choice by token count (the reference's kGroupedMinTokens / kWideMin*, runtime/qwen4exp.hpp:724):
+    T <  tc_min_tokens : exact-product streaming kernels (HBM-bound regime; MoeMath.F32)
+    T >= tc_min_tokens : tcgen05 grouped GEMMs (MoeMath.WmmaF16)
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import kernels as K
+from .kernels import Act, MoeMath, QDeviceView
+
+
+@dataclass
+class MoeWeights:
+    """runtime/qwen4exp.hpp:129-132 Layer{gate_up, down, shared_gate_up, shared_down}; experts stacked along N."""
+
+    gate_up: QDeviceView                       # [E * 2I, d]
+    down: QDeviceView                          # [E * d, I]
+    shared_gate_up: Optional[QDeviceView] = None  # [2I, d]
+    shared_down: Optional[QDeviceView] = None     # [d, I]
+
+    def bytes(self) -> int:
+        n = self.gate_up.bytes() + self.down.bytes()
+        if self.shared_gate_up is not None:
+            n += self.shared_gate_up.bytes() + self.shared_down.bytes()
+        return n
+
+
+class MoeBuffers:
+    """Workspaces for up to max_tokens tokens; shared by every layer of a stack (the reference's session buffers)."""
+
+    def __init__(self, max_tokens: int, d: int, I: int, E_buckets: int, A: int, device, shared: bool):
+        T, S = max_tokens, max_tokens * A
+        dev = device
+        self.max_tokens, self.A = T, A
+        self.ids = torch.empty((T, A), dtype=torch.int32, device=dev)
+        self.coef = torch.empty((T, A), dtype=torch.float32, device=dev)
+        self.ws_bytes = K.moe_route_workspace_bytes(T, A, E_buckets)
+        self.ws = torch.empty(self.ws_bytes // 4, dtype=torch.int32, device=dev)
+        self.h = torch.empty((S, I), dtype=torch.bfloat16, device=dev)
+        self.partial = torch.empty((S, d), dtype=torch.float32, device=dev)
+        self.router_err = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.expert_err = torch.zeros(4, dtype=torch.int32, device=dev)
+        if shared:
+            self.sh_ids = torch.zeros((T, 1), dtype=torch.int32, device=dev)
+            self.sh_coef = torch.ones((T, 1), dtype=torch.float32, device=dev)
+            self.sh_ws_bytes = K.moe_route_workspace_bytes(T, 1, 1)
+            self.sh_ws = torch.empty(self.sh_ws_bytes // 4, dtype=torch.int32, device=dev)
+            self.sh_ws_tokens = -1
+            self.sh_gu = torch.empty((T, 2 * I), dtype=torch.bfloat16, device=dev)
+            self.sh_h = torch.empty((T, I), dtype=torch.bfloat16, device=dev)
+            self.sh_partial = torch.empty((T, d), dtype=torch.float32, device=dev)
+            self.sh_y = torch.empty((T, d), dtype=torch.bfloat16, device=dev)
+
+
+class MoeLayer:
+    """One MoE sublayer.  E_total / e_lo: expert-parallel ranks hold experts [e_lo, e_lo + E_local) of E_total in their
+    weight views and return their partial sum of y (see `ep.ExpertParallelMoe`)."""
+
+    tc_min_tokens = 256
+
+    def __init__(self, weights: MoeWeights, n_experts: int, top_k: int, buffers: MoeBuffers, E_total: Optional[int] = None,
+                 e_lo: int = 0):
+        self.w = weights
+        self.E = n_experts                      # experts in the weight views
+        self.E_total = n_experts if E_total is None else E_total
+        self.e_lo = e_lo
+        self.k = top_k
+        self.buf = buffers
+        self.d = weights.gate_up.K
+        self.I = weights.gate_up.N // n_experts // 2
+        assert weights.down.N == n_experts * self.d and weights.down.K == self.I
+        self.ep = self.E_total != self.E
+
+    def math_for(self, T: int, math: Optional[MoeMath]) -> MoeMath:
+        if math is not None:
+            return math
+        return MoeMath.WmmaF16 if T >= self.tc_min_tokens else MoeMath.F32
+
+    def route(self, logits: torch.Tensor, T: int):
+        """moe_router on logits [T, ld] FP32 (column E_total = the shared gate when ld > E_total)."""
+        b = self.buf
+        K.moe_router(logits, logits.stride(0), T, self.E_total, self.k, None, 1, 0, b.ids, b.coef, Act.F32, b.router_err)
+
+    def shared_expert(self, x: torch.Tensor, T: int, math: MoeMath):
+        """The always-on shared expert as dense projections -> buf.sh_y [T, d] BF16 (runtime/qwen4exp.cpp:3163-3168)."""
+        b, w = self.buf, self.w
+        if not K_is_f16(math):
+            K.linear_qw(x, w.shared_gate_up, b.sh_gu, T, Act.BF16)
+            K.swiglu(b.sh_gu, b.sh_h, T, self.I, Act.BF16)
+            K.linear_qw(b.sh_h, w.shared_down, b.sh_y, T, Act.BF16)
+            return
+        # Prefill: the same tcgen05 grouped kernels with one "expert" that every token is routed to.
+        if b.sh_ws_tokens != T:
+            K.moe_group_routes(b.sh_ids, T, 1, 1, b.sh_ws, b.sh_ws_bytes, b.expert_err)
+            b.sh_ws_tokens = T
+        K.linear_qw_experts_gather_grouped_swiglu(x, w.shared_gate_up, 1, b.sh_ws, b.sh_ws_bytes, T, 1, b.sh_h, Act.BF16, math)
+        K.linear_qw_experts_combine_grouped(b.sh_h, w.shared_down, 1, b.sh_ids, b.sh_coef, b.sh_ws, b.sh_ws_bytes,
+                                            b.sh_partial, T, 1, b.sh_y, Act.BF16, math)
+
+    def experts(self, x: torch.Tensor, T: int, y: torch.Tensor, math: MoeMath, gate_logit=None, gate_ld: int = 0):
+        """pack -> gate/up + SwiGLU -> down + combine into y [T, d] (BF16 or FP32), ids / coef already in the buffers."""
+        b, w, A = self.buf, self.w, self.k
+        out_act = Act.F32 if y.dtype == torch.float32 else Act.BF16
+        if self.ep:
+            K.moe_group_routes_ep(b.ids, T, A, self.E_total, self.e_lo, self.E, b.ws, b.ws_bytes, b.expert_err)
+        else:
+            K.moe_group_routes(b.ids, T, A, self.E, b.ws, b.ws_bytes, b.expert_err)
+        K.linear_qw_experts_gather_grouped_swiglu(x, w.gate_up, self.E, b.ws, b.ws_bytes, T, A, b.h, Act.BF16, math)
+        if self.ep:
+            K.linear_qw_experts_combine_grouped_ep(b.h, w.down, self.E, self.E_total, self.e_lo, b.ids, b.coef, b.ws,
+                                                   b.ws_bytes, b.partial, T, A, y, Act.BF16, math, out_act=out_act)
+        else:
+            shared = None
+            if gate_logit is not None:
+                shared = K.MoeSharedAdd(b.sh_y, gate_logit, gate_ld, self.E_total, b.router_err)
+            K.linear_qw_experts_combine_grouped(b.h, w.down, self.E, b.ids, b.coef, b.ws, b.ws_bytes, b.partial, T, A, y,
+                                                Act.BF16, math, shared=shared, out_act=out_act)
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor, y: torch.Tensor, math: Optional[MoeMath] = None):
+        """x [T, d] BF16, logits [T, >= E (+1)] FP32 -> y [T, d] (BF16, or FP32 = the unrounded sums).
+        With a shared expert, logits[:, E] is its gate logit and its gated output is folded into the combine."""
+        T = x.shape[0]
+        assert T <= self.buf.max_tokens and x.dtype == torch.bfloat16 and logits.dtype == torch.float32
+        math = self.math_for(T, math)
+        self.route(logits, T)
+        if self.w.shared_gate_up is not None and not self.ep:
+            self.shared_expert(x, T, math)
+            gate = logits.data_ptr() + 4 * self.E_total
+            self.experts(x, T, y, math, gate_logit=gate, gate_ld=logits.stride(0))
+        else:
+            self.experts(x, T, y, math)
+        return y
+
+    def check_errors(self, what: str = "moe layer"):
+        """Blocking: the reference's read_back of the error words (runtime/qwen4exp.cpp:2391-2404)."""
+        K.check_router_error(self.buf.router_err, what)
+        K.check_expert_error(self.buf.expert_err, what)
+
+
+def K_is_f16(math: MoeMath) -> bool:
+    return int(math) >= int(MoeMath.WmmaF16)

@@ -1,0 +1,90 @@
+"""CPU tests of the drop-in boundary: the library loads, exports every symbol the header declares, and refuses bad
+arguments before touching the GPU (the reference's STRIX_CHECK preconditions, returned as codes)."""
+import ctypes as C
+import pathlib
+import re
+import subprocess
+
+import pytest
+
+ROOT = pathlib.Path(__file__).resolve().parent.parent
+HEADER = ROOT / "include" / "strix_b200.h"
+
+
+def declared_symbols():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(sxb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported_and_bound(lib):
+    from strixite_b200 import _lib
+    names = declared_symbols()
+    assert len(names) >= 30
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in strix_b200.h but not exported by the library"
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes signature in strixite_b200/_lib.py"
+    assert set(_lib.SIGNATURES) <= set(names)
+    assert lib.sxb_version().decode().endswith("sm_100a")
+
+
+def test_header_compiles_as_c_and_cxx(tmp_path):
+    for lang, std in (("c", "-std=c99"), ("c++", "-std=c++17")):
+        src = tmp_path / f"t.{ 'c' if lang == 'c' else 'cpp'}"
+        src.write_text('#include "strix_b200.h"\nint main(void) { SxbQView v; (void)v; return SXB_OK; }\n')
+        subprocess.run(["gcc", "-x", lang, std, "-fsyntax-only", "-Wall", "-Werror", f"-I{ROOT / 'include'}", str(src)], check=True)
+
+
+def test_shim_compiles(tmp_path):
+    """The header-only C++ shim that re-creates strix::kernels:: over the C ABI."""
+    src = tmp_path / "t.cpp"
+    src.write_text('#include "strix_b200_shim.hpp"\nint main() { return 0; }\n')
+    subprocess.run(["g++", "-std=c++20", "-fsyntax-only", "-Wall", f"-I{ROOT / 'include'}", "-I/usr/local/cuda/include",
+                    str(src)], check=True)
+
+
+def test_preconditions_fail_before_any_launch(lib):
+    from strixite_b200 import kernels as K
+    with pytest.raises(K.Error, match="null pointer"):
+        K.moe_router(0, 513, 4, 512, 10, None, 1, 0, 0, 0, K.Act.F32, 0, stream=0)
+    with pytest.raises(K.Error, match=r"E = 2000 experts, expected 1\.\.1024"):
+        K.moe_router(16, 2000, 4, 2000, 10, None, 1, 0, 16, 32, K.Act.F32, 48, stream=0)
+    with pytest.raises(K.Error, match="k = 40"):
+        K.moe_router(16, 513, 4, 512, 40, None, 1, 0, 16, 32, K.Act.F32, 48, stream=0)
+    with pytest.raises(K.Error, match="ld = 100 < E"):
+        K.moe_router(16, 100, 4, 512, 10, None, 1, 0, 16, 32, K.Act.F32, 48, stream=0)
+    with pytest.raises(K.Error, match=r"M \* A <= 2\^20"):
+        K.moe_route_workspace_bytes(1 << 20, 2, 512)
+    with pytest.raises(K.Error, match="workspace of 16 bytes, needs"):
+        K.moe_group_routes(16, 16, 10, 512, 32, 16, 48, stream=0)
+    with pytest.raises(K.Error, match="overlaps"):
+        K.swiglu(4096, 4096 + 64, 4, 64, K.Act.BF16, stream=0)
+    with pytest.raises(K.Error, match="H = 3 streams"):
+        K.moe_shared_add_inject(4096, 1 << 20, 16, 1, 2, 64, 512, 1 << 24, 32, 3, K.Act.BF16, 48, stream=0)
+    assert K.moe_route_workspace_bytes(16, 10, 512) == K.route_layout(16, 10, 512)["total"] * 4
+
+
+def test_weight_view_checks(lib):
+    from strixite_b200 import _lib, kernels as K
+    def call(q=4096, scale=8192, minv=12288, N=64, K_=256, G=128, x=1 << 20, y=1 << 24, M=4):
+        v = _lib.SxbQView(q, scale, minv, N, K_, G)
+        rc = lib.sxb_linear_q4(x, C.byref(v), y, M, 1, 1, None)
+        return rc, lib.sxb_last_error().decode()
+    assert call(G=48) == (1, call(G=48)[1]) and "group size 48 unsupported" in call(G=48)[1]
+    assert "must be a positive multiple of group size" in call(K_=200)[1]
+    assert "16-byte aligned" in call(q=4100)[1]
+    assert "16-byte aligned" in call(x=(1 << 20) + 2)[1]
+    assert "overlaps" in call(y=(1 << 20) + 64)[1]
+    assert "M (rows of x) = 0" in call(M=0)[1]
+    rc, msg = call(q=0)
+    assert rc == 1 and "null weight pointer" in msg
+    rc = lib.sxb_linear_q4(1 << 20, C.byref(_lib.SxbQView(4096, 8192, 12288, 64, 256, 128)), 1 << 24, 4, 0, 0, None)
+    assert rc == 1 and "FP32 activations are not implemented" in lib.sxb_last_error().decode()
+
+
+def test_report_errors(lib):
+    from strixite_b200 import kernels as K
+    K.report_router_error([0, 0, 0], "layer 3")
+    with pytest.raises(K.Error, match="layer 3: non-finite router logit at token 7, expert 512"):
+        K.report_router_error([1, 7, 512], "layer 3")
+    with pytest.raises(K.Error, match="expert id -1 at slot 42"):
+        K.report_expert_error([1, 0xFFFFFFFF, 42], "L0")

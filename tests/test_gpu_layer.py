@@ -1,0 +1,105 @@
+"""Whole MoE sublayer on the GPU against the CPU oracle, on the benchmark configurations.
+
+Gate (the acceptance rule of the path): router ids bit-exact given identical FP32 logits; layer output within
+max-abs error <= 1e-2 x output RMS of the oracle's FP32 output.  The streaming (exact-product) path is in practice
+three orders of magnitude inside that bar; its own, tighter bar is asserted too."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import bits_of, download, max_abs_over_rms
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-2  # max |y - y_ref| <= TOL * rms(y_ref), the path's stated tolerance
+
+
+def oracle_layer_on_touched_experts(oracle, cfg, w, x_bits, logits, rows, semantics, threads=0):
+    """Runs the oracle on the token subset `rows`, downloading only the experts those tokens are routed to (the
+    stacked matrices of the large configurations are gigabytes; rows are independent)."""
+    ids, _ = oracle.moe_router(logits[rows], cfg.E, cfg.k)
+    touched = np.unique(ids)
+    remap = -np.ones(cfg.E, dtype=np.int64)
+    remap[touched] = np.arange(len(touched))
+    n_gu, n_dn = 2 * cfg.I, cfg.d
+    def take(view, n):
+        idx = torch.from_numpy(np.concatenate([np.arange(e * n, (e + 1) * n) for e in touched])).to(view.q.device)
+        return oracle.QWeight(view.q[idx].cpu().numpy(), view.scale[idx].cpu().numpy().view(np.uint16),
+                              view.minv[idx].cpu().numpy().view(np.uint16), len(touched) * n, view.K, view.G, view.bits)
+    lw = oracle.LayerWeights(take(w.gate_up, n_gu), take(w.down, n_dn))
+    if w.shared_gate_up is not None:
+        lw.shared_gate_up, lw.shared_down = download(w.shared_gate_up, oracle), download(w.shared_down, oracle)
+    # the oracle routes on the original logits; present it logits whose columns are the touched experts only
+    E2 = len(touched)
+    sub = np.full((len(rows), E2 + 1), -1e30, dtype=np.float32)
+    sub[:, :E2] = logits[rows][:, touched]
+    sub[:, E2] = logits[rows][:, cfg.E]
+    out = oracle.moe_layer(x_bits[rows], sub, lw, E2, cfg.k, semantics=semantics, threads=threads)
+    assert np.array_equal(touched[out["ids"]], ids)  # same picks through the remapping
+    out["ids"] = ids
+    return out
+
+
+def run_layer(cfg, seed, dev, math=None):
+    from strixite_b200 import workloads as W
+    from strixite_b200.layer import MoeBuffers, MoeLayer
+    w = W.make_layer_weights(cfg, seed, dev)
+    x = W.activations(cfg, seed, dev)
+    logits = W.router_logits(x, W.router_weight(cfg, seed, dev), W.expert_bias(cfg, seed, dev))
+    buf = MoeBuffers(cfg.T, cfg.d, cfg.I, cfg.E, cfg.k, dev, cfg.shared)
+    layer = MoeLayer(w, cfg.E, cfg.k, buf)
+    y32 = torch.empty((cfg.T, cfg.d), dtype=torch.float32, device=dev)
+    ybf = torch.empty((cfg.T, cfg.d), dtype=torch.bfloat16, device=dev)
+    layer.forward(x, logits, y32, math=math)
+    layer.forward(x, logits, ybf, math=math)
+    torch.cuda.synchronize()
+    layer.check_errors(cfg.name)
+    return w, x, logits, buf, y32, ybf
+
+
+@pytest.mark.parametrize("name", ["c0", "c1", "c2"])
+def test_layer_streaming_path(cuda, oracle, name):
+    from strixite_b200 import workloads as W
+    from strixite_b200.kernels import MoeMath
+    cfg = W.c2_config(0) if name == "c2" else W.CONFIGS[name]
+    w, x, logits, buf, y32, ybf = run_layer(cfg, 0, cuda, math=MoeMath.F32)
+    xb, lg = bits_of(x), logits.cpu().numpy()
+    ref = oracle_layer_on_touched_experts(oracle, cfg, w, xb, lg, np.arange(cfg.T), "decode")
+    assert np.array_equal(buf.ids[: cfg.T].cpu().numpy(), ref["ids"]), "router ids must be bit-exact"
+    np.testing.assert_allclose(buf.coef[: cfg.T].cpu().numpy(), ref["coef"], rtol=2e-6)
+    # pack offsets: bit-exact against the CPU counting sort of the same ids
+    offsets, slots = oracle.moe_group_routes(ref["ids"], cfg.E)
+    from strixite_b200 import kernels as K
+    L = K.route_layout(cfg.T, cfg.k, cfg.E)
+    ws = buf.ws.cpu().numpy()
+    assert np.array_equal(ws[L["offsets"]:L["offsets"] + cfg.E + 2], offsets)
+    assert np.array_equal(ws[L["slots"]:L["slots"] + cfg.T * cfg.k], slots)
+    err = max_abs_over_rms(y32.cpu().numpy(), ref["y_f32"])
+    assert err <= TOL, f"{cfg.name}: max-abs error {err:.3e} x RMS exceeds the path's tolerance {TOL}"
+    assert err <= 2e-3, f"{cfg.name}: the exact-product path should be far inside the tolerance, got {err:.3e}"
+    # BF16 output = one rounding of (almost) the same FP32 value
+    from helpers import bf16_ulps
+    ulps = bf16_ulps(bits_of(ybf), ref["y_bf16"])
+    assert ulps.max() <= 2 and (ulps > 0).mean() < 0.02
+
+
+def test_layer_rows_do_not_depend_on_batch(cuda):
+    """A conversation's rows give the same outputs alone or packed with others (runtime/qwen4exp.hpp:804-809:
+    a batch of one equals forward())."""
+    from strixite_b200 import workloads as W
+    from strixite_b200.kernels import MoeMath
+    from strixite_b200.layer import MoeBuffers, MoeLayer
+    cfg = W.c2_config(0)
+    w = W.make_layer_weights(cfg, 0, cuda)
+    x = W.activations(cfg, 0, cuda)
+    logits = W.router_logits(x, W.router_weight(cfg, 0, cuda), W.expert_bias(cfg, 0, cuda))
+    layer = MoeLayer(w, cfg.E, cfg.k, MoeBuffers(cfg.T, cfg.d, cfg.I, cfg.E, cfg.k, cuda, cfg.shared))
+    y_all = torch.empty((cfg.T, cfg.d), dtype=torch.float32, device=cuda)
+    layer.forward(x, logits, y_all, math=MoeMath.F32)
+    start = 0
+    for n in cfg.runs[:3]:
+        y_run = torch.empty((n, cfg.d), dtype=torch.float32, device=cuda)
+        layer.forward(x[start:start + n].contiguous(), logits[start:start + n].contiguous(), y_run, math=MoeMath.F32)
+        torch.cuda.synchronize()
+        assert torch.equal(y_run, y_all[start:start + n])
+        start += n
