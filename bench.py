@@ -1,0 +1,499 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized MoE FFN path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c3|c2|c1] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
+
+One JSON line on rank 0.  The headline workload (every N) is C4, the configuration the metric "MoE-layer tokens/s at
+1/2/4/8 B200" is quoted on: a stack of 8 MoE layers, T = 16384 prefill tokens, hidden 4096, 512 experts (512 / N per
+GPU), top-10, intermediate 1024, Q4 G128 gate/up and Q8 G64 down, Zipf(1.1) expert popularity; synthetic seeded inputs
+(strixite_b200/workloads.py).  A step = one pass of the T tokens through the 8 layers (router projection, router top-k,
+pack, gate/up + SwiGLU, down + combine, residual; with N > 1 an all-gather of activations and a reduce-scatter of expert
+outputs per layer).  value = T * layers / step time, "MoE-layer tokens per second", whole job.  Strong scaling: T is
+fixed as N grows.
+
+At N = 1 the line also carries, under "other_workloads", the decode configuration C1 (HBM-bound: achieved GB/s of
+algorithmic bytes) and the single-layer prefill configuration C3 (tensor-bound), each with its own roofline entry.
+
+--impl reference times the CPU oracle (the restatement of the reference's arithmetic; the reference ships no CPU or
+CUDA implementation of this path) on the host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import pathlib
+import sys
+import threading
+import time
+
+ROOT = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c4", choices=["c1", "c2", "c3", "c4"])
+    ap.add_argument("--layers", type=int, default=0, help="layers resident (default: the configuration's)")
+    ap.add_argument("--no-extra", action="store_true", help="skip the C1 / C3 side measurements at N = 1")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--cpu-tokens", type=int, default=0, help="tokens of the CPU baseline sample (default by workload)")
+    ap.add_argument("--seed", type=int, default=0)
+    return ap.parse_args()
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# peaks, clocks
+# ------------------------------------------------------------------------------------------------------------------
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        p = json.loads(path.read_text())
+        return dict(hbm_gbs=p["hbm_gbs"], tflops_burst=p["bf16_tflops"], tflops_sustained=p["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, tflops_burst=1590.0, tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs (read-only)."""
+
+    def __init__(self, index: int, period_s: float = 0.1):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:  # NVML missing: clocks are reported as unknown, never guessed
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            nv.nvmlClocksEventReasonHwSlowdown if hasattr(nv, "nvmlClocksEventReasonHwSlowdown") else 0x8: "hw_slowdown",
+            0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h) if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons") \
+                    else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return dict(sm_mhz=(s[len(s) // 2] if s else None), sm_max_mhz=self.max_mhz, reasons=sorted(self.reasons),
+                    samples=len(s))
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# the workloads
+# ------------------------------------------------------------------------------------------------------------------
+
+class Stack:
+    """Resident state of a configuration on this rank: per-layer weights (this rank's experts), router weights, biases,
+    the shared workspaces, and the expert-parallel driver."""
+
+    def __init__(self, cfg, layers, seed, dev, rank, world):
+        import torch
+        from strixite_b200 import workloads as W
+        from strixite_b200.ep import Compute, ExpertParallelMoe, shard_bounds
+        from strixite_b200.layer import MoeBuffers, MoeLayer
+
+        self.cfg, self.n_layers, self.dev, self.rank, self.world = cfg, layers, dev, rank, world
+        self.e_lo, self.e_hi = shard_bounds(cfg.E, world, rank)
+        self.t_lo, self.t_hi = shard_bounds(cfg.T, world, rank)
+        E_local = self.e_hi - self.e_lo
+        self.buf = MoeBuffers(cfg.T, cfg.d, cfg.I, E_local, cfg.k, dev, cfg.shared and world == 1)
+        self.layers, self.wr, self.bias = [], [], []
+        for l in range(layers):
+            w = W.make_layer_weights(cfg, seed, dev, layer=l, e_lo=self.e_lo, e_hi=self.e_hi)
+            self.layers.append(MoeLayer(w, E_local, cfg.k, self.buf, E_total=cfg.E, e_lo=self.e_lo))
+            self.wr.append(W.router_weight(cfg, seed, dev, layer=l))
+            self.bias.append(W.expert_bias(cfg, seed, dev, layer=l))
+        t = self.t_hi - self.t_lo
+        self.ids_loc = torch.empty((t, cfg.k), dtype=torch.int32, device=dev)
+        self.coef_loc = torch.empty((t, cfg.k), dtype=torch.float32, device=dev)
+        self.y_part = torch.empty((cfg.T, cfg.d), dtype=torch.float32, device=dev)
+        self.router_err = self.buf.router_err
+        self.math = None          # None = by token count (tcgen05 from MoeLayer.tc_min_tokens up)
+        self.events = None        # (list, list) of CUDA events around the dominant kernel when roofline timing is on
+        self.ep = ExpertParallelMoe(Compute(self._route, self._experts), layers, cfg.T, cfg.d, cfg.k, dev)
+        self.weight_bytes = sum(ly.w.bytes() for ly in self.layers)
+
+    def _route(self, l, x_loc):
+        from strixite_b200 import kernels as K, workloads as W
+        logits = W.router_logits(x_loc, self.wr[l], self.bias[l])
+        self.logits = logits
+        t = x_loc.shape[0]
+        if self.world == 1:
+            ids, coef = self.buf.ids, self.buf.coef
+        else:
+            ids, coef = self.ids_loc, self.coef_loc
+        K.moe_router(logits, logits.stride(0), t, self.cfg.E, self.cfg.k, None, 1, 0, ids, coef, K.Act.F32, self.router_err)
+        return ids, coef
+
+    def _experts(self, l, x_all, ids_all, coef_all):
+        layer = self.layers[l]
+        T = x_all.shape[0]
+        if self.world > 1:
+            self.buf.ids.copy_(ids_all)
+            self.buf.coef.copy_(coef_all)
+        math = layer.math_for(T, self.math)
+        y = self.y_part[:T]
+        if self.cfg.shared and self.world == 1:
+            sh = self.buf.sh_y32
+            layer.shared_expert(x_all, T, math, sh)
+            gate = self.logits.data_ptr() + 4 * self.cfg.E
+            layer.experts(x_all, T, y, math, gate_logit=gate, gate_ld=self.logits.stride(0), shared_out=sh, events=self.events)
+        else:
+            layer.experts(x_all, T, y, math, events=self.events)
+        return y
+
+    def step(self, x_loc):
+        return self.ep.forward(x_loc)
+
+    def one_layer(self, l, x_loc):
+        return self.ep.layer(l, x_loc)
+
+
+def algorithmic_flops(cfg, layers, shared):
+    routed = 2.0 * cfg.T * cfg.k * 3 * cfg.I * cfg.d
+    sh = 2.0 * cfg.T * 3 * cfg.I * cfg.d if shared else 0.0
+    router = 2.0 * cfg.T * (cfg.E + 1) * cfg.d
+    return layers * (routed + sh + router)
+
+
+def timed(fn, steps, warmup, dist_on, dev):
+    """W untimed steps, then exactly K steps between a barrier + synchronize on both sides; CUDA events on the current
+    stream; the maximum over ranks."""
+    import torch
+    import torch.distributed as dist
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if dist_on:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if dist_on:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if dist_on:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms / steps
+
+
+def kernel_ms(events):
+    """Average duration (ms) of the dominant kernel from the CUDA events recorded around each of its launches."""
+    starts, ends = events
+    if not starts:
+        return None
+    return sum(s.elapsed_time(e) for s, e in zip(starts, ends)) / len(starts)
+
+
+def run_stack(cfg, args, dev, rank, world, peaks, layers=None, rotate=False):
+    """Times a configuration.  rotate: a step runs ONE layer, cycling through the resident layers so consecutive steps
+    never find their weights in L2 (decode); otherwise a step runs the whole stack."""
+    import torch
+    from strixite_b200 import kernels as K, workloads as W
+
+    layers = layers or args.layers or cfg.layers
+    st = Stack(cfg, layers, args.seed, dev, rank, world)
+    t_loc = st.t_hi - st.t_lo
+    x_full = W.activations(cfg, args.seed, dev)
+    x_loc = x_full[st.t_lo:st.t_hi].contiguous()
+    x_host = x_loc.cpu().pin_memory()
+    x_dev = torch.empty_like(x_loc)
+    y_host = torch.empty((t_loc, cfg.d), dtype=torch.bfloat16).pin_memory()
+    counter = {"i": 0}
+
+    def device_step():
+        if rotate:
+            st.one_layer(counter["i"] % layers, x_loc)
+            counter["i"] += 1
+        else:
+            st.step(x_loc)
+
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        if rotate:
+            y = st.one_layer(counter["i"] % layers, x_dev)
+            counter["i"] += 1
+            y_host.copy_(y.to(torch.bfloat16), non_blocking=True)
+        else:
+            y_host.copy_(st.step(x_dev), non_blocking=True)
+
+    dist_on = world > 1
+    K.LAUNCHES = 0
+    device_step()
+    torch.cuda.synchronize()
+    launches_per_step = K.LAUNCHES
+    K.check_router_error(st.router_err, cfg.name)
+    for ly in st.layers[:1]:
+        ly.check_errors(cfg.name)
+
+    with ClockSampler(dev.index or 0) as clocks:
+        st.events = ([], [])
+        ms = timed(device_step, args.steps, args.warmup, dist_on, dev)
+        ev = st.events
+        st.events = None
+        # the events recorded during warm-up are dropped: keep those of the timed steps only
+        per_step = len(ev[0]) // (args.steps + args.warmup) if ev[0] else 0
+        ev = (ev[0][per_step * args.warmup:], ev[1][per_step * args.warmup:])
+        k_ms = kernel_ms(ev)
+        e2e_ms = timed(e2e_step, args.steps, 1, dist_on, dev)
+    layer_tokens = cfg.T * (1 if rotate else layers)
+    out = dict(
+        ms_per_step=ms, value=layer_tokens / (ms * 1e-3), e2e_value=layer_tokens / (e2e_ms * 1e-3), e2e_ms=e2e_ms,
+        h2d=x_host.numel() * 2 * world, d2h=y_host.numel() * 2 * world, launches=launches_per_step, clocks=clocks.summary(),
+        kernel_ms=k_ms, layers=layers, stack=st, x_full=x_full,
+    )
+    return out
+
+
+def roofline_tensor(cfg, res, peaks, world):
+    """Dominant kernel of the prefill regime: the grouped gate/up + SwiGLU GEMM, 2 * S * 2I * d flops per launch (this
+    rank's share of the slots: S / N on average)."""
+    flops = 2.0 * cfg.T * cfg.k * 2 * cfg.I * cfg.d / world
+    if not res["kernel_ms"]:
+        return None
+    achieved = flops / (res["kernel_ms"] * 1e-3) / 1e12
+    peak = peaks["tflops_sustained"]
+    return dict(bound="tensor", kernel="grouped_tc_kernel<gate_up+swiglu>", achieved=achieved, peak=peak, unit="TFLOP/s",
+                frac=achieved / peak, peak_source=peaks["source"] + " (sustained bf16)", traffic=None,
+                flops_per_launch=flops, kernel_ms=res["kernel_ms"])
+
+
+def decode_bytes(cfg, stack, layer_idx):
+    """Algorithmic bytes of one decode layer: every DISTINCT routed expert's gate/up and down once, the shared expert,
+    the router weight, x in and y out."""
+    import torch
+    ly = stack.layers[layer_idx]
+    ids = stack.buf.ids[: cfg.T]
+    U = int(torch.unique(ids).numel())
+    per_expert = ly.w.gate_up.bytes() // ly.E + ly.w.down.bytes() // ly.E
+    b = U * per_expert
+    gu_b = U * (ly.w.gate_up.bytes() // ly.E)
+    if ly.w.shared_gate_up is not None:
+        b += ly.w.shared_gate_up.bytes() + ly.w.shared_down.bytes()
+    b += (cfg.E + 1) * cfg.d * 4 + 2 * cfg.T * cfg.d * 2
+    return b, U, gu_b
+
+
+def cpu_baseline(cfg, res, n_tokens, semantics):
+    """The oracle on the host cores for a sample of the workload's tokens through layer 0 (rank 0, N = 1)."""
+    import numpy as np
+    sys.path.insert(0, str(ROOT / "tests"))
+    from helpers import bits_of
+    from oracle import cpu
+    from test_gpu_layer import oracle_layer_on_touched_experts
+    st = res["stack"]
+    from strixite_b200 import workloads as W
+    x = res["x_full"]
+    logits = W.router_logits(x[:n_tokens], st.wr[0], st.bias[0]).cpu().numpy()
+    xb = bits_of(x[:n_tokens])
+    rows = np.arange(n_tokens)
+    w = st.layers[0].w
+    # time only the oracle's arithmetic: the download of the touched experts happens inside, so run it twice and
+    # time the second pass on warmed page cache... the download dominates nothing: it is excluded by timing the
+    # oracle call through a wrapper that stamps the clock around moe_layer itself.
+    stamps = {}
+    real = cpu.moe_layer
+
+    def stamped(*a, **k):
+        t0 = time.perf_counter()
+        out = real(*a, **k)
+        stamps["s"] = time.perf_counter() - t0
+        return out
+
+    cpu.moe_layer = stamped
+    try:
+        ref = oracle_layer_on_touched_experts(cpu, cfg, w, xb, logits, rows, semantics)
+    finally:
+        cpu.moe_layer = real
+    return dict(value=n_tokens / stamps["s"], unit="MoE-layer tokens/s", cores=cpu.hardware_threads(), kind="port",
+                sample=f"{n_tokens} tokens of layer 0 of {cfg.name} through the CPU oracle ({semantics} semantics), "
+                       f"{stamps['s']:.2f} s"), ref
+
+
+def run_reference(args):
+    """--impl reference: the CPU oracle on the host cores, same configuration, bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import cpu
+    from strixite_b200 import workloads as W
+    cpu.build(None)
+    cfg = W.CONFIGS[args.workload]
+    n_tok = args.cpu_tokens or (8 if cfg.T > 64 else cfg.T)
+    rng = np.random.default_rng(args.seed)
+    # The sample's experts: quantized on the host by the oracle's quantizer from the same distributions.
+    k, E, d, I = cfg.k, cfg.E, cfg.d, cfg.I
+    x = cpu.f32_to_bf16(rng.standard_normal((n_tok, d)).astype(np.float32))
+    wr = (rng.standard_normal((E + 1, d)) * 0.02).astype(np.float32)
+    logits = (cpu.bf16_to_f32(x) @ wr.T).astype(np.float32)
+    ids, _ = cpu.moe_router(logits, E, k)
+    touched = np.unique(ids)
+    E2 = len(touched)
+    gu = cpu.quantize((rng.standard_normal((E2 * 2 * I, d)) * 0.02).astype(np.float32), cfg.group(cfg.gu_bits), cfg.gu_bits)
+    dn = cpu.quantize((rng.standard_normal((E2 * d, I)) * 0.02).astype(np.float32), cfg.group(cfg.dn_bits), cfg.dn_bits)
+    lw = cpu.LayerWeights(gu, dn)
+    if cfg.shared:
+        lw.shared_gate_up = cpu.quantize((rng.standard_normal((2 * I, d)) * 0.02).astype(np.float32), 64, 8)
+        lw.shared_down = cpu.quantize((rng.standard_normal((d, I)) * 0.02).astype(np.float32), 64, 8)
+    sub = np.full((n_tok, E2 + 1), -1e30, dtype=np.float32)
+    sub[:, :E2] = logits[:, touched]
+    sub[:, E2] = logits[:, E]
+    sem = "grouped" if cfg.T >= 256 else "decode"
+    times = []
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        cpu.moe_layer(x, sub, lw, E2, k, semantics=sem)
+        if i >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    s = sum(times) / len(times)
+    value = n_tok / s
+    unit = "MoE-layer tokens/s"
+    print(json.dumps({
+        "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": value, "unit": unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": s * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f64 accumulate, bf16 activations", "data": "synthetic",
+        "config": {"workload": cfg.name, "T": cfg.T, "hidden": d, "experts": E, "top_k": k, "intermediate": I,
+                   "gate_up": f"q{cfg.gu_bits}", "down": f"q{cfg.dn_bits}"},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": cpu.hardware_threads(), "kind": "port",
+                         "sample": f"{n_tok} tokens through one layer per step (the reference has no CPU or CUDA "
+                                   f"implementation of this path; this is the CPU oracle restating its arithmetic)"},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    import torch
+    import torch.distributed as dist
+    from strixite_b200 import workloads as W
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the MoE path has no CPU implementation (see --impl reference)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if world != args.gpus and rank == 0:
+        print(f"note: --gpus {args.gpus} but WORLD_SIZE={world}; using {world}", file=sys.stderr)
+    peaks = measured_peaks()
+    cfg = W.c2_config(args.seed) if args.workload == "c2" else W.CONFIGS[args.workload]
+    decode = cfg.T <= 64
+
+    res = run_stack(cfg, args, dev, rank, world, peaks, layers=(8 if decode else None), rotate=decode)
+    line = {
+        "metric": "moe_layer_tokens_per_s", "value": res["value"], "unit": "MoE-layer tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16 x f16 -> f32 (tcgen05), bf16 activations" if not decode
+        else "bf16 x int4/int8 codes -> f32 (mma.sync), bf16 activations",
+        "data": "synthetic",
+        "config": {"workload": cfg.name, "T": cfg.T, "layers": res["layers"], "hidden": cfg.d, "experts": cfg.E,
+                   "experts_per_gpu": cfg.E // world, "top_k": cfg.k, "intermediate": cfg.I, "gate_up": f"q{cfg.gu_bits}g{cfg.group(cfg.gu_bits)}",
+                   "down": f"q{cfg.dn_bits}g{cfg.group(cfg.dn_bits)}", "shared_expert": cfg.shared, "expert_bias": cfg.bias,
+                   "parallelism": f"ep{world}", "value_is": "T * layers / step time",
+                   "l2": "weights resident per step exceed L2 (126 MB): %.1f GB on this rank" % (res["stack"].weight_bytes / 1e9)},
+        "clocks": res["clocks"], "gpu_launches": res["launches"],
+        "e2e": {"value": res["e2e_value"], "unit": "MoE-layer tokens/s", "h2d_bytes_per_step": res["h2d"],
+                "d2h_bytes_per_step": res["d2h"], "ms_per_step": res["e2e_ms"]},
+    }
+    if decode:
+        b, U, gu_b = decode_bytes(cfg, res["stack"], 0)
+        line["roofline"] = dict(bound="hbm", kernel="whole layer", achieved=b / (res["ms_per_step"] * 1e-3) / 1e9,
+                                peak=peaks["hbm_gbs"], unit="GB/s", frac=b / (res["ms_per_step"] * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                peak_source=peaks["source"], traffic=None, bytes_per_launch=b, distinct_experts=U)
+    else:
+        line["roofline"] = roofline_tensor(cfg, res, peaks, world)
+        line["achieved_tflops_whole_step"] = algorithmic_flops(cfg, res["layers"], cfg.shared and world == 1) / (res["ms_per_step"] * 1e-3) / 1e12
+
+    if rank == 0 and world == 1 and not args.no_cpu:
+        n_tok = args.cpu_tokens or (cfg.T if decode else 24)
+        try:
+            cb, _ = cpu_baseline(cfg, res, n_tok, "decode" if decode else "grouped")
+            line["cpu_baseline"] = cb
+        except Exception as e:  # the baseline is a reported extra: never lose the GPU line to it
+            line["cpu_baseline"] = {"value": None, "unit": "MoE-layer tokens/s", "cores": None, "kind": "port",
+                                    "sample": f"failed: {type(e).__name__}: {e}"}
+    del res
+
+    if rank == 0 and world == 1 and not args.no_extra and args.workload == "c4":
+        extra = {}
+        torch.cuda.empty_cache()
+        for name in ("c1", "c3"):
+            c = W.CONFIGS[name]
+            dec = c.T <= 64
+            r = run_stack(c, args, dev, 0, 1, peaks, layers=(8 if dec else 1), rotate=dec)
+            e = {"tokens_per_s": r["value"], "ms_per_step": r["ms_per_step"], "e2e_tokens_per_s": r["e2e_value"],
+                 "gpu_launches": r["launches"], "clocks": r["clocks"]}
+            if dec:
+                b, U, gu_b = decode_bytes(c, r["stack"], 0)
+                gbs = b / (r["ms_per_step"] * 1e-3) / 1e9
+                e["roofline"] = dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s", frac=gbs / peaks["hbm_gbs"],
+                                     bytes_per_step=b, distinct_experts=U, peak_source=peaks["source"])
+                if r["kernel_ms"]:
+                    e["roofline"]["gate_up_kernel"] = dict(ms=r["kernel_ms"], gbs=gu_b / (r["kernel_ms"] * 1e-3) / 1e9,
+                                                           frac=gu_b / (r["kernel_ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"])
+            else:
+                e["roofline"] = roofline_tensor(c, r, peaks, 1)
+                e["achieved_tflops_whole_step"] = algorithmic_flops(c, 1, c.shared) / (r["ms_per_step"] * 1e-3) / 1e12
+            extra[c.name] = e
+            del r
+            torch.cuda.empty_cache()
+        line["other_workloads"] = extra
+
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -80,7 +80,8 @@ typedef struct SxbQView {
 
 /* kernels/moe_grouped.hpp:75-81  struct MoeSharedAdd. */
 typedef struct SxbMoeSharedAdd {
-    const void *s;           /* the shared expert's output [M, N], activation dtype, not overlapping y */
+    const void *s;           /* the shared expert's output [M, N] in y's dtype (the reference's y is in the activation
+                                dtype; with out_act = SXB_ACT_F32 s is FP32 too), not overlapping y */
     const float *gate_logit; /* token m's gate logit at gate_logit[m * gate_ld] */
     int64_t gate_ld;
     uint32_t gate_index;
@@ -126,6 +127,10 @@ size_t sxb_moe_route_workspace_bytes(int64_t M, int64_t A, int64_t E);
  * slot order, so the whole workspace is reproducible.  1 <= A <= 64, 1 <= E <= 1023, M*A <= 2^20. */
 int sxb_moe_group_routes(const int32_t *ids, int64_t M, int64_t A, int64_t E, void *ws, size_t ws_bytes, uint32_t *err,
                          sxb_stream_t stream);
+/* No counterpart in the reference.  The tcgen05 grouped kernels bound every device-side wait; one that runs out writes
+ * {2, work item, role} into words 5..7 of the workspace header (zeroed by every pack) and the kernel returns.  This
+ * reads the header back (it synchronizes, like sxb_check_expert_error) and returns SXB_ERR_DATA if that happened. */
+int sxb_check_grouped_status(const void *ws, const char *what);
 /* No counterpart in the reference (which has one GPU).  The expert-parallel form: this rank owns experts
  * [e_lo, e_lo + E_local) of E_total; bucket b = expert e_lo + b; slots of other ranks' experts and invalid ids go to
  * bucket E_local.  err is raised only for ids outside [0, E_total). */

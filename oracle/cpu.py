@@ -262,10 +262,12 @@ def moe_layer(x: np.ndarray, logits: np.ndarray, w: LayerWeights, E: int, k: int
         hs = swiglu(gu)
         s = linear_q(hs, w.shared_down, threads=threads)
         gate = np.ascontiguousarray(logits[:, E], dtype=np.float32)
-        out["shared_s"] = s
-        # FP32 view: the unrounded routed sum plus g * s (s as stored); BF16 view: the reference's two roundings.
-        g = 1.0 / (1.0 + np.exp(-gate.astype(np.float32)))
-        out["y_f32"] = (y_routed + g[:, None].astype(np.float32) * bf16_to_f32(s)).astype(np.float32)
+        s32 = linear_q(hs, w.shared_down, out_act=F32, threads=threads)
+        out["shared_s"], out["shared_s_f32"] = s, s32
+        # FP32 view: nothing after h is rounded - the routed sum and the shared expert's output stay FP32, so the
+        # comparison is not at the mercy of one BF16 rounding of s or y falling the other way (one such flip of an
+        # s near 1 is 4e-3, the size of the whole tolerance).  BF16 view: the reference's roundings of s, y, y + g s.
+        out["y_f32"] = moe_shared_add(y_routed, s32, gate, E)
         out["y_bf16"] = moe_shared_add(f32_to_bf16(y_routed), s, gate, E)
     else:
         out["y_f32"] = y_routed

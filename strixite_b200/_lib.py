@@ -41,6 +41,7 @@ SIGNATURES = {
     "sxb_moe_route_workspace_bytes": (sz, [i64, i64, i64]),
     "sxb_moe_group_routes": (C.c_int, [vp, i64, i64, i64, vp, sz, vp, vp]),
     "sxb_moe_group_routes_ep": (C.c_int, [vp, i64, i64, i64, i64, i64, vp, sz, vp, vp]),
+    "sxb_check_grouped_status": (C.c_int, [vp, cp]),
     "sxb_route_layout": (C.c_int, [i64, i64, i64, C.POINTER(i64)]),
     "sxb_linear_q4": (C.c_int, [vp, QV, vp, i64, C.c_int, C.c_int, vp]),
     "sxb_linear_q8": (C.c_int, [vp, QV, vp, i64, C.c_int, C.c_int, vp]),

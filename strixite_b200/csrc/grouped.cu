@@ -38,7 +38,7 @@ int combine_grouped(const char *fn, const void *h, const SxbQView *w, int64_t E_
                  ? tc_partial_grouped<BITS>(fn, h, w, E_view, ws, ws_bytes, M, A, partial, act, h_f16, stream)
                  : stream_partial_grouped<BITS>(fn, h, w, E_view, ws, ws_bytes, M, A, partial, act, stream);
     if (rc) return rc;
-    return combine_reduce(fn, partial, ids, coef, M, A, E_total, e_lo, E_view, N, y, out_act, shared, act, stream);
+    return combine_reduce(fn, partial, ids, coef, M, A, E_total, e_lo, E_view, N, y, out_act, shared, out_act, stream);
 }
 
 }  // namespace

@@ -1,20 +1,553 @@
-// tcgen05 grouped expert GEMMs (placeholder translation unit while the kernels are brought up).
+// Grouped expert GEMMs for the dense-contraction regime (prefill: thousands of tokens, ~80 and up per expert) on the
+// 5th-generation tensor cores: tcgen05.mma with FP32 accumulators in tensor memory.  C ABI side: the MoeMath::WmmaF16
+// forms of linear_q*_experts_gather_grouped[_swiglu] / _combine_grouped (kernels/moe_grouped.hpp:58-91).
+//
+// Numerics are those of the reference's matrix-unit path (kernels/moe_grouped.hpp:29-38, kernels/wmma_gemm.hpp:116-129):
+// activations as F16 (exact from BF16 in F16's range), weights dequantized to F16 as code * scale + min with one
+// rounding, FP32 accumulation over the whole K, and - fused SwiGLU - h = silu(g) * u from the FP32 accumulators,
+// rounded once to BF16 (kernels/moe_grouped.hip:508-524).
+//
+// Shape of the computation ("swap AB"): the weight rows sit on the MMA's M (128 per instruction, two accumulators =
+// 256 rows per work item) and the tokens of one expert on its N (a multiple of 16 up to 128), so an expert with 80
+// tokens costs 80 columns, not a padded 128-row tile.  D[row, token] lives in tensor memory, one row per TMEM lane:
+// the epilogue thread of lane j holds gate row j and up row j of the same tokens, and SwiGLU needs no data movement.
+//
+// One persistent CTA per SM, warp-specialised:
+//   warps 0-3   epilogue: tcgen05.ld of a finished accumulator pair -> SwiGLU / stores, while the next item runs
+//   warp  4     one elected thread issues tcgen05.mma (operands: shared-memory descriptors, K-major, 128-byte swizzle)
+//   warps 5-12  producers.  Thread p owns weight row p of the item: it streams the row's packed codes from global
+//               memory 128 bytes at a time (kept in registers one super-block ahead), dequantizes 64 codes per k-block
+//               with lop3 / packed-half arithmetic and writes the row's 128-byte line of the A tile.  The same
+//               threads gather the tokens' activation rows (16 bytes a chunk), convert BF16 -> F16 and write the B
+//               tile.  Within every group of 8 consecutive k both operands use the order [0 4 1 5 2 6 3 7] (Q4),
+//               the order in which a nibble pair falls out of one lop3, so no element is moved after dequantization.
+// Stages are handed over with mbarriers (producers -> MMA: arrive after fence.proxy.async; MMA -> producers and
+// MMA -> epilogue: tcgen05.commit).  Every wait is bounded: past the limit the CTA raises its abort flag, records
+// {2, item, role} in the status words, drains the tensor pipe and frees its tensor memory before returning.
+//
+// No tensor map, no multicast: the operands never come through TMA, so nothing here can touch a peer GPU's memory.
+
 #include "experts.cuh"
 
+#include <cuda_fp16.h>
+
 namespace sxb {
+namespace {
+
+constexpr int kEpiWarps = 4, kMmaWarp = 4, kFirstProducerWarp = 5, kProducerWarps = 8;
+constexpr int kThreads = 32 * (kFirstProducerWarp + kProducerWarps);  // 416
+constexpr int kProducers = 32 * kProducerWarps;                       // 256 = weight rows per item
+constexpr int kBK = 64;                                               // k per stage: one 128-byte swizzle line of F16
+constexpr int kMaxTileTokens = 128;
+constexpr int kStages = 4;
+constexpr int kABytes = kProducers * kBK * 2;       // 32 KB: two 128-row MMA operands
+constexpr int kBBytes = kMaxTileTokens * kBK * 2;   // 16 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kTmemCols = 512;                      // 2 buffers x 2 accumulators x 128 columns
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any legitimate wait
+
+enum TcMode { kTcGather = 0, kTcSwiglu = 1, kTcPartial = 2 };
+
+struct TcArgs {
+    const uint16_t *x;  // activations: BF16 bits, or F16 bits when x_f16
+    const uint8_t *q;
+    const uint16_t *scale, *minv;
+    int64_t N, K;     // weight rows per expert, codes per row
+    int64_t A, E;     // slots per token, experts in the view
+    const int32_t *ws;
+    RouteWords L;
+    void *out;
+    int x_f16;    // the activations already hold F16 bits (h stored with h_f16)
+    int out_f16;  // SwiGLU: store h as F16 bits of its BF16 rounding
+    uint32_t *status;  // >= 3 words: {2, item, role} on a wait that ran out
+};
+
+// ---- PTX wrappers ----------------------------------------------------------------------------------------------
+__device__ inline uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ inline void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ inline void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ inline bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ inline unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait.  False when the CTA is aborting or the limit ran out (then the caller raises the abort itself).
+__device__ inline bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (uint32_t spins = 1;; ++spins) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spins & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > kWaitLimitNs) return false;
+        }
+    }
+}
+__device__ inline void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ inline void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ inline void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ inline void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ inline void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 16 consecutive columns of this thread's TMEM lane.
+__device__ inline void tc_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart.
+//   bits [0,14) start address >> 4 | [16,30) leading byte offset >> 4 (unused for swizzled K-major: 1)
+//   [32,46) stride byte offset >> 4 (1024 B) | [46,48) descriptor version 1 | [61,64) layout 2 = SWIZZLE_128B
+__device__ inline uint64_t smem_desc(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor for kind::f16: D FP32 (bits [4,6) = 1), A and B F16 (formats 0), both K-major,
+// N >> 3 at bits [17,23), M >> 4 at bits [24,29).
+__device__ inline uint32_t instr_desc(int n_cols) { return (1u << 4) | ((uint32_t)(n_cols >> 3) << 17) | ((128u >> 4) << 24); }
+
+__device__ inline uint32_t h2_as_u32(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
+__device__ inline __half2 u32_as_h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
+
+// Byte offset of 16-byte chunk c of row r inside a K-major, 128-byte-swizzled tile.
+__device__ inline uint32_t swz(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
+
+// Eight activations (one 16-byte chunk of BF16 or F16) -> F16 in the operand's k order.
+template <int BITS>
+__device__ inline uint4 b_chunk(uint4 s, bool is_f16) {
+    uint4 d;
+    if (is_f16) {
+        if (BITS == 4) {
+            d.x = __byte_perm(s.x, s.z, 0x5410), d.y = __byte_perm(s.x, s.z, 0x7632);
+            d.z = __byte_perm(s.y, s.w, 0x5410), d.w = __byte_perm(s.y, s.w, 0x7632);
+        } else {
+            d = s;
+        }
+        return d;
+    }
+    const uint32_t w[4] = {s.x, s.y, s.z, s.w};
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[2 * i] = __uint_as_float(w[i] << 16), f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    if (BITS == 4) {  // [x0 x4 | x1 x5 | x2 x6 | x3 x7]
+        d.x = h2_as_u32(__floats2half2_rn(f[0], f[4])), d.y = h2_as_u32(__floats2half2_rn(f[1], f[5]));
+        d.z = h2_as_u32(__floats2half2_rn(f[2], f[6])), d.w = h2_as_u32(__floats2half2_rn(f[3], f[7]));
+    } else {
+        d.x = h2_as_u32(__floats2half2_rn(f[0], f[1])), d.y = h2_as_u32(__floats2half2_rn(f[2], f[3]));
+        d.z = h2_as_u32(__floats2half2_rn(f[4], f[5])), d.w = h2_as_u32(__floats2half2_rn(f[6], f[7]));
+    }
+    return d;
+}
+
+// Eight weights = one 16-byte chunk of the A line, from one word of Q4 codes or two words of Q8 codes.
+// w = code * s + m with one F16 rounding (kernels/wmma_gemm.hpp:116-129).
+__device__ inline uint4 dequant_q4_word(uint32_t w, __half2 s, __half2 s16, __half2 m) {
+    const __half2 k1024 = __float2half2_rn(1024.f);
+    const uint32_t w8 = w >> 8;
+    // (w & 0x000F000F) | 0x64006400 = (1024 + n0, 1024 + n4); the 0x00F0 nibbles give 1024 + 16 n and meet s / 16
+    const __half2 p0 = __hsub2(u32_as_h2((w & 0x000F000Fu) | 0x64006400u), k1024);
+    const __half2 p1 = __hsub2(u32_as_h2((w & 0x00F000F0u) | 0x64006400u), k1024);
+    const __half2 p2 = __hsub2(u32_as_h2((w8 & 0x000F000Fu) | 0x64006400u), k1024);
+    const __half2 p3 = __hsub2(u32_as_h2((w8 & 0x00F000F0u) | 0x64006400u), k1024);
+    uint4 d;
+    d.x = h2_as_u32(__hfma2(p0, s, m)), d.y = h2_as_u32(__hfma2(p1, s16, m));
+    d.z = h2_as_u32(__hfma2(p2, s, m)), d.w = h2_as_u32(__hfma2(p3, s16, m));
+    return d;
+}
+__device__ inline uint4 dequant_q8_words(uint32_t w0, uint32_t w1, __half2 s, __half2 m) {
+    const __half2 k1024 = __float2half2_rn(1024.f);
+    uint4 d;  // __byte_perm(w, 0x64646464, 0x4140) = (0x6400 | b0, 0x6400 | b1) = (1024 + b0, 1024 + b1)
+    d.x = h2_as_u32(__hfma2(__hsub2(u32_as_h2(__byte_perm(w0, 0x64646464u, 0x4140)), k1024), s, m));
+    d.y = h2_as_u32(__hfma2(__hsub2(u32_as_h2(__byte_perm(w0, 0x64646464u, 0x4342)), k1024), s, m));
+    d.z = h2_as_u32(__hfma2(__hsub2(u32_as_h2(__byte_perm(w1, 0x64646464u, 0x4140)), k1024), s, m));
+    d.w = h2_as_u32(__hfma2(__hsub2(u32_as_h2(__byte_perm(w1, 0x64646464u, 0x4342)), k1024), s, m));
+    return d;
+}
+
+struct ItemInfo {
+    int bucket, start, cnt;  // expert (bucket E = invalid ids), first position in slots[], tokens in the tile
+    int rb;                  // row block
+};
+
+template <int MODE>
+__device__ inline int row_blocks(const TcArgs &a) {
+    return MODE == kTcSwiglu ? (int)((a.N / 2 + 127) / 128) : (int)((a.N + kProducers - 1) / kProducers);
+}
+template <int MODE>
+__device__ inline ItemInfo item_info(const TcArgs &a, int item, int rbs) {
+    ItemInfo it;
+    const int tile = item / rbs;
+    it.rb = item % rbs;
+    it.bucket = a.ws[a.L.t128_bucket + tile];
+    it.start = a.ws[a.L.t128_start + tile];
+    it.cnt = min(kMaxTileTokens, a.ws[a.L.offsets + it.bucket + 1] - it.start);
+    return it;
+}
+
+template <int BITS, int G, int MODE>
+__global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // 1024-byte alignment of the operand tiles (the swizzle pattern repeats every 1024 bytes).
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t full_bar[kStages], empty_bar[kStages], acc_full[2], acc_empty[2], drain_bar;
+    __shared__ uint32_t tmem_base_smem;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int K = (int)a.K, n_kb = K / kBK, groups = K / G;
+    const int rbs = row_blocks<MODE>(a);
+    const int n_items = a.ws[3] * rbs;
+    volatile int *abort_v = &abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], kProducerWarps), mbar_init(&empty_bar[s], 1);
+        for (int b = 0; b < 2; ++b) mbar_init(&acc_full[b], 1), mbar_init(&acc_empty[b], kEpiWarps);
+        mbar_init(&drain_bar, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kMmaWarp) {  // one warp allocates the CTA's tensor memory (all 512 columns: one CTA per SM)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_smem)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_smem;
+
+    auto raise_abort = [&](int item, int role) {
+        if (atomicExch(&abort_flag, 1) == 0 && atomicCAS(&a.status[0], 0u, 2u) == 0u) {
+            a.status[1] = (uint32_t)item;
+            a.status[2] = (uint32_t)role;
+        }
+    };
+
+    if (warp >= kFirstProducerWarp) {
+        // ===================== producers =====================
+        const int p = threadIdx.x - 32 * kFirstProducerWarp;  // weight row of the item, 0..255
+        const int64_t row_bytes = BITS == 4 ? a.K / 2 : a.K;
+        constexpr int kSuperKb = BITS == 4 ? 4 : 2;  // k-blocks per 128 bytes of packed codes
+        constexpr int kWordsPerKb = BITS == 4 ? 8 : 16;
+        uint32_t it_count = 0;  // k-blocks produced so far (stage / phase bookkeeping)
+        for (int item = blockIdx.x; item < n_items && !*abort_v; item += gridDim.x) {
+            const ItemInfo it = item_info<MODE>(a, item, rbs);
+            if (it.bucket >= a.E) continue;  // invalid ids: no weights to multiply, the epilogue writes NaN
+            // this thread's weight row
+            int64_t wrow;
+            bool wvalid;
+            if (MODE == kTcSwiglu) {
+                const int64_t I = a.N / 2, j = (int64_t)it.rb * 128 + (p & 127);
+                wvalid = j < I;
+                wrow = (int64_t)it.bucket * a.N + (p < 128 ? j : I + j);
+            } else {
+                const int64_t r = (int64_t)it.rb * kProducers + p;
+                wvalid = r < a.N;
+                wrow = (int64_t)it.bucket * a.N + r;
+            }
+            const uint4 *qrow = reinterpret_cast<const uint4 *>(a.q + wrow * row_bytes);
+            const uint16_t *srow = a.scale + wrow * groups, *mrow = a.minv + wrow * groups;
+            // the activation rows this thread copies: chunk ids p, p + 256, ... -> token (id >> 3) = p / 8 + 32 i
+            const uint16_t *brow[kMaxTileTokens * 8 / kProducers];
+#pragma unroll
+            for (int i = 0; i < kMaxTileTokens * 8 / kProducers; ++i) {
+                const int n = (p >> 3) + 32 * i;
+                brow[i] = a.x;
+                if (n < it.cnt) {
+                    const int64_t slot = a.ws[a.L.slots + it.start + n];
+                    brow[i] = a.x + (MODE == kTcPartial ? slot : slot / a.A) * a.K;
+                }
+            }
+            // 128 bytes of the row's packed codes at a time (a "super-block": 4 k-blocks of Q4, 2 of Q8), held in
+            // registers one super-block ahead of the one being dequantized, so the row is read as whole 128-byte lines
+            // and each load has several k-blocks of work to hide behind.
+            uint4 cur[8], nxt[8];
+            const int n_sb = (n_kb + kSuperKb - 1) / kSuperKb;
+            auto load_super = [&](uint4(&dst)[8], int sb) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    dst[i] = make_uint4(0u, 0u, 0u, 0u);
+                    if (wvalid && sb < n_sb && (sb * kSuperKb + i * kSuperKb / 8) < n_kb) dst[i] = __ldg(qrow + sb * 8 + i);
+                }
+            };
+            load_super(cur, 0);
+            bool live = true;
+            for (int sb = 0; sb < n_sb && live; ++sb) {
+                load_super(nxt, sb + 1);
+#pragma unroll
+                for (int sub = 0; sub < kSuperKb; ++sub) {
+                    const int kb = sb * kSuperKb + sub;
+                    if (kb >= n_kb) break;
+                    const int stage = it_count % kStages;
+                    const uint32_t phase = (it_count / kStages) & 1u;
+                    ++it_count;
+                    if (lane == 0 && !mbar_wait(&empty_bar[stage], phase ^ 1u, abort_v)) raise_abort(item, 1);
+                    __syncwarp();
+                    if (*abort_v) {
+                        live = false;
+                        break;
+                    }
+                    unsigned char *sa = smem + stage * kStageBytes, *sb_ = sa + kABytes;
+                    // ---- A: this thread's row, 64 codes -> 8 chunks of 8 F16
+                    {
+                        unsigned char *line = sa + (p >> 7) * (128 * 128);
+                        const int r = p & 127;
+                        uint32_t words[kWordsPerKb];
+#pragma unroll
+                        for (int i = 0; i < kWordsPerKb / 4; ++i) {
+                            const uint4 v = cur[sub * (kWordsPerKb / 4) + i];
+                            words[4 * i] = v.x, words[4 * i + 1] = v.y, words[4 * i + 2] = v.z, words[4 * i + 3] = v.w;
+                        }
+                        constexpr int kGroupsPerKb = G >= kBK ? 1 : kBK / G;
+                        __half2 s2[kGroupsPerKb], s16[kGroupsPerKb], m2[kGroupsPerKb];
+#pragma unroll
+                        for (int gi = 0; gi < kGroupsPerKb; ++gi) {
+                            const int g = (kb * kBK) / G + gi;
+                            const float sf = wvalid ? bf16_bits_to_f32(__ldg(srow + g)) : 0.f;
+                            const float mf = wvalid ? bf16_bits_to_f32(__ldg(mrow + g)) : 0.f;
+                            s2[gi] = __float2half2_rn(sf), s16[gi] = __float2half2_rn(sf * 0.0625f), m2[gi] = __float2half2_rn(mf);
+                        }
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            const int gi = kGroupsPerKb == 1 ? 0 : (c * 8) / G;
+                            uint4 d;
+                            if (BITS == 4) d = dequant_q4_word(words[c], s2[gi], s16[gi], m2[gi]);
+                            else d = dequant_q8_words(words[2 * c], words[2 * c + 1], s2[gi], m2[gi]);
+                            *reinterpret_cast<uint4 *>(line + swz(r, c)) = d;
+                        }
+                    }
+                    // ---- B: the tile's tokens, 8 chunks of 8 activations each
+#pragma unroll
+                    for (int i = 0; i < kMaxTileTokens * 8 / kProducers; ++i) {
+                        const int n = (p >> 3) + 32 * i, c = p & 7;
+                        if (n < it.cnt) {
+                            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(brow[i] + kb * kBK + c * 8));
+                            *reinterpret_cast<uint4 *>(sb_ + swz(n, c)) = b_chunk<BITS>(v, a.x_f16 != 0);
+                        }
+                    }
+                    fence_proxy_async();  // the tensor core reads these lines through the async proxy
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&full_bar[stage]);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) cur[i] = nxt[i];
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ===================== MMA issue =====================
+        uint32_t it_count = 0, acc_count = 0;
+        for (int item = blockIdx.x; item < n_items && !*abort_v; item += gridDim.x) {
+            const ItemInfo it = item_info<MODE>(a, item, rbs);
+            if (it.bucket >= a.E) continue;
+            const int buf = acc_count & 1;
+            const uint32_t acc_phase = (acc_count >> 1) & 1u;
+            ++acc_count;
+            if (lane == 0 && !mbar_wait(&acc_empty[buf], acc_phase ^ 1u, abort_v)) raise_abort(item, 2);
+            __syncwarp();
+            if (*abort_v) break;
+            tc_fence_after();
+            const int n_cols = (it.cnt + 15) & ~15;
+            const uint32_t idesc = instr_desc(n_cols);
+            for (int kb = 0; kb < n_kb; ++kb, ++it_count) {
+                const int stage = it_count % kStages;
+                const uint32_t phase = (it_count / kStages) & 1u;
+                if (lane == 0 && !mbar_wait(&full_bar[stage], phase, abort_v)) raise_abort(item, 3);
+                __syncwarp();
+                if (*abort_v) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t sa = smem_u32(smem + stage * kStageBytes), sb_ = sa + kABytes;
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const uint32_t d = tmem_base + (uint32_t)((buf * 2 + half) * kMaxTileTokens);
+#pragma unroll
+                        for (int j = 0; j < kBK / 16; ++j)
+                            tc_mma_f16(d, smem_desc(sa + half * (128 * 128) + j * 32), smem_desc(sb_ + j * 32), idesc,
+                                       (kb | j) != 0);
+                    }
+                    tc_commit(&empty_bar[stage]);                      // frees the stage when these MMAs have read it
+                    if (kb == n_kb - 1) tc_commit(&acc_full[buf]);     // and hands the accumulators to the epilogue
+                }
+                __syncwarp();
+            }
+        }
+        // Drain: every MMA issued by this CTA has completed before tensor memory is released.
+        if (lane == 0) {
+            tc_commit(&drain_bar);
+            mbar_wait(&drain_bar, 0u, abort_v);
+        }
+        __syncwarp();
+    } else {
+        // ===================== epilogue =====================
+        uint32_t acc_count = 0;
+        const int64_t I = a.N / 2;
+        for (int item = blockIdx.x; item < n_items && !*abort_v; item += gridDim.x) {
+            const ItemInfo it = item_info<MODE>(a, item, rbs);
+            const bool valid = it.bucket < a.E;
+            int buf = 0;
+            if (valid) {
+                buf = acc_count & 1;
+                const uint32_t acc_phase = (acc_count >> 1) & 1u;
+                ++acc_count;
+                if (lane == 0 && !mbar_wait(&acc_full[buf], acc_phase, abort_v)) raise_abort(item, 4);
+                __syncwarp();
+                if (*abort_v) break;
+                tc_fence_after();
+            }
+            const int row = warp * 32 + lane;  // TMEM lane = weight row inside a 128-row accumulator
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+            for (int c0 = 0; c0 < it.cnt; c0 += 16) {
+                float v0[16], v1[16];
+                if (valid) {
+                    tc_ld16(lane_addr + (uint32_t)((buf * 2 + 0) * kMaxTileTokens + c0), v0);
+                    tc_ld16(lane_addr + (uint32_t)((buf * 2 + 1) * kMaxTileTokens + c0), v1);
+                } else {
+#pragma unroll
+                    for (int t = 0; t < 16; ++t) v0[t] = v1[t] = qnan_f32();
+                }
+#pragma unroll
+                for (int t = 0; t < 16; ++t) {
+                    const int n = c0 + t;
+                    if (n >= it.cnt) break;
+                    const int64_t slot = a.ws[a.L.slots + it.start + n];
+                    if (MODE == kTcSwiglu) {
+                        const int64_t j = (int64_t)it.rb * 128 + row;
+                        if (j < I) {
+                            // kernels/moe_grouped.hip:508-524: from the FP32 accumulators, rounded once
+                            const uint16_t hb = f32_to_bf16_bits(silu_f32(v0[t]) * v1[t]);
+                            uint16_t *out = static_cast<uint16_t *>(a.out);
+                            out[slot * I + j] = a.out_f16 ? __half_as_ushort(__float2half_rn(bf16_bits_to_f32(hb))) : hb;
+                        }
+                    } else {
+                        const int64_t r0 = (int64_t)it.rb * kProducers + row, r1 = r0 + 128;
+                        if (MODE == kTcPartial) {
+                            float *out = static_cast<float *>(a.out);
+                            if (r0 < a.N) out[slot * a.N + r0] = v0[t];
+                            if (r1 < a.N) out[slot * a.N + r1] = v1[t];
+                        } else {
+                            uint16_t *out = static_cast<uint16_t *>(a.out);
+                            if (r0 < a.N) out[slot * a.N + r0] = f32_to_bf16_bits(v0[t]);
+                            if (r1 < a.N) out[slot * a.N + r1] = f32_to_bf16_bits(v1[t]);
+                        }
+                    }
+                }
+            }
+            if (valid) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+int check_tc(const char *fn, const void *x, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes, int64_t M,
+             int64_t A, const void *out, int act) {
+    SXB_CHECK(x != nullptr && out != nullptr && ws != nullptr && w != nullptr, fn, ": null pointer (x=", x, ", out=", out,
+              ", ws=", ws, ")");
+    SXB_CHECK(w->q != nullptr && w->scale != nullptr && w->minv != nullptr, fn, ": null weight pointer");
+    SXB_CHECK(w->G == 32 || w->G == 64 || w->G == 128, fn, ": group size ", w->G, " unsupported (32, 64 or 128)");
+    SXB_CHECK(w->K >= 128 && w->K % 128 == 0 && w->K <= (1 << 24), fn, ": K = ", w->K,
+              ", the tcgen05 kernels need a multiple of 128 (two 64-wide k-blocks per 128 bytes of Q8 codes)");
+    SXB_CHECK(E >= 1 && E <= kMoeMaxExperts && w->N % E == 0, fn, ": weight has ", w->N, " rows for E = ", E, " experts");
+    SXB_CHECK(M >= 1 && A >= 1 && A <= 64 && A <= E && M * A <= kMoeMaxSlots, fn, ": M = ", M, " tokens x A = ", A, " slots");
+    SXB_CHECK(ws_bytes >= (size_t)route_words(M, A, E).total * 4, fn, ": workspace of ", ws_bytes, " bytes, needs ",
+              route_words(M, A, E).total * 4);
+    SXB_CHECK(aligned16(w->q) && aligned16(x), fn, ": code array ", (const void *)w->q, " and input ", x,
+              " must be 16-byte aligned");
+    SXB_CHECK(act == SXB_ACT_BF16, fn, ": the WMMA_F16 kernels take BF16 activations, got ", act_name(act));
+    return SXB_OK;
+}
+
+// The status words of a launch live in the grouping workspace's header (words 5..7, zeroed by the pack).
+template <int BITS, int MODE>
+int launch_tc(const char *fn, const TcArgs &a, int64_t G, cudaStream_t st) {
+    const size_t smem = (size_t)kStages * kStageBytes + 1024;
+    auto go = [&](auto kern) -> int {
+        SXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn,
+                 ": reserving shared memory");
+        kern<<<(unsigned)sm_count(), kThreads, smem, st>>>(a);
+        return SXB_OK;
+    };
+    switch (G) {
+        case 32: return go(grouped_tc_kernel<BITS, 32, MODE>);
+        case 64: return go(grouped_tc_kernel<BITS, 64, MODE>);
+        default: return go(grouped_tc_kernel<BITS, 128, MODE>);
+    }
+}
+
+}  // namespace
 
 template <int BITS>
-int tc_gather_grouped(const char *fn, const void *, const SxbQView *, int64_t, const void *, size_t, int64_t, int64_t, void *,
-                      int, bool, bool, sxb_stream_t) {
-    SXB_CHECK(false, fn, ": the WMMA_F16 (tcgen05) kernels are not built into this library");
+int tc_gather_grouped(const char *fn, const void *x, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes, int64_t M,
+                      int64_t A, void *y, int act, bool swiglu, bool h_f16, sxb_stream_t stream) {
+    if (int rc = check_tc(fn, x, w, E, ws, ws_bytes, M, A, y, act)) return rc;
+    const int64_t N = w->N / E;
+    SXB_CHECK(!swiglu || N % 2 == 0, fn, ": gate_up has ", N, " rows an expert, expected an even count");
+    SXB_CHECK(apart(x, M * w->K * 2, y, M * A * (swiglu ? N / 2 : N) * 2), fn, ": output overlaps input x");
+    TcArgs a{};
+    a.x = static_cast<const uint16_t *>(x), a.q = w->q, a.scale = w->scale, a.minv = w->minv;
+    a.N = N, a.K = w->K, a.A = A, a.E = E, a.ws = static_cast<const int32_t *>(ws), a.L = route_words(M, A, E);
+    a.out = y, a.x_f16 = 0, a.out_f16 = h_f16 ? 1 : 0;
+    a.status = reinterpret_cast<uint32_t *>(const_cast<void *>(ws)) + 5;
+    auto st = static_cast<cudaStream_t>(stream);
+    int rc = swiglu ? launch_tc<BITS, kTcSwiglu>(fn, a, w->G, st) : launch_tc<BITS, kTcGather>(fn, a, w->G, st);
+    if (rc) return rc;
+    SXB_CHECK_LAUNCH(fn, " tcgen05 M=", M, " A=", A, " E=", E, " N=", N, " K=", w->K, " G=", w->G);
     return SXB_OK;
 }
+
 template <int BITS>
-int tc_partial_grouped(const char *fn, const void *, const SxbQView *, int64_t, const void *, size_t, int64_t, int64_t, float *,
-                       int, bool, sxb_stream_t) {
-    SXB_CHECK(false, fn, ": the WMMA_F16 (tcgen05) kernels are not built into this library");
+int tc_partial_grouped(const char *fn, const void *h, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes, int64_t M,
+                       int64_t A, float *partial, int act, bool h_f16, sxb_stream_t stream) {
+    if (int rc = check_tc(fn, h, w, E, ws, ws_bytes, M, A, partial, act)) return rc;
+    const int64_t N = w->N / E;
+    TcArgs a{};
+    a.x = static_cast<const uint16_t *>(h), a.q = w->q, a.scale = w->scale, a.minv = w->minv;
+    a.N = N, a.K = w->K, a.A = A, a.E = E, a.ws = static_cast<const int32_t *>(ws), a.L = route_words(M, A, E);
+    a.out = partial, a.x_f16 = h_f16 ? 1 : 0, a.out_f16 = 0;
+    a.status = reinterpret_cast<uint32_t *>(const_cast<void *>(ws)) + 5;
+    auto st = static_cast<cudaStream_t>(stream);
+    if (int rc = launch_tc<BITS, kTcPartial>(fn, a, w->G, st)) return rc;
+    SXB_CHECK_LAUNCH(fn, " tcgen05 partial M=", M, " A=", A, " E=", E, " N=", N, " K=", w->K, " G=", w->G);
     return SXB_OK;
 }
+
 template int tc_gather_grouped<4>(const char *, const void *, const SxbQView *, int64_t, const void *, size_t, int64_t, int64_t,
                                   void *, int, bool, bool, sxb_stream_t);
 template int tc_gather_grouped<8>(const char *, const void *, const SxbQView *, int64_t, const void *, size_t, int64_t, int64_t,

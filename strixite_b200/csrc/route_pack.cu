@@ -272,6 +272,18 @@ int sxb_route_layout(int64_t M, int64_t A, int64_t E, int64_t out[8]) {
     return SXB_OK;
 }
 
+int sxb_check_grouped_status(const void *ws, const char *what) {
+    SXB_CHECK(ws != nullptr, "check_grouped_status(", what, "): null workspace");
+    int32_t head[8];
+    SXB_CUDA(cudaMemcpy(head, ws, sizeof(head), cudaMemcpyDeviceToHost), "reading the workspace header for ", what);
+    if (head[5] == 0) return SXB_OK;
+    static const char *roles[] = {"?", "a producer waiting for a free stage", "the MMA warp waiting for free accumulators",
+                                  "the MMA warp waiting for a filled stage", "the epilogue waiting for the accumulators"};
+    last_error() = cat(what, ": a tcgen05 grouped kernel gave up a wait at work item ", head[6], " (",
+                       roles[head[7] >= 1 && head[7] <= 4 ? head[7] : 0], "); its outputs are incomplete");
+    return SXB_ERR_DATA;
+}
+
 int sxb_moe_group_routes(const int32_t *ids, int64_t M, int64_t A, int64_t E, void *ws, size_t ws_bytes, uint32_t *err,
                          sxb_stream_t stream) {
     return group_routes("moe_group_routes", ids, M, A, E, 0, E, false, ws, ws_bytes, err, stream);

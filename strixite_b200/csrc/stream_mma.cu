@@ -12,14 +12,14 @@
 //   * a warp owns 16 weight rows; lane (g = lane / 4, c = lane % 4) streams rows g and g + 8 with one 16-byte
 //     `ld.global.nc` each per step, the four lanes of a quad covering 64 contiguous bytes of a row, which for the
 //     served formats (Q4 G = 128, Q8 G = 64) is exactly one quantization group;
-//   * nibbles become BF16 pairs in registers with one shift + one `lop3` per pair: (w >> 4s) & 0x000F000F | 0x43004300
-//     is the pair (128 + code, 128 + code') exactly; the 128 offset is removed in FP32 with the group's sum(x);
+//   * nibbles become BF16 pairs in registers with a shift, a `lop3` and a packed subtract per pair:
+//     (w >> 4s) & 0x000F000F | 0x43004300 is the pair (128 + code, 128 + code') exactly, minus (128, 128) the codes;
 //     a Q8 byte is split into its two nibbles and the high one meets 16 * x;
 //   * the activations of the tile's <= 8 tokens sit in shared memory already permuted into `mma.m16n8k16` B-fragment
 //     order, so a lane fetches its fragments with conflict-free 16-byte loads; k is permuted consistently on both
 //     operands, which a dot product does not notice;
-//   * per step: D = sum over the quad's codes of (128 + q) * x on the tensor cores, then
-//     acc += s * D + (m - 128 s) * sum(x) in FP32.
+//   * per step: D = sum over the quad's codes of q * x on the tensor cores (exact products, FP32 sums), then
+//     acc += s * D + m * sum(x) in FP32.
 // Work is cut into units of 16 rows x one tile of <= 8 tokens of one expert; CTAs take contiguous ranges of units so
 // a CTA restages activations only when it crosses into another tile, and every touched expert's weights are read
 // once per tile (once in total when an expert has <= 8 tokens, the decode case).
@@ -50,7 +50,6 @@ struct Geo {
     static constexpr int kStepCodes = 4 * kCodesPerLane;  // codes of one row a quad consumes per step (<= G)
     static constexpr int kUnits = kCodesPerLane / 8;      // 16-byte activation units per lane per step
     static constexpr int kStepsPerGroup = G / kStepCodes;
-    static constexpr float kOffset = BITS == 4 ? 128.f : 128.f * 17.f;
 };
 
 template <int WORDS> __device__ inline void load_codes(uint32_t (&w)[WORDS], const uint8_t *p, bool pred);
@@ -77,8 +76,13 @@ __device__ inline void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Nibbles s and s + 4 of w as the BF16 pair (128 + n_s, 128 + n_{s+4}).
-template <int S> __device__ inline uint32_t nibble_pair(uint32_t w) { return ((w >> (4 * S)) & 0x000F000Fu) | 0x43004300u; }
+// Nibbles s and s + 4 of w as the BF16 pair (n_s, n_{s+4}): `(w >> 4s) & 0x000F000F | 0x43004300` is the pair
+// (128 + n_s, 128 + n_{s+4}) exactly (BF16 keeps 8 significant bits), and one packed subtract removes the 128s.
+template <int S> __device__ inline uint32_t nibble_pair(uint32_t w) {
+    uint32_t v = ((w >> (4 * S)) & 0x000F000Fu) | 0x43004300u, r;
+    asm("sub.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(0x43004300u));
+    return r;
+}
 
 __device__ inline uint32_t times16(uint32_t bf16x2) {
     __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162 *>(&bf16x2);
@@ -200,11 +204,10 @@ __device__ inline void rows_dot(float (&acc)[4], const StreamArgs &a, int64_t ro
                 const float2 xs2 = *reinterpret_cast<const float2 *>(xsum + step * kTileTokens + 2 * c);
                 const float s_a = bf16_bits_to_f32(qs[p][0]), m_a = bf16_bits_to_f32(qs[p][1]);
                 const float s_b = bf16_bits_to_f32(qs[p][2]), m_b = bf16_bits_to_f32(qs[p][3]);
-                const float off_a = fmaf(-geo::kOffset, s_a, m_a), off_b = fmaf(-geo::kOffset, s_b, m_b);
-                acc[0] = fmaf(s_a, d[0], fmaf(off_a, xs2.x, acc[0]));
-                acc[1] = fmaf(s_a, d[1], fmaf(off_a, xs2.y, acc[1]));
-                acc[2] = fmaf(s_b, d[2], fmaf(off_b, xs2.x, acc[2]));
-                acc[3] = fmaf(s_b, d[3], fmaf(off_b, xs2.y, acc[3]));
+                acc[0] = fmaf(s_a, d[0], fmaf(m_a, xs2.x, acc[0]));
+                acc[1] = fmaf(s_a, d[1], fmaf(m_a, xs2.y, acc[1]));
+                acc[2] = fmaf(s_b, d[2], fmaf(m_b, xs2.x, acc[2]));
+                acc[3] = fmaf(s_b, d[3], fmaf(m_b, xs2.y, acc[3]));
             }
             fetch(p, step + kPrefetch);  // refill the slot just consumed
         }

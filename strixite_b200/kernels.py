@@ -43,7 +43,16 @@ class MoeMath(enum.IntEnum):  # kernels/moe_grouped.hpp:39
     WmmaF16Wide256 = 5
 
 
+LAUNCHES = 0  # kernels of this library launched through this module (the benchmark's gpu_launches)
+
+
+def _count(n: int = 1) -> None:
+    global LAUNCHES
+    LAUNCHES += n
+
+
 def _check(rc: int) -> None:
+    _count()
     if rc != 0:
         msg = _lib.load().sxb_last_error().decode()
         raise (GpuFatalError if rc == 3 else Error)(rc, msg)
@@ -136,10 +145,16 @@ def route_layout(M, A, E) -> dict:
 
 
 def moe_group_routes(ids, M, A, E, ws, ws_bytes, err, stream=None):
+    _count(2 if M * A > 2048 else 0)  # the multi-CTA pack is three launches
     _check(_lib.load().sxb_moe_group_routes(_ptr(ids), M, A, E, _ptr(ws), ws_bytes, _ptr(err), _stream(stream)))
 
 
+def check_grouped_status(ws, what: str):
+    _check(_lib.load().sxb_check_grouped_status(_ptr(ws), what.encode()))
+
+
 def moe_group_routes_ep(ids, M, A, E_total, e_lo, E_local, ws, ws_bytes, err, stream=None):
+    _count(2 if M * A > 2048 else 0)
     _check(_lib.load().sxb_moe_group_routes_ep(_ptr(ids), M, A, E_total, e_lo, E_local, _ptr(ws), ws_bytes, _ptr(err),
                                                _stream(stream)))
 
@@ -172,6 +187,7 @@ def linear_qw_experts_combine_grouped(h, w: QDeviceView, E, ids, coef, ws, ws_by
                                       stream=None, shared: Optional[MoeSharedAdd] = None, h_f16=False, out_act=None):
     fn = getattr(_lib.load(), f"sxb_linear_{_b(w)}_experts_combine_grouped")
     sh = C.byref(shared.c()) if shared is not None else None
+    _count(1)  # the per-slot dots, then the reduce
     _check(fn(_ptr(h), C.byref(w.c()), E, _ptr(ids), _ptr(coef), _ptr(ws), ws_bytes, _ptr(partial), M, A, _ptr(y),
               int(act), int(act if out_act is None else out_act), int(math), _stream(stream), sh, int(h_f16)))
 
@@ -179,6 +195,7 @@ def linear_qw_experts_combine_grouped(h, w: QDeviceView, E, ids, coef, ws, ws_by
 def linear_qw_experts_combine_grouped_ep(h, w: QDeviceView, E_local, E_total, e_lo, ids, coef, ws, ws_bytes, partial, M,
                                          A, y, act, math, stream=None, h_f16=False, out_act=None):
     fn = getattr(_lib.load(), f"sxb_linear_{_b(w)}_experts_combine_grouped_ep")
+    _count(1)
     _check(fn(_ptr(h), C.byref(w.c()), E_local, E_total, e_lo, _ptr(ids), _ptr(coef), _ptr(ws), ws_bytes, _ptr(partial),
               M, A, _ptr(y), int(act), int(act if out_act is None else out_act), int(math), _stream(stream), int(h_f16)))
 

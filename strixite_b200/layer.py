@@ -63,6 +63,7 @@ class MoeBuffers:
             self.sh_h = torch.empty((T, I), dtype=torch.bfloat16, device=dev)
             self.sh_partial = torch.empty((T, d), dtype=torch.float32, device=dev)
             self.sh_y = torch.empty((T, d), dtype=torch.bfloat16, device=dev)
+            self.sh_y32 = torch.empty((T, d), dtype=torch.float32, device=dev)
 
 
 class MoeLayer:
@@ -94,13 +95,15 @@ class MoeLayer:
         b = self.buf
         K.moe_router(logits, logits.stride(0), T, self.E_total, self.k, None, 1, 0, b.ids, b.coef, Act.F32, b.router_err)
 
-    def shared_expert(self, x: torch.Tensor, T: int, math: MoeMath):
-        """The always-on shared expert as dense projections -> buf.sh_y [T, d] BF16 (runtime/qwen4exp.cpp:3163-3168)."""
+    def shared_expert(self, x: torch.Tensor, T: int, math: MoeMath, out: torch.Tensor):
+        """The always-on shared expert as dense projections -> out [T, d] (runtime/qwen4exp.cpp:3163-3168): BF16 as the
+        reference stores it, or FP32 (the unrounded sums) when the layer's output is asked for in FP32."""
         b, w = self.buf, self.w
+        out_act = Act.F32 if out.dtype == torch.float32 else Act.BF16
         if not K_is_f16(math):
             K.linear_qw(x, w.shared_gate_up, b.sh_gu, T, Act.BF16)
             K.swiglu(b.sh_gu, b.sh_h, T, self.I, Act.BF16)
-            K.linear_qw(b.sh_h, w.shared_down, b.sh_y, T, Act.BF16)
+            K.linear_qw(b.sh_h, w.shared_down, out, T, Act.BF16, out_act)
             return
         # Prefill: the same tcgen05 grouped kernels with one "expert" that every token is routed to.
         if b.sh_ws_tokens != T:
@@ -108,9 +111,10 @@ class MoeLayer:
             b.sh_ws_tokens = T
         K.linear_qw_experts_gather_grouped_swiglu(x, w.shared_gate_up, 1, b.sh_ws, b.sh_ws_bytes, T, 1, b.sh_h, Act.BF16, math)
         K.linear_qw_experts_combine_grouped(b.sh_h, w.shared_down, 1, b.sh_ids, b.sh_coef, b.sh_ws, b.sh_ws_bytes,
-                                            b.sh_partial, T, 1, b.sh_y, Act.BF16, math)
+                                            b.sh_partial, T, 1, out, Act.BF16, math, out_act=out_act)
 
-    def experts(self, x: torch.Tensor, T: int, y: torch.Tensor, math: MoeMath, gate_logit=None, gate_ld: int = 0):
+    def experts(self, x: torch.Tensor, T: int, y: torch.Tensor, math: MoeMath, gate_logit=None, gate_ld: int = 0,
+                shared_out: Optional[torch.Tensor] = None, events=None):
         """pack -> gate/up + SwiGLU -> down + combine into y [T, d] (BF16 or FP32), ids / coef already in the buffers."""
         b, w, A = self.buf, self.w, self.k
         out_act = Act.F32 if y.dtype == torch.float32 else Act.BF16
@@ -118,14 +122,21 @@ class MoeLayer:
             K.moe_group_routes_ep(b.ids, T, A, self.E_total, self.e_lo, self.E, b.ws, b.ws_bytes, b.expert_err)
         else:
             K.moe_group_routes(b.ids, T, A, self.E, b.ws, b.ws_bytes, b.expert_err)
+        if events is not None:  # CUDA events around the dominant kernel (the benchmark's roofline timing)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
         K.linear_qw_experts_gather_grouped_swiglu(x, w.gate_up, self.E, b.ws, b.ws_bytes, T, A, b.h, Act.BF16, math)
+        if events is not None:
+            e1.record()
+            events[0].append(e0)
+            events[1].append(e1)
         if self.ep:
             K.linear_qw_experts_combine_grouped_ep(b.h, w.down, self.E, self.E_total, self.e_lo, b.ids, b.coef, b.ws,
                                                    b.ws_bytes, b.partial, T, A, y, Act.BF16, math, out_act=out_act)
         else:
             shared = None
             if gate_logit is not None:
-                shared = K.MoeSharedAdd(b.sh_y, gate_logit, gate_ld, self.E_total, b.router_err)
+                shared = K.MoeSharedAdd(shared_out, gate_logit, gate_ld, self.E_total, b.router_err)
             K.linear_qw_experts_combine_grouped(b.h, w.down, self.E, b.ids, b.coef, b.ws, b.ws_bytes, b.partial, T, A, y,
                                                 Act.BF16, math, shared=shared, out_act=out_act)
 
@@ -137,9 +148,10 @@ class MoeLayer:
         math = self.math_for(T, math)
         self.route(logits, T)
         if self.w.shared_gate_up is not None and not self.ep:
-            self.shared_expert(x, T, math)
+            sh = self.buf.sh_y32 if y.dtype == torch.float32 else self.buf.sh_y
+            self.shared_expert(x, T, math, sh)
             gate = logits.data_ptr() + 4 * self.E_total
-            self.experts(x, T, y, math, gate_logit=gate, gate_ld=logits.stride(0))
+            self.experts(x, T, y, math, gate_logit=gate, gate_ld=logits.stride(0), shared_out=sh)
         else:
             self.experts(x, T, y, math)
         return y
@@ -148,6 +160,7 @@ class MoeLayer:
         """Blocking: the reference's read_back of the error words (runtime/qwen4exp.cpp:2391-2404)."""
         K.check_router_error(self.buf.router_err, what)
         K.check_expert_error(self.buf.expert_err, what)
+        K.check_grouped_status(self.buf.ws, what)
 
 
 def K_is_f16(math: MoeMath) -> bool:

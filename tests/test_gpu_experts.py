@@ -15,10 +15,17 @@ pytestmark = pytest.mark.gpu
 FORMATS = [(4, 128), (4, 64), (4, 32), (8, 64), (8, 128), (8, 32)]
 
 
-def assert_bf16_close(got_bits, ref_bits, oracle, what, frac_off=2e-3):
-    ulps = bf16_ulps(got_bits, ref_bits)
-    assert ulps.max() <= 1, f"{what}: {ulps.max()} BF16 ulps apart"
-    assert (ulps > 0).mean() <= frac_off, f"{what}: {(ulps > 0).mean():.2e} of the elements differ by an ulp"
+def assert_bf16_close(got_bits, ref_bits, oracle, what, frac_off=5e-2):
+    """Both sides round nearly equal FP32 values to BF16: they agree except where the value sits on a rounding
+    boundary (then one BF16 ulp apart), plus the FP32 summation-order noise (3e-5 of the output scale) that matters
+    only for outputs near zero."""
+    got, ref = oracle.bf16_to_f32(got_bits).astype(np.float64), oracle.bf16_to_f32(ref_bits).astype(np.float64)
+    scale = np.sqrt(np.mean(ref ** 2))
+    tol = np.abs(ref) * 2.0 ** -7 + 3e-5 * scale
+    bad = np.abs(got - ref) > tol
+    assert not bad.any(), f"{what}: {bad.sum()} elements beyond one BF16 ulp, worst {np.abs(got - ref).max():.3e}"
+    frac = (got_bits != ref_bits).mean()
+    assert frac <= frac_off, f"{what}: {frac:.2e} of the elements differ"
 
 
 @pytest.mark.parametrize("bits,G", FORMATS)
@@ -195,3 +202,68 @@ def test_grouped_experts_exact_math(cuda, oracle, bits, G, M, A, E, I, d):
     assert np.array_equal(bits_of(ya)[rows], bits_of(yb)[rows])
     ref = oracle.moe_shared_add(oracle.f32_to_bf16(y_ref), s, gate[:, 1], E)
     assert_bf16_close(bits_of(ya)[rows], ref[rows], oracle, "combine + shared add", frac_off=5e-3)
+
+
+@pytest.mark.parametrize("bits,G", [(4, 128), (8, 64), (4, 32)])
+@pytest.mark.parametrize("M,A,E,I,d", [(40, 2, 4, 128, 256), (300, 2, 8, 128, 256), (700, 4, 8, 256, 384)])
+def test_grouped_experts_tcgen05(cuda, oracle, bits, G, M, A, E, I, d):
+    """MoeMath.WmmaF16: tcgen05 grouped GEMMs (F16 operands, FP32 accumulation in tensor memory) against the oracle's
+    matrix-unit semantics (h = silu(g) * u rounded once).  F16 weights carry 2^-11 relative rounding error, so the
+    comparison is on the scale of that: <= 2e-3 of the output RMS for the raw dots, and BF16 h within one ulp."""
+    from strixite_b200 import kernels as K
+    rng = np.random.default_rng(M + E + bits)
+    gu = make_experts(oracle, rng, E, 2 * I, d, G, bits)
+    dn = make_experts(oracle, rng, E, d, I, G if I % G == 0 else 64, bits)
+    x = oracle.f32_to_bf16(rng.standard_normal((M, d)).astype(np.float32))
+    ids = np.stack([rng.permutation(E)[:A] for _ in range(M)]).astype(np.int32)
+    if M >= 300:
+        ids[:200, 0] = 1  # one expert with > 128 slots: several token tiles
+        for m in range(200):
+            if (ids[m, 1:] == 1).any():
+                ids[m, np.argmax(ids[m, 1:] == 1) + 1] = 0 if 0 not in ids[m] else 2
+    ids[5, 1] = E + 9
+    coef = rng.random((M, A)).astype(np.float32)
+    gud, dnd, xd = upload(gu, cuda), upload(dn, cuda), bf16_tensor(x, cuda)
+    idd, cfd = torch.from_numpy(ids).to(cuda), torch.from_numpy(coef).to(cuda)
+    nbytes = K.moe_route_workspace_bytes(M, A, E)
+    ws = torch.empty(nbytes // 4, dtype=torch.int32, device=cuda)
+    err = torch.zeros(4, dtype=torch.int32, device=cuda)
+    K.moe_group_routes(idd, M, A, E, ws, nbytes, err)
+    g = torch.zeros((M * A, 2 * I), dtype=torch.bfloat16, device=cuda)
+    K.linear_qw_experts_gather_grouped(xd, gud, E, ws, nbytes, M, A, g, K.Act.BF16, K.MoeMath.WmmaF16)
+    h = torch.zeros((M * A, I), dtype=torch.bfloat16, device=cuda)
+    K.linear_qw_experts_gather_grouped_swiglu(xd, gud, E, ws, nbytes, M, A, h, K.Act.BF16, K.MoeMath.WmmaF16)
+    hf = torch.zeros((M * A, I), dtype=torch.float16, device=cuda)
+    K.linear_qw_experts_gather_grouped_swiglu(xd, gud, E, ws, nbytes, M, A, hf, K.Act.BF16, K.MoeMath.WmmaF16, h_f16=True)
+    torch.cuda.synchronize()
+    K.check_grouped_status(ws, "tcgen05 gather")
+    ok = np.ones(M * A, bool)
+    ok[5 * A + 1] = False
+    g_ref = oracle.bf16_to_f32(oracle.experts_gather(x, gu, E, ids, 0).reshape(M * A, -1))
+    g_got = g.float().cpu().numpy().astype(np.float64)
+    g_scale = np.sqrt(np.mean(g_ref[ok] ** 2))
+    assert np.all(np.abs(g_got[ok] - g_ref[ok]) <= np.abs(g_ref[ok]) * 2.0 ** -7 + 2e-3 * g_scale)
+    h_ref = oracle.experts_gather(x, gu, E, ids, 2).reshape(M * A, -1)
+    got_h = oracle.bf16_to_f32(bits_of(h)).astype(np.float64)
+    want_h = oracle.bf16_to_f32(h_ref).astype(np.float64)
+    scale = np.sqrt(np.mean(want_h[ok] ** 2))
+    assert np.all(np.abs(got_h[ok] - want_h[ok]) <= np.abs(want_h[ok]) * 2.0 ** -7 + 3e-3 * scale)
+    assert np.all(np.isnan(got_h[~ok]))
+    # h_f16 holds the F16 bits of the same BF16-rounded values
+    assert torch.equal(hf.float()[torch.from_numpy(ok).to(cuda)], h.float()[torch.from_numpy(ok).to(cuda)])
+    # down + combine on the oracle's h (identical inputs on both sides), from BF16 h and from F16 h
+    y_ref, p_ref = oracle.experts_combine(h_ref.reshape(M, A, I), dn, E, ids, coef, out_act=oracle.F32, want_partial=True)
+    rows = [m for m in range(M) if m != 5]
+    for f16 in (False, True):
+        hd = bf16_tensor(h_ref, cuda)
+        if f16:
+            hd = hd.float().to(torch.float16)
+        partial = torch.zeros((M * A, d), dtype=torch.float32, device=cuda)
+        y = torch.empty((M, d), dtype=torch.float32, device=cuda)
+        K.linear_qw_experts_combine_grouped(hd, dnd, E, idd, cfd, ws, nbytes, partial, M, A, y, K.Act.BF16, K.MoeMath.WmmaF16,
+                                            out_act=K.Act.F32, h_f16=f16)
+        torch.cuda.synchronize()
+        K.check_grouped_status(ws, "tcgen05 combine")
+        assert max_abs_over_rms(partial.cpu().numpy()[ok], p_ref[ok]) < 2e-3
+        assert max_abs_over_rms(y.cpu().numpy()[rows], y_ref[rows]) < 2e-3
+        assert np.all(np.isnan(y.cpu().numpy()[5]))
