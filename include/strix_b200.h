@@ -48,7 +48,13 @@ enum {
 };
 
 /* kernels/norm.hpp:20  enum class Act { F32, BF16 }.  BF16 buffers hold raw uint16_t bits. */
-enum { SXB_ACT_F32 = 0, SXB_ACT_BF16 = 1 };
+enum {
+    SXB_ACT_F32 = 0,
+    SXB_ACT_BF16 = 1,
+    /* Not in the reference: F16 activations laid out by sxb_stage_f16 for a tensor-core operand.  Accepted as the
+     * input dtype of the WMMA_F16 grouped gathers only. */
+    SXB_ACT_F16_STAGED = 2
+};
 
 /* kernels/moe_grouped.hpp:39  enum class MoeMath.  Here:
  *   F32, WMMA_BF16            exact products: BF16 activations times the integer codes on mma.sync tensor cores,
@@ -184,8 +190,12 @@ int sxb_report_expert_error(const uint32_t e[3], const char *what);
 int sxb_linear_q4_experts_gather_grouped(const void *x, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes,
                                          int64_t M, int64_t A, void *y, int act, int math, sxb_stream_t stream);
 /* kernels/moe_grouped.hpp:67-69  linear_q4_experts_gather_grouped_swiglu.  With a WMMA_F16 math: h = silu(g) * u from
- * the FP32 accumulators, rounded once; h_f16: h stored as F16 bits of its BF16 rounding.  With SXB_MATH_F32 /
- * WMMA_BF16 (an extension: the reference refuses them here) the decode form's rounding points are kept. */
+ * the FP32 accumulators, rounded once.  h_f16 (WMMA_F16 only): 0 = h stored as BF16; 1 = h stored as F16 bits of its
+ * BF16 rounding (the reference's h_f16); 2 = the same values with every 8 consecutive columns in the order
+ * [0 4 1 5 2 6 3 7], the k order of a Q4 tensor-core operand, so the Q4 down GEMM can copy h rows without touching
+ * them (pass the same h_f16 to the combine).  With SXB_MATH_F32 / WMMA_BF16 (an extension: the reference refuses them
+ * here) the decode form's rounding points are kept.  act may be SXB_ACT_F16_STAGED: x then holds the F16 copy made by
+ * sxb_stage_f16 for this weight's bit width. */
 int sxb_linear_q4_experts_gather_grouped_swiglu(const void *x, const SxbQView *w, int64_t E, const void *ws,
                                                 size_t ws_bytes, int64_t M, int64_t A, void *h, int act, int math,
                                                 sxb_stream_t stream, int h_f16);
@@ -219,6 +229,12 @@ int sxb_linear_q8_experts_combine_grouped_ep(const void *h, const SxbQView *w, i
                                              int64_t e_lo, const int32_t *ids, const float *coef, const void *ws,
                                              size_t ws_bytes, float *partial, int64_t M, int64_t A, void *y, int act,
                                              int out_act, int math, sxb_stream_t stream, int h_f16);
+
+/* No counterpart in the reference (its kernels convert BF16 -> F16 while staging every tile, kernels/moe_grouped.hip:29-32).
+ * x [M, K] BF16 -> xh [M, K] F16, every 8 consecutive k in the order a `bits`-bit weight operand uses on the tensor
+ * cores ([0 4 1 5 2 6 3 7] for Q4, natural for Q8).  Done once per layer, it lets the grouped GEMMs copy activation rows
+ * asynchronously instead of converting them per tile.  xh: caller-owned, M*K*2 bytes, 16-byte aligned. */
+int sxb_stage_f16(const void *x, int64_t M, int64_t K, int bits, void *xh, sxb_stream_t stream);
 
 /* ---- Quantizers on the device ------------------------------------------------------------------------------- */
 

@@ -156,7 +156,7 @@ def moe_group_routes(ids: np.ndarray, E: int, err: Optional[np.ndarray] = None):
     return offsets, slots
 
 
-def linear_q(x: np.ndarray, w: QWeight, out_act: Optional[int] = None, threads: int = 0) -> np.ndarray:
+def linear_q(x: np.ndarray, w: QWeight, out_act: Optional[int] = None, threads: int = 0, w_f16: bool = False) -> np.ndarray:
     x = np.ascontiguousarray(x)
     M = x.shape[0]
     act = _act_of(x)
@@ -164,7 +164,7 @@ def linear_q(x: np.ndarray, w: QWeight, out_act: Optional[int] = None, threads: 
     y = np.empty((M, w.N), dtype=np.float32 if out_act == F32 else np.uint16)
     lib().orc_linear_q(_p(x), C.c_int(act), _p(np.ascontiguousarray(w.q)), _p(np.ascontiguousarray(w.scale)),
                        _p(np.ascontiguousarray(w.minv)), i64(w.N), i64(w.K), i64(w.G), C.c_int(w.bits), _p(y),
-                       C.c_int(out_act), i64(M), C.c_int(threads))
+                       C.c_int(out_act), i64(M), C.c_int(threads), C.c_int(int(w_f16)))
     return y
 
 
@@ -177,8 +177,9 @@ def swiglu(gu: np.ndarray) -> np.ndarray:
 
 
 def experts_gather(x: np.ndarray, w: QWeight, E: int, ids: np.ndarray, swiglu_mode: int = 0,
-                   err: Optional[np.ndarray] = None, threads: int = 0) -> np.ndarray:
-    """swiglu_mode 0: y [M, A, N]; 1: h [M, A, N/2] with the decode rounding points; 2: one rounding (grouped F16)."""
+                   err: Optional[np.ndarray] = None, threads: int = 0, w_f16: bool = False) -> np.ndarray:
+    """swiglu_mode 0: y [M, A, N]; 1: h [M, A, N/2] with the decode rounding points; 2: one rounding (grouped F16).
+    w_f16: weights as the matrix-unit path's F16 operand, f16(code * f16(scale) + f16(min))."""
     x = np.ascontiguousarray(x)
     ids = np.ascontiguousarray(ids, dtype=np.int32)
     M, A = ids.shape
@@ -188,12 +189,12 @@ def experts_gather(x: np.ndarray, w: QWeight, E: int, ids: np.ndarray, swiglu_mo
     lib().orc_experts_gather(_p(x), C.c_int(_act_of(x)), _p(np.ascontiguousarray(w.q)),
                              _p(np.ascontiguousarray(w.scale)), _p(np.ascontiguousarray(w.minv)), i64(w.N), i64(w.K),
                              i64(w.G), C.c_int(w.bits), i64(E), _p(ids), i64(M), i64(A), _p(y), C.c_int(swiglu_mode),
-                             _p(err), C.c_int(threads))
+                             _p(err), C.c_int(threads), C.c_int(int(w_f16)))
     return y
 
 
 def experts_combine(h: np.ndarray, w: QWeight, E: int, ids: np.ndarray, coef: np.ndarray, out_act: Optional[int] = None,
-                    err: Optional[np.ndarray] = None, threads: int = 0, want_partial: bool = False):
+                    err: Optional[np.ndarray] = None, threads: int = 0, want_partial: bool = False, w_f16: bool = False):
     """h [M, A, K] -> y [M, N] (and the per-slot dots [M*A, N] FP32 when asked)."""
     h = np.ascontiguousarray(h)
     ids = np.ascontiguousarray(ids, dtype=np.int32)
@@ -207,7 +208,7 @@ def experts_combine(h: np.ndarray, w: QWeight, E: int, ids: np.ndarray, coef: np
     lib().orc_experts_combine(_p(h), C.c_int(act), _p(np.ascontiguousarray(w.q)), _p(np.ascontiguousarray(w.scale)),
                               _p(np.ascontiguousarray(w.minv)), i64(w.N), i64(w.K), i64(w.G), C.c_int(w.bits), i64(E),
                               _p(ids), _p(coef), i64(M), i64(A), _p(y), C.c_int(out_act), _p(partial), _p(err),
-                              C.c_int(threads))
+                              C.c_int(threads), C.c_int(int(w_f16)))
     return (y, partial) if want_partial else y
 
 
@@ -250,19 +251,27 @@ class LayerWeights:
 def moe_layer(x: np.ndarray, logits: np.ndarray, w: LayerWeights, E: int, k: int, semantics: str = "decode",
               threads: int = 0):
     """One MoE sublayer as the reference's forward composes it (runtime/qwen4exp.cpp:3143-3217), shared expert
-    separate.  x [T, d] BF16 bits, logits [T, E + 1] float32 (column E = the shared gate).  semantics "decode" keeps
-    the per-slot kernels' rounding points, "grouped" the matrix-unit path's single rounding of h.
+    separate.  x [T, d] BF16 bits, logits [T, E + 1] float32 (column E = the shared gate).
+    semantics "decode": the per-slot / vector-unit kernels' numerics - FP32 dequantized weights, g and u rounded as
+        stored, h = bf16(bf16(silu(g)) * u) (kernels/linear_q4.hip:268-274);
+    semantics "grouped": the matrix-unit path's numerics served from 6 tokens up - weights as F16 operands
+        f16(code * scale + min), h = bf16(silu(g) * u) from the unrounded accumulators (kernels/moe_grouped.hpp:29-38,
+        kernels/moe_grouped.hip:508-524); per-slot partials stay FP32 here (the reference rounds them to BF16).
     Returns dict(ids, coef, h, y_routed_f32, y_f32, y_bf16)."""
     ids, coef = moe_router(logits, E, k)
-    h = experts_gather(x, w.gate_up, E, ids, swiglu_mode=1 if semantics == "decode" else 2, threads=threads)
-    y_routed = experts_combine(h, w.down, E, ids, coef, out_act=F32, threads=threads)
+    f16 = semantics != "decode"
+    h = experts_gather(x, w.gate_up, E, ids, swiglu_mode=2 if f16 else 1, threads=threads, w_f16=f16)
+    y_routed = experts_combine(h, w.down, E, ids, coef, out_act=F32, threads=threads, w_f16=f16)
     out = dict(ids=ids, coef=coef, h=h, y_routed_f32=y_routed)
     if w.shared_gate_up is not None:
-        gu = linear_q(x, w.shared_gate_up, threads=threads)
-        hs = swiglu(gu)
-        s = linear_q(hs, w.shared_down, threads=threads)
+        if f16:  # the shared expert through the same matrix-unit numerics: one "expert" every token is routed to
+            zero = np.zeros((x.shape[0], 1), dtype=np.int32)
+            hs = experts_gather(x, w.shared_gate_up, 1, zero, swiglu_mode=2, threads=threads, w_f16=True)[:, 0]
+        else:
+            hs = swiglu(linear_q(x, w.shared_gate_up, threads=threads))
+        s = linear_q(hs, w.shared_down, threads=threads, w_f16=f16)
         gate = np.ascontiguousarray(logits[:, E], dtype=np.float32)
-        s32 = linear_q(hs, w.shared_down, out_act=F32, threads=threads)
+        s32 = linear_q(hs, w.shared_down, out_act=F32, threads=threads, w_f16=f16)
         out["shared_s"], out["shared_s_f32"] = s, s32
         # FP32 view: nothing after h is rounded - the routed sum and the shared expert's output stay FP32, so the
         # comparison is not at the mercy of one BF16 rounding of s or y falling the other way (one such flip of an

@@ -85,12 +85,52 @@ inline int code_at(const QView &w, int64_t row, int64_t k) {
     return (w.q[(row * w.K + k) / 2] >> ((k & 1) ? 4 : 0)) & 0xF;  // formats/q4.hpp:5 low nibble = even k
 }
 
-// One dequantized row, the FP32 values of formats/q4.cpp:121-134 / formats/q8.cpp:117-127:
-// code * scale, then + min, each rounded separately (no FMA contraction).
-void dequant_row(const QView &w, int64_t row, float *out) {
+// IEEE binary16 <-> double, round to nearest even, subnormals kept (what the device's packed-half arithmetic does).
+double f16_bits_to_double(uint16_t h) {
+    const int sign = h >> 15, e = (h >> 10) & 0x1F, f = h & 0x3FF;
+    double v;
+    if (e == 0) v = std::ldexp((double)f, -24);
+    else if (e == 31) v = f ? std::numeric_limits<double>::quiet_NaN() : std::numeric_limits<double>::infinity();
+    else v = std::ldexp((double)(f | 0x400), e - 25);
+    return sign ? -v : v;
+}
+uint16_t double_to_f16_bits(double v) {
+    const uint16_t sign = std::signbit(v) ? 0x8000 : 0;
+    v = std::fabs(v);
+    if (std::isnan(v)) return sign | 0x7E00;
+    if (v >= 65520.0) return sign | 0x7C00;  // rounds to infinity
+    if (v < std::ldexp(1.0, -25)) return sign;  // below half the smallest subnormal (ties to even: 0)
+    int e;
+    std::frexp(v, &e);                  // v = m * 2^e, m in [0.5, 1)
+    int exp = e - 1;                    // v = 1.xxx * 2^exp
+    if (exp < -14) exp = -14;           // subnormal: fixed exponent
+    const double scaled = std::ldexp(v, 10 - exp);  // units of the last place
+    double r = std::nearbyint(scaled);  // half to even
+    int64_t q = (int64_t)r;
+    if (exp == -14 && q < 0x400) return sign | (uint16_t)q;  // subnormal (or rounds up into the first normal below)
+    if (q >= 0x800) q >>= 1, ++exp;     // the rounding carried into the next binade
+    if (exp > 15) return sign | 0x7C00;
+    return sign | (uint16_t)(((exp + 15) << 10) | (q & 0x3FF));
+}
+inline float round_f16(double v) { return (float)f16_bits_to_double(double_to_f16_bits(v)); }
+
+// One dequantized row.
+//   f16 == false: the FP32 values of formats/q4.cpp:121-134 / formats/q8.cpp:117-127 - code * scale, then + min, each
+//                 rounded separately (no FMA contraction): the weights of the exact / vector-unit paths.
+//   f16 == true:  the matrix-unit path's operand (kernels/moe_grouped.hpp:32-33, kernels/wmma_gemm.hpp:116-129):
+//                 scale and min converted to F16, then f16(code * scale + min) with ONE rounding (an F16 fma).
+void dequant_row(const QView &w, int64_t row, float *out, bool f16 = false) {
     const int64_t groups = w.K / w.G;
     for (int64_t g = 0; g < groups; ++g) {
         const float s = bf16_to_f32(w.scale[row * groups + g]), m = bf16_to_f32(w.minv[row * groups + g]);
+        if (f16) {
+            const double sh = round_f16(s), mh = round_f16(m);
+            for (int64_t i = 0; i < w.G; ++i) {
+                const int64_t k = g * w.G + i;
+                out[k] = round_f16((double)code_at(w, row, k) * sh + mh);  // exact in double, then one rounding
+            }
+            continue;
+        }
         for (int64_t i = 0; i < w.G; ++i) {
             const int64_t k = g * w.G + i;
             out[k] = (float)code_at(w, row, k) * s + m;  // two roundings: built with -ffp-contract=off
@@ -250,7 +290,7 @@ void orc_moe_group_routes(const int32_t *ids, int64_t M, int64_t A, int64_t E, i
 //   y[M, N] = x[M, K] * dequant(W)^T, accumulated here in double and cast to FP32 (the
 //   kernels accumulate in FP32; only the summation order differs), one rounding at the store.
 void orc_linear_q(const void *x, int act, const uint8_t *q, const uint16_t *scale, const uint16_t *minv, int64_t N,
-                  int64_t K, int64_t G, int bits, void *y, int out_act, int64_t M, int threads) {
+                  int64_t K, int64_t G, int bits, void *y, int out_act, int64_t M, int threads, int w_f16) {
     const QView w{q, scale, minv, N, K, G, bits};
     std::vector<float> xf((size_t)(M * K));
     for (int64_t i = 0; i < M * K; ++i) xf[(size_t)i] = load_act(x, i, act);
@@ -258,7 +298,7 @@ void orc_linear_q(const void *x, int act, const uint8_t *q, const uint16_t *scal
     parallel_for(blocks, threads, [&](int64_t b) {
         std::vector<float> row((size_t)K);
         for (int64_t n = b * kRowBlock; n < std::min(N, (b + 1) * kRowBlock); ++n) {
-            dequant_row(w, n, row.data());
+            dequant_row(w, n, row.data(), w_f16 != 0);
             for (int64_t m = 0; m < M; ++m) store_act(y, m * N + n, (float)dot_f32(&xf[(size_t)(m * K)], row.data(), K), out_act);
         }
     });
@@ -283,10 +323,11 @@ void orc_swiglu(const void *gu, void *h, int64_t rows, int64_t I, int act) {
 //                 h = stored(stored(silu(g)) * u), h [M, A, N/2].
 //   swiglu_mode 2 (grouped matrix-unit semantics, kernels/moe_grouped.hip:508-524):
 //                 h = stored(silu(g_f32) * u_f32), one rounding.
+//   w_f16: the weights are the matrix-unit path's F16 operand (see dequant_row) instead of the FP32 dequantization.
 // An id outside [0, E): err = {1, id, slot}, that slot's outputs NaN.
 void orc_experts_gather(const void *x, int act, const uint8_t *q, const uint16_t *scale, const uint16_t *minv,
                         int64_t Ntot, int64_t K, int64_t G, int bits, int64_t E, const int32_t *ids, int64_t M,
-                        int64_t A, void *y, int swiglu_mode, uint32_t *err, int threads) {
+                        int64_t A, void *y, int swiglu_mode, uint32_t *err, int threads, int w_f16) {
     const QView w{q, scale, minv, Ntot, K, G, bits};
     const int64_t N = Ntot / E, S = M * A, I = N / 2, out_cols = swiglu_mode ? I : N;
     std::vector<float> xf((size_t)(M * K));
@@ -304,8 +345,8 @@ void orc_experts_gather(const void *x, int act, const uint8_t *q, const uint16_t
         if (slots.empty()) return;
         std::vector<float> row((size_t)K), row2((size_t)K);
         for (int64_t c = blk * kRowBlock; c < std::min(out_cols, (blk + 1) * kRowBlock); ++c) {
-            dequant_row(w, e * N + c, row.data());
-            if (swiglu_mode) dequant_row(w, e * N + I + c, row2.data());
+            dequant_row(w, e * N + c, row.data(), w_f16 != 0);
+            if (swiglu_mode) dequant_row(w, e * N + I + c, row2.data(), w_f16 != 0);
             for (int64_t s : slots) {
                 const float *xr = &xf[(size_t)((s / A) * K)];
                 const float g = (float)dot_f32(xr, row.data(), K);
@@ -332,7 +373,7 @@ void orc_experts_gather(const void *x, int act, const uint8_t *q, const uint16_t
 void orc_experts_combine(const void *h, int act, const uint8_t *q, const uint16_t *scale, const uint16_t *minv,
                          int64_t Ntot, int64_t K, int64_t G, int bits, int64_t E, const int32_t *ids,
                          const float *coef, int64_t M, int64_t A, void *y, int out_act, float *partial_out,
-                         uint32_t *err, int threads) {
+                         uint32_t *err, int threads, int w_f16) {
     const QView w{q, scale, minv, Ntot, K, G, bits};
     const int64_t N = Ntot / E, S = M * A;
     std::vector<float> hf((size_t)(S * K));
@@ -356,7 +397,7 @@ void orc_experts_combine(const void *h, int act, const uint8_t *q, const uint16_
         if (slots.empty()) return;
         std::vector<float> row((size_t)K);
         for (int64_t n = blk * kRowBlock; n < std::min(N, (blk + 1) * kRowBlock); ++n) {
-            dequant_row(w, e * N + n, row.data());
+            dequant_row(w, e * N + n, row.data(), w_f16 != 0);
             for (int64_t s : slots) partial[s * N + n] = (float)dot_f32(&hf[(size_t)(s * K)], row.data(), K);
         }
     });

@@ -23,10 +23,10 @@ int combine_reduce(const char *fn, const float *partial, const int32_t *ids, con
 // grouped_tc.cu - tcgen05 kernels (F16 operands, FP32 accumulation in tensor memory).
 template <int BITS>
 int tc_gather_grouped(const char *fn, const void *x, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes,
-                      int64_t M, int64_t A, void *y, int act, bool swiglu, bool h_f16, sxb_stream_t stream);
+                      int64_t M, int64_t A, void *y, int act, bool swiglu, int h_f16, sxb_stream_t stream);
 template <int BITS>
 int tc_partial_grouped(const char *fn, const void *h, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes,
-                       int64_t M, int64_t A, float *partial, int act, bool h_f16, sxb_stream_t stream);
+                       int64_t M, int64_t A, float *partial, int act, int h_f16, sxb_stream_t stream);
 
 inline bool math_is_f16(int math) { return math >= SXB_MATH_WMMA_F16 && math <= SXB_MATH_WMMA_F16_WIDE256; }
 inline bool math_ok(int math) { return math >= SXB_MATH_F32 && math <= SXB_MATH_WMMA_F16_WIDE256; }

@@ -9,10 +9,12 @@ namespace {
 
 template <int BITS>
 int gather_grouped(const char *fn, const void *x, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes, int64_t M,
-                   int64_t A, void *y, int act, int math, bool swiglu, bool h_f16, sxb_stream_t stream) {
+                   int64_t A, void *y, int act, int math, bool swiglu, int h_f16, sxb_stream_t stream) {
     SXB_CHECK(math_ok(math), fn, ": unknown math ", math);
-    SXB_CHECK(!h_f16 || (act == SXB_ACT_BF16 && math_is_f16(math)), fn,
+    SXB_CHECK(h_f16 >= 0 && h_f16 <= 2, fn, ": h_f16 = ", h_f16, ", expected 0, 1 or 2");
+    SXB_CHECK(!h_f16 || (act != SXB_ACT_F32 && math_is_f16(math)), fn,
               ": F16 h needs BF16 activations and a WMMA_F16 math, got ", act_name(act), " math ", math);
+    SXB_CHECK(act != SXB_ACT_F16_STAGED || math_is_f16(math), fn, ": staged F16 activations need a WMMA_F16 math");
     if (math_is_f16(math)) return tc_gather_grouped<BITS>(fn, x, w, E, ws, ws_bytes, M, A, y, act, swiglu, h_f16, stream);
     return stream_gather_grouped<BITS>(fn, x, w, E, ws, ws_bytes, M, A, y, act, swiglu, stream);
 }
@@ -20,9 +22,10 @@ int gather_grouped(const char *fn, const void *x, const SxbQView *w, int64_t E, 
 template <int BITS>
 int combine_grouped(const char *fn, const void *h, const SxbQView *w, int64_t E_view, const int32_t *ids, const float *coef,
                     const void *ws, size_t ws_bytes, float *partial, int64_t M, int64_t A, void *y, int act, int out_act,
-                    int math, sxb_stream_t stream, const SxbMoeSharedAdd *shared, bool h_f16, int64_t E_total,
+                    int math, sxb_stream_t stream, const SxbMoeSharedAdd *shared, int h_f16, int64_t E_total,
                     int64_t e_lo) {
     SXB_CHECK(math_ok(math), fn, ": unknown math ", math);
+    SXB_CHECK(h_f16 >= 0 && h_f16 <= 2, fn, ": h_f16 = ", h_f16, ", expected 0, 1 or 2");
     SXB_CHECK(!h_f16 || (act == SXB_ACT_BF16 && math_is_f16(math)), fn,
               ": F16 h needs BF16 activations and a WMMA_F16 math, got ", act_name(act), " math ", math);
     SXB_CHECK(ids != nullptr && coef != nullptr && partial != nullptr && y != nullptr && w != nullptr, fn,
@@ -50,39 +53,39 @@ extern "C" {
 
 int sxb_linear_q4_experts_gather_grouped(const void *x, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes,
                                          int64_t M, int64_t A, void *y, int act, int math, sxb_stream_t stream) {
-    return gather_grouped<4>("linear_q4_experts_gather_grouped", x, w, E, ws, ws_bytes, M, A, y, act, math, false, false,
+    return gather_grouped<4>("linear_q4_experts_gather_grouped", x, w, E, ws, ws_bytes, M, A, y, act, math, false, 0,
                              stream);
 }
 int sxb_linear_q8_experts_gather_grouped(const void *x, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes,
                                          int64_t M, int64_t A, void *y, int act, int math, sxb_stream_t stream) {
-    return gather_grouped<8>("linear_q8_experts_gather_grouped", x, w, E, ws, ws_bytes, M, A, y, act, math, false, false,
+    return gather_grouped<8>("linear_q8_experts_gather_grouped", x, w, E, ws, ws_bytes, M, A, y, act, math, false, 0,
                              stream);
 }
 int sxb_linear_q4_experts_gather_grouped_swiglu(const void *x, const SxbQView *w, int64_t E, const void *ws,
                                                 size_t ws_bytes, int64_t M, int64_t A, void *h, int act, int math,
                                                 sxb_stream_t stream, int h_f16) {
     return gather_grouped<4>("linear_q4_experts_gather_grouped_swiglu", x, w, E, ws, ws_bytes, M, A, h, act, math, true,
-                             h_f16 != 0, stream);
+                             h_f16, stream);
 }
 int sxb_linear_q8_experts_gather_grouped_swiglu(const void *x, const SxbQView *w, int64_t E, const void *ws,
                                                 size_t ws_bytes, int64_t M, int64_t A, void *h, int act, int math,
                                                 sxb_stream_t stream, int h_f16) {
     return gather_grouped<8>("linear_q8_experts_gather_grouped_swiglu", x, w, E, ws, ws_bytes, M, A, h, act, math, true,
-                             h_f16 != 0, stream);
+                             h_f16, stream);
 }
 int sxb_linear_q4_experts_combine_grouped(const void *h, const SxbQView *w, int64_t E, const int32_t *ids,
                                           const float *coef, const void *ws, size_t ws_bytes, float *partial, int64_t M,
                                           int64_t A, void *y, int act, int out_act, int math, sxb_stream_t stream,
                                           const SxbMoeSharedAdd *shared, int h_f16) {
     return combine_grouped<4>("linear_q4_experts_combine_grouped", h, w, E, ids, coef, ws, ws_bytes, partial, M, A, y, act,
-                              out_act, math, stream, shared, h_f16 != 0, E, 0);
+                              out_act, math, stream, shared, h_f16, E, 0);
 }
 int sxb_linear_q8_experts_combine_grouped(const void *h, const SxbQView *w, int64_t E, const int32_t *ids,
                                           const float *coef, const void *ws, size_t ws_bytes, float *partial, int64_t M,
                                           int64_t A, void *y, int act, int out_act, int math, sxb_stream_t stream,
                                           const SxbMoeSharedAdd *shared, int h_f16) {
     return combine_grouped<8>("linear_q8_experts_combine_grouped", h, w, E, ids, coef, ws, ws_bytes, partial, M, A, y, act,
-                              out_act, math, stream, shared, h_f16 != 0, E, 0);
+                              out_act, math, stream, shared, h_f16, E, 0);
 }
 int sxb_linear_q4_experts_combine_grouped_ep(const void *h, const SxbQView *w, int64_t E_local, int64_t E_total,
                                              int64_t e_lo, const int32_t *ids, const float *coef, const void *ws,
@@ -91,7 +94,7 @@ int sxb_linear_q4_experts_combine_grouped_ep(const void *h, const SxbQView *w, i
     SXB_CHECK(e_lo >= 0 && E_local >= 1 && e_lo + E_local <= E_total, "linear_q4_experts_combine_grouped_ep: experts [",
               e_lo, ", ", e_lo + E_local, ") outside [0, ", E_total, ")");
     return combine_grouped<4>("linear_q4_experts_combine_grouped_ep", h, w, E_local, ids, coef, ws, ws_bytes, partial, M, A,
-                              y, act, out_act, math, stream, nullptr, h_f16 != 0, E_total, e_lo);
+                              y, act, out_act, math, stream, nullptr, h_f16, E_total, e_lo);
 }
 int sxb_linear_q8_experts_combine_grouped_ep(const void *h, const SxbQView *w, int64_t E_local, int64_t E_total,
                                              int64_t e_lo, const int32_t *ids, const float *coef, const void *ws,
@@ -100,7 +103,7 @@ int sxb_linear_q8_experts_combine_grouped_ep(const void *h, const SxbQView *w, i
     SXB_CHECK(e_lo >= 0 && E_local >= 1 && e_lo + E_local <= E_total, "linear_q8_experts_combine_grouped_ep: experts [",
               e_lo, ", ", e_lo + E_local, ") outside [0, ", E_total, ")");
     return combine_grouped<8>("linear_q8_experts_combine_grouped_ep", h, w, E_local, ids, coef, ws, ws_bytes, partial, M, A,
-                              y, act, out_act, math, stream, nullptr, h_f16 != 0, E_total, e_lo);
+                              y, act, out_act, math, stream, nullptr, h_f16, E_total, e_lo);
 }
 
 int sxb_linear_q4_experts_combine(const void *h, const SxbQView *w, int64_t E, const int32_t *ids, const float *coef,

@@ -34,9 +34,12 @@
 namespace sxb {
 namespace {
 
-constexpr int kEpiWarps = 4, kMmaWarp = 4, kFirstProducerWarp = 5, kProducerWarps = 8;
-constexpr int kThreads = 32 * (kFirstProducerWarp + kProducerWarps);  // 416
-constexpr int kProducers = 32 * kProducerWarps;                       // 256 = weight rows per item
+constexpr int kEpiWarps = 4, kMmaWarp = 4, kFirstAWarp = 5, kAWarps = 8, kFirstBWarp = kFirstAWarp + kAWarps, kBWarps = 2;
+constexpr int kThreads = 32 * (kFirstBWarp + kBWarps);  // 480
+constexpr int kAThreads = 32 * kAWarps;                 // 256 = weight rows per item
+constexpr int kBThreads = 32 * kBWarps;                 // 64
+constexpr int kProducers = kAThreads;
+constexpr int kBAhead = 3;                              // k-blocks of activations in flight (cp.async groups)
 constexpr int kBK = 64;                                               // k per stage: one 128-byte swizzle line of F16
 constexpr int kMaxTileTokens = 128;
 constexpr int kStages = 4;
@@ -49,7 +52,7 @@ constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s: far beyond a
 enum TcMode { kTcGather = 0, kTcSwiglu = 1, kTcPartial = 2 };
 
 struct TcArgs {
-    const uint16_t *x;  // activations: BF16 bits, or F16 bits when x_f16
+    const uint16_t *x;  // activations: BF16 or F16 bits, see x_kind
     const uint8_t *q;
     const uint16_t *scale, *minv;
     int64_t N, K;     // weight rows per expert, codes per row
@@ -57,8 +60,8 @@ struct TcArgs {
     const int32_t *ws;
     RouteWords L;
     void *out;
-    int x_f16;    // the activations already hold F16 bits (h stored with h_f16)
-    int out_f16;  // SwiGLU: store h as F16 bits of its BF16 rounding
+    int x_kind;   // activations: 0 BF16, 1 F16 in natural k order, 2 F16 in this weight operand's k order (staged)
+    int out_f16;  // SwiGLU output h: 0 BF16, 1 F16 bits of its BF16 rounding, 2 the same in the Q4 operand's k order
     uint32_t *status;  // >= 3 words: {2, item, role} on a wait that ran out
 };
 
@@ -213,6 +216,13 @@ __device__ inline ItemInfo item_info(const TcArgs &a, int item, int rbs) {
     return it;
 }
 
+// Next item of this CTA (stride gridDim.x) at or after `item` whose bucket is a real expert.
+template <int MODE>
+__device__ inline int next_valid_item(const TcArgs &a, int item, int n_items, int rbs) {
+    while (item < n_items && a.ws[a.L.t128_bucket + item / rbs] >= a.E) item += gridDim.x;
+    return item;
+}
+
 template <int BITS, int G, int MODE>
 __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -221,6 +231,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
     __shared__ uint64_t full_bar[kStages], empty_bar[kStages], acc_full[2], acc_empty[2], drain_bar;
     __shared__ uint32_t tmem_base_smem;
     __shared__ int abort_flag;
+    __shared__ int64_t b_row_off[kBWarps][kMaxTileTokens / kBWarps];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int K = (int)a.K, n_kb = K / kBK, groups = K / G;
@@ -229,7 +240,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
     volatile int *abort_v = &abort_flag;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], kProducerWarps), mbar_init(&empty_bar[s], 1);
+        for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], kAWarps + kBWarps), mbar_init(&empty_bar[s], 1);
         for (int b = 0; b < 2; ++b) mbar_init(&acc_full[b], 1), mbar_init(&acc_empty[b], kEpiWarps);
         mbar_init(&drain_bar, 1);
         abort_flag = 0;
@@ -251,57 +262,72 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
         }
     };
 
-    if (warp >= kFirstProducerWarp) {
-        // ===================== producers =====================
-        const int p = threadIdx.x - 32 * kFirstProducerWarp;  // weight row of the item, 0..255
+    if (warp >= kFirstAWarp && warp < kFirstBWarp) {
+        // ===================== A producers: weights =====================
+        const int p = threadIdx.x - 32 * kFirstAWarp;  // weight row of the item, 0..255
         const int64_t row_bytes = BITS == 4 ? a.K / 2 : a.K;
         constexpr int kSuperKb = BITS == 4 ? 4 : 2;  // k-blocks per 128 bytes of packed codes
         constexpr int kWordsPerKb = BITS == 4 ? 8 : 16;
-        uint32_t it_count = 0;  // k-blocks produced so far (stage / phase bookkeeping)
-        for (int item = blockIdx.x; item < n_items && !*abort_v; item += gridDim.x) {
+        constexpr int kSuperGroups = (kSuperKb * kBK) / G > 0 ? (kSuperKb * kBK) / G : 1;  // scale groups per super-block
+        constexpr int kGroupsPerKb = G >= kBK ? 1 : kBK / G;
+        const int n_sb = (n_kb + kSuperKb - 1) / kSuperKb;
+
+        struct Row {
+            const uint4 *q;
+            const uint16_t *s, *m;
+            bool valid;
+        };
+        auto row_of = [&](int item) {
+            Row r{nullptr, nullptr, nullptr, false};
+            if (item >= n_items) return r;
             const ItemInfo it = item_info<MODE>(a, item, rbs);
-            if (it.bucket >= a.E) continue;  // invalid ids: no weights to multiply, the epilogue writes NaN
-            // this thread's weight row
             int64_t wrow;
-            bool wvalid;
             if (MODE == kTcSwiglu) {
                 const int64_t I = a.N / 2, j = (int64_t)it.rb * 128 + (p & 127);
-                wvalid = j < I;
+                r.valid = j < I;
                 wrow = (int64_t)it.bucket * a.N + (p < 128 ? j : I + j);
             } else {
-                const int64_t r = (int64_t)it.rb * kProducers + p;
-                wvalid = r < a.N;
-                wrow = (int64_t)it.bucket * a.N + r;
+                const int64_t rr = (int64_t)it.rb * kAThreads + p;
+                r.valid = rr < a.N;
+                wrow = (int64_t)it.bucket * a.N + rr;
             }
-            const uint4 *qrow = reinterpret_cast<const uint4 *>(a.q + wrow * row_bytes);
-            const uint16_t *srow = a.scale + wrow * groups, *mrow = a.minv + wrow * groups;
-            // the activation rows this thread copies: chunk ids p, p + 256, ... -> token (id >> 3) = p / 8 + 32 i
-            const uint16_t *brow[kMaxTileTokens * 8 / kProducers];
+            r.q = reinterpret_cast<const uint4 *>(a.q + wrow * row_bytes);
+            r.s = a.scale + wrow * groups, r.m = a.minv + wrow * groups;
+            return r;
+        };
+        // A super-block: 128 bytes of the row's packed codes (4 k-blocks of Q4, 2 of Q8) and the scales / mins of its
+        // groups, fetched one super-block ahead of the one being dequantized - across item boundaries too - so the row
+        // is read as whole 128-byte lines and every load has several k-blocks of work to hide behind.
+        struct Super {
+            uint4 code[8];
+            uint32_t sm[kSuperGroups];  // scale | min << 16 (BF16 bits)
+        };
+        auto load_super = [&](Super &dst, const Row &r, int sb) {
 #pragma unroll
-            for (int i = 0; i < kMaxTileTokens * 8 / kProducers; ++i) {
-                const int n = (p >> 3) + 32 * i;
-                brow[i] = a.x;
-                if (n < it.cnt) {
-                    const int64_t slot = a.ws[a.L.slots + it.start + n];
-                    brow[i] = a.x + (MODE == kTcPartial ? slot : slot / a.A) * a.K;
-                }
+            for (int i = 0; i < 8; ++i) {
+                dst.code[i] = make_uint4(0u, 0u, 0u, 0u);
+                if (r.valid && (sb * kSuperKb + i * kSuperKb / 8) < n_kb) dst.code[i] = __ldg(r.q + sb * 8 + i);
             }
-            // 128 bytes of the row's packed codes at a time (a "super-block": 4 k-blocks of Q4, 2 of Q8), held in
-            // registers one super-block ahead of the one being dequantized, so the row is read as whole 128-byte lines
-            // and each load has several k-blocks of work to hide behind.
-            uint4 cur[8], nxt[8];
-            const int n_sb = (n_kb + kSuperKb - 1) / kSuperKb;
-            auto load_super = [&](uint4(&dst)[8], int sb) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    dst[i] = make_uint4(0u, 0u, 0u, 0u);
-                    if (wvalid && sb < n_sb && (sb * kSuperKb + i * kSuperKb / 8) < n_kb) dst[i] = __ldg(qrow + sb * 8 + i);
-                }
-            };
-            load_super(cur, 0);
-            bool live = true;
+            for (int g = 0; g < kSuperGroups; ++g) {
+                const int gi = G >= kSuperKb * kBK ? (sb * kSuperKb * kBK) / G : sb * kSuperGroups + g;
+                dst.sm[g] = 0u;
+                if (r.valid && gi < groups) dst.sm[g] = (uint32_t)__ldg(r.s + gi) | ((uint32_t)__ldg(r.m + gi) << 16);
+            }
+        };
+
+        uint32_t it_count = 0;  // k-blocks produced so far (stage / phase bookkeeping)
+        int item = next_valid_item<MODE>(a, blockIdx.x, n_items, rbs);
+        Row row = row_of(item);
+        Super cur, nxt;
+        if (item < n_items) load_super(cur, row, 0);
+        bool live = true;
+        while (item < n_items && live && !*abort_v) {
+            const int next = next_valid_item<MODE>(a, item + gridDim.x, n_items, rbs);
+            const Row next_row = row_of(next);
             for (int sb = 0; sb < n_sb && live; ++sb) {
-                load_super(nxt, sb + 1);
+                if (sb + 1 < n_sb) load_super(nxt, row, sb + 1);
+                else if (next < n_items) load_super(nxt, next_row, 0);
 #pragma unroll
                 for (int sub = 0; sub < kSuperKb; ++sub) {
                     const int kb = sb * kSuperKb + sub;
@@ -315,51 +341,118 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                         live = false;
                         break;
                     }
-                    unsigned char *sa = smem + stage * kStageBytes, *sb_ = sa + kABytes;
-                    // ---- A: this thread's row, 64 codes -> 8 chunks of 8 F16
-                    {
-                        unsigned char *line = sa + (p >> 7) * (128 * 128);
-                        const int r = p & 127;
-                        uint32_t words[kWordsPerKb];
+                    // this thread's row: 64 codes -> the row's 128-byte line, 8 chunks of 8 F16
+                    unsigned char *line = smem + stage * kStageBytes + (p >> 7) * (128 * 128);
+                    const int r = p & 127;
+                    uint32_t words[kWordsPerKb];
 #pragma unroll
-                        for (int i = 0; i < kWordsPerKb / 4; ++i) {
-                            const uint4 v = cur[sub * (kWordsPerKb / 4) + i];
-                            words[4 * i] = v.x, words[4 * i + 1] = v.y, words[4 * i + 2] = v.z, words[4 * i + 3] = v.w;
-                        }
-                        constexpr int kGroupsPerKb = G >= kBK ? 1 : kBK / G;
-                        __half2 s2[kGroupsPerKb], s16[kGroupsPerKb], m2[kGroupsPerKb];
-#pragma unroll
-                        for (int gi = 0; gi < kGroupsPerKb; ++gi) {
-                            const int g = (kb * kBK) / G + gi;
-                            const float sf = wvalid ? bf16_bits_to_f32(__ldg(srow + g)) : 0.f;
-                            const float mf = wvalid ? bf16_bits_to_f32(__ldg(mrow + g)) : 0.f;
-                            s2[gi] = __float2half2_rn(sf), s16[gi] = __float2half2_rn(sf * 0.0625f), m2[gi] = __float2half2_rn(mf);
-                        }
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            const int gi = kGroupsPerKb == 1 ? 0 : (c * 8) / G;
-                            uint4 d;
-                            if (BITS == 4) d = dequant_q4_word(words[c], s2[gi], s16[gi], m2[gi]);
-                            else d = dequant_q8_words(words[2 * c], words[2 * c + 1], s2[gi], m2[gi]);
-                            *reinterpret_cast<uint4 *>(line + swz(r, c)) = d;
-                        }
+                    for (int i = 0; i < kWordsPerKb / 4; ++i) {
+                        const uint4 v = cur.code[sub * (kWordsPerKb / 4) + i];
+                        words[4 * i] = v.x, words[4 * i + 1] = v.y, words[4 * i + 2] = v.z, words[4 * i + 3] = v.w;
                     }
-                    // ---- B: the tile's tokens, 8 chunks of 8 activations each
+                    __half2 s2[kGroupsPerKb], s16[kGroupsPerKb], m2[kGroupsPerKb];
 #pragma unroll
-                    for (int i = 0; i < kMaxTileTokens * 8 / kProducers; ++i) {
-                        const int n = (p >> 3) + 32 * i, c = p & 7;
-                        if (n < it.cnt) {
-                            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(brow[i] + kb * kBK + c * 8));
-                            *reinterpret_cast<uint4 *>(sb_ + swz(n, c)) = b_chunk<BITS>(v, a.x_f16 != 0);
-                        }
+                    for (int gi = 0; gi < kGroupsPerKb; ++gi) {
+                        const int g = G >= kSuperKb * kBK ? 0 : (sub * kBK) / G + gi;  // group inside the super-block
+                        const uint32_t packed = cur.sm[g < kSuperGroups ? g : 0];
+                        const float sf = bf16_bits_to_f32((uint16_t)(packed & 0xffffu)), mf = bf16_bits_to_f32((uint16_t)(packed >> 16));
+                        s2[gi] = __float2half2_rn(sf), s16[gi] = __float2half2_rn(sf * 0.0625f), m2[gi] = __float2half2_rn(mf);
+                    }
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const int gi = kGroupsPerKb == 1 ? 0 : (c * 8) / G;
+                        uint4 d;
+                        if (BITS == 4) d = dequant_q4_word(words[c], s2[gi], s16[gi], m2[gi]);
+                        else d = dequant_q8_words(words[2 * c], words[2 * c + 1], s2[gi], m2[gi]);
+                        *reinterpret_cast<uint4 *>(line + swz(r, c)) = d;
                     }
                     fence_proxy_async();  // the tensor core reads these lines through the async proxy
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&full_bar[stage]);
                 }
-#pragma unroll
-                for (int i = 0; i < 8; ++i) cur[i] = nxt[i];
+                cur = nxt;
             }
+            item = next;
+            row = next_row;
+        }
+    } else if (warp >= kFirstBWarp) {
+        // ===================== B producers: activations =====================
+        // B warp w owns tokens [64 w, 64 w + 64) of the tile; lane l copies 16-byte chunk c = l % 8 of tokens
+        // 64 w + l / 8 + 4 i (i < 16), every k-block, so eight lanes cover one 128-byte line of one activation row.
+        const int bw = warp - kFirstBWarp, c = lane & 7, rg = lane >> 3;
+        constexpr int kRowsPerWarp = kMaxTileTokens / kBWarps, kRowsPerLane = kRowsPerWarp / 4;  // 64, 16
+        int64_t *row_off = b_row_off[bw];  // element offset of every owned token's activation row (this warp only)
+        const bool staged = a.x_kind == 2 || (a.x_kind == 1 && BITS == 8);  // F16 already in this operand's k order
+        uint32_t it_count = 0;
+        for (int item = next_valid_item<MODE>(a, blockIdx.x, n_items, rbs); item < n_items && !*abort_v;
+             item = next_valid_item<MODE>(a, item + gridDim.x, n_items, rbs)) {
+            const ItemInfo it = item_info<MODE>(a, item, rbs);
+            const int n_mine = min(max(it.cnt - bw * kRowsPerWarp, 0), kRowsPerWarp);
+            __syncwarp();
+            for (int n = lane; n < n_mine; n += 32) {
+                const int64_t slot = a.ws[a.L.slots + it.start + bw * kRowsPerWarp + n];
+                row_off[n] = (MODE == kTcPartial ? slot : slot / a.A) * a.K;
+            }
+            __syncwarp();
+            bool live = true;
+            if (staged) {
+                // cp.async straight into the swizzled tile, kBAhead k-blocks in flight; a k-block is handed over when
+                // its group has landed (wait_group), behind a proxy fence.
+                for (int kb = 0; kb < n_kb + kBAhead && live; ++kb) {
+                    if (kb < n_kb) {
+                        const uint32_t cnt = it_count + kb;
+                        const int stage = cnt % kStages;
+                        if (lane == 0 && !mbar_wait(&empty_bar[stage], ((cnt / kStages) & 1u) ^ 1u, abort_v)) raise_abort(item, 5);
+                        __syncwarp();
+                        if (*abort_v) {
+                            live = false;
+                            break;
+                        }
+                        const uint32_t sb_ = smem_u32(smem + stage * kStageBytes + kABytes);
+#pragma unroll 4
+                        for (int i = 0; i < kRowsPerLane; ++i) {
+                            const int nl = rg + 4 * i;
+                            if (nl < n_mine)
+                                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sb_ + swz(bw * kRowsPerWarp + nl, c)),
+                                             "l"(a.x + row_off[nl] + kb * kBK + c * 8)
+                                             : "memory");
+                        }
+                    }
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                    if (kb >= kBAhead) {
+                        asm volatile("cp.async.wait_group %0;" ::"n"(kBAhead) : "memory");
+                        fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&full_bar[(it_count + kb - kBAhead) % kStages]);
+                    }
+                }
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+            } else {
+                // BF16 (or F16 in natural order) activations: through registers, converted and permuted on the way.
+                for (int kb = 0; kb < n_kb && live; ++kb) {
+                    const uint32_t cnt = it_count + kb;
+                    const int stage = cnt % kStages;
+                    if (lane == 0 && !mbar_wait(&empty_bar[stage], ((cnt / kStages) & 1u) ^ 1u, abort_v)) raise_abort(item, 5);
+                    __syncwarp();
+                    if (*abort_v) {
+                        live = false;
+                        break;
+                    }
+                    unsigned char *sb_ = smem + stage * kStageBytes + kABytes;
+#pragma unroll 4
+                    for (int i = 0; i < kRowsPerLane; ++i) {
+                        const int nl = rg + 4 * i;
+                        if (nl < n_mine) {
+                            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(a.x + row_off[nl] + kb * kBK + c * 8));
+                            *reinterpret_cast<uint4 *>(sb_ + swz(bw * kRowsPerWarp + nl, c)) = b_chunk<BITS>(v, a.x_kind == 1);
+                        }
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&full_bar[stage]);
+                }
+            }
+            it_count += n_kb;
         }
     } else if (warp == kMmaWarp) {
         // ===================== MMA issue =====================
@@ -424,6 +517,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
             }
             const int row = warp * 32 + lane;  // TMEM lane = weight row inside a 128-row accumulator
             const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+            // where this thread's h column lands: natural position, or its place in the Q4 operand's k order
+            const int64_t j = (int64_t)it.rb * 128 + row;
+            const int64_t jpos = a.out_f16 == 2 ? ((j & ~(int64_t)7) | ((j & 3) << 1) | ((j >> 2) & 1)) : j;
             for (int c0 = 0; c0 < it.cnt; c0 += 16) {
                 float v0[16], v1[16];
                 if (valid) {
@@ -439,15 +535,14 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                     if (n >= it.cnt) break;
                     const int64_t slot = a.ws[a.L.slots + it.start + n];
                     if (MODE == kTcSwiglu) {
-                        const int64_t j = (int64_t)it.rb * 128 + row;
                         if (j < I) {
                             // kernels/moe_grouped.hip:508-524: from the FP32 accumulators, rounded once
                             const uint16_t hb = f32_to_bf16_bits(silu_f32(v0[t]) * v1[t]);
                             uint16_t *out = static_cast<uint16_t *>(a.out);
-                            out[slot * I + j] = a.out_f16 ? __half_as_ushort(__float2half_rn(bf16_bits_to_f32(hb))) : hb;
+                            out[slot * I + jpos] = a.out_f16 ? __half_as_ushort(__float2half_rn(bf16_bits_to_f32(hb))) : hb;
                         }
                     } else {
-                        const int64_t r0 = (int64_t)it.rb * kProducers + row, r1 = r0 + 128;
+                        const int64_t r0 = (int64_t)it.rb * kAThreads + row, r1 = r0 + 128;
                         if (MODE == kTcPartial) {
                             float *out = static_cast<float *>(a.out);
                             if (r0 < a.N) out[slot * a.N + r0] = v0[t];
@@ -476,6 +571,14 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
     }
 }
 
+// x [M, K] BF16 -> F16 in the k order of a `bits`-bit weight operand (every 8 consecutive k: [0 4 1 5 2 6 3 7] for
+// Q4, natural for Q8): what the B producers would otherwise do per k-block, once per layer instead.
+template <int BITS>
+__global__ void __launch_bounds__(256) stage_f16_kernel(const uint4 *__restrict__ x, uint4 *__restrict__ xh, int64_t chunks) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < chunks; i += (int64_t)gridDim.x * blockDim.x)
+        xh[i] = b_chunk<BITS>(x[i], false);
+}
+
 int check_tc(const char *fn, const void *x, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes, int64_t M,
              int64_t A, const void *out, int act) {
     SXB_CHECK(x != nullptr && out != nullptr && ws != nullptr && w != nullptr, fn, ": null pointer (x=", x, ", out=", out,
@@ -490,7 +593,8 @@ int check_tc(const char *fn, const void *x, const SxbQView *w, int64_t E, const 
               route_words(M, A, E).total * 4);
     SXB_CHECK(aligned16(w->q) && aligned16(x), fn, ": code array ", (const void *)w->q, " and input ", x,
               " must be 16-byte aligned");
-    SXB_CHECK(act == SXB_ACT_BF16, fn, ": the WMMA_F16 kernels take BF16 activations, got ", act_name(act));
+    SXB_CHECK(act == SXB_ACT_BF16 || act == SXB_ACT_F16_STAGED, fn,
+              ": the WMMA_F16 kernels take BF16 activations (or F16 ones staged by sxb_stage_f16), got ", act);
     return SXB_OK;
 }
 
@@ -515,7 +619,7 @@ int launch_tc(const char *fn, const TcArgs &a, int64_t G, cudaStream_t st) {
 
 template <int BITS>
 int tc_gather_grouped(const char *fn, const void *x, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes, int64_t M,
-                      int64_t A, void *y, int act, bool swiglu, bool h_f16, sxb_stream_t stream) {
+                      int64_t A, void *y, int act, bool swiglu, int h_f16, sxb_stream_t stream) {
     if (int rc = check_tc(fn, x, w, E, ws, ws_bytes, M, A, y, act)) return rc;
     const int64_t N = w->N / E;
     SXB_CHECK(!swiglu || N % 2 == 0, fn, ": gate_up has ", N, " rows an expert, expected an even count");
@@ -523,7 +627,7 @@ int tc_gather_grouped(const char *fn, const void *x, const SxbQView *w, int64_t 
     TcArgs a{};
     a.x = static_cast<const uint16_t *>(x), a.q = w->q, a.scale = w->scale, a.minv = w->minv;
     a.N = N, a.K = w->K, a.A = A, a.E = E, a.ws = static_cast<const int32_t *>(ws), a.L = route_words(M, A, E);
-    a.out = y, a.x_f16 = 0, a.out_f16 = h_f16 ? 1 : 0;
+    a.out = y, a.x_kind = act == SXB_ACT_F16_STAGED ? 2 : 0, a.out_f16 = h_f16;
     a.status = reinterpret_cast<uint32_t *>(const_cast<void *>(ws)) + 5;
     auto st = static_cast<cudaStream_t>(stream);
     int rc = swiglu ? launch_tc<BITS, kTcSwiglu>(fn, a, w->G, st) : launch_tc<BITS, kTcGather>(fn, a, w->G, st);
@@ -534,13 +638,14 @@ int tc_gather_grouped(const char *fn, const void *x, const SxbQView *w, int64_t 
 
 template <int BITS>
 int tc_partial_grouped(const char *fn, const void *h, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes, int64_t M,
-                       int64_t A, float *partial, int act, bool h_f16, sxb_stream_t stream) {
+                       int64_t A, float *partial, int act, int h_f16, sxb_stream_t stream) {
+    SXB_CHECK(h_f16 != 2 || BITS == 4, fn, ": h_f16 = 2 (the Q4 operand's k order) with a Q8 down weight");
     if (int rc = check_tc(fn, h, w, E, ws, ws_bytes, M, A, partial, act)) return rc;
     const int64_t N = w->N / E;
     TcArgs a{};
     a.x = static_cast<const uint16_t *>(h), a.q = w->q, a.scale = w->scale, a.minv = w->minv;
     a.N = N, a.K = w->K, a.A = A, a.E = E, a.ws = static_cast<const int32_t *>(ws), a.L = route_words(M, A, E);
-    a.out = partial, a.x_f16 = h_f16 ? 1 : 0, a.out_f16 = 0;
+    a.out = partial, a.x_kind = h_f16, a.out_f16 = 0;
     a.status = reinterpret_cast<uint32_t *>(const_cast<void *>(ws)) + 5;
     auto st = static_cast<cudaStream_t>(stream);
     if (int rc = launch_tc<BITS, kTcPartial>(fn, a, w->G, st)) return rc;
@@ -549,12 +654,28 @@ int tc_partial_grouped(const char *fn, const void *h, const SxbQView *w, int64_t
 }
 
 template int tc_gather_grouped<4>(const char *, const void *, const SxbQView *, int64_t, const void *, size_t, int64_t, int64_t,
-                                  void *, int, bool, bool, sxb_stream_t);
+                                  void *, int, bool, int, sxb_stream_t);
 template int tc_gather_grouped<8>(const char *, const void *, const SxbQView *, int64_t, const void *, size_t, int64_t, int64_t,
-                                  void *, int, bool, bool, sxb_stream_t);
+                                  void *, int, bool, int, sxb_stream_t);
 template int tc_partial_grouped<4>(const char *, const void *, const SxbQView *, int64_t, const void *, size_t, int64_t, int64_t,
-                                   float *, int, bool, sxb_stream_t);
+                                   float *, int, int, sxb_stream_t);
 template int tc_partial_grouped<8>(const char *, const void *, const SxbQView *, int64_t, const void *, size_t, int64_t, int64_t,
-                                   float *, int, bool, sxb_stream_t);
+                                   float *, int, int, sxb_stream_t);
 
 }  // namespace sxb
+
+extern "C" int sxb_stage_f16(const void *x, int64_t M, int64_t K, int bits, void *xh, sxb_stream_t stream) {
+    using namespace sxb;
+    SXB_CHECK(x != nullptr && xh != nullptr, "stage_f16: null pointer (x=", x, ", xh=", xh, ")");
+    SXB_CHECK(M >= 1 && K >= 8 && K % 8 == 0, "stage_f16: M = ", M, ", K = ", K, " (K must be a multiple of 8)");
+    SXB_CHECK(bits == 4 || bits == 8, "stage_f16: k order of a ", bits, "-bit operand unsupported (4 or 8)");
+    SXB_CHECK(aligned16(x) && aligned16(xh), "stage_f16: x and xh must be 16-byte aligned");
+    SXB_CHECK(apart(x, M * K * 2, xh, M * K * 2), "stage_f16: xh overlaps x");
+    const int64_t chunks = M * K / 8;
+    const unsigned blocks = (unsigned)std::min<int64_t>((chunks + 255) / 256, (int64_t)sm_count() * 8);
+    auto st = static_cast<cudaStream_t>(stream);
+    if (bits == 4) stage_f16_kernel<4><<<blocks, 256, 0, st>>>((const uint4 *)x, (uint4 *)xh, chunks);
+    else stage_f16_kernel<8><<<blocks, 256, 0, st>>>((const uint4 *)x, (uint4 *)xh, chunks);
+    SXB_CHECK_LAUNCH("stage_f16 M=", M, " K=", K, " bits=", bits);
+    return SXB_OK;
+}

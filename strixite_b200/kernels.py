@@ -32,6 +32,7 @@ class GpuFatalError(Error):
 class Act(enum.IntEnum):  # kernels/norm.hpp:20
     F32 = 0
     BF16 = 1
+    F16_STAGED = 2  # not in the reference: F16 laid out by stage_f16 for a tensor-core operand
 
 
 class MoeMath(enum.IntEnum):  # kernels/moe_grouped.hpp:39
@@ -236,6 +237,11 @@ def check_expert_error(err, what: str):
 
 def report_expert_error(e, what: str):
     _check(_lib.load().sxb_report_expert_error((C.c_uint32 * 3)(*[int(v) for v in e]), what.encode()))
+
+
+def stage_f16(x, M, K, bits, xh, stream=None):
+    """x [M, K] BF16 -> xh [M, K] F16 in the k order of a `bits`-bit tensor-core weight operand."""
+    _check(_lib.load().sxb_stage_f16(_ptr(x), M, K, bits, _ptr(xh), _stream(stream)))
 
 
 # ---- kernels/swiglu.hpp ---------------------------------------------------------------------------------------

@@ -51,6 +51,9 @@ class MoeBuffers:
         self.ws = torch.empty(self.ws_bytes // 4, dtype=torch.int32, device=dev)
         self.h = torch.empty((S, I), dtype=torch.bfloat16, device=dev)
         self.partial = torch.empty((S, d), dtype=torch.float32, device=dev)
+        self.xh4 = torch.empty((T, d), dtype=torch.float16, device=dev)  # x staged for Q4 operands (tcgen05 path)
+        self.xh8 = torch.empty((T, d), dtype=torch.float16, device=dev)  # x staged for Q8 operands
+        self.staged = {4: False, 8: False}
         self.router_err = torch.zeros(4, dtype=torch.int32, device=dev)
         self.expert_err = torch.zeros(4, dtype=torch.int32, device=dev)
         if shared:
@@ -109,9 +112,22 @@ class MoeLayer:
         if b.sh_ws_tokens != T:
             K.moe_group_routes(b.sh_ids, T, 1, 1, b.sh_ws, b.sh_ws_bytes, b.expert_err)
             b.sh_ws_tokens = T
-        K.linear_qw_experts_gather_grouped_swiglu(x, w.shared_gate_up, 1, b.sh_ws, b.sh_ws_bytes, T, 1, b.sh_h, Act.BF16, math)
+        xs = self.staged_x(x, T, w.shared_gate_up.bits)
+        hf = 2 if w.shared_down.bits == 4 else 1
+        K.linear_qw_experts_gather_grouped_swiglu(xs, w.shared_gate_up, 1, b.sh_ws, b.sh_ws_bytes, T, 1, b.sh_h,
+                                                  Act.F16_STAGED, math, h_f16=hf)
         K.linear_qw_experts_combine_grouped(b.sh_h, w.shared_down, 1, b.sh_ids, b.sh_coef, b.sh_ws, b.sh_ws_bytes,
-                                            b.sh_partial, T, 1, out, Act.BF16, math, out_act=out_act)
+                                            b.sh_partial, T, 1, out, Act.BF16, math, out_act=out_act, h_f16=hf)
+
+    def staged_x(self, x: torch.Tensor, T: int, bits: int) -> torch.Tensor:
+        """The F16 copy of x in the k order of a `bits`-bit operand, made once per forward and shared by the routed and
+        the shared experts' gate/up GEMMs of that bit width."""
+        b = self.buf
+        xh = b.xh4 if bits == 4 else b.xh8
+        if not b.staged[bits]:
+            K.stage_f16(x, T, self.d, bits, xh)
+            b.staged[bits] = True
+        return xh
 
     def experts(self, x: torch.Tensor, T: int, y: torch.Tensor, math: MoeMath, gate_logit=None, gate_ld: int = 0,
                 shared_out: Optional[torch.Tensor] = None, events=None):
@@ -125,20 +141,26 @@ class MoeLayer:
         if events is not None:  # CUDA events around the dominant kernel (the benchmark's roofline timing)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-        K.linear_qw_experts_gather_grouped_swiglu(x, w.gate_up, self.E, b.ws, b.ws_bytes, T, A, b.h, Act.BF16, math)
+        tc = K_is_f16(math)
+        hf = (2 if w.down.bits == 4 else 1) if tc else 0
+        if tc:
+            K.linear_qw_experts_gather_grouped_swiglu(self.staged_x(x, T, w.gate_up.bits), w.gate_up, self.E, b.ws, b.ws_bytes,
+                                                      T, A, b.h, Act.F16_STAGED, math, h_f16=hf)
+        else:
+            K.linear_qw_experts_gather_grouped_swiglu(x, w.gate_up, self.E, b.ws, b.ws_bytes, T, A, b.h, Act.BF16, math)
         if events is not None:
             e1.record()
             events[0].append(e0)
             events[1].append(e1)
         if self.ep:
             K.linear_qw_experts_combine_grouped_ep(b.h, w.down, self.E, self.E_total, self.e_lo, b.ids, b.coef, b.ws,
-                                                   b.ws_bytes, b.partial, T, A, y, Act.BF16, math, out_act=out_act)
+                                                   b.ws_bytes, b.partial, T, A, y, Act.BF16, math, out_act=out_act, h_f16=hf)
         else:
             shared = None
             if gate_logit is not None:
                 shared = K.MoeSharedAdd(shared_out, gate_logit, gate_ld, self.E_total, b.router_err)
             K.linear_qw_experts_combine_grouped(b.h, w.down, self.E, b.ids, b.coef, b.ws, b.ws_bytes, b.partial, T, A, y,
-                                                Act.BF16, math, shared=shared, out_act=out_act)
+                                                Act.BF16, math, shared=shared, out_act=out_act, h_f16=hf)
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor, y: torch.Tensor, math: Optional[MoeMath] = None):
         """x [T, d] BF16, logits [T, >= E (+1)] FP32 -> y [T, d] (BF16, or FP32 = the unrounded sums).
@@ -146,6 +168,7 @@ class MoeLayer:
         T = x.shape[0]
         assert T <= self.buf.max_tokens and x.dtype == torch.bfloat16 and logits.dtype == torch.float32
         math = self.math_for(T, math)
+        self.new_input()
         self.route(logits, T)
         if self.w.shared_gate_up is not None and not self.ep:
             sh = self.buf.sh_y32 if y.dtype == torch.float32 else self.buf.sh_y
@@ -155,6 +178,10 @@ class MoeLayer:
         else:
             self.experts(x, T, y, math)
         return y
+
+    def new_input(self):
+        """Call when x changes (forward does): the staged F16 copies of the previous x are stale."""
+        self.buf.staged = {4: False, 8: False}
 
     def check_errors(self, what: str = "moe layer"):
         """Blocking: the reference's read_back of the error words (runtime/qwen4exp.cpp:2391-2404)."""
