@@ -90,14 +90,17 @@ __device__ inline unsigned long long global_ns() {
     return t;
 }
 // Bounded wait.  False when the CTA is aborting or the limit ran out (then the caller raises the abort itself).
+// The common case must stay cheap: the first polls touch nothing but the barrier; the abort flag and the (slow to read)
+// global timer are consulted only once a wait has lasted thousands of polls.
 __device__ inline bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_ns();
-    for (uint32_t spins = 1;; ++spins) {
+    unsigned long long t0 = 0;
+    for (uint32_t spins = 0;; ++spins) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((spins & 63u) == 0u) {
+        if ((spins & 4095u) == 4095u) {
             if (*abort_flag) return false;
-            if (global_ns() - t0 > kWaitLimitNs) return false;
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) return false;
         }
     }
 }

@@ -253,7 +253,7 @@ def test_grouped_experts_tcgen05(cuda, oracle, bits, G, M, A, E, I, d):
     xh = torch.empty((M, d), dtype=torch.float16, device=cuda)
     K.stage_f16(xd, M, d, bits, xh)
     want_x = xd.float().view(M, d // 8, 8)[:, :, PERM].reshape(M, d) if bits == 4 else xd.float()
-    assert torch.equal(xh.float(), want_x)
+    assert torch.allclose(xh.float(), want_x, rtol=0, atol=2.0 ** -25)  # exact above F16's subnormal range
     hs = torch.zeros((M * A, I), dtype=torch.float16, device=cuda)
     K.linear_qw_experts_gather_grouped_swiglu(xh, gud, E, ws, nbytes, M, A, hs, K.Act.F16_STAGED, K.MoeMath.WmmaF16, h_f16=hk)
     torch.cuda.synchronize()
