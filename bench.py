@@ -43,6 +43,8 @@ def parse():
     ap.add_argument("--no-extra", action="store_true", help="skip the C1 / C3 side measurements at N = 1")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-tokens", type=int, default=0, help="tokens of the CPU baseline sample (default by workload)")
+    ap.add_argument("--experts", type=int, default=0, help="override the expert count (profiling on a small case)")
+    ap.add_argument("--tokens", type=int, default=0, help="override the token count (profiling on a small case)")
     ap.add_argument("--seed", type=int, default=0)
     return ap.parse_args()
 
@@ -426,6 +428,9 @@ def main():
         print(f"note: --gpus {args.gpus} but WORLD_SIZE={world}; using {world}", file=sys.stderr)
     peaks = measured_peaks()
     cfg = W.c2_config(args.seed) if args.workload == "c2" else W.CONFIGS[args.workload]
+    if args.experts or args.tokens:
+        from dataclasses import replace
+        cfg = replace(cfg, E=args.experts or cfg.E, T=args.tokens or cfg.T, name=cfg.name + "_reduced")
     decode = cfg.T <= 64
 
     res = run_stack(cfg, args, dev, rank, world, peaks, layers=(8 if decode else None), rotate=decode)

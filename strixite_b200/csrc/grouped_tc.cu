@@ -31,15 +31,18 @@
 
 #include <cuda_fp16.h>
 
+#ifdef SXB_TC_PROF
+__device__ unsigned long long g_tc_prof[32];
+#endif
+
 namespace sxb {
 namespace {
 
 constexpr int kEpiWarps = 4, kMmaWarp = 4, kFirstAWarp = 5, kAWarps = 8, kFirstBWarp = kFirstAWarp + kAWarps, kBWarps = 2;
 constexpr int kThreads = 32 * (kFirstBWarp + kBWarps);  // 480
 constexpr int kAThreads = 32 * kAWarps;                 // 256 = weight rows per item
-constexpr int kBThreads = 32 * kBWarps;                 // 64
 constexpr int kProducers = kAThreads;
-constexpr int kBAhead = 3;                              // k-blocks of activations in flight (cp.async groups)
+constexpr int kBAhead = 2;                              // k-blocks of activations in flight (cp.async groups)
 constexpr int kBK = 64;                                               // k per stage: one 128-byte swizzle line of F16
 constexpr int kMaxTileTokens = 128;
 constexpr int kStages = 4;
@@ -50,6 +53,19 @@ constexpr int kTmemCols = 512;                      // 2 buffers x 2 accumulator
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any legitimate wait
 
 enum TcMode { kTcGather = 0, kTcSwiglu = 1, kTcPartial = 2 };
+
+// Optional cycle accounting per warp role (development builds only: -DSXB_TC_PROF).  CTA 0, lane 0 of one warp per role.
+#ifdef SXB_TC_PROF
+#define PROF_BEGIN() const long long prof_t0_ = clock64()
+#define PROF_ADD(slot) \
+    do { if (blockIdx.x == 0 && lane == 0) atomicAdd(&g_tc_prof[slot], (unsigned long long)(clock64() - prof_t0_)); } while (0)
+#define PROF_COUNT(slot) \
+    do { if (blockIdx.x == 0 && lane == 0) atomicAdd(&g_tc_prof[slot], 1ull); } while (0)
+#else
+#define PROF_BEGIN() do {} while (0)
+#define PROF_ADD(slot) do {} while (0)
+#define PROF_COUNT(slot) do {} while (0)
+#endif
 
 struct TcArgs {
     const uint16_t *x;  // activations: BF16 or F16 bits, see x_kind
@@ -338,12 +354,17 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                     const int stage = it_count % kStages;
                     const uint32_t phase = (it_count / kStages) & 1u;
                     ++it_count;
-                    if (lane == 0 && !mbar_wait(&empty_bar[stage], phase ^ 1u, abort_v)) raise_abort(item, 1);
-                    __syncwarp();
+                    {
+                        PROF_BEGIN();
+                        if (lane == 0 && !mbar_wait(&empty_bar[stage], phase ^ 1u, abort_v)) raise_abort(item, 1);
+                        __syncwarp();
+                        if (warp == kFirstAWarp) PROF_ADD(0);
+                    }
                     if (*abort_v) {
                         live = false;
                         break;
                     }
+                    PROF_BEGIN();
                     // this thread's row: 64 codes -> the row's 128-byte line, 8 chunks of 8 F16
                     unsigned char *line = smem + stage * kStageBytes + (p >> 7) * (128 * 128);
                     const int r = p & 127;
@@ -369,11 +390,27 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                         else d = dequant_q8_words(words[2 * c], words[2 * c + 1], s2[gi], m2[gi]);
                         *reinterpret_cast<uint4 *>(line + swz(r, c)) = d;
                     }
-                    fence_proxy_async();  // the tensor core reads these lines through the async proxy
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&full_bar[stage]);
+                    if (warp == kFirstAWarp) PROF_ADD(1);
+                    {
+                        PROF_BEGIN();
+                        fence_proxy_async();  // the tensor core reads these lines through the async proxy
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&full_bar[stage]);
+                        if (warp == kFirstAWarp) {
+                            PROF_ADD(2);
+                            PROF_ADD(16 + sub);
+                            PROF_COUNT(4);
+                        }
+                    }
                 }
-                cur = nxt;
+                {
+                    PROF_BEGIN();
+                    cur = nxt;
+#ifdef SXB_TC_PROF
+                    asm volatile("" ::"r"(cur.code[7].w), "r"(cur.code[0].x), "r"(cur.sm[0]));
+#endif
+                    if (warp == kFirstAWarp) PROF_ADD(3);
+                }
             }
             item = next;
             row = next_row;
@@ -402,10 +439,24 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                 // cp.async straight into the swizzled tile, kBAhead k-blocks in flight; a k-block is handed over when
                 // its group has landed (wait_group), behind a proxy fence.
                 for (int kb = 0; kb < n_kb + kBAhead && live; ++kb) {
+                    // hand over k-block kb - kBAhead first: its group is the oldest of the kBAhead still pending, and the
+                    // MMA warp must not have to wait for this warp's next free stage to learn that it has landed
+                    if (kb >= kBAhead) {
+                        PROF_BEGIN();
+                        asm volatile("cp.async.wait_group %0;" ::"n"(kBAhead - 1) : "memory");
+                        fence_proxy_async();
+                        if (bw == 0) PROF_ADD(14);
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&full_bar[(it_count + kb - kBAhead) % kStages]);
+                    }
                     if (kb < n_kb) {
                         const uint32_t cnt = it_count + kb;
                         const int stage = cnt % kStages;
-                        if (lane == 0 && !mbar_wait(&empty_bar[stage], ((cnt / kStages) & 1u) ^ 1u, abort_v)) raise_abort(item, 5);
+                        {
+                            PROF_BEGIN();
+                            if (lane == 0 && !mbar_wait(&empty_bar[stage], ((cnt / kStages) & 1u) ^ 1u, abort_v)) raise_abort(item, 5);
+                            if (bw == 0) PROF_ADD(12);
+                        }
                         __syncwarp();
                         if (*abort_v) {
                             live = false;
@@ -422,12 +473,6 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                         }
                     }
                     asm volatile("cp.async.commit_group;" ::: "memory");
-                    if (kb >= kBAhead) {
-                        asm volatile("cp.async.wait_group %0;" ::"n"(kBAhead) : "memory");
-                        fence_proxy_async();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&full_bar[(it_count + kb - kBAhead) % kStages]);
-                    }
                 }
                 asm volatile("cp.async.wait_group 0;" ::: "memory");
             } else {
@@ -466,7 +511,11 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
             const int buf = acc_count & 1;
             const uint32_t acc_phase = (acc_count >> 1) & 1u;
             ++acc_count;
-            if (lane == 0 && !mbar_wait(&acc_empty[buf], acc_phase ^ 1u, abort_v)) raise_abort(item, 2);
+            {
+                PROF_BEGIN();
+                if (lane == 0 && !mbar_wait(&acc_empty[buf], acc_phase ^ 1u, abort_v)) raise_abort(item, 2);
+                PROF_ADD(7);
+            }
             __syncwarp();
             if (*abort_v) break;
             tc_fence_after();
@@ -475,10 +524,16 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
             for (int kb = 0; kb < n_kb; ++kb, ++it_count) {
                 const int stage = it_count % kStages;
                 const uint32_t phase = (it_count / kStages) & 1u;
-                if (lane == 0 && !mbar_wait(&full_bar[stage], phase, abort_v)) raise_abort(item, 3);
+                {
+                    PROF_BEGIN();
+                    if (lane == 0 && !mbar_wait(&full_bar[stage], phase, abort_v)) raise_abort(item, 3);
+                    PROF_ADD(5);
+                    PROF_COUNT(8);
+                }
                 __syncwarp();
                 if (*abort_v) break;
                 tc_fence_after();
+                PROF_BEGIN();
                 if (lane == 0) {
                     const uint32_t sa = smem_u32(smem + stage * kStageBytes), sb_ = sa + kABytes;
 #pragma unroll
@@ -492,6 +547,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                     tc_commit(&empty_bar[stage]);                      // frees the stage when these MMAs have read it
                     if (kb == n_kb - 1) tc_commit(&acc_full[buf]);     // and hands the accumulators to the epilogue
                 }
+                PROF_ADD(6);
                 __syncwarp();
             }
         }
@@ -513,11 +569,19 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                 buf = acc_count & 1;
                 const uint32_t acc_phase = (acc_count >> 1) & 1u;
                 ++acc_count;
-                if (lane == 0 && !mbar_wait(&acc_full[buf], acc_phase, abort_v)) raise_abort(item, 4);
+                {
+                    PROF_BEGIN();
+                    if (lane == 0 && !mbar_wait(&acc_full[buf], acc_phase, abort_v)) raise_abort(item, 4);
+                    if (warp == 0) {
+                        PROF_ADD(9);
+                        PROF_COUNT(11);
+                    }
+                }
                 __syncwarp();
                 if (*abort_v) break;
                 tc_fence_after();
             }
+            PROF_BEGIN();
             const int row = warp * 32 + lane;  // TMEM lane = weight row inside a 128-row accumulator
             const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
             // where this thread's h column lands: natural position, or its place in the Q4 operand's k order
@@ -558,6 +622,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                     }
                 }
             }
+            if (warp == 0) PROF_ADD(10);
             if (valid) {
                 tc_fence_before();
                 __syncwarp();
@@ -666,6 +731,17 @@ template int tc_partial_grouped<8>(const char *, const void *, const SxbQView *,
                                    float *, int, int, sxb_stream_t);
 
 }  // namespace sxb
+
+#ifdef SXB_TC_PROF
+extern "C" __attribute__((visibility("default"))) int sxb_debug_tc_prof(unsigned long long *out, int reset) {
+    cudaMemcpyFromSymbol(out, g_tc_prof, sizeof(unsigned long long) * 32);
+    if (reset) {
+        unsigned long long z[32] = {};
+        cudaMemcpyToSymbol(g_tc_prof, z, sizeof(z));
+    }
+    return 0;
+}
+#endif
 
 extern "C" int sxb_stage_f16(const void *x, int64_t M, int64_t K, int bits, void *xh, sxb_stream_t stream) {
     using namespace sxb;
