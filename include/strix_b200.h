@@ -206,6 +206,16 @@ int sxb_linear_q4_experts_combine_grouped(const void *h, const SxbQView *w, int6
                                           const float *coef, const void *ws, size_t ws_bytes, float *partial,
                                           int64_t M, int64_t A, void *y, int act, int out_act, int math,
                                           sxb_stream_t stream, const SxbMoeSharedAdd *shared, int h_f16);
+/* No counterpart in the reference.  sxb_linear_q4_experts_combine_grouped for callers that cannot supply `partial`: an
+ * engine whose memory plan left no spare device memory, or a decode loop that must not call cudaMalloc (it synchronizes
+ * the device).  The per-slot dots go to a 16 MiB array inside the library image instead; x / h / y stay the caller's.
+ * Refuses M * A * N > 4 Mi floats (4,194,304) with SXB_ERR_CHECK.  Allocates nothing.  The first call on a device looks the
+ * array's address up (a blocking runtime call): make it before any stream capture.  Every call on a device shares the
+ * array: calls that overlap on the GPU race. */
+int sxb_linear_q4_experts_combine_grouped_noalloc(const void *h, const SxbQView *w, int64_t E, const int32_t *ids,
+                                                  const float *coef, const void *ws, size_t ws_bytes, int64_t M, int64_t A,
+                                                  void *y, int act, int out_act, int math, sxb_stream_t stream,
+                                                  const SxbMoeSharedAdd *shared, int h_f16);
 /* The same three for Q8 experts (no counterpart in the reference, see above). */
 int sxb_linear_q8_experts_gather_grouped(const void *x, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes,
                                          int64_t M, int64_t A, void *y, int act, int math, sxb_stream_t stream);

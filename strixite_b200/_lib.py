@@ -9,7 +9,10 @@ import ctypes as C
 import pathlib
 
 _PKG = pathlib.Path(__file__).resolve().parent
-LIB_PATH = _PKG / "libstrix_b200.so"
+import os
+
+# STRIX_B200_LIB: load another build of the same library (e.g. one compiled with development counters).
+LIB_PATH = pathlib.Path(os.environ.get("STRIX_B200_LIB") or _PKG / "libstrix_b200.so")
 
 i64, i32, u32, sz, vp, cp = C.c_int64, C.c_int32, C.c_uint32, C.c_size_t, C.c_void_p, C.c_char_p
 
@@ -64,6 +67,9 @@ for _b in ("q4", "q8"):
         C.c_int, [vp, QV, i64, vp, vp, vp, sz, vp, i64, i64, vp, C.c_int, C.c_int, C.c_int, vp, SA, C.c_int])
     SIGNATURES[f"sxb_linear_{_b}_experts_combine_grouped_ep"] = (
         C.c_int, [vp, QV, i64, i64, i64, vp, vp, vp, sz, vp, i64, i64, vp, C.c_int, C.c_int, C.c_int, vp, C.c_int])
+
+SIGNATURES["sxb_linear_q4_experts_combine_grouped_noalloc"] = (
+    C.c_int, [vp, QV, i64, vp, vp, vp, sz, i64, i64, vp, C.c_int, C.c_int, C.c_int, vp, SA, C.c_int])
 
 _lib = None
 
