@@ -53,7 +53,10 @@ enum {
     SXB_ACT_BF16 = 1,
     /* Not in the reference: F16 activations laid out by sxb_stage_f16 for a tensor-core operand.  Accepted as the
      * input dtype of the WMMA_F16 grouped gathers only. */
-    SXB_ACT_F16_STAGED = 2
+    SXB_ACT_F16_STAGED = 2,
+    /* Not in the reference: F16 activations in the tile-blocked form made by sxb_stage_f16_tiles (rows in the pack's slot
+     * order, one contiguous run per 128-slot tile and k-block).  Same use as SXB_ACT_F16_STAGED, faster. */
+    SXB_ACT_F16_TILED = 3
 };
 
 /* kernels/moe_grouped.hpp:39  enum class MoeMath.  Here:
@@ -193,7 +196,7 @@ int sxb_linear_q4_experts_gather_grouped(const void *x, const SxbQView *w, int64
  * the FP32 accumulators, rounded once.  h_f16 (WMMA_F16 only): 0 = h stored as BF16; 1 = h stored as F16 bits of its
  * BF16 rounding (the reference's h_f16); 2 = the same values with every 8 consecutive columns in the order
  * [0 4 1 5 2 6 3 7], the k order of a Q4 tensor-core operand, so the Q4 down GEMM can copy h rows without touching
- * them (pass the same h_f16 to the combine).  With SXB_MATH_F32 / WMMA_BF16 (an extension: the reference refuses them
+ * them (pass the same h_f16 to the combine); 3 / 4 = tile-blocked for a Q4 / Q8 down operand (sxb_stage_f16_tiles).  With SXB_MATH_F32 / WMMA_BF16 (an extension: the reference refuses them
  * here) the decode form's rounding points are kept.  act may be SXB_ACT_F16_STAGED: x then holds the F16 copy made by
  * sxb_stage_f16 for this weight's bit width. */
 int sxb_linear_q4_experts_gather_grouped_swiglu(const void *x, const SxbQView *w, int64_t E, const void *ws,
@@ -245,6 +248,14 @@ int sxb_linear_q8_experts_combine_grouped_ep(const void *h, const SxbQView *w, i
  * cores ([0 4 1 5 2 6 3 7] for Q4, natural for Q8).  Done once per layer, it lets the grouped GEMMs copy activation rows
  * asynchronously instead of converting them per tile.  xh: caller-owned, M*K*2 bytes, 16-byte aligned. */
 int sxb_stage_f16(const void *x, int64_t M, int64_t K, int bits, void *xh, sxb_stream_t stream);
+/* No counterpart in the reference.  The tile-blocked form of the same: for a grouping workspace ws (after the pack), xs
+ * receives, for every slot position pos of the slot order and every k-block kb of 64, the 128-byte F16 line of token
+ * slots[pos] / A at byte (kb * S + pos) * 128, swizzled for its place in its 128-slot tile, so that a tile's operand of a
+ * k-block is one contiguous run and reaches shared memory with a single bulk copy.  xs: caller-owned, M*A*K*2 bytes.
+ * Pass act = SXB_ACT_F16_TILED to the grouped gather.  The SwiGLU gather writes h in the same form with h_f16 = 3 (Q4
+ * down) or 4 (Q8 down); pass the same h_f16 to the combine. */
+int sxb_stage_f16_tiles(const void *x, const void *ws, size_t ws_bytes, int64_t M, int64_t A, int64_t E, int64_t K, int bits,
+                        void *xs, sxb_stream_t stream);
 
 /* ---- Quantizers on the device ------------------------------------------------------------------------------- */
 

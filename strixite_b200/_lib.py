@@ -49,6 +49,7 @@ SIGNATURES = {
     "sxb_linear_q4": (C.c_int, [vp, QV, vp, i64, C.c_int, C.c_int, vp]),
     "sxb_linear_q8": (C.c_int, [vp, QV, vp, i64, C.c_int, C.c_int, vp]),
     "sxb_stage_f16": (C.c_int, [vp, i64, i64, C.c_int, vp, vp]),
+    "sxb_stage_f16_tiles": (C.c_int, [vp, vp, sz, i64, i64, i64, i64, C.c_int, vp, vp]),
     "sxb_swiglu": (C.c_int, [vp, vp, i64, i64, C.c_int, vp]),
     "sxb_check_expert_error": (C.c_int, [vp, cp]),
     "sxb_report_expert_error": (C.c_int, [C.POINTER(u32), cp]),

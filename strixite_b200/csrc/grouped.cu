@@ -11,10 +11,10 @@ template <int BITS>
 int gather_grouped(const char *fn, const void *x, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes, int64_t M,
                    int64_t A, void *y, int act, int math, bool swiglu, int h_f16, sxb_stream_t stream) {
     SXB_CHECK(math_ok(math), fn, ": unknown math ", math);
-    SXB_CHECK(h_f16 >= 0 && h_f16 <= 2, fn, ": h_f16 = ", h_f16, ", expected 0, 1 or 2");
+    SXB_CHECK(h_f16 >= 0 && h_f16 <= 4, fn, ": h_f16 = ", h_f16, ", expected 0..4");
     SXB_CHECK(!h_f16 || (act != SXB_ACT_F32 && math_is_f16(math)), fn,
               ": F16 h needs BF16 activations and a WMMA_F16 math, got ", act_name(act), " math ", math);
-    SXB_CHECK(act != SXB_ACT_F16_STAGED || math_is_f16(math), fn, ": staged F16 activations need a WMMA_F16 math");
+    SXB_CHECK((act != SXB_ACT_F16_STAGED && act != SXB_ACT_F16_TILED) || math_is_f16(math), fn, ": staged F16 activations need a WMMA_F16 math");
     if (math_is_f16(math)) return tc_gather_grouped<BITS>(fn, x, w, E, ws, ws_bytes, M, A, y, act, swiglu, h_f16, stream);
     return stream_gather_grouped<BITS>(fn, x, w, E, ws, ws_bytes, M, A, y, act, swiglu, stream);
 }
@@ -25,7 +25,7 @@ int combine_grouped(const char *fn, const void *h, const SxbQView *w, int64_t E_
                     int math, sxb_stream_t stream, const SxbMoeSharedAdd *shared, int h_f16, int64_t E_total,
                     int64_t e_lo) {
     SXB_CHECK(math_ok(math), fn, ": unknown math ", math);
-    SXB_CHECK(h_f16 >= 0 && h_f16 <= 2, fn, ": h_f16 = ", h_f16, ", expected 0, 1 or 2");
+    SXB_CHECK(h_f16 >= 0 && h_f16 <= 4, fn, ": h_f16 = ", h_f16, ", expected 0..4");
     SXB_CHECK(!h_f16 || (act == SXB_ACT_BF16 && math_is_f16(math)), fn,
               ": F16 h needs BF16 activations and a WMMA_F16 math, got ", act_name(act), " math ", math);
     SXB_CHECK(ids != nullptr && coef != nullptr && partial != nullptr && y != nullptr && w != nullptr, fn,

@@ -33,6 +33,11 @@
 
 #ifdef SXB_TC_PROF
 __device__ unsigned long long g_tc_prof[32];
+__device__ long long g_tc_trace[4][64][2];  // role (A, B, MMA, -), k-block index of CTA 0, two timestamps
+#define TRACE(role, idx, which) \
+    do { if (blockIdx.x == 0 && lane == 0 && (idx) < 64) g_tc_trace[role][idx][which] = clock64(); } while (0)
+#else
+#define TRACE(role, idx, which) do {} while (0)
 #endif
 
 namespace sxb {
@@ -46,10 +51,18 @@ constexpr int kBAhead = 2;                              // k-blocks of activatio
 constexpr int kBK = 64;                                               // k per stage: one 128-byte swizzle line of F16
 constexpr int kMaxTileTokens = 128;
 constexpr int kStages = 4;
-constexpr int kABytes = kProducers * kBK * 2;       // 32 KB: two 128-row MMA operands
-constexpr int kBBytes = kMaxTileTokens * kBK * 2;   // 16 KB
-constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kTmemCols = 512;                      // 2 buffers x 2 accumulators x 128 columns
+constexpr int kBBytes = kMaxTileTokens * kBK * 2;   // 16 KB: the activation tile of one k-block
+constexpr int kStageBytes = kBBytes;                // shared memory per stage (the weights travel through tensor memory)
+// Tensor memory, 512 columns x 128 lanes: two accumulators (weight rows 0-127 and 128-255 of the item) of up to 128 token
+// columns each, then kStages stages of the A operand - per stage and accumulator 32 columns = 64 F16 of one weight row
+// per lane.
+constexpr int kTmemCols = 512;
+constexpr int kAccCols = kMaxTileTokens;
+constexpr int kAStageCol0 = 2 * kAccCols, kAStageCols = 2 * (kBK / 2);
+// SwiGLU epilogue parking area in shared memory: 16-bit h values [token][row], token stride padded to 136 (272 bytes:
+// 16-byte aligned rows, and neighbouring tokens start in different banks).
+constexpr int kEpiTokStride = 136;
+constexpr int kEpiBytes = kMaxTileTokens * kEpiTokStride * 2;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any legitimate wait
 
 enum TcMode { kTcGather = 0, kTcSwiglu = 1, kTcPartial = 2 };
@@ -76,8 +89,10 @@ struct TcArgs {
     const int32_t *ws;
     RouteWords L;
     void *out;
-    int x_kind;   // activations: 0 BF16, 1 F16 in natural k order, 2 F16 in this weight operand's k order (staged)
-    int out_f16;  // SwiGLU output h: 0 BF16, 1 F16 bits of its BF16 rounding, 2 the same in the Q4 operand's k order
+    int x_kind;   // activations: 0 BF16, 1 F16 in natural k order, 2 F16 in this weight operand's k order (staged),
+                  // 3 F16 "tile-blocked" (see tiled_offset): one bulk copy per k-block
+    int out_f16;  // SwiGLU output h: 0 BF16, 1 F16 bits of its BF16 rounding, 2 the same in the Q4 operand's k order,
+                  // 3 / 4 tile-blocked for a Q4 / Q8 down operand
     uint32_t *status;  // >= 3 words: {2, item, role} on a wait that ran out
 };
 
@@ -93,7 +108,11 @@ __device__ inline bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
+#ifdef SXB_TC_EXP_TESTWAIT
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#else
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#endif
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(smem_u32(bar)), "r"(parity)
@@ -147,6 +166,24 @@ __device__ inline void tc_ld16(uint32_t taddr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 16 consecutive columns of this thread's TMEM lane, written from registers.
+__device__ inline void tc_st16(uint32_t taddr, const uint4 (&d)[4]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+        "r"(d[0].x), "r"(d[0].y), "r"(d[0].z), "r"(d[0].w), "r"(d[1].x), "r"(d[1].y), "r"(d[1].z), "r"(d[1].w), "r"(d[2].x),
+        "r"(d[2].y), "r"(d[2].z), "r"(d[2].w), "r"(d[3].x), "r"(d[3].y), "r"(d[3].z), "r"(d[3].w)
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (128 rows x 16 k of F16, two per 32-bit column) read from tensor memory.
+__device__ inline void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart.
 //   bits [0,14) start address >> 4 | [16,30) leading byte offset >> 4 (unused for swizzled K-major: 1)
 //   [32,46) stride byte offset >> 4 (1024 B) | [46,48) descriptor version 1 | [61,64) layout 2 = SWIZZLE_128B
@@ -162,6 +199,21 @@ __device__ inline __half2 u32_as_h2(uint32_t v) { return *reinterpret_cast<__hal
 
 // Byte offset of 16-byte chunk c of row r inside a K-major, 128-byte-swizzled tile.
 __device__ inline uint32_t swz(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
+
+// Tile-blocked activations: rows live at their position `pos` in the pack's slot order, k-block-major, each row's 128-byte
+// line of a k-block already swizzled for its place n = pos - tile_start in the tile.  The B operand of (tile, k-block) is
+// then ONE contiguous run of cnt * 128 bytes at byte offset (kb * S + tile_start) * 128: a single bulk copy.
+__device__ inline int64_t tiled_offset(int64_t S, int kb, int64_t pos, int n, int c) {
+    return ((int64_t)kb * S + pos) * 128 + ((c ^ (n & 7)) << 4);
+}
+__device__ inline void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ inline void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
 
 // Eight activations (one 16-byte chunk of BF16 or F16) -> F16 in the operand's k order.
 template <int BITS>
@@ -247,7 +299,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment of the operand tiles (the swizzle pattern repeats every 1024 bytes).
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    __shared__ uint64_t full_bar[kStages], empty_bar[kStages], acc_full[2], acc_empty[2], drain_bar;
+    __shared__ uint64_t full_bar[kStages], empty_bar[kStages], acc_full[1], acc_empty[1], drain_bar;
     __shared__ uint32_t tmem_base_smem;
     __shared__ int abort_flag;
     __shared__ int64_t b_row_off[kBWarps][kMaxTileTokens / kBWarps];
@@ -259,8 +311,8 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
     volatile int *abort_v = &abort_flag;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], kAWarps + kBWarps), mbar_init(&empty_bar[s], 1);
-        for (int b = 0; b < 2; ++b) mbar_init(&acc_full[b], 1), mbar_init(&acc_empty[b], kEpiWarps);
+        for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], kAWarps + (a.x_kind == 3 ? 1 : kBWarps)), mbar_init(&empty_bar[s], 1);
+        mbar_init(&acc_full[0], 1), mbar_init(&acc_empty[0], kEpiWarps);
         mbar_init(&drain_bar, 1);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -283,7 +335,10 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
 
     if (warp >= kFirstAWarp && warp < kFirstBWarp) {
         // ===================== A producers: weights =====================
-        const int p = threadIdx.x - 32 * kFirstAWarp;  // weight row of the item, 0..255
+        // A thread owns one weight row of the item and writes it into its own tensor-memory lane; a warp may only touch
+        // the lane quadrant warp % 4, so the row is (accumulator, quadrant, lane).
+        const int a_half = (warp - kFirstAWarp) >> 2, a_quad = warp & 3;
+        const int p = a_half * 128 + a_quad * 32 + lane;  // weight row of the item, 0..255
         const int64_t row_bytes = BITS == 4 ? a.K / 2 : a.K;
         constexpr int kSuperKb = BITS == 4 ? 4 : 2;  // k-blocks per 128 bytes of packed codes
         constexpr int kWordsPerKb = BITS == 4 ? 8 : 16;
@@ -359,15 +414,14 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                         if (lane == 0 && !mbar_wait(&empty_bar[stage], phase ^ 1u, abort_v)) raise_abort(item, 1);
                         __syncwarp();
                         if (warp == kFirstAWarp) PROF_ADD(0);
+                        if (warp == kFirstAWarp) TRACE(0, it_count - 1, 0);
                     }
                     if (*abort_v) {
                         live = false;
                         break;
                     }
                     PROF_BEGIN();
-                    // this thread's row: 64 codes -> the row's 128-byte line, 8 chunks of 8 F16
-                    unsigned char *line = smem + stage * kStageBytes + (p >> 7) * (128 * 128);
-                    const int r = p & 127;
+                    // this thread's row: 64 codes -> 64 F16 = 32 tensor-memory columns of its lane
                     uint32_t words[kWordsPerKb];
 #pragma unroll
                     for (int i = 0; i < kWordsPerKb / 4; ++i) {
@@ -382,20 +436,28 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                         const float sf = bf16_bits_to_f32((uint16_t)(packed & 0xffffu)), mf = bf16_bits_to_f32((uint16_t)(packed >> 16));
                         s2[gi] = __float2half2_rn(sf), s16[gi] = __float2half2_rn(sf * 0.0625f), m2[gi] = __float2half2_rn(mf);
                     }
+                    const uint32_t a_addr = tmem_base + ((uint32_t)(a_quad * 32) << 16) +
+                                            (uint32_t)(kAStageCol0 + stage * kAStageCols + a_half * (kBK / 2));
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        const int gi = kGroupsPerKb == 1 ? 0 : (c * 8) / G;
-                        uint4 d;
-                        if (BITS == 4) d = dequant_q4_word(words[c], s2[gi], s16[gi], m2[gi]);
-                        else d = dequant_q8_words(words[2 * c], words[2 * c + 1], s2[gi], m2[gi]);
-                        *reinterpret_cast<uint4 *>(line + swz(r, c)) = d;
+                    for (int hc = 0; hc < 2; ++hc) {  // two stores of 16 columns keep the live registers down
+                        uint4 d[4];
+#pragma unroll
+                        for (int cc = 0; cc < 4; ++cc) {
+                            const int c = hc * 4 + cc;
+                            const int gi = kGroupsPerKb == 1 ? 0 : (c * 8) / G;
+                            if (BITS == 4) d[cc] = dequant_q4_word(words[c], s2[gi], s16[gi], m2[gi]);
+                            else d[cc] = dequant_q8_words(words[2 * c], words[2 * c + 1], s2[gi], m2[gi]);
+                        }
+                        tc_st16(a_addr + hc * 16, d);
                     }
                     if (warp == kFirstAWarp) PROF_ADD(1);
                     {
                         PROF_BEGIN();
-                        fence_proxy_async();  // the tensor core reads these lines through the async proxy
+                        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                        tc_fence_before();  // orders the stores before the MMA warp's reads across the barrier
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&full_bar[stage]);
+                        if (warp == kFirstAWarp) TRACE(0, it_count - 1, 1);
                         if (warp == kFirstAWarp) {
                             PROF_ADD(2);
                             PROF_ADD(16 + sub);
@@ -419,6 +481,28 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
         // ===================== B producers: activations =====================
         // B warp w owns tokens [64 w, 64 w + 64) of the tile; lane l copies 16-byte chunk c = l % 8 of tokens
         // 64 w + l / 8 + 4 i (i < 16), every k-block, so eight lanes cover one 128-byte line of one activation row.
+        if (a.x_kind == 3) {
+            // Tile-blocked activations: one thread, one bulk copy per k-block, completion counted in bytes on the
+            // stage's barrier; every free stage is refilled at once, so kStages k-blocks are in flight.
+            if (warp == kFirstBWarp && lane == 0) {
+                uint32_t it_count = 0;
+                for (int item = next_valid_item<MODE>(a, blockIdx.x, n_items, rbs); item < n_items && !*abort_v;
+                     item = next_valid_item<MODE>(a, item + gridDim.x, n_items, rbs)) {
+                    const ItemInfo it = item_info<MODE>(a, item, rbs);
+                    const uint32_t bytes = (uint32_t)it.cnt * 128u;
+                    const unsigned char *src = reinterpret_cast<const unsigned char *>(a.x) + (int64_t)it.start * 128;
+                    for (int kb = 0; kb < n_kb; ++kb, ++it_count) {
+                        const int stage = it_count % kStages;
+                        if (!mbar_wait(&empty_bar[stage], ((it_count / kStages) & 1u) ^ 1u, abort_v)) {
+                            raise_abort(item, 5);
+                            break;
+                        }
+                        mbar_expect_tx(&full_bar[stage], bytes);
+                        bulk_g2s(smem_u32(smem + stage * kStageBytes), src + (int64_t)kb * a.L.S * 128, bytes, &full_bar[stage]);
+                    }
+                }
+            }
+        } else {
         const int bw = warp - kFirstBWarp, c = lane & 7, rg = lane >> 3;
         constexpr int kRowsPerWarp = kMaxTileTokens / kBWarps, kRowsPerLane = kRowsPerWarp / 4;  // 64, 16
         int64_t *row_off = b_row_off[bw];  // element offset of every owned token's activation row (this warp only)
@@ -448,6 +532,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                         if (bw == 0) PROF_ADD(14);
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&full_bar[(it_count + kb - kBAhead) % kStages]);
+                        if (bw == 0) TRACE(1, it_count + kb - kBAhead, 1);
                     }
                     if (kb < n_kb) {
                         const uint32_t cnt = it_count + kb;
@@ -456,13 +541,14 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                             PROF_BEGIN();
                             if (lane == 0 && !mbar_wait(&empty_bar[stage], ((cnt / kStages) & 1u) ^ 1u, abort_v)) raise_abort(item, 5);
                             if (bw == 0) PROF_ADD(12);
+                            if (bw == 0) TRACE(1, cnt, 0);
                         }
                         __syncwarp();
                         if (*abort_v) {
                             live = false;
                             break;
                         }
-                        const uint32_t sb_ = smem_u32(smem + stage * kStageBytes + kABytes);
+                        const uint32_t sb_ = smem_u32(smem + stage * kStageBytes);
 #pragma unroll 4
                         for (int i = 0; i < kRowsPerLane; ++i) {
                             const int nl = rg + 4 * i;
@@ -486,7 +572,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                         live = false;
                         break;
                     }
-                    unsigned char *sb_ = smem + stage * kStageBytes + kABytes;
+                    unsigned char *sb_ = smem + stage * kStageBytes;
 #pragma unroll 4
                     for (int i = 0; i < kRowsPerLane; ++i) {
                         const int nl = rg + 4 * i;
@@ -502,18 +588,18 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
             }
             it_count += n_kb;
         }
+        }
     } else if (warp == kMmaWarp) {
         // ===================== MMA issue =====================
         uint32_t it_count = 0, acc_count = 0;
         for (int item = blockIdx.x; item < n_items && !*abort_v; item += gridDim.x) {
             const ItemInfo it = item_info<MODE>(a, item, rbs);
             if (it.bucket >= a.E) continue;
-            const int buf = acc_count & 1;
-            const uint32_t acc_phase = (acc_count >> 1) & 1u;
+            const uint32_t acc_phase = acc_count & 1u;
             ++acc_count;
             {
                 PROF_BEGIN();
-                if (lane == 0 && !mbar_wait(&acc_empty[buf], acc_phase ^ 1u, abort_v)) raise_abort(item, 2);
+                if (lane == 0 && !mbar_wait(&acc_empty[0], acc_phase ^ 1u, abort_v)) raise_abort(item, 2);
                 PROF_ADD(7);
             }
             __syncwarp();
@@ -529,25 +615,32 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                     if (lane == 0 && !mbar_wait(&full_bar[stage], phase, abort_v)) raise_abort(item, 3);
                     PROF_ADD(5);
                     PROF_COUNT(8);
+                    TRACE(2, it_count, 0);
                 }
                 __syncwarp();
                 if (*abort_v) break;
                 tc_fence_after();
                 PROF_BEGIN();
                 if (lane == 0) {
-                    const uint32_t sa = smem_u32(smem + stage * kStageBytes), sb_ = sa + kABytes;
+                    const uint32_t sb_ = smem_u32(smem + stage * kStageBytes);
+                    // the two accumulators alternate, so consecutive instructions never depend on each other
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        const uint32_t d = tmem_base + (uint32_t)((buf * 2 + half) * kMaxTileTokens);
+                    for (int j = 0; j < kBK / 16; ++j) {
+#ifdef SXB_TC_EXP_SKIP
+                        if (j >= 2) break;  // timing experiment only: half of the instructions, wrong results
+#endif
 #pragma unroll
-                        for (int j = 0; j < kBK / 16; ++j)
-                            tc_mma_f16(d, smem_desc(sa + half * (128 * 128) + j * 32), smem_desc(sb_ + j * 32), idesc,
-                                       (kb | j) != 0);
+                        for (int half = 0; half < 2; ++half) {
+                            const uint32_t d = tmem_base + (uint32_t)(half * kAccCols);
+                            const uint32_t at = tmem_base + (uint32_t)(kAStageCol0 + stage * kAStageCols + half * (kBK / 2));
+                            tc_mma_f16_ts(d, at + j * 8, smem_desc(sb_ + j * 32), idesc, (kb | j) != 0);
+                        }
                     }
-                    tc_commit(&empty_bar[stage]);                      // frees the stage when these MMAs have read it
-                    if (kb == n_kb - 1) tc_commit(&acc_full[buf]);     // and hands the accumulators to the epilogue
+                    tc_commit(&empty_bar[stage]);                    // frees the stage when these MMAs have read it
+                    if (kb == n_kb - 1) tc_commit(&acc_full[0]);     // and hands the accumulators to the epilogue
                 }
                 PROF_ADD(6);
+                TRACE(2, it_count, 1);
                 __syncwarp();
             }
         }
@@ -559,19 +652,24 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
         __syncwarp();
     } else {
         // ===================== epilogue =====================
+        // Lane = weight row of a 128-row accumulator.  Gather / partial outputs leave straight from the registers: for
+        // one token a warp's 32 lanes hold 32 consecutive rows, one coalesced store.  SwiGLU: h = silu(g) * u is formed
+        // here (gate and up row j sit in the same lane of the two accumulators), parked as 16-bit values in shared
+        // memory [token][row], tensor memory is handed back, and then every thread takes one token x 8 consecutive
+        // columns of its own warp's rows and stores them as one 16-byte chunk in the layout the down GEMM wants.
         uint32_t acc_count = 0;
         const int64_t I = a.N / 2;
+        uint16_t *stage_h = reinterpret_cast<uint16_t *>(smem + kStages * kStageBytes);
         for (int item = blockIdx.x; item < n_items && !*abort_v; item += gridDim.x) {
             const ItemInfo it = item_info<MODE>(a, item, rbs);
             const bool valid = it.bucket < a.E;
-            int buf = 0;
+            const int row = warp * 32 + lane;
             if (valid) {
-                buf = acc_count & 1;
-                const uint32_t acc_phase = (acc_count >> 1) & 1u;
+                const uint32_t acc_phase = acc_count & 1u;
                 ++acc_count;
                 {
                     PROF_BEGIN();
-                    if (lane == 0 && !mbar_wait(&acc_full[buf], acc_phase, abort_v)) raise_abort(item, 4);
+                    if (lane == 0 && !mbar_wait(&acc_full[0], acc_phase, abort_v)) raise_abort(item, 4);
                     if (warp == 0) {
                         PROF_ADD(9);
                         PROF_COUNT(11);
@@ -582,34 +680,30 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                 tc_fence_after();
             }
             PROF_BEGIN();
-            const int row = warp * 32 + lane;  // TMEM lane = weight row inside a 128-row accumulator
             const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-            // where this thread's h column lands: natural position, or its place in the Q4 operand's k order
-            const int64_t j = (int64_t)it.rb * 128 + row;
-            const int64_t jpos = a.out_f16 == 2 ? ((j & ~(int64_t)7) | ((j & 3) << 1) | ((j >> 2) & 1)) : j;
             for (int c0 = 0; c0 < it.cnt; c0 += 16) {
                 float v0[16], v1[16];
                 if (valid) {
-                    tc_ld16(lane_addr + (uint32_t)((buf * 2 + 0) * kMaxTileTokens + c0), v0);
-                    tc_ld16(lane_addr + (uint32_t)((buf * 2 + 1) * kMaxTileTokens + c0), v1);
+                    tc_ld16(lane_addr + (uint32_t)(c0), v0);
+                    tc_ld16(lane_addr + (uint32_t)(kAccCols + c0), v1);
                 } else {
 #pragma unroll
                     for (int t = 0; t < 16; ++t) v0[t] = v1[t] = qnan_f32();
                 }
+                if (MODE == kTcSwiglu) {
 #pragma unroll
-                for (int t = 0; t < 16; ++t) {
-                    const int n = c0 + t;
-                    if (n >= it.cnt) break;
-                    const int64_t slot = a.ws[a.L.slots + it.start + n];
-                    if (MODE == kTcSwiglu) {
-                        if (j < I) {
-                            // kernels/moe_grouped.hip:508-524: from the FP32 accumulators, rounded once
-                            const uint16_t hb = f32_to_bf16_bits(silu_f32(v0[t]) * v1[t]);
-                            uint16_t *out = static_cast<uint16_t *>(a.out);
-                            out[slot * I + jpos] = a.out_f16 ? __half_as_ushort(__float2half_rn(bf16_bits_to_f32(hb))) : hb;
-                        }
-                    } else {
-                        const int64_t r0 = (int64_t)it.rb * kAThreads + row, r1 = r0 + 128;
+                    for (int t = 0; t < 16; ++t) {
+                        // kernels/moe_grouped.hip:508-524: from the FP32 accumulators, rounded once
+                        const uint16_t b = f32_to_bf16_bits(silu_f32(v0[t]) * v1[t]);
+                        stage_h[(c0 + t) * kEpiTokStride + row] = a.out_f16 ? __half_as_ushort(__float2half_rn(bf16_bits_to_f32(b))) : b;
+                    }
+                } else {
+                    const int64_t r0 = (int64_t)it.rb * kAThreads + row, r1 = r0 + 128;
+                    const int my_slot = c0 + (lane & 15) < it.cnt ? a.ws[a.L.slots + it.start + c0 + (lane & 15)] : 0;
+#pragma unroll
+                    for (int t = 0; t < 16; ++t) {
+                        const int64_t slot = __shfl_sync(0xffffffffu, my_slot, t);
+                        if (c0 + t >= it.cnt) break;
                         if (MODE == kTcPartial) {
                             float *out = static_cast<float *>(a.out);
                             if (r0 < a.N) out[slot * a.N + r0] = v0[t];
@@ -622,12 +716,33 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                     }
                 }
             }
-            if (warp == 0) PROF_ADD(10);
             if (valid) {
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                if (lane == 0) mbar_arrive(&acc_empty[0]);
             }
+            if (MODE == kTcSwiglu) {
+                __syncwarp();
+                const int tl = lane >> 2, g8 = warp * 32 + (lane & 3) * 8;  // token inside a pass of 8; first of 8 rows
+                const int64_t j = (int64_t)it.rb * 128 + g8;               // h columns j .. j + 7 (I % 8 == 0)
+                for (int n = tl; n < it.cnt && j < I; n += 8) {
+                    const uint4 hv = *reinterpret_cast<const uint4 *>(stage_h + n * kEpiTokStride + g8);
+                    uint4 o = hv;
+                    if (a.out_f16 == 2 || a.out_f16 == 3) {  // the Q4 operand's k order inside every 8: [0 4 1 5 2 6 3 7]
+                        o.x = __byte_perm(hv.x, hv.z, 0x5410), o.y = __byte_perm(hv.x, hv.z, 0x7632);
+                        o.z = __byte_perm(hv.y, hv.w, 0x5410), o.w = __byte_perm(hv.y, hv.w, 0x7632);
+                    }
+                    unsigned char *out = static_cast<unsigned char *>(a.out);
+                    if (a.out_f16 >= 3) {
+                        *reinterpret_cast<uint4 *>(out + tiled_offset(a.L.S, (int)(j >> 6), it.start + n, n, (int)((j & 63) >> 3))) = o;
+                    } else {
+                        const int64_t slot = a.ws[a.L.slots + it.start + n];
+                        *reinterpret_cast<uint4 *>(out + (slot * I + j) * 2) = o;
+                    }
+                }
+                __syncwarp();  // this warp's rows of the parking area are free for its next item
+            }
+            if (warp == 0) PROF_ADD(10);
         }
     }
 
@@ -647,6 +762,26 @@ __global__ void __launch_bounds__(256) stage_f16_kernel(const uint4 *__restrict_
         xh[i] = b_chunk<BITS>(x[i], false);
 }
 
+// x [M, K] BF16 -> the tile-blocked F16 form (tiled_offset) for the tiles of a grouping workspace: row pos of the
+// slot order holds the activation row of token slots[pos] / A, converted, in the operand's k order, swizzled for its place
+// in its tile.  One CTA per tile at a time.
+template <int BITS>
+__global__ void __launch_bounds__(256) stage_tiles_kernel(const uint16_t *__restrict__ x, const int32_t *__restrict__ ws,
+                                                          RouteWords L, int64_t A, int64_t K, unsigned char *__restrict__ xs) {
+    const int n_tiles = ws[3], chunks_per_row = (int)(K / 8);
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const int bucket = ws[L.t128_bucket + tile], start = ws[L.t128_start + tile];
+        const int cnt = min(kMaxTileTokens, ws[L.offsets + bucket + 1] - start);
+        if (bucket >= L.E) continue;
+        for (int idx = threadIdx.x; idx < cnt * chunks_per_row; idx += blockDim.x) {
+            const int n = idx / chunks_per_row, k8 = idx % chunks_per_row;
+            const int64_t tok = ws[L.slots + start + n] / A;
+            const uint4 v = *reinterpret_cast<const uint4 *>(x + tok * K + (int64_t)k8 * 8);
+            *reinterpret_cast<uint4 *>(xs + tiled_offset(L.S, k8 >> 3, start + n, n, k8 & 7)) = b_chunk<BITS>(v, false);
+        }
+    }
+}
+
 int check_tc(const char *fn, const void *x, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes, int64_t M,
              int64_t A, const void *out, int act) {
     SXB_CHECK(x != nullptr && out != nullptr && ws != nullptr && w != nullptr, fn, ": null pointer (x=", x, ", out=", out,
@@ -661,15 +796,17 @@ int check_tc(const char *fn, const void *x, const SxbQView *w, int64_t E, const 
               route_words(M, A, E).total * 4);
     SXB_CHECK(aligned16(w->q) && aligned16(x), fn, ": code array ", (const void *)w->q, " and input ", x,
               " must be 16-byte aligned");
-    SXB_CHECK(act == SXB_ACT_BF16 || act == SXB_ACT_F16_STAGED, fn,
-              ": the WMMA_F16 kernels take BF16 activations (or F16 ones staged by sxb_stage_f16), got ", act);
+    SXB_CHECK((w->N / E) % 16 == 0, fn, ": ", w->N / E, " rows an expert, the tcgen05 kernels store 8 rows (SwiGLU: 8 h columns) at a time");
+    SXB_CHECK(reinterpret_cast<uintptr_t>(out) % 16 == 0, fn, ": output ", out, " must be 16-byte aligned");
+    SXB_CHECK(act == SXB_ACT_BF16 || act == SXB_ACT_F16_STAGED || act == SXB_ACT_F16_TILED, fn,
+              ": the WMMA_F16 kernels take BF16 activations (or F16 ones staged by sxb_stage_f16 / sxb_stage_f16_tiles), got ", act);
     return SXB_OK;
 }
 
 // The status words of a launch live in the grouping workspace's header (words 5..7, zeroed by the pack).
 template <int BITS, int MODE>
 int launch_tc(const char *fn, const TcArgs &a, int64_t G, cudaStream_t st) {
-    const size_t smem = (size_t)kStages * kStageBytes + 1024;
+    const size_t smem = (size_t)kStages * kStageBytes + kEpiBytes + 1024;
     auto go = [&](auto kern) -> int {
         SXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn,
                  ": reserving shared memory");
@@ -695,7 +832,7 @@ int tc_gather_grouped(const char *fn, const void *x, const SxbQView *w, int64_t 
     TcArgs a{};
     a.x = static_cast<const uint16_t *>(x), a.q = w->q, a.scale = w->scale, a.minv = w->minv;
     a.N = N, a.K = w->K, a.A = A, a.E = E, a.ws = static_cast<const int32_t *>(ws), a.L = route_words(M, A, E);
-    a.out = y, a.x_kind = act == SXB_ACT_F16_STAGED ? 2 : 0, a.out_f16 = h_f16;
+    a.out = y, a.x_kind = act == SXB_ACT_F16_TILED ? 3 : act == SXB_ACT_F16_STAGED ? 2 : 0, a.out_f16 = h_f16;
     a.status = reinterpret_cast<uint32_t *>(const_cast<void *>(ws)) + 5;
     auto st = static_cast<cudaStream_t>(stream);
     int rc = swiglu ? launch_tc<BITS, kTcSwiglu>(fn, a, w->G, st) : launch_tc<BITS, kTcGather>(fn, a, w->G, st);
@@ -707,13 +844,14 @@ int tc_gather_grouped(const char *fn, const void *x, const SxbQView *w, int64_t 
 template <int BITS>
 int tc_partial_grouped(const char *fn, const void *h, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes, int64_t M,
                        int64_t A, float *partial, int act, int h_f16, sxb_stream_t stream) {
-    SXB_CHECK(h_f16 != 2 || BITS == 4, fn, ": h_f16 = 2 (the Q4 operand's k order) with a Q8 down weight");
+    SXB_CHECK((h_f16 != 2 && h_f16 != 3) || BITS == 4, fn, ": h_f16 = ", h_f16, " (the Q4 operand's k order) with a Q8 down weight");
+    SXB_CHECK(h_f16 != 4 || BITS == 8, fn, ": h_f16 = 4 (tile-blocked, natural k order) with a Q4 down weight");
     if (int rc = check_tc(fn, h, w, E, ws, ws_bytes, M, A, partial, act)) return rc;
     const int64_t N = w->N / E;
     TcArgs a{};
     a.x = static_cast<const uint16_t *>(h), a.q = w->q, a.scale = w->scale, a.minv = w->minv;
     a.N = N, a.K = w->K, a.A = A, a.E = E, a.ws = static_cast<const int32_t *>(ws), a.L = route_words(M, A, E);
-    a.out = partial, a.x_kind = h_f16, a.out_f16 = 0;
+    a.out = partial, a.x_kind = h_f16 >= 3 ? 3 : h_f16, a.out_f16 = 0;
     a.status = reinterpret_cast<uint32_t *>(const_cast<void *>(ws)) + 5;
     auto st = static_cast<cudaStream_t>(stream);
     if (int rc = launch_tc<BITS, kTcPartial>(fn, a, w->G, st)) return rc;
@@ -732,7 +870,33 @@ template int tc_partial_grouped<8>(const char *, const void *, const SxbQView *,
 
 }  // namespace sxb
 
+extern "C" int sxb_stage_f16_tiles(const void *x, const void *ws, size_t ws_bytes, int64_t M, int64_t A, int64_t E, int64_t K,
+                                   int bits, void *xs, sxb_stream_t stream) {
+    using namespace sxb;
+    SXB_CHECK(x != nullptr && ws != nullptr && xs != nullptr, "stage_f16_tiles: null pointer (x=", x, ", ws=", ws, ", xs=", xs, ")");
+    SXB_CHECK(M >= 1 && A >= 1 && A <= 64 && E >= 1 && E <= kMoeMaxExperts && M * A <= kMoeMaxSlots, "stage_f16_tiles: M = ", M,
+              ", A = ", A, ", E = ", E);
+    SXB_CHECK(K >= 64 && K % 64 == 0, "stage_f16_tiles: K = ", K, " must be a multiple of 64 (one 128-byte line per k-block)");
+    SXB_CHECK(bits == 4 || bits == 8, "stage_f16_tiles: k order of a ", bits, "-bit operand unsupported (4 or 8)");
+    SXB_CHECK(ws_bytes >= (size_t)route_words(M, A, E).total * 4, "stage_f16_tiles: workspace of ", ws_bytes, " bytes, needs ",
+              route_words(M, A, E).total * 4);
+    SXB_CHECK(aligned16(x) && aligned16(xs), "stage_f16_tiles: x and xs must be 16-byte aligned");
+    const RouteWords L = route_words(M, A, E);
+    const unsigned blocks = (unsigned)std::min<int64_t>(L.T128max, (int64_t)sm_count() * 4);
+    auto st = static_cast<cudaStream_t>(stream);
+    if (bits == 4)
+        stage_tiles_kernel<4><<<blocks, 256, 0, st>>>((const uint16_t *)x, (const int32_t *)ws, L, A, K, (unsigned char *)xs);
+    else
+        stage_tiles_kernel<8><<<blocks, 256, 0, st>>>((const uint16_t *)x, (const int32_t *)ws, L, A, K, (unsigned char *)xs);
+    SXB_CHECK_LAUNCH("stage_f16_tiles M=", M, " A=", A, " K=", K, " bits=", bits);
+    return SXB_OK;
+}
+
 #ifdef SXB_TC_PROF
+extern "C" __attribute__((visibility("default"))) int sxb_debug_tc_trace(long long *out) {
+    cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(long long) * 4 * 64 * 2);
+    return 0;
+}
 extern "C" __attribute__((visibility("default"))) int sxb_debug_tc_prof(unsigned long long *out, int reset) {
     cudaMemcpyFromSymbol(out, g_tc_prof, sizeof(unsigned long long) * 32);
     if (reset) {

@@ -62,7 +62,7 @@ extern "C" int sxb_linear_q4_experts_combine_grouped_noalloc(const void *h, cons
                                                              sxb_stream_t stream, const SxbMoeSharedAdd *shared, int h_f16) {
     const char *fn = "linear_q4_experts_combine_grouped_noalloc";
     SXB_CHECK(math_ok(math), fn, ": unknown math ", math);
-    SXB_CHECK(h_f16 >= 0 && h_f16 <= 2, fn, ": h_f16 = ", h_f16, ", expected 0, 1 or 2");
+    SXB_CHECK(h_f16 >= 0 && h_f16 <= 4, fn, ": h_f16 = ", h_f16, ", expected 0..4");
     SXB_CHECK(!h_f16 || (act == SXB_ACT_BF16 && math_is_f16(math)), fn, ": F16 h needs BF16 activations and a WMMA_F16 math");
     SXB_CHECK(h != nullptr && w != nullptr && ids != nullptr && coef != nullptr && y != nullptr && ws != nullptr, fn,
               ": null pointer (h=", h, ", ids=", (const void *)ids, ", coef=", (const void *)coef, ", y=", y, ", ws=", ws, ")");

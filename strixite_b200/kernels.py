@@ -33,6 +33,7 @@ class Act(enum.IntEnum):  # kernels/norm.hpp:20
     F32 = 0
     BF16 = 1
     F16_STAGED = 2  # not in the reference: F16 laid out by stage_f16 for a tensor-core operand
+    F16_TILED = 3   # not in the reference: the tile-blocked form made by stage_f16_tiles
 
 
 class MoeMath(enum.IntEnum):  # kernels/moe_grouped.hpp:39
@@ -242,6 +243,11 @@ def report_expert_error(e, what: str):
 def stage_f16(x, M, K, bits, xh, stream=None):
     """x [M, K] BF16 -> xh [M, K] F16 in the k order of a `bits`-bit tensor-core weight operand."""
     _check(_lib.load().sxb_stage_f16(_ptr(x), M, K, bits, _ptr(xh), _stream(stream)))
+
+
+def stage_f16_tiles(x, ws, ws_bytes, M, A, E, K, bits, xs, stream=None):
+    """x [M, K] BF16 -> xs, the tile-blocked F16 operand form for the tiles of grouping workspace ws."""
+    _check(_lib.load().sxb_stage_f16_tiles(_ptr(x), _ptr(ws), ws_bytes, M, A, E, K, bits, _ptr(xs), _stream(stream)))
 
 
 # ---- kernels/swiglu.hpp ---------------------------------------------------------------------------------------

@@ -51,9 +51,8 @@ class MoeBuffers:
         self.ws = torch.empty(self.ws_bytes // 4, dtype=torch.int32, device=dev)
         self.h = torch.empty((S, I), dtype=torch.bfloat16, device=dev)
         self.partial = torch.empty((S, d), dtype=torch.float32, device=dev)
-        self.xh4 = torch.empty((T, d), dtype=torch.float16, device=dev)  # x staged for Q4 operands (tcgen05 path)
-        self.xh8 = torch.empty((T, d), dtype=torch.float16, device=dev)  # x staged for Q8 operands
-        self.staged = {4: False, 8: False}
+        self.tiled_x = None     # x in tile-blocked F16 form for the routed experts (tcgen05 path), made on first use
+        self.tiled_x_sh = None  # the same for the shared expert's single bucket
         self.router_err = torch.zeros(4, dtype=torch.int32, device=dev)
         self.expert_err = torch.zeros(4, dtype=torch.int32, device=dev)
         if shared:
@@ -112,22 +111,14 @@ class MoeLayer:
         if b.sh_ws_tokens != T:
             K.moe_group_routes(b.sh_ids, T, 1, 1, b.sh_ws, b.sh_ws_bytes, b.expert_err)
             b.sh_ws_tokens = T
-        xs = self.staged_x(x, T, w.shared_gate_up.bits)
-        hf = 2 if w.shared_down.bits == 4 else 1
-        K.linear_qw_experts_gather_grouped_swiglu(xs, w.shared_gate_up, 1, b.sh_ws, b.sh_ws_bytes, T, 1, b.sh_h,
-                                                  Act.F16_STAGED, math, h_f16=hf)
+        if b.tiled_x_sh is None:
+            b.tiled_x_sh = torch.empty((b.max_tokens, self.d), dtype=torch.float16, device=x.device)
+        K.stage_f16_tiles(x, b.sh_ws, b.sh_ws_bytes, T, 1, 1, self.d, w.shared_gate_up.bits, b.tiled_x_sh)
+        hf = 3 if w.shared_down.bits == 4 else 4
+        K.linear_qw_experts_gather_grouped_swiglu(b.tiled_x_sh, w.shared_gate_up, 1, b.sh_ws, b.sh_ws_bytes, T, 1, b.sh_h,
+                                                  Act.F16_TILED, math, h_f16=hf)
         K.linear_qw_experts_combine_grouped(b.sh_h, w.shared_down, 1, b.sh_ids, b.sh_coef, b.sh_ws, b.sh_ws_bytes,
                                             b.sh_partial, T, 1, out, Act.BF16, math, out_act=out_act, h_f16=hf)
-
-    def staged_x(self, x: torch.Tensor, T: int, bits: int) -> torch.Tensor:
-        """The F16 copy of x in the k order of a `bits`-bit operand, made once per forward and shared by the routed and
-        the shared experts' gate/up GEMMs of that bit width."""
-        b = self.buf
-        xh = b.xh4 if bits == 4 else b.xh8
-        if not b.staged[bits]:
-            K.stage_f16(x, T, self.d, bits, xh)
-            b.staged[bits] = True
-        return xh
 
     def experts(self, x: torch.Tensor, T: int, y: torch.Tensor, math: MoeMath, gate_logit=None, gate_ld: int = 0,
                 shared_out: Optional[torch.Tensor] = None, events=None):
@@ -142,10 +133,14 @@ class MoeLayer:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
         tc = K_is_f16(math)
-        hf = (2 if w.down.bits == 4 else 1) if tc else 0
+        hf = (3 if w.down.bits == 4 else 4) if tc else 0
         if tc:
-            K.linear_qw_experts_gather_grouped_swiglu(self.staged_x(x, T, w.gate_up.bits), w.gate_up, self.E, b.ws, b.ws_bytes,
-                                                      T, A, b.h, Act.F16_STAGED, math, h_f16=hf)
+            # x gathered into the tile-blocked F16 form once; every row block of every tile then bulk-copies its operand
+            if b.tiled_x is None:
+                b.tiled_x = torch.empty((b.max_tokens * A, self.d), dtype=torch.float16, device=x.device)
+            K.stage_f16_tiles(x, b.ws, b.ws_bytes, T, A, self.E, self.d, w.gate_up.bits, b.tiled_x)
+            K.linear_qw_experts_gather_grouped_swiglu(b.tiled_x, w.gate_up, self.E, b.ws, b.ws_bytes, T, A, b.h,
+                                                      Act.F16_TILED, math, h_f16=hf)
         else:
             K.linear_qw_experts_gather_grouped_swiglu(x, w.gate_up, self.E, b.ws, b.ws_bytes, T, A, b.h, Act.BF16, math)
         if events is not None:
@@ -168,7 +163,6 @@ class MoeLayer:
         T = x.shape[0]
         assert T <= self.buf.max_tokens and x.dtype == torch.bfloat16 and logits.dtype == torch.float32
         math = self.math_for(T, math)
-        self.new_input()
         self.route(logits, T)
         if self.w.shared_gate_up is not None and not self.ep:
             sh = self.buf.sh_y32 if y.dtype == torch.float32 else self.buf.sh_y
@@ -178,10 +172,6 @@ class MoeLayer:
         else:
             self.experts(x, T, y, math)
         return y
-
-    def new_input(self):
-        """Call when x changes (forward does): the staged F16 copies of the previous x are stale."""
-        self.buf.staged = {4: False, 8: False}
 
     def check_errors(self, what: str = "moe layer"):
         """Blocking: the reference's read_back of the error words (runtime/qwen4exp.cpp:2391-2404)."""

@@ -260,12 +260,52 @@ def test_grouped_experts_tcgen05(cuda, oracle, bits, G, M, A, E, I, d):
     K.check_grouped_status(ws, "tcgen05 staged gather")
     want_hs = hf.view(M * A, I // 8, 8)[:, :, PERM].reshape(M * A, I) if hk == 2 else hf
     assert torch.equal(hs[okd].view(torch.int16), want_hs[okd].view(torch.int16))
+    # the tile-blocked form: x gathered by stage_f16_tiles, h written tile-blocked; same values again
+    xt = torch.zeros((M * A, d), dtype=torch.float16, device=cuda)
+    K.stage_f16_tiles(xd, ws, nbytes, M, A, E, d, bits, xt)
+    ht = torch.zeros((M * A, I), dtype=torch.float16, device=cuda)
+    K.linear_qw_experts_gather_grouped_swiglu(xt, gud, E, ws, nbytes, M, A, ht, K.Act.F16_TILED, K.MoeMath.WmmaF16,
+                                              h_f16=3 if bits == 4 else 4)
+    torch.cuda.synchronize()
+    K.check_grouped_status(ws, "tcgen05 tiled gather")
+
+    def untile(buf, width):
+        """Tile-blocked [S, width] F16 -> natural [slot, width] (host-side inverse of the layout, for checking)."""
+        L = K.route_layout(M, A, E)
+        w_ = ws.cpu().numpy()
+        offs, slots_ = w_[L["offsets"]:L["offsets"] + E + 2], w_[L["slots"]:L["slots"] + M * A]
+        raw = buf.cpu().numpy().view(np.uint16).reshape(-1)
+        out = np.zeros((M * A, width), dtype=np.uint16)
+        S = M * A
+        for b in range(E):
+            for pos in range(int(offs[b]), int(offs[b + 1])):
+                n = (pos - int(offs[b])) % 128
+                for kb in range(width // 64):
+                    line = raw[((kb * S + pos) * 128) // 2:((kb * S + pos) * 128) // 2 + 64].reshape(8, 8)
+                    for c in range(8):
+                        chunk = line[c ^ (n & 7)]
+                        out[slots_[pos], kb * 64 + c * 8:kb * 64 + c * 8 + 8] = chunk[np.argsort(PERM)] if bits == 4 else chunk
+        return torch.from_numpy(out.view(np.float16)).to(cuda)
+
+    assert torch.equal(untile(ht, I)[okd].view(torch.int16), hf[okd].view(torch.int16))
     # down + combine on the oracle's h (identical inputs on both sides), from BF16 h and from F16 h
     y_ref, p_ref = oracle.experts_combine(h_ref.reshape(M, A, I), dn, E, ids, coef, out_act=oracle.F32, want_partial=True,
                                           w_f16=True)
     rows = [m for m in range(M) if m != 5]
-    for f16 in (0, 1, 2):
+    for f16 in (0, 1, 2, 34):
         if f16 == 2 and bits != 4:
+            continue
+        if f16 == 34:  # tile-blocked h as the tiled gather leaves it, from the GPU's own h (== oracle h up to rare flips)
+            partial = torch.zeros((M * A, d), dtype=torch.float32, device=cuda)
+            y = torch.empty((M, d), dtype=torch.float32, device=cuda)
+            K.linear_qw_experts_combine_grouped(ht, dnd, E, idd, cfd, ws, nbytes, partial, M, A, y, K.Act.BF16, K.MoeMath.WmmaF16,
+                                                out_act=K.Act.F16_TILED if False else K.Act.F32, h_f16=3 if bits == 4 else 4)
+            y2 = torch.empty((M, d), dtype=torch.float32, device=cuda)
+            K.linear_qw_experts_combine_grouped(hf, dnd, E, idd, cfd, ws, nbytes, partial, M, A, y2, K.Act.BF16, K.MoeMath.WmmaF16,
+                                                out_act=K.Act.F32, h_f16=1)
+            torch.cuda.synchronize()
+            K.check_grouped_status(ws, "tcgen05 tiled combine")
+            assert torch.equal(y[rows], y2[rows])  # the same values through the bulk-copy path and the per-row path
             continue
         hd = bf16_tensor(h_ref, cuda)
         if f16:
