@@ -170,13 +170,7 @@ class Stack:
             self.buf.coef.copy_(coef_all)
         math = layer.math_for(T, self.math)
         y = self.y_part[:T]
-        if self.cfg.shared and self.world == 1:
-            sh = self.buf.sh_y32
-            layer.shared_expert(x_all, T, math, sh)
-            gate = self.logits.data_ptr() + 4 * self.cfg.E
-            layer.experts(x_all, T, y, math, gate_logit=gate, gate_ld=self.logits.stride(0), shared_out=sh, events=self.events)
-        else:
-            layer.experts(x_all, T, y, math, events=self.events)
+        layer.run_experts(x_all, T, y, math, self.logits, events=self.events)
         return y
 
     def step(self, x_loc):

@@ -59,10 +59,10 @@ constexpr int kStageBytes = kBBytes;                // shared memory per stage (
 constexpr int kTmemCols = 512;
 constexpr int kAccCols = kMaxTileTokens;
 constexpr int kAStageCol0 = 2 * kAccCols, kAStageCols = 2 * (kBK / 2);
-// SwiGLU epilogue parking area in shared memory: 16-bit h values [token][row], token stride padded to 136 (272 bytes:
-// 16-byte aligned rows, and neighbouring tokens start in different banks).
-constexpr int kEpiTokStride = 136;
-constexpr int kEpiBytes = kMaxTileTokens * kEpiTokStride * 2;
+// Epilogue staging in shared memory: FP32 [accumulator][token][row], token stride padded to 132 words so that the drain
+// (lane = row) and the read-back (8 consecutive rows of a token per thread) are both free of bank conflicts.
+constexpr int kEpiTokStride = 132;
+constexpr int kEpiBytes = 2 * kMaxTileTokens * kEpiTokStride * 4;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any legitimate wait
 
 enum TcMode { kTcGather = 0, kTcSwiglu = 1, kTcPartial = 2 };
@@ -636,6 +636,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                             tc_mma_f16_ts(d, at + j * 8, smem_desc(sb_ + j * 32), idesc, (kb | j) != 0);
                         }
                     }
+                    PROF_ADD(20);
                     tc_commit(&empty_bar[stage]);                    // frees the stage when these MMAs have read it
                     if (kb == n_kb - 1) tc_commit(&acc_full[0]);     // and hands the accumulators to the epilogue
                 }
@@ -652,18 +653,16 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
         __syncwarp();
     } else {
         // ===================== epilogue =====================
-        // Lane = weight row of a 128-row accumulator.  Gather / partial outputs leave straight from the registers: for
-        // one token a warp's 32 lanes hold 32 consecutive rows, one coalesced store.  SwiGLU: h = silu(g) * u is formed
-        // here (gate and up row j sit in the same lane of the two accumulators), parked as 16-bit values in shared
-        // memory [token][row], tensor memory is handed back, and then every thread takes one token x 8 consecutive
-        // columns of its own warp's rows and stores them as one 16-byte chunk in the layout the down GEMM wants.
+        // Phase 1 (lane = weight row): the finished accumulators are drained from tensor memory into shared memory
+        // [accumulator][token][row] and tensor memory is handed back at once - the next item's MMAs run under phase 2.
+        // Phase 2: a thread takes one token x 8 consecutive rows, all inside its own warp's 32 rows (no cross-warp
+        // dependency): SwiGLU / rounding, then one 16-byte (h, y) or two 16-byte (FP32 partial) stores.
         uint32_t acc_count = 0;
         const int64_t I = a.N / 2;
-        uint16_t *stage_h = reinterpret_cast<uint16_t *>(smem + kStages * kStageBytes);
+        float *stage_f = reinterpret_cast<float *>(smem + kStages * kStageBytes);
         for (int item = blockIdx.x; item < n_items && !*abort_v; item += gridDim.x) {
             const ItemInfo it = item_info<MODE>(a, item, rbs);
             const bool valid = it.bucket < a.E;
-            const int row = warp * 32 + lane;
             if (valid) {
                 const uint32_t acc_phase = acc_count & 1u;
                 ++acc_count;
@@ -678,59 +677,52 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                 __syncwarp();
                 if (*abort_v) break;
                 tc_fence_after();
-            }
-            PROF_BEGIN();
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-            for (int c0 = 0; c0 < it.cnt; c0 += 16) {
-                float v0[16], v1[16];
-                if (valid) {
-                    tc_ld16(lane_addr + (uint32_t)(c0), v0);
-                    tc_ld16(lane_addr + (uint32_t)(kAccCols + c0), v1);
-                } else {
+                const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+                for (int c0 = 0; c0 < it.cnt; c0 += 16) {
 #pragma unroll
-                    for (int t = 0; t < 16; ++t) v0[t] = v1[t] = qnan_f32();
-                }
-                if (MODE == kTcSwiglu) {
+                    for (int half = 0; half < 2; ++half) {
+                        float v[16];
+                        tc_ld16(lane_addr + (uint32_t)(half * kAccCols + c0), v);
+                        float *dst = stage_f + ((size_t)half * kMaxTileTokens + c0) * kEpiTokStride + warp * 32 + lane;
 #pragma unroll
-                    for (int t = 0; t < 16; ++t) {
-                        // kernels/moe_grouped.hip:508-524: from the FP32 accumulators, rounded once
-                        const uint16_t b = f32_to_bf16_bits(silu_f32(v0[t]) * v1[t]);
-                        stage_h[(c0 + t) * kEpiTokStride + row] = a.out_f16 ? __half_as_ushort(__float2half_rn(bf16_bits_to_f32(b))) : b;
-                    }
-                } else {
-                    const int64_t r0 = (int64_t)it.rb * kAThreads + row, r1 = r0 + 128;
-                    const int my_slot = c0 + (lane & 15) < it.cnt ? a.ws[a.L.slots + it.start + c0 + (lane & 15)] : 0;
-#pragma unroll
-                    for (int t = 0; t < 16; ++t) {
-                        const int64_t slot = __shfl_sync(0xffffffffu, my_slot, t);
-                        if (c0 + t >= it.cnt) break;
-                        if (MODE == kTcPartial) {
-                            float *out = static_cast<float *>(a.out);
-                            if (r0 < a.N) out[slot * a.N + r0] = v0[t];
-                            if (r1 < a.N) out[slot * a.N + r1] = v1[t];
-                        } else {
-                            uint16_t *out = static_cast<uint16_t *>(a.out);
-                            if (r0 < a.N) out[slot * a.N + r0] = f32_to_bf16_bits(v0[t]);
-                            if (r1 < a.N) out[slot * a.N + r1] = f32_to_bf16_bits(v1[t]);
-                        }
+                        for (int t = 0; t < 16; ++t) dst[t * kEpiTokStride] = v[t];
                     }
                 }
-            }
-            if (valid) {
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[0]);
             }
-            if (MODE == kTcSwiglu) {
-                __syncwarp();
-                const int tl = lane >> 2, g8 = warp * 32 + (lane & 3) * 8;  // token inside a pass of 8; first of 8 rows
-                const int64_t j = (int64_t)it.rb * 128 + g8;               // h columns j .. j + 7 (I % 8 == 0)
-                for (int n = tl; n < it.cnt && j < I; n += 8) {
-                    const uint4 hv = *reinterpret_cast<const uint4 *>(stage_h + n * kEpiTokStride + g8);
-                    uint4 o = hv;
+            PROF_BEGIN();
+            const int tl = lane >> 2, g8 = (warp * 32) + (lane & 3) * 8;  // token inside a pass of 8, first of 8 rows
+            for (int n = tl; n < it.cnt; n += 8) {
+                float r0[8], r1[8];
+                if (valid) {
+                    const float4 *p0 = reinterpret_cast<const float4 *>(stage_f + (size_t)n * kEpiTokStride + g8);
+                    const float4 *p1 = reinterpret_cast<const float4 *>(stage_f + ((size_t)kMaxTileTokens + n) * kEpiTokStride + g8);
+                    const float4 x0 = p0[0], x1 = p0[1], y0 = p1[0], y1 = p1[1];
+                    r0[0] = x0.x, r0[1] = x0.y, r0[2] = x0.z, r0[3] = x0.w, r0[4] = x1.x, r0[5] = x1.y, r0[6] = x1.z, r0[7] = x1.w;
+                    r1[0] = y0.x, r1[1] = y0.y, r1[2] = y0.z, r1[3] = y0.w, r1[4] = y1.x, r1[5] = y1.y, r1[6] = y1.z, r1[7] = y1.w;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) r0[i] = r1[i] = qnan_f32();
+                }
+                if (MODE == kTcSwiglu) {
+                    const int64_t j = (int64_t)it.rb * 128 + g8;  // h columns j .. j + 7 (I is a multiple of 8)
+                    if (j >= I) continue;
+                    uint16_t hb[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        // kernels/moe_grouped.hip:508-524: from the FP32 accumulators, rounded once
+                        const uint16_t b = f32_to_bf16_bits(silu_f32(r0[i]) * r1[i]);
+                        hb[i] = a.out_f16 ? __half_as_ushort(__float2half_rn(bf16_bits_to_f32(b))) : b;
+                    }
+                    uint4 o;
                     if (a.out_f16 == 2 || a.out_f16 == 3) {  // the Q4 operand's k order inside every 8: [0 4 1 5 2 6 3 7]
-                        o.x = __byte_perm(hv.x, hv.z, 0x5410), o.y = __byte_perm(hv.x, hv.z, 0x7632);
-                        o.z = __byte_perm(hv.y, hv.w, 0x5410), o.w = __byte_perm(hv.y, hv.w, 0x7632);
+                        o.x = hb[0] | ((uint32_t)hb[4] << 16), o.y = hb[1] | ((uint32_t)hb[5] << 16);
+                        o.z = hb[2] | ((uint32_t)hb[6] << 16), o.w = hb[3] | ((uint32_t)hb[7] << 16);
+                    } else {
+                        o.x = hb[0] | ((uint32_t)hb[1] << 16), o.y = hb[2] | ((uint32_t)hb[3] << 16);
+                        o.z = hb[4] | ((uint32_t)hb[5] << 16), o.w = hb[6] | ((uint32_t)hb[7] << 16);
                     }
                     unsigned char *out = static_cast<unsigned char *>(a.out);
                     if (a.out_f16 >= 3) {
@@ -739,9 +731,29 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                         const int64_t slot = a.ws[a.L.slots + it.start + n];
                         *reinterpret_cast<uint4 *>(out + (slot * I + j) * 2) = o;
                     }
+                } else {
+                    const int64_t slot = a.ws[a.L.slots + it.start + n];
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const int64_t r = (int64_t)it.rb * kAThreads + half * 128 + g8;  // rows r .. r + 7 (N % 8 == 0)
+                        const float *v = half ? r1 : r0;
+                        if (r >= a.N) continue;
+                        if (MODE == kTcPartial) {
+                            float4 *o = reinterpret_cast<float4 *>(static_cast<float *>(a.out) + slot * a.N + r);
+                            o[0] = make_float4(v[0], v[1], v[2], v[3]);
+                            o[1] = make_float4(v[4], v[5], v[6], v[7]);
+                        } else {
+                            uint4 o;
+                            o.x = f32_to_bf16_bits(v[0]) | ((uint32_t)f32_to_bf16_bits(v[1]) << 16);
+                            o.y = f32_to_bf16_bits(v[2]) | ((uint32_t)f32_to_bf16_bits(v[3]) << 16);
+                            o.z = f32_to_bf16_bits(v[4]) | ((uint32_t)f32_to_bf16_bits(v[5]) << 16);
+                            o.w = f32_to_bf16_bits(v[6]) | ((uint32_t)f32_to_bf16_bits(v[7]) << 16);
+                            *reinterpret_cast<uint4 *>(static_cast<uint16_t *>(a.out) + slot * a.N + r) = o;
+                        }
+                    }
                 }
-                __syncwarp();  // this warp's rows of the parking area are free for its next item
             }
+            __syncwarp();  // this warp's rows of the staging area are free for its next drain
             if (warp == 0) PROF_ADD(10);
         }
     }

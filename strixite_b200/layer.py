@@ -51,6 +51,7 @@ class MoeBuffers:
         self.ws = torch.empty(self.ws_bytes // 4, dtype=torch.int32, device=dev)
         self.h = torch.empty((S, I), dtype=torch.bfloat16, device=dev)
         self.partial = torch.empty((S, d), dtype=torch.float32, device=dev)
+        self.side_stream = None  # second stream for the shared expert in the decode regime (made on first use)
         self.tiled_x = None     # x in tile-blocked F16 form for the routed experts (tcgen05 path), made on first use
         self.tiled_x_sh = None  # the same for the shared expert's single bucket
         self.router_err = torch.zeros(4, dtype=torch.int32, device=dev)
@@ -121,7 +122,7 @@ class MoeLayer:
                                             b.sh_partial, T, 1, out, Act.BF16, math, out_act=out_act, h_f16=hf)
 
     def experts(self, x: torch.Tensor, T: int, y: torch.Tensor, math: MoeMath, gate_logit=None, gate_ld: int = 0,
-                shared_out: Optional[torch.Tensor] = None, events=None):
+                shared_out: Optional[torch.Tensor] = None, events=None, before_combine=None):
         """pack -> gate/up + SwiGLU -> down + combine into y [T, d] (BF16 or FP32), ids / coef already in the buffers."""
         b, w, A = self.buf, self.w, self.k
         out_act = Act.F32 if y.dtype == torch.float32 else Act.BF16
@@ -147,6 +148,8 @@ class MoeLayer:
             e1.record()
             events[0].append(e0)
             events[1].append(e1)
+        if before_combine is not None:
+            before_combine()
         if self.ep:
             K.linear_qw_experts_combine_grouped_ep(b.h, w.down, self.E, self.E_total, self.e_lo, b.ids, b.coef, b.ws,
                                                    b.ws_bytes, b.partial, T, A, y, Act.BF16, math, out_act=out_act, h_f16=hf)
@@ -164,13 +167,33 @@ class MoeLayer:
         assert T <= self.buf.max_tokens and x.dtype == torch.bfloat16 and logits.dtype == torch.float32
         math = self.math_for(T, math)
         self.route(logits, T)
-        if self.w.shared_gate_up is not None and not self.ep:
-            sh = self.buf.sh_y32 if y.dtype == torch.float32 else self.buf.sh_y
+        return self.run_experts(x, T, y, math, logits)
+
+    def run_experts(self, x: torch.Tensor, T: int, y: torch.Tensor, math: MoeMath, logits: torch.Tensor, events=None):
+        """Everything after the router: shared expert, pack, routed experts, combine (+ gated shared add)."""
+        if self.w.shared_gate_up is None or self.ep:
+            self.experts(x, T, y, math, events=events)
+            return y
+        b = self.buf
+        sh = b.sh_y32 if y.dtype == torch.float32 else b.sh_y
+        gate = logits.data_ptr() + 4 * self.E_total
+        if K_is_f16(math):
             self.shared_expert(x, T, math, sh)
-            gate = logits.data_ptr() + 4 * self.E_total
-            self.experts(x, T, y, math, gate_logit=gate, gate_ld=logits.stride(0), shared_out=sh)
-        else:
-            self.experts(x, T, y, math)
+            self.experts(x, T, y, math, gate_logit=gate, gate_ld=logits.stride(0), shared_out=sh, events=events)
+            return y
+        # Decode: the shared expert's three small launches run on a second stream under the routed experts' weight
+        # streaming (they leave most SMs idle on their own) and are joined just before the combine that adds them.
+        cur = torch.cuda.current_stream()
+        if b.side_stream is None:
+            b.side_stream = torch.cuda.Stream(device=x.device)
+            b.ev_fork, b.ev_join = torch.cuda.Event(), torch.cuda.Event()
+        b.ev_fork.record(cur)
+        b.side_stream.wait_event(b.ev_fork)
+        with torch.cuda.stream(b.side_stream):
+            self.shared_expert(x, T, math, sh)
+            b.ev_join.record(b.side_stream)
+        self.experts(x, T, y, math, gate_logit=gate, gate_ld=logits.stride(0), shared_out=sh, events=events,
+                     before_combine=lambda: cur.wait_event(b.ev_join))
         return y
 
     def check_errors(self, what: str = "moe layer"):
