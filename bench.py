@@ -152,7 +152,7 @@ class Stack:
 
     def _route(self, l, x_loc):
         from strixite_b200 import kernels as K, workloads as W
-        logits = W.router_logits(x_loc, self.wr[l], self.bias[l])
+        logits = W.router_logits(x_loc, self.wr[l], self.bias[l], tf32=x_loc.shape[0] >= 256)
         self.logits = logits
         t = x_loc.shape[0]
         if self.world == 1:
@@ -436,7 +436,7 @@ def main():
         "data": "synthetic",
         "config": {"workload": cfg.name, "T": cfg.T, "layers": res["layers"], "hidden": cfg.d, "experts": cfg.E,
                    "experts_per_gpu": cfg.E // world, "top_k": cfg.k, "intermediate": cfg.I, "gate_up": f"q{cfg.gu_bits}g{cfg.group(cfg.gu_bits)}",
-                   "down": f"q{cfg.dn_bits}g{cfg.group(cfg.dn_bits)}", "shared_expert": cfg.shared, "expert_bias": cfg.bias,
+                   "down": f"q{cfg.dn_bits}g{cfg.group(cfg.dn_bits)}", "shared_expert": cfg.shared, "expert_bias": cfg.bias, "router_projection": "cuBLAS " + ("tf32" if cfg.T // world >= 256 else "fp32") + " (torch.matmul), inside the timed step",
                    "parallelism": f"ep{world}", "value_is": "T * layers / step time",
                    "l2": "weights resident per step exceed L2 (126 MB): %.1f GB on this rank" % (res["stack"].weight_bytes / 1e9)},
         "clocks": res["clocks"], "gpu_launches": res["launches"],

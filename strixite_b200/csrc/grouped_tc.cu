@@ -43,10 +43,13 @@ __device__ long long g_tc_trace[4][64][2];  // role (A, B, MMA, -), k-block inde
 namespace sxb {
 namespace {
 
-constexpr int kEpiWarps = 4, kMmaWarp = 4, kFirstAWarp = 5, kAWarps = 8, kFirstBWarp = kFirstAWarp + kAWarps, kBWarps = 2;
-constexpr int kThreads = 32 * (kFirstBWarp + kBWarps);  // 480
+// warps 0-3 epilogue, 4-5 MMA issue (one per accumulator), 6-13 weight producers, 14-15 activation producers
+constexpr int kEpiWarps = 4, kMmaWarp = 4, kMmaWarps = 2, kFirstAWarp = kMmaWarp + kMmaWarps, kAWarps = 8,
+              kFirstBWarp = kFirstAWarp + kAWarps, kBWarps = 2;
+constexpr int kThreads = 32 * (kFirstBWarp + kBWarps);  // 512
 constexpr int kAThreads = 32 * kAWarps;                 // 256 = weight rows per item
 constexpr int kProducers = kAThreads;
+constexpr int kBPrefetch = 12;                          // k-blocks of tile-blocked activations pulled into L2 ahead of their copy
 constexpr int kBAhead = 2;                              // k-blocks of activations in flight (cp.async groups)
 constexpr int kBK = 64;                                               // k per stage: one 128-byte swizzle line of F16
 constexpr int kMaxTileTokens = 128;
@@ -311,9 +314,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
     volatile int *abort_v = &abort_flag;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], kAWarps + (a.x_kind == 3 ? 1 : kBWarps)), mbar_init(&empty_bar[s], 1);
-        mbar_init(&acc_full[0], 1), mbar_init(&acc_empty[0], kEpiWarps);
-        mbar_init(&drain_bar, 1);
+        for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], kAWarps + (a.x_kind == 3 ? 1 : kBWarps)), mbar_init(&empty_bar[s], kMmaWarps);
+        mbar_init(&acc_full[0], kMmaWarps), mbar_init(&acc_empty[0], kEpiWarps);
+        mbar_init(&drain_bar, kMmaWarps);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -485,13 +488,25 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
             // Tile-blocked activations: one thread, one bulk copy per k-block, completion counted in bytes on the
             // stage's barrier; every free stage is refilled at once, so kStages k-blocks are in flight.
             if (warp == kFirstBWarp && lane == 0) {
+                // A second cursor runs kBPrefetch k-blocks ahead of the copies (across items) and pulls those runs into
+                // L2, so a copy issued the moment its stage frees up is an L2 hit, not a DRAM round trip.
                 uint32_t it_count = 0;
+                int p_item = next_valid_item<MODE>(a, blockIdx.x, n_items, rbs), p_kb = 0;
+                auto prefetch_next = [&]() {
+                    if (p_item >= n_items) return;
+                    const ItemInfo pi = item_info<MODE>(a, p_item, rbs);
+                    const unsigned char *src = reinterpret_cast<const unsigned char *>(a.x) + ((int64_t)p_kb * a.L.S + pi.start) * 128;
+                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"((uint32_t)pi.cnt * 128u) : "memory");
+                    if (++p_kb == n_kb) p_kb = 0, p_item = next_valid_item<MODE>(a, p_item + gridDim.x, n_items, rbs);
+                };
+                for (int i = 0; i < kBPrefetch; ++i) prefetch_next();
                 for (int item = next_valid_item<MODE>(a, blockIdx.x, n_items, rbs); item < n_items && !*abort_v;
                      item = next_valid_item<MODE>(a, item + gridDim.x, n_items, rbs)) {
                     const ItemInfo it = item_info<MODE>(a, item, rbs);
                     const uint32_t bytes = (uint32_t)it.cnt * 128u;
                     const unsigned char *src = reinterpret_cast<const unsigned char *>(a.x) + (int64_t)it.start * 128;
                     for (int kb = 0; kb < n_kb; ++kb, ++it_count) {
+                        prefetch_next();
                         const int stage = it_count % kStages;
                         if (!mbar_wait(&empty_bar[stage], ((it_count / kStages) & 1u) ^ 1u, abort_v)) {
                             raise_abort(item, 5);
@@ -589,8 +604,11 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
             it_count += n_kb;
         }
         }
-    } else if (warp == kMmaWarp) {
+    } else if (warp >= kMmaWarp) {
         // ===================== MMA issue =====================
+        // Two issuing warps, one per accumulator: each instruction costs its issuing thread far more than an N <= 128
+        // MMA's arithmetic, so the two halves are issued side by side; a stage is free when both have committed.
+        const int half = warp - kMmaWarp;
         uint32_t it_count = 0, acc_count = 0;
         for (int item = blockIdx.x; item < n_items && !*abort_v; item += gridDim.x) {
             const ItemInfo it = item_info<MODE>(a, item, rbs);
@@ -600,7 +618,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
             {
                 PROF_BEGIN();
                 if (lane == 0 && !mbar_wait(&acc_empty[0], acc_phase ^ 1u, abort_v)) raise_abort(item, 2);
-                PROF_ADD(7);
+                if (half == 0) PROF_ADD(7);
             }
             __syncwarp();
             if (*abort_v) break;
@@ -613,9 +631,11 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                 {
                     PROF_BEGIN();
                     if (lane == 0 && !mbar_wait(&full_bar[stage], phase, abort_v)) raise_abort(item, 3);
-                    PROF_ADD(5);
-                    PROF_COUNT(8);
-                    TRACE(2, it_count, 0);
+                    if (half == 0) {
+                        PROF_ADD(5);
+                        PROF_COUNT(8);
+                        TRACE(2, it_count, 0);
+                    }
                 }
                 __syncwarp();
                 if (*abort_v) break;
@@ -623,25 +643,18 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                 PROF_BEGIN();
                 if (lane == 0) {
                     const uint32_t sb_ = smem_u32(smem + stage * kStageBytes);
-                    // the two accumulators alternate, so consecutive instructions never depend on each other
+                    const uint32_t d = tmem_base + (uint32_t)(half * kAccCols);
+                    const uint32_t at = tmem_base + (uint32_t)(kAStageCol0 + stage * kAStageCols + half * (kBK / 2));
 #pragma unroll
-                    for (int j = 0; j < kBK / 16; ++j) {
-#ifdef SXB_TC_EXP_SKIP
-                        if (j >= 2) break;  // timing experiment only: half of the instructions, wrong results
-#endif
-#pragma unroll
-                        for (int half = 0; half < 2; ++half) {
-                            const uint32_t d = tmem_base + (uint32_t)(half * kAccCols);
-                            const uint32_t at = tmem_base + (uint32_t)(kAStageCol0 + stage * kAStageCols + half * (kBK / 2));
-                            tc_mma_f16_ts(d, at + j * 8, smem_desc(sb_ + j * 32), idesc, (kb | j) != 0);
-                        }
-                    }
-                    PROF_ADD(20);
+                    for (int j = 0; j < kBK / 16; ++j) tc_mma_f16_ts(d, at + j * 8, smem_desc(sb_ + j * 32), idesc, (kb | j) != 0);
+                    if (half == 0) PROF_ADD(20);
                     tc_commit(&empty_bar[stage]);                    // frees the stage when these MMAs have read it
                     if (kb == n_kb - 1) tc_commit(&acc_full[0]);     // and hands the accumulators to the epilogue
                 }
-                PROF_ADD(6);
-                TRACE(2, it_count, 1);
+                if (half == 0) {
+                    PROF_ADD(6);
+                    TRACE(2, it_count, 1);
+                }
                 __syncwarp();
             }
         }
@@ -785,11 +798,24 @@ __global__ void __launch_bounds__(256) stage_tiles_kernel(const uint16_t *__rest
         const int bucket = ws[L.t128_bucket + tile], start = ws[L.t128_start + tile];
         const int cnt = min(kMaxTileTokens, ws[L.offsets + bucket + 1] - start);
         if (bucket >= L.E) continue;
-        for (int idx = threadIdx.x; idx < cnt * chunks_per_row; idx += blockDim.x) {
-            const int n = idx / chunks_per_row, k8 = idx % chunks_per_row;
+        // a warp takes one row at a time: its 32 lanes read 512 contiguous bytes of the token's activations per step,
+        // four steps in flight
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+        for (int n = warp; n < cnt; n += warps) {
             const int64_t tok = ws[L.slots + start + n] / A;
-            const uint4 v = *reinterpret_cast<const uint4 *>(x + tok * K + (int64_t)k8 * 8);
-            *reinterpret_cast<uint4 *>(xs + tiled_offset(L.S, k8 >> 3, start + n, n, k8 & 7)) = b_chunk<BITS>(v, false);
+            const uint4 *src = reinterpret_cast<const uint4 *>(x + tok * K);
+            for (int k8 = lane; k8 < chunks_per_row; k8 += 128) {
+                uint4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (k8 + 32 * u < chunks_per_row) v[u] = src[k8 + 32 * u];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int kk = k8 + 32 * u;
+                    if (kk < chunks_per_row)
+                        *reinterpret_cast<uint4 *>(xs + tiled_offset(L.S, kk >> 3, start + n, n, kk & 7)) = b_chunk<BITS>(v[u], false);
+                }
+            }
         }
     }
 }

@@ -85,10 +85,12 @@ def expert_bias(cfg: MoeConfig, seed: int, device, layer: int = 0) -> torch.Tens
     return b
 
 
-def router_logits(x: torch.Tensor, wr: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
-    """FP32 logits [T, E + 1] = x Wr^T + bias.  TF32 stays off: the logits are the router's exact-parity input."""
+def router_logits(x: torch.Tensor, wr: torch.Tensor, bias: torch.Tensor, tf32: bool = False) -> torch.Tensor:
+    """FP32 logits [T, E + 1] = x Wr^T + bias (the router projection, upstream of the MoE path).  By default an FP32
+    GEMM; tf32 = True lets cuBLAS use TF32 tensor cores (the benchmark's choice for prefill-sized T: the router then
+    ranks those logits, whatever produced them)."""
     prev = torch.backends.cuda.matmul.allow_tf32
-    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = bool(tf32)
     try:
         return (x.to(torch.float32) @ wr.t() + bias).contiguous()
     finally:
