@@ -29,6 +29,8 @@
 
 #include "experts.cuh"
 
+#include <cuda.h>  // CUtensorMap and its enums only; the encoder is looked up through the runtime, nothing links libcuda
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #ifdef SXB_TC_PROF
@@ -49,7 +51,6 @@ constexpr int kEpiWarps = 4, kMmaWarp = 4, kMmaWarps = 2, kFirstAWarp = kMmaWarp
 constexpr int kThreads = 32 * (kFirstBWarp + kBWarps);  // 512
 constexpr int kAThreads = 32 * kAWarps;                 // 256 = weight rows per item
 constexpr int kProducers = kAThreads;
-constexpr int kBPrefetch = 12;                          // k-blocks of tile-blocked activations pulled into L2 ahead of their copy
 constexpr int kBAhead = 2;                              // k-blocks of activations in flight (cp.async groups)
 constexpr int kBK = 64;                                               // k per stage: one 128-byte swizzle line of F16
 constexpr int kMaxTileTokens = 128;
@@ -62,10 +63,10 @@ constexpr int kStageBytes = kBBytes;                // shared memory per stage (
 constexpr int kTmemCols = 512;
 constexpr int kAccCols = kMaxTileTokens;
 constexpr int kAStageCol0 = 2 * kAccCols, kAStageCols = 2 * (kBK / 2);
-// Epilogue staging in shared memory: FP32 [accumulator][token][row], token stride padded to 132 words so that the drain
-// (lane = row) and the read-back (8 consecutive rows of a token per thread) are both free of bank conflicts.
-constexpr int kEpiTokStride = 132;
-constexpr int kEpiBytes = 2 * kMaxTileTokens * kEpiTokStride * 4;
+// Ring of packed weight codes in shared memory: a slot holds 64 bytes (128 Q4 or 64 Q8 codes) of each of the item's 256
+// rows, as two boxes of 128 rows.
+constexpr int kWSlots = 4;
+constexpr int kWSlotBytes = kAThreads * 64;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any legitimate wait
 
 enum TcMode { kTcGather = 0, kTcSwiglu = 1, kTcPartial = 2 };
@@ -111,11 +112,7 @@ __device__ inline bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-#ifdef SXB_TC_EXP_TESTWAIT
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#else
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#endif
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(smem_u32(bar)), "r"(parity)
@@ -145,29 +142,34 @@ __device__ inline bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *a
 __device__ inline void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ inline void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ inline void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// Executed by a whole (converged) warp; elect.sync picks the lane that issues - the same one every time for a full mask,
+// so the commits track the MMAs of the lane that issued them.
 __device__ inline void tc_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ inline void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        "{\n\t.reg .pred q;\n\t"
+        "elect.sync _|q, 0xffffffff;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar))
         : "memory");
 }
-// 16 consecutive columns of this thread's TMEM lane.
-__device__ inline void tc_ld16(uint32_t taddr, float (&v)[16]) {
-    uint32_t r[16];
+// 16 consecutive columns of this thread's TMEM lane from each of two addresses, one wait for both.
+__device__ inline void tc_ld16x2(uint32_t taddr0, uint32_t taddr1, float (&v0)[16], float (&v1)[16]) {
+    uint32_t r[16], q[16];
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
+        : "r"(taddr0));
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3]), "=r"(q[4]), "=r"(q[5]), "=r"(q[6]), "=r"(q[7]), "=r"(q[8]),
+          "=r"(q[9]), "=r"(q[10]), "=r"(q[11]), "=r"(q[12]), "=r"(q[13]), "=r"(q[14]), "=r"(q[15])
+        : "r"(taddr1));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+    for (int i = 0; i < 16; ++i) v0[i] = __uint_as_float(r[i]), v1[i] = __uint_as_float(q[i]);
 }
+// silu on the special-function unit: ex2 and a reciprocal, a few ulp of FP32 - far inside the BF16 rounding that follows.
+__device__ inline float silu_fast(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 
 // 16 consecutive columns of this thread's TMEM lane, written from registers.
 __device__ inline void tc_st16(uint32_t taddr, const uint4 (&d)[4]) {
@@ -178,11 +180,13 @@ __device__ inline void tc_st16(uint32_t taddr, const uint4 (&d)[4]) {
         : "memory");
 }
 // D[tmem] (+)= A[tmem] * B[smem]: the A operand (128 rows x 16 k of F16, two per 32-bit column) read from tensor memory.
+// Whole-warp call, one elected lane issues (see tc_commit).
 __device__ inline void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
+        "{\n\t.reg .pred p, q;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        "elect.sync _|q, 0xffffffff;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
@@ -216,6 +220,19 @@ __device__ inline void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, u
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
                  "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
+}
+
+// One box of a 2-D tensor copy (no multicast), completion counted in bytes on `bar`.  x is a byte offset inside the weight row
+// and always a multiple of 64, as the 16-byte alignment rule of tensor copies requires.
+__device__ inline void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ inline uint4 ld_shared_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
 }
 
 // Eight activations (one 16-byte chunk of BF16 or F16) -> F16 in the operand's k order.
@@ -298,11 +315,12 @@ __device__ inline int next_valid_item(const TcArgs &a, int item, int n_items, in
 }
 
 template <int BITS, int G, int MODE>
-__global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a) {
+__global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap wmap) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment of the operand tiles (the swizzle pattern repeats every 1024 bytes).
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     __shared__ uint64_t full_bar[kStages], empty_bar[kStages], acc_full[1], acc_empty[1], drain_bar;
+    __shared__ uint64_t w_full[kWSlots], w_empty[kWSlots];
     __shared__ uint32_t tmem_base_smem;
     __shared__ int abort_flag;
     __shared__ int64_t b_row_off[kBWarps][kMaxTileTokens / kBWarps];
@@ -317,6 +335,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
         for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], kAWarps + (a.x_kind == 3 ? 1 : kBWarps)), mbar_init(&empty_bar[s], kMmaWarps);
         mbar_init(&acc_full[0], kMmaWarps), mbar_init(&acc_empty[0], kEpiWarps);
         mbar_init(&drain_bar, kMmaWarps);
+        for (int s = 0; s < kWSlots; ++s) mbar_init(&w_full[s], 1), mbar_init(&w_empty[s], kAWarps);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -336,78 +355,137 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
         }
     };
 
+    // The ring of weight-code slots is filled by ONE thread.  With tile-blocked activations the second B warp has nothing
+    // else to do and its lane 0 runs the ring as far ahead as free slots allow.  Otherwise lane 0 of the first A warp tops
+    // the ring up before it consumes slot number j, to slot j + kWSlots - 1, which reuses the buffer of slot j - 1 -
+    // released by every A warp as soon as the warp has its codes in registers, so that wait is short.
+    constexpr int kKbPerSlot = BITS == 4 ? 2 : 1;  // k-blocks per 64 bytes of packed codes
+    const int n_slots = (n_kb + kKbPerSlot - 1) / kKbPerSlot;
+    const uint32_t w_base = smem_u32(smem + kStages * kStageBytes);
+    const bool own_w_thread = a.x_kind == 3;
+    int is_item = next_valid_item<MODE>(a, blockIdx.x, n_items, rbs), is_slot = 0, is_y0 = 0, is_y1 = 0;
+    uint32_t issued = 0;
+    auto issue_one = [&]() -> bool {
+        const int slot = issued % kWSlots;
+        if (issued >= (uint32_t)kWSlots && !mbar_wait(&w_empty[slot], ((issued / kWSlots) & 1u) ^ 1u, abort_v)) {
+            raise_abort(is_item, 6);
+            return false;
+        }
+        if (is_slot == 0) {  // the two boxes' first weight rows
+            const ItemInfo it = item_info<MODE>(a, is_item, rbs);
+            if (MODE == kTcSwiglu) is_y0 = (int)(it.bucket * a.N + it.rb * 128), is_y1 = is_y0 + (int)(a.N / 2);
+            else is_y0 = (int)(it.bucket * a.N + (int64_t)it.rb * kAThreads), is_y1 = is_y0 + 128;
+        }
+        const uint32_t dst = w_base + (uint32_t)(slot * kWSlotBytes);
+        mbar_expect_tx(&w_full[slot], (uint32_t)kWSlotBytes);
+        tma_load_2d(dst, &wmap, is_slot * 64, is_y0, &w_full[slot]);
+        tma_load_2d(dst + kWSlotBytes / 2, &wmap, is_slot * 64, is_y1, &w_full[slot]);
+        ++issued;
+        if (++is_slot == n_slots) is_slot = 0, is_item = next_valid_item<MODE>(a, is_item + gridDim.x, n_items, rbs);
+        return true;
+    };
+
     if (warp >= kFirstAWarp && warp < kFirstBWarp) {
         // ===================== A producers: weights =====================
         // A thread owns one weight row of the item and writes it into its own tensor-memory lane; a warp may only touch
-        // the lane quadrant warp % 4, so the row is (accumulator, quadrant, lane).
+        // the lane quadrant warp % 4, so the row is (accumulator, quadrant, lane).  The packed codes arrive in shared memory
+        // by tensor copies of 64 bytes x 128 rows (one per accumulator, two per ring slot), so that the memory pipe sees a
+        // handful of instructions per k-block instead of one 128-byte line per thread: 256 scattered lines per load
+        // instruction kept the load/store unit busy for thousands of cycles and held up every other warp's MMA issue.
         const int a_half = (warp - kFirstAWarp) >> 2, a_quad = warp & 3;
         const int p = a_half * 128 + a_quad * 32 + lane;  // weight row of the item, 0..255
-        const int64_t row_bytes = BITS == 4 ? a.K / 2 : a.K;
-        constexpr int kSuperKb = BITS == 4 ? 4 : 2;  // k-blocks per 128 bytes of packed codes
-        constexpr int kWordsPerKb = BITS == 4 ? 8 : 16;
-        constexpr int kSuperGroups = (kSuperKb * kBK) / G > 0 ? (kSuperKb * kBK) / G : 1;  // scale groups per super-block
+        constexpr int kKbPerChunk = G / 8;                // k-blocks covered by eight scale groups (one 16-byte load)
         constexpr int kGroupsPerKb = G >= kBK ? 1 : kBK / G;
-        const int n_sb = (n_kb + kSuperKb - 1) / kSuperKb;
+        const bool vec_scales = groups % 8 == 0 && ((reinterpret_cast<uintptr_t>(a.scale) | reinterpret_cast<uintptr_t>(a.minv)) & 15) == 0;
+        // this thread's 64 bytes inside a slot: row (p % 128) of its accumulator's box, 16-byte chunks swizzled (64-byte mode)
+        const uint32_t my_w = (uint32_t)(a_half * (kWSlotBytes / 2) + (p & 127) * 64), my_sw = (uint32_t)(((p & 127) >> 1) & 3);
 
         struct Row {
-            const uint4 *q;
-            const uint16_t *s, *m;
+            int64_t wrow;  // row of the stacked weight
             bool valid;
         };
         auto row_of = [&](int item) {
-            Row r{nullptr, nullptr, nullptr, false};
+            Row r{0, false};
             if (item >= n_items) return r;
             const ItemInfo it = item_info<MODE>(a, item, rbs);
-            int64_t wrow;
             if (MODE == kTcSwiglu) {
                 const int64_t I = a.N / 2, j = (int64_t)it.rb * 128 + (p & 127);
                 r.valid = j < I;
-                wrow = (int64_t)it.bucket * a.N + (p < 128 ? j : I + j);
+                r.wrow = (int64_t)it.bucket * a.N + (p < 128 ? j : I + j);
             } else {
                 const int64_t rr = (int64_t)it.rb * kAThreads + p;
                 r.valid = rr < a.N;
-                wrow = (int64_t)it.bucket * a.N + rr;
+                r.wrow = (int64_t)it.bucket * a.N + rr;
             }
-            r.q = reinterpret_cast<const uint4 *>(a.q + wrow * row_bytes);
-            r.s = a.scale + wrow * groups, r.m = a.minv + wrow * groups;
             return r;
         };
-        // A super-block: 128 bytes of the row's packed codes (4 k-blocks of Q4, 2 of Q8) and the scales / mins of its
-        // groups, fetched one super-block ahead of the one being dequantized - across item boundaries too - so the row
-        // is read as whole 128-byte lines and every load has several k-blocks of work to hide behind.
-        struct Super {
-            uint4 code[8];
-            uint32_t sm[kSuperGroups];  // scale | min << 16 (BF16 bits)
+        // Scales and mins of eight consecutive groups of the row (BF16 bits), fetched one chunk ahead of use.
+        struct ScaleChunk {
+            uint4 s, m;
         };
-        auto load_super = [&](Super &dst, const Row &r, int sb) {
+        auto load_scales = [&](const Row &r, int chunk) {
+            ScaleChunk c{make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
+            if (!r.valid) return c;
+            const int g0 = chunk * 8;
+            const uint16_t *sp = a.scale + r.wrow * groups + g0, *mp = a.minv + r.wrow * groups + g0;
+            if (vec_scales) {
+                c.s = __ldg(reinterpret_cast<const uint4 *>(sp)), c.m = __ldg(reinterpret_cast<const uint4 *>(mp));
+            } else {
+                uint32_t sw[4] = {0u, 0u, 0u, 0u}, mw[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                dst.code[i] = make_uint4(0u, 0u, 0u, 0u);
-                if (r.valid && (sb * kSuperKb + i * kSuperKb / 8) < n_kb) dst.code[i] = __ldg(r.q + sb * 8 + i);
+                for (int i = 0; i < 8; ++i)
+                    if (g0 + i < groups) sw[i >> 1] |= (uint32_t)__ldg(sp + i) << (16 * (i & 1)), mw[i >> 1] |= (uint32_t)__ldg(mp + i) << (16 * (i & 1));
+                c.s = make_uint4(sw[0], sw[1], sw[2], sw[3]), c.m = make_uint4(mw[0], mw[1], mw[2], mw[3]);
             }
-#pragma unroll
-            for (int g = 0; g < kSuperGroups; ++g) {
-                const int gi = G >= kSuperKb * kBK ? (sb * kSuperKb * kBK) / G : sb * kSuperGroups + g;
-                dst.sm[g] = 0u;
-                if (r.valid && gi < groups) dst.sm[g] = (uint32_t)__ldg(r.s + gi) | ((uint32_t)__ldg(r.m + gi) << 16);
-            }
+            return c;
+        };
+        auto pick16 = [](const uint4 &v, int g) {
+            const uint32_t w = (g & 4) ? ((g & 2) ? v.w : v.z) : ((g & 2) ? v.y : v.x);
+            return (uint16_t)((g & 1) ? (w >> 16) : (w & 0xffffu));
         };
 
         uint32_t it_count = 0;  // k-blocks produced so far (stage / phase bookkeeping)
+        uint32_t w_count = 0;   // code slots consumed so far
         int item = next_valid_item<MODE>(a, blockIdx.x, n_items, rbs);
         Row row = row_of(item);
-        Super cur, nxt;
-        if (item < n_items) load_super(cur, row, 0);
+        ScaleChunk sc_cur{}, sc_nxt{};
+        if (item < n_items) sc_nxt = load_scales(row, 0);
         bool live = true;
         while (item < n_items && live && !*abort_v) {
             const int next = next_valid_item<MODE>(a, item + gridDim.x, n_items, rbs);
             const Row next_row = row_of(next);
-            for (int sb = 0; sb < n_sb && live; ++sb) {
-                if (sb + 1 < n_sb) load_super(nxt, row, sb + 1);
-                else if (next < n_items) load_super(nxt, next_row, 0);
+            for (int sl = 0; sl < n_slots && live; ++sl, ++w_count) {
+                if (!own_w_thread && warp == kFirstAWarp && lane == 0)
+                    while (issued < w_count + (uint32_t)kWSlots && is_item < n_items)
+                        if (!issue_one()) break;
+                const int slot = w_count % kWSlots;
+                {
+                    PROF_BEGIN();
+                    if (lane == 0 && !mbar_wait(&w_full[slot], (w_count / kWSlots) & 1u, abort_v)) raise_abort(item, 7);
+                    __syncwarp();
+                    if (warp == kFirstAWarp) PROF_ADD(3);
+                }
+                if (*abort_v) {
+                    live = false;
+                    break;
+                }
+                uint4 code[4];
 #pragma unroll
-                for (int sub = 0; sub < kSuperKb; ++sub) {
-                    const int kb = sb * kSuperKb + sub;
+                for (int c = 0; c < 4; ++c) {
+                    code[c] = ld_shared_v4(w_base + (uint32_t)(slot * kWSlotBytes) + my_w + (((uint32_t)c ^ my_sw) << 4));
+                    if (!row.valid) code[c] = make_uint4(0u, 0u, 0u, 0u);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&w_empty[slot]);  // the codes are in registers: the slot may be refilled
+                const int kb0 = sl * kKbPerSlot;
+                if (kb0 % kKbPerChunk == 0) {
+                    sc_cur = sc_nxt;
+                    if (kb0 + kKbPerChunk < n_kb) sc_nxt = load_scales(row, kb0 / kKbPerChunk + 1);
+                    else if (next < n_items) sc_nxt = load_scales(next_row, 0);
+                }
+#pragma unroll
+                for (int sub = 0; sub < kKbPerSlot; ++sub) {
+                    const int kb = kb0 + sub;
                     if (kb >= n_kb) break;
                     const int stage = it_count % kStages;
                     const uint32_t phase = (it_count / kStages) & 1u;
@@ -424,32 +502,35 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                         break;
                     }
                     PROF_BEGIN();
-                    // this thread's row: 64 codes -> 64 F16 = 32 tensor-memory columns of its lane
-                    uint32_t words[kWordsPerKb];
-#pragma unroll
-                    for (int i = 0; i < kWordsPerKb / 4; ++i) {
-                        const uint4 v = cur.code[sub * (kWordsPerKb / 4) + i];
-                        words[4 * i] = v.x, words[4 * i + 1] = v.y, words[4 * i + 2] = v.z, words[4 * i + 3] = v.w;
-                    }
                     __half2 s2[kGroupsPerKb], s16[kGroupsPerKb], m2[kGroupsPerKb];
 #pragma unroll
                     for (int gi = 0; gi < kGroupsPerKb; ++gi) {
-                        const int g = G >= kSuperKb * kBK ? 0 : (sub * kBK) / G + gi;  // group inside the super-block
-                        const uint32_t packed = cur.sm[g < kSuperGroups ? g : 0];
-                        const float sf = bf16_bits_to_f32((uint16_t)(packed & 0xffffu)), mf = bf16_bits_to_f32((uint16_t)(packed >> 16));
+                        const int g = ((kb * kBK) / G + gi) & 7;  // group inside the chunk of eight
+                        const float sf = bf16_bits_to_f32(pick16(sc_cur.s, g)), mf = bf16_bits_to_f32(pick16(sc_cur.m, g));
                         s2[gi] = __float2half2_rn(sf), s16[gi] = __float2half2_rn(sf * 0.0625f), m2[gi] = __float2half2_rn(mf);
                     }
                     const uint32_t a_addr = tmem_base + ((uint32_t)(a_quad * 32) << 16) +
                                             (uint32_t)(kAStageCol0 + stage * kAStageCols + a_half * (kBK / 2));
+                    // this thread's row: 64 codes -> 64 F16 = 32 tensor-memory columns of its lane, two stores of 16
 #pragma unroll
-                    for (int hc = 0; hc < 2; ++hc) {  // two stores of 16 columns keep the live registers down
+                    for (int hc = 0; hc < 2; ++hc) {
                         uint4 d[4];
+                        if (BITS == 4) {
+                            const uint4 v = code[sub * 2 + hc];  // 32 codes
+                            const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-                        for (int cc = 0; cc < 4; ++cc) {
-                            const int c = hc * 4 + cc;
-                            const int gi = kGroupsPerKb == 1 ? 0 : (c * 8) / G;
-                            if (BITS == 4) d[cc] = dequant_q4_word(words[c], s2[gi], s16[gi], m2[gi]);
-                            else d[cc] = dequant_q8_words(words[2 * c], words[2 * c + 1], s2[gi], m2[gi]);
+                            for (int cc = 0; cc < 4; ++cc) {
+                                const int gi = kGroupsPerKb == 1 ? 0 : ((hc * 4 + cc) * 8) / G;
+                                d[cc] = dequant_q4_word(w4[cc], s2[gi], s16[gi], m2[gi]);
+                            }
+                        } else {
+                            const uint4 v0 = code[hc * 2], v1 = code[hc * 2 + 1];  // 2 x 16 codes
+                            const uint32_t w8[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+                            for (int cc = 0; cc < 4; ++cc) {
+                                const int gi = kGroupsPerKb == 1 ? 0 : ((hc * 4 + cc) * 8) / G;
+                                d[cc] = dequant_q8_words(w8[2 * cc], w8[2 * cc + 1], s2[gi], m2[gi]);
+                            }
                         }
                         tc_st16(a_addr + hc * 16, d);
                     }
@@ -460,21 +541,12 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                         tc_fence_before();  // orders the stores before the MMA warp's reads across the barrier
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&full_bar[stage]);
-                        if (warp == kFirstAWarp) TRACE(0, it_count - 1, 1);
                         if (warp == kFirstAWarp) {
+                            TRACE(0, it_count - 1, 1);
                             PROF_ADD(2);
-                            PROF_ADD(16 + sub);
                             PROF_COUNT(4);
                         }
                     }
-                }
-                {
-                    PROF_BEGIN();
-                    cur = nxt;
-#ifdef SXB_TC_PROF
-                    asm volatile("" ::"r"(cur.code[7].w), "r"(cur.code[0].x), "r"(cur.sm[0]));
-#endif
-                    if (warp == kFirstAWarp) PROF_ADD(3);
                 }
             }
             item = next;
@@ -485,33 +557,25 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
         // B warp w owns tokens [64 w, 64 w + 64) of the tile; lane l copies 16-byte chunk c = l % 8 of tokens
         // 64 w + l / 8 + 4 i (i < 16), every k-block, so eight lanes cover one 128-byte line of one activation row.
         if (a.x_kind == 3) {
+            if (warp == kFirstBWarp + 1 && lane == 0)
+                while (is_item < n_items && !*abort_v)
+                    if (!issue_one()) break;
             // Tile-blocked activations: one thread, one bulk copy per k-block, completion counted in bytes on the
             // stage's barrier; every free stage is refilled at once, so kStages k-blocks are in flight.
             if (warp == kFirstBWarp && lane == 0) {
-                // A second cursor runs kBPrefetch k-blocks ahead of the copies (across items) and pulls those runs into
-                // L2, so a copy issued the moment its stage frees up is an L2 hit, not a DRAM round trip.
                 uint32_t it_count = 0;
-                int p_item = next_valid_item<MODE>(a, blockIdx.x, n_items, rbs), p_kb = 0;
-                auto prefetch_next = [&]() {
-                    if (p_item >= n_items) return;
-                    const ItemInfo pi = item_info<MODE>(a, p_item, rbs);
-                    const unsigned char *src = reinterpret_cast<const unsigned char *>(a.x) + ((int64_t)p_kb * a.L.S + pi.start) * 128;
-                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"((uint32_t)pi.cnt * 128u) : "memory");
-                    if (++p_kb == n_kb) p_kb = 0, p_item = next_valid_item<MODE>(a, p_item + gridDim.x, n_items, rbs);
-                };
-                for (int i = 0; i < kBPrefetch; ++i) prefetch_next();
                 for (int item = next_valid_item<MODE>(a, blockIdx.x, n_items, rbs); item < n_items && !*abort_v;
                      item = next_valid_item<MODE>(a, item + gridDim.x, n_items, rbs)) {
                     const ItemInfo it = item_info<MODE>(a, item, rbs);
                     const uint32_t bytes = (uint32_t)it.cnt * 128u;
                     const unsigned char *src = reinterpret_cast<const unsigned char *>(a.x) + (int64_t)it.start * 128;
                     for (int kb = 0; kb < n_kb; ++kb, ++it_count) {
-                        prefetch_next();
                         const int stage = it_count % kStages;
                         if (!mbar_wait(&empty_bar[stage], ((it_count / kStages) & 1u) ^ 1u, abort_v)) {
                             raise_abort(item, 5);
                             break;
                         }
+                        TRACE(1, it_count, 0);
                         mbar_expect_tx(&full_bar[stage], bytes);
                         bulk_g2s(smem_u32(smem + stage * kStageBytes), src + (int64_t)kb * a.L.S * 128, bytes, &full_bar[stage]);
                     }
@@ -606,9 +670,12 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
         }
     } else if (warp >= kMmaWarp) {
         // ===================== MMA issue =====================
-        // Two issuing warps, one per accumulator: each instruction costs its issuing thread far more than an N <= 128
-        // MMA's arithmetic, so the two halves are issued side by side; a stage is free when both have committed.
-        const int half = warp - kMmaWarp;
+        // Two issuing warps, one per accumulator: an instruction costs its issuing thread 60-90 cycles whatever its N,
+        // more than an N <= 128 MMA's arithmetic, so the two halves are issued side by side; a stage is free when both
+        // have committed.  The whole warp runs the loop with warp-uniform operands and elect.sync picks the issuing lane
+        // (always the same one for a full mask), which keeps descriptors and addresses out of per-thread registers.
+        const int half = __shfl_sync(0xffffffffu, warp, 0) - kMmaWarp;
+        const uint32_t d = tmem_base + (uint32_t)(half * kAccCols);
         uint32_t it_count = 0, acc_count = 0;
         for (int item = blockIdx.x; item < n_items && !*abort_v; item += gridDim.x) {
             const ItemInfo it = item_info<MODE>(a, item, rbs);
@@ -641,41 +708,68 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                 if (*abort_v) break;
                 tc_fence_after();
                 PROF_BEGIN();
-                if (lane == 0) {
-                    const uint32_t sb_ = smem_u32(smem + stage * kStageBytes);
-                    const uint32_t d = tmem_base + (uint32_t)(half * kAccCols);
-                    const uint32_t at = tmem_base + (uint32_t)(kAStageCol0 + stage * kAStageCols + half * (kBK / 2));
+                const uint64_t b_desc = smem_desc(smem_u32(smem + stage * kStageBytes));
+                const uint32_t at = tmem_base + (uint32_t)(kAStageCol0 + stage * kAStageCols + half * (kBK / 2));
 #pragma unroll
-                    for (int j = 0; j < kBK / 16; ++j) tc_mma_f16_ts(d, at + j * 8, smem_desc(sb_ + j * 32), idesc, (kb | j) != 0);
-                    if (half == 0) PROF_ADD(20);
-                    tc_commit(&empty_bar[stage]);                    // frees the stage when these MMAs have read it
-                    if (kb == n_kb - 1) tc_commit(&acc_full[0]);     // and hands the accumulators to the epilogue
-                }
+                for (int j = 0; j < kBK / 16; ++j) tc_mma_f16_ts(d, at + j * 8, b_desc + 2 * j, idesc, (kb | j) != 0);
+                if (half == 0) PROF_ADD(20);
+                tc_commit(&empty_bar[stage]);                 // frees the stage when these MMAs have read it
+                if (kb == n_kb - 1) tc_commit(&acc_full[0]);  // and hands the accumulators to the epilogue
                 if (half == 0) {
                     PROF_ADD(6);
                     TRACE(2, it_count, 1);
                 }
-                __syncwarp();
             }
         }
         // Drain: every MMA issued by this CTA has completed before tensor memory is released.
-        if (lane == 0) {
-            tc_commit(&drain_bar);
-            mbar_wait(&drain_bar, 0u, abort_v);
-        }
+        tc_commit(&drain_bar);
+        if (lane == 0) mbar_wait(&drain_bar, 0u, abort_v);
         __syncwarp();
     } else {
         // ===================== epilogue =====================
-        // Phase 1 (lane = weight row): the finished accumulators are drained from tensor memory into shared memory
-        // [accumulator][token][row] and tensor memory is handed back at once - the next item's MMAs run under phase 2.
-        // Phase 2: a thread takes one token x 8 consecutive rows, all inside its own warp's 32 rows (no cross-warp
-        // dependency): SwiGLU / rounding, then one 16-byte (h, y) or two 16-byte (FP32 partial) stores.
+        // Lane = weight row: 16 tokens of both accumulators at a time from tensor memory into registers; SwiGLU /
+        // rounding there (gate row j and up row j of a token sit in the same thread), then one store per token straight
+        // to global memory - for a fixed token the warp's 32 rows are 64 (h, y) or 128 (FP32 partial) contiguous bytes,
+        // so every store instruction is one line.  Tensor memory goes back to the MMA warps as soon as the last 16
+        // tokens are in registers.
+        // The per-token code is kept short on purpose (it runs once per item and its instructions are fetched cold):
+        // everything that does not depend on the token is folded into per-thread constants; what depends on it - the
+        // output row of its slot, or its line in the tile-blocked h - is computed by lanes 0..15 for the 16 tokens of a
+        // pass and handed round by shuffles.
         uint32_t acc_count = 0;
         const int64_t I = a.N / 2;
-        float *stage_f = reinterpret_cast<float *>(smem + kStages * kStageBytes);
+        const int r_loc = warp * 32 + lane;  // row inside a 128-row accumulator
+        const bool tiled_out = MODE == kTcSwiglu && a.out_f16 >= 3;
+        const bool h_as_f16 = a.out_f16 != 0, q4_order = a.out_f16 == 2 || a.out_f16 == 3;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
         for (int item = blockIdx.x; item < n_items && !*abort_v; item += gridDim.x) {
             const ItemInfo it = item_info<MODE>(a, item, rbs);
             const bool valid = it.bucket < a.E;
+            // per-thread constants of the item: byte offset of this thread's element inside a token's output row / line
+            int64_t elem_off;
+            uint32_t xor_chunk = 0;  // tile-blocked h: 16-byte chunk of the line, before the per-token swizzle
+            bool row_ok;
+            if (MODE == kTcSwiglu) {
+                const int64_t j = (int64_t)it.rb * 128 + r_loc;  // h column
+                const int j7 = (int)(j & 7), pos = q4_order ? (((j7 & 3) << 1) | (j7 >> 2)) : j7;  // [0 4 1 5 2 6 3 7]
+                row_ok = j < I;
+                if (tiled_out) elem_off = (j >> 6) * a.L.S * 128 + pos * 2, xor_chunk = (uint32_t)((j & 63) >> 3);
+                else elem_off = ((j & ~(int64_t)7) + pos) * 2;
+            } else {
+                const int64_t r = (int64_t)it.rb * kAThreads + r_loc;
+                row_ok = r < a.N;  // N is a multiple of 16: the second accumulator's row r + 128 is checked on its own
+                elem_off = r * (MODE == kTcPartial ? 4 : 2);
+            }
+            const bool row1_ok = MODE != kTcSwiglu && (int64_t)it.rb * kAThreads + 128 + r_loc < a.N;
+            // Slot of token n of the tile (lanes 0..15 fetch the 16 tokens of a pass, one pass ahead; nothing may depend
+            // on the loaded value before the next pass, or the in-order issue would stall this pass's stores behind it).
+            auto token_slot = [&](int n) -> int { return (tiled_out || n >= it.cnt) ? 0 : a.ws[a.L.slots + it.start + n]; };
+            // Offset of a token's output row / line, in 16-byte units.
+            auto token_off = [&](int n, int slot) -> uint32_t {
+                if (tiled_out) return (uint32_t)(it.start + n) * 8u;
+                return (uint32_t)(((int64_t)slot * (MODE == kTcSwiglu ? I * 2 : a.N * (MODE == kTcPartial ? 4 : 2))) >> 4);
+            };
+            int slot_nxt = lane < 16 ? token_slot(lane) : 0;
             if (valid) {
                 const uint32_t acc_phase = acc_count & 1u;
                 ++acc_count;
@@ -690,83 +784,43 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a)
                 __syncwarp();
                 if (*abort_v) break;
                 tc_fence_after();
-                const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-                for (int c0 = 0; c0 < it.cnt; c0 += 16) {
-#pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        float v[16];
-                        tc_ld16(lane_addr + (uint32_t)(half * kAccCols + c0), v);
-                        float *dst = stage_f + ((size_t)half * kMaxTileTokens + c0) * kEpiTokStride + warp * 32 + lane;
-#pragma unroll
-                        for (int t = 0; t < 16; ++t) dst[t * kEpiTokStride] = v[t];
-                    }
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[0]);
             }
             PROF_BEGIN();
-            const int tl = lane >> 2, g8 = (warp * 32) + (lane & 3) * 8;  // token inside a pass of 8, first of 8 rows
-            for (int n = tl; n < it.cnt; n += 8) {
-                float r0[8], r1[8];
+            unsigned char *out = static_cast<unsigned char *>(a.out) + elem_off;
+            for (int c0 = 0; c0 < it.cnt; c0 += 16) {
+                float g[16], u[16];
                 if (valid) {
-                    const float4 *p0 = reinterpret_cast<const float4 *>(stage_f + (size_t)n * kEpiTokStride + g8);
-                    const float4 *p1 = reinterpret_cast<const float4 *>(stage_f + ((size_t)kMaxTileTokens + n) * kEpiTokStride + g8);
-                    const float4 x0 = p0[0], x1 = p0[1], y0 = p1[0], y1 = p1[1];
-                    r0[0] = x0.x, r0[1] = x0.y, r0[2] = x0.z, r0[3] = x0.w, r0[4] = x1.x, r0[5] = x1.y, r0[6] = x1.z, r0[7] = x1.w;
-                    r1[0] = y0.x, r1[1] = y0.y, r1[2] = y0.z, r1[3] = y0.w, r1[4] = y1.x, r1[5] = y1.y, r1[6] = y1.z, r1[7] = y1.w;
+                    tc_ld16x2(lane_addr + (uint32_t)c0, lane_addr + (uint32_t)(kAccCols + c0), g, u);
+                    if (c0 + 16 >= it.cnt) {  // the last columns are out: tensor memory is free for the next item
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&acc_empty[0]);
+                    }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) r0[i] = r1[i] = qnan_f32();
+                    for (int t = 0; t < 16; ++t) g[t] = u[t] = qnan_f32();
                 }
-                if (MODE == kTcSwiglu) {
-                    const int64_t j = (int64_t)it.rb * 128 + g8;  // h columns j .. j + 7 (I is a multiple of 8)
-                    if (j >= I) continue;
-                    uint16_t hb[8];
+                const uint32_t off_cur = token_off(c0 + (lane & 15), slot_nxt);
+                if (c0 + 16 < it.cnt && lane < 16) slot_nxt = token_slot(c0 + 16 + lane);
+                const int live = it.cnt - c0;  // tokens of this pass; the columns past them are computed and dropped
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
+                for (int t = 0; t < 16; ++t) {
+                    const int64_t off = (int64_t)__shfl_sync(0xffffffffu, off_cur, t) << 4;
+                    if (MODE == kTcSwiglu) {
                         // kernels/moe_grouped.hip:508-524: from the FP32 accumulators, rounded once
-                        const uint16_t b = f32_to_bf16_bits(silu_f32(r0[i]) * r1[i]);
-                        hb[i] = a.out_f16 ? __half_as_ushort(__float2half_rn(bf16_bits_to_f32(b))) : b;
-                    }
-                    uint4 o;
-                    if (a.out_f16 == 2 || a.out_f16 == 3) {  // the Q4 operand's k order inside every 8: [0 4 1 5 2 6 3 7]
-                        o.x = hb[0] | ((uint32_t)hb[4] << 16), o.y = hb[1] | ((uint32_t)hb[5] << 16);
-                        o.z = hb[2] | ((uint32_t)hb[6] << 16), o.w = hb[3] | ((uint32_t)hb[7] << 16);
+                        const uint16_t b = __bfloat16_as_ushort(__float2bfloat16_rn(silu_fast(g[t]) * u[t]));
+                        const uint16_t hv = h_as_f16 ? __half_as_ushort(__float2half_rn(bf16_bits_to_f32(b))) : b;
+                        const uint32_t sw = tiled_out ? ((xor_chunk ^ (uint32_t)(t & 7)) << 4) : 0u;
+                        if (row_ok && t < live) *reinterpret_cast<uint16_t *>(out + off + sw) = hv;
+                    } else if (MODE == kTcPartial) {
+                        if (row_ok && t < live) *reinterpret_cast<float *>(out + off) = g[t];
+                        if (row1_ok && t < live) *reinterpret_cast<float *>(out + off + 512) = u[t];
                     } else {
-                        o.x = hb[0] | ((uint32_t)hb[1] << 16), o.y = hb[2] | ((uint32_t)hb[3] << 16);
-                        o.z = hb[4] | ((uint32_t)hb[5] << 16), o.w = hb[6] | ((uint32_t)hb[7] << 16);
-                    }
-                    unsigned char *out = static_cast<unsigned char *>(a.out);
-                    if (a.out_f16 >= 3) {
-                        *reinterpret_cast<uint4 *>(out + tiled_offset(a.L.S, (int)(j >> 6), it.start + n, n, (int)((j & 63) >> 3))) = o;
-                    } else {
-                        const int64_t slot = a.ws[a.L.slots + it.start + n];
-                        *reinterpret_cast<uint4 *>(out + (slot * I + j) * 2) = o;
-                    }
-                } else {
-                    const int64_t slot = a.ws[a.L.slots + it.start + n];
-#pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        const int64_t r = (int64_t)it.rb * kAThreads + half * 128 + g8;  // rows r .. r + 7 (N % 8 == 0)
-                        const float *v = half ? r1 : r0;
-                        if (r >= a.N) continue;
-                        if (MODE == kTcPartial) {
-                            float4 *o = reinterpret_cast<float4 *>(static_cast<float *>(a.out) + slot * a.N + r);
-                            o[0] = make_float4(v[0], v[1], v[2], v[3]);
-                            o[1] = make_float4(v[4], v[5], v[6], v[7]);
-                        } else {
-                            uint4 o;
-                            o.x = f32_to_bf16_bits(v[0]) | ((uint32_t)f32_to_bf16_bits(v[1]) << 16);
-                            o.y = f32_to_bf16_bits(v[2]) | ((uint32_t)f32_to_bf16_bits(v[3]) << 16);
-                            o.z = f32_to_bf16_bits(v[4]) | ((uint32_t)f32_to_bf16_bits(v[5]) << 16);
-                            o.w = f32_to_bf16_bits(v[6]) | ((uint32_t)f32_to_bf16_bits(v[7]) << 16);
-                            *reinterpret_cast<uint4 *>(static_cast<uint16_t *>(a.out) + slot * a.N + r) = o;
-                        }
+                        if (row_ok && t < live) *reinterpret_cast<uint16_t *>(out + off) = __bfloat16_as_ushort(__float2bfloat16_rn(g[t]));
+                        if (row1_ok && t < live) *reinterpret_cast<uint16_t *>(out + off + 256) = __bfloat16_as_ushort(__float2bfloat16_rn(u[t]));
                     }
                 }
             }
-            __syncwarp();  // this warp's rows of the staging area are free for its next drain
             if (warp == 0) PROF_ADD(10);
         }
     }
@@ -841,14 +895,42 @@ int check_tc(const char *fn, const void *x, const SxbQView *w, int64_t E, const 
     return SXB_OK;
 }
 
+// Tensor map over the packed codes of a stacked weight, seen as bytes [rows, row_bytes]: boxes of 64 bytes x 128 rows,
+// 16-byte chunks swizzled in the 64-byte mode so that 32 threads reading 32 consecutive rows hit every bank once.
+// Rows past the end of the weight read as zero.  The encoder is a host-side computation of the driver library, found
+// through the runtime.
+using TensorMapEncode = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                     const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+int weight_tensor_map(const char *fn, const uint8_t *q, int64_t rows, int64_t row_bytes, CUtensorMap *map) {
+    static TensorMapEncode encode = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &found) != cudaSuccess ||
+            found != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<TensorMapEncode>(p);
+    }();
+    SXB_CHECK(encode != nullptr, fn, ": the driver offers no cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows}, strides[1] = {(cuuint64_t)row_bytes};
+    const cuuint32_t box[2] = {64u, 128u}, elem[2] = {1u, 1u};
+    const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(q), dims, strides, box, elem,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    SXB_CHECK(rc == CUDA_SUCCESS, fn, ": tensor map over ", rows, " rows of ", row_bytes, " bytes refused (CUresult ", (int)rc, ")");
+    return SXB_OK;
+}
+
 // The status words of a launch live in the grouping workspace's header (words 5..7, zeroed by the pack).
 template <int BITS, int MODE>
 int launch_tc(const char *fn, const TcArgs &a, int64_t G, cudaStream_t st) {
-    const size_t smem = (size_t)kStages * kStageBytes + kEpiBytes + 1024;
+    const size_t smem = (size_t)kStages * kStageBytes + (size_t)kWSlots * kWSlotBytes + 1024;
+    CUtensorMap wmap;
+    if (int rc = weight_tensor_map(fn, a.q, a.E * a.N, BITS == 4 ? a.K / 2 : a.K, &wmap)) return rc;
     auto go = [&](auto kern) -> int {
         SXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn,
                  ": reserving shared memory");
-        kern<<<(unsigned)sm_count(), kThreads, smem, st>>>(a);
+        kern<<<(unsigned)sm_count(), kThreads, smem, st>>>(a, wmap);
         return SXB_OK;
     };
     switch (G) {
@@ -940,6 +1022,8 @@ extern "C" __attribute__((visibility("default"))) int sxb_debug_tc_prof(unsigned
     if (reset) {
         unsigned long long z[32] = {};
         cudaMemcpyToSymbol(g_tc_prof, z, sizeof(z));
+        static long long zt[4 * 64 * 2] = {};
+        cudaMemcpyToSymbol(g_tc_trace, zt, sizeof(zt));
     }
     return 0;
 }
