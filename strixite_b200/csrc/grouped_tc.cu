@@ -33,13 +33,18 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
-#ifdef SXB_TC_PROF
+#if defined(SXB_TC_PROF) || defined(SXB_TC_TRACE)
 __device__ unsigned long long g_tc_prof[32];
 __device__ long long g_tc_trace[4][64][2];  // role (A, B, MMA, -), k-block index of CTA 0, two timestamps
+__device__ long long g_tc_trace8[8][64];    // arrival time of every A warp, per k-block of CTA 0
+__device__ long long g_tc_stamp[64][8];     // fine-grained stamps of the first A warp, per k-block of CTA 0
+#define STAMP(idx, which) \
+    do { if (blockIdx.x == 0 && warp == kFirstAWarp && lane == 0 && (idx) < 64) g_tc_stamp[idx][which] = clock64(); } while (0)
 #define TRACE(role, idx, which) \
     do { if (blockIdx.x == 0 && lane == 0 && (idx) < 64) g_tc_trace[role][idx][which] = clock64(); } while (0)
 #else
 #define TRACE(role, idx, which) do {} while (0)
+#define STAMP(idx, which) do {} while (0)
 #endif
 
 namespace sxb {
@@ -444,31 +449,41 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
             return (uint16_t)((g & 1) ? (w >> 16) : (w & 0xffffu));
         };
 
+        // Loop shape.  A producer warp is never waiting for the MMA warps (it is the slower side), so every barrier poll
+        // and every wait for the tensor-memory stores is latency, and the two are made to overlap: right after the
+        // stores of k-block kb are issued, lane 0 polls what the NEXT step needs (its stage, and at a slot boundary the
+        // next slot of codes), and only then does the warp wait for the stores and hand kb over.  The stores' source
+        // registers must stay untouched until that wait, which is why no more than one k-block's stores are in flight.
         uint32_t it_count = 0;  // k-blocks produced so far (stage / phase bookkeeping)
         uint32_t w_count = 0;   // code slots consumed so far
         int item = next_valid_item<MODE>(a, blockIdx.x, n_items, rbs);
         Row row = row_of(item);
         ScaleChunk sc_cur{}, sc_nxt{};
         if (item < n_items) sc_nxt = load_scales(row, 0);
+        auto top_up = [&](uint32_t upto) {  // lane 0 of the first A warp, when no thread of its own runs the ring
+            while (issued < upto + (uint32_t)kWSlots && is_item < n_items)
+                if (!issue_one()) break;
+        };
+        auto poll_slot = [&](uint32_t wc, int it_for_status) {  // lane 0
+            if (!mbar_wait(&w_full[wc % kWSlots], (wc / kWSlots) & 1u, abort_v)) raise_abort(it_for_status, 7);
+        };
+        auto poll_stage = [&](uint32_t cnt, int it_for_status) {  // lane 0
+            if (!mbar_wait(&empty_bar[cnt % kStages], ((cnt / kStages) & 1u) ^ 1u, abort_v)) raise_abort(it_for_status, 1);
+        };
+        if (item < n_items && lane == 0) {
+            if (!own_w_thread && warp == kFirstAWarp) top_up(0);
+            poll_slot(0, item);
+            poll_stage(0, item);
+        }
+        __syncwarp();
         bool live = true;
         while (item < n_items && live && !*abort_v) {
             const int next = next_valid_item<MODE>(a, item + gridDim.x, n_items, rbs);
             const Row next_row = row_of(next);
             for (int sl = 0; sl < n_slots && live; ++sl, ++w_count) {
-                if (!own_w_thread && warp == kFirstAWarp && lane == 0)
-                    while (issued < w_count + (uint32_t)kWSlots && is_item < n_items)
-                        if (!issue_one()) break;
+                // the slot's codes have landed (polled under the previous k-block's stores)
                 const int slot = w_count % kWSlots;
-                {
-                    PROF_BEGIN();
-                    if (lane == 0 && !mbar_wait(&w_full[slot], (w_count / kWSlots) & 1u, abort_v)) raise_abort(item, 7);
-                    __syncwarp();
-                    if (warp == kFirstAWarp) PROF_ADD(3);
-                }
-                if (*abort_v) {
-                    live = false;
-                    break;
-                }
+                STAMP(it_count, 0);
                 uint4 code[4];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
@@ -483,24 +498,14 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
                     if (kb0 + kKbPerChunk < n_kb) sc_nxt = load_scales(row, kb0 / kKbPerChunk + 1);
                     else if (next < n_items) sc_nxt = load_scales(next_row, 0);
                 }
+                const int n_sub = min(kKbPerSlot, n_kb - kb0);
 #pragma unroll
                 for (int sub = 0; sub < kKbPerSlot; ++sub) {
                     const int kb = kb0 + sub;
-                    if (kb >= n_kb) break;
+                    if (sub >= n_sub) break;
                     const int stage = it_count % kStages;
-                    const uint32_t phase = (it_count / kStages) & 1u;
-                    ++it_count;
-                    {
-                        PROF_BEGIN();
-                        if (lane == 0 && !mbar_wait(&empty_bar[stage], phase ^ 1u, abort_v)) raise_abort(item, 1);
-                        __syncwarp();
-                        if (warp == kFirstAWarp) PROF_ADD(0);
-                        if (warp == kFirstAWarp) TRACE(0, it_count - 1, 0);
-                    }
-                    if (*abort_v) {
-                        live = false;
-                        break;
-                    }
+                    if (warp == kFirstAWarp) TRACE(0, it_count, 0);
+                    STAMP(it_count, 1);
                     PROF_BEGIN();
                     __half2 s2[kGroupsPerKb], s16[kGroupsPerKb], m2[kGroupsPerKb];
 #pragma unroll
@@ -535,17 +540,46 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
                         tc_st16(a_addr + hc * 16, d);
                     }
                     if (warp == kFirstAWarp) PROF_ADD(1);
+                    STAMP(it_count, 2);
+                    {
+                        PROF_BEGIN();
+                        // under the stores: what the next k-block needs
+                        if (lane == 0) {
+                            const bool slot_ends = sub + 1 >= n_sub;
+                            const bool more = !slot_ends || sl + 1 < n_slots || next < n_items;
+                            if (more) {
+                                if (slot_ends) {
+                                    if (!own_w_thread && warp == kFirstAWarp) top_up(w_count + 1);
+                                    poll_slot(w_count + 1, item);
+                                }
+                                poll_stage(it_count + 1, item);
+                            }
+                        }
+                        if (warp == kFirstAWarp) PROF_ADD(0);
+                    }
+                    STAMP(it_count, 3);
                     {
                         PROF_BEGIN();
                         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                        STAMP(it_count, 4);
                         tc_fence_before();  // orders the stores before the MMA warp's reads across the barrier
                         __syncwarp();
+                        STAMP(it_count, 5);
                         if (lane == 0) mbar_arrive(&full_bar[stage]);
+                        STAMP(it_count, 6);
+#if defined(SXB_TC_PROF) || defined(SXB_TC_TRACE)
+                        if (blockIdx.x == 0 && lane == 0 && it_count < 64) g_tc_trace8[warp - kFirstAWarp][it_count] = clock64();
+#endif
                         if (warp == kFirstAWarp) {
-                            TRACE(0, it_count - 1, 1);
+                            TRACE(0, it_count, 1);
                             PROF_ADD(2);
                             PROF_COUNT(4);
                         }
+                    }
+                    ++it_count;
+                    if (*abort_v) {
+                        live = false;
+                        break;
                     }
                 }
             }
@@ -1012,7 +1046,15 @@ extern "C" int sxb_stage_f16_tiles(const void *x, const void *ws, size_t ws_byte
     return SXB_OK;
 }
 
-#ifdef SXB_TC_PROF
+#if defined(SXB_TC_PROF) || defined(SXB_TC_TRACE)
+extern "C" __attribute__((visibility("default"))) int sxb_debug_tc_stamp(long long *out) {
+    cudaMemcpyFromSymbol(out, g_tc_stamp, sizeof(long long) * 64 * 8);
+    return 0;
+}
+extern "C" __attribute__((visibility("default"))) int sxb_debug_tc_trace8(long long *out) {
+    cudaMemcpyFromSymbol(out, g_tc_trace8, sizeof(long long) * 8 * 64);
+    return 0;
+}
 extern "C" __attribute__((visibility("default"))) int sxb_debug_tc_trace(long long *out) {
     cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(long long) * 4 * 64 * 2);
     return 0;
