@@ -39,7 +39,7 @@ __device__ long long g_tc_trace[4][64][2];  // role (A, B, MMA, -), k-block inde
 __device__ long long g_tc_trace8[8][64];    // arrival time of every A warp, per k-block of CTA 0
 __device__ long long g_tc_stamp[64][8];     // fine-grained stamps of the first A warp, per k-block of CTA 0
 #define STAMP(idx, which) \
-    do { if (blockIdx.x == 0 && warp == kFirstAWarp && lane == 0 && (idx) < 64) g_tc_stamp[idx][which] = clock64(); } while (0)
+    do { if (blockIdx.x == 0 && (warp & 3) == (kFirstAWarp & 3) && lane == 0 && (idx) < 64) g_tc_stamp[idx][which] = clock64(); } while (0)
 #define TRACE(role, idx, which) \
     do { if (blockIdx.x == 0 && lane == 0 && (idx) < 64) g_tc_trace[role][idx][which] = clock64(); } while (0)
 #else
@@ -337,10 +337,10 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
     volatile int *abort_v = &abort_flag;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], kAWarps + (a.x_kind == 3 ? 1 : kBWarps)), mbar_init(&empty_bar[s], kMmaWarps);
+        for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], kAWarps / 2 + (a.x_kind == 3 ? 1 : kBWarps)), mbar_init(&empty_bar[s], kMmaWarps);
         mbar_init(&acc_full[0], kMmaWarps), mbar_init(&acc_empty[0], kEpiWarps);
         mbar_init(&drain_bar, kMmaWarps);
-        for (int s = 0; s < kWSlots; ++s) mbar_init(&w_full[s], 1), mbar_init(&w_empty[s], kAWarps);
+        for (int s = 0; s < kWSlots; ++s) mbar_init(&w_full[s], 1), mbar_init(&w_empty[s], BITS == 4 ? kAWarps : kAWarps / 2);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -392,39 +392,45 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
 
     if (warp >= kFirstAWarp && warp < kFirstBWarp) {
         // ===================== A producers: weights =====================
-        // A thread owns one weight row of the item and writes it into its own tensor-memory lane; a warp may only touch
-        // the lane quadrant warp % 4, so the row is (accumulator, quadrant, lane).  The packed codes arrive in shared memory
-        // by tensor copies of 64 bytes x 128 rows (one per accumulator, two per ring slot), so that the memory pipe sees a
-        // handful of instructions per k-block instead of one 128-byte line per thread: 256 scattered lines per load
-        // instruction kept the load/store unit busy for thousands of cycles and held up every other warp's MMA issue.
-        const int a_half = (warp - kFirstAWarp) >> 2, a_quad = warp & 3;
-        const int p = a_half * 128 + a_quad * 32 + lane;  // weight row of the item, 0..255
-        constexpr int kKbPerChunk = G / 8;                // k-blocks covered by eight scale groups (one 16-byte load)
+        // A thread writes weight rows into its own tensor-memory lane; a warp may only touch the lane quadrant warp % 4.
+        // Each quadrant has two producer warps and they split the k-blocks, not the rows: the warp of parity 0 takes the
+        // even k-blocks, the other the odd ones, and a thread dequantizes BOTH rows of its lane (accumulator 0's and
+        // accumulator 1's).  The two warps that share an SM sub-partition are thereby out of step - while one is in the
+        // long dependent chain of barrier polls and hand-over, the other has the arithmetic pipes to itself - and a
+        // warp's fixed per-k-block latencies are paid once per two k-blocks of the pipeline.
+        // The packed codes arrive in shared memory by tensor copies of 64 bytes x 128 rows (one per accumulator, two per
+        // ring slot), so the memory pipe sees a handful of instructions per k-block instead of one 128-byte line per
+        // thread: 256 scattered lines per load instruction kept the load/store unit busy for thousands of cycles and
+        // held up every other warp's MMA issue.
+        const int a_par = (warp - kFirstAWarp) >> 2, a_quad = warp & 3;
+        const int p0 = a_quad * 32 + lane;    // row inside either accumulator, 0..127
+        constexpr int kKbPerChunk = G / 8;    // k-blocks covered by eight scale groups (one 16-byte load)
         constexpr int kGroupsPerKb = G >= kBK ? 1 : kBK / G;
+        constexpr int kCodeRegs = BITS == 4 ? 2 : 4;  // 16-byte chunks of codes per row and k-block
         const bool vec_scales = groups % 8 == 0 && ((reinterpret_cast<uintptr_t>(a.scale) | reinterpret_cast<uintptr_t>(a.minv)) & 15) == 0;
-        // this thread's 64 bytes inside a slot: row (p % 128) of its accumulator's box, 16-byte chunks swizzled (64-byte mode)
-        const uint32_t my_w = (uint32_t)(a_half * (kWSlotBytes / 2) + (p & 127) * 64), my_sw = (uint32_t)(((p & 127) >> 1) & 3);
+        // this thread's 64 bytes of row p0 inside a box of a slot; 16-byte chunks swizzled (64-byte mode)
+        const uint32_t my_w = (uint32_t)(p0 * 64), my_sw = (uint32_t)((p0 >> 1) & 3);
 
         struct Row {
             int64_t wrow;  // row of the stacked weight
             bool valid;
         };
-        auto row_of = [&](int item) {
+        auto row_of = [&](int item, int h) {
             Row r{0, false};
             if (item >= n_items) return r;
             const ItemInfo it = item_info<MODE>(a, item, rbs);
             if (MODE == kTcSwiglu) {
-                const int64_t I = a.N / 2, j = (int64_t)it.rb * 128 + (p & 127);
+                const int64_t I = a.N / 2, j = (int64_t)it.rb * 128 + p0;
                 r.valid = j < I;
-                r.wrow = (int64_t)it.bucket * a.N + (p < 128 ? j : I + j);
+                r.wrow = (int64_t)it.bucket * a.N + (h == 0 ? j : I + j);
             } else {
-                const int64_t rr = (int64_t)it.rb * kAThreads + p;
+                const int64_t rr = (int64_t)it.rb * kAThreads + h * 128 + p0;
                 r.valid = rr < a.N;
                 r.wrow = (int64_t)it.bucket * a.N + rr;
             }
             return r;
         };
-        // Scales and mins of eight consecutive groups of the row (BF16 bits), fetched one chunk ahead of use.
+        // Scales and mins of eight consecutive groups of a row (BF16 bits), fetched one chunk ahead of use.
         struct ScaleChunk {
             uint4 s, m;
         };
@@ -448,80 +454,75 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
             const uint32_t w = (g & 4) ? ((g & 2) ? v.w : v.z) : ((g & 2) ? v.y : v.x);
             return (uint16_t)((g & 1) ? (w >> 16) : (w & 0xffffu));
         };
-
-        // Loop shape.  A producer warp is never waiting for the MMA warps (it is the slower side), so every barrier poll
-        // and every wait for the tensor-memory stores is latency, and the two are made to overlap: right after the
-        // stores of k-block kb are issued, lane 0 polls what the NEXT step needs (its stage, and at a slot boundary the
-        // next slot of codes), and only then does the warp wait for the stores and hand kb over.  The stores' source
-        // registers must stay untouched until that wait, which is why no more than one k-block's stores are in flight.
-        uint32_t it_count = 0;  // k-blocks produced so far (stage / phase bookkeeping)
-        uint32_t w_count = 0;   // code slots consumed so far
-        int item = next_valid_item<MODE>(a, blockIdx.x, n_items, rbs);
-        Row row = row_of(item);
-        ScaleChunk sc_cur{}, sc_nxt{};
-        if (item < n_items) sc_nxt = load_scales(row, 0);
         auto top_up = [&](uint32_t upto) {  // lane 0 of the first A warp, when no thread of its own runs the ring
             while (issued < upto + (uint32_t)kWSlots && is_item < n_items)
                 if (!issue_one()) break;
         };
-        auto poll_slot = [&](uint32_t wc, int it_for_status) {  // lane 0
+        // lane 0: the codes of slot number wc have landed and the stage of k-block number cnt is free
+        auto poll = [&](uint32_t wc, uint32_t cnt, int it_for_status) {
+            if (!own_w_thread && warp == kFirstAWarp) top_up(wc);
             if (!mbar_wait(&w_full[wc % kWSlots], (wc / kWSlots) & 1u, abort_v)) raise_abort(it_for_status, 7);
+            else if (!mbar_wait(&empty_bar[cnt % kStages], ((cnt / kStages) & 1u) ^ 1u, abort_v)) raise_abort(it_for_status, 1);
         };
-        auto poll_stage = [&](uint32_t cnt, int it_for_status) {  // lane 0
-            if (!mbar_wait(&empty_bar[cnt % kStages], ((cnt / kStages) & 1u) ^ 1u, abort_v)) raise_abort(it_for_status, 1);
-        };
-        if (item < n_items && lane == 0) {
-            if (!own_w_thread && warp == kFirstAWarp) top_up(0);
-            poll_slot(0, item);
-            poll_stage(0, item);
-        }
+
+        // This warp's k-blocks of an item: kb = a_par, a_par + 2, ...; k-block kb lives in slot kb / kKbPerSlot.
+        // Right after the stores of one k-block are issued, lane 0 polls what the warp's NEXT k-block needs, and only then
+        // does the warp wait for the stores and hand the k-block over.  The stores' source registers must stay untouched
+        // until that wait, hence one row's stores in flight at a time.
+        int item = next_valid_item<MODE>(a, blockIdx.x, n_items, rbs);
+        uint32_t kb_base = 0, w_base_count = 0;  // k-blocks / slots of the items before this one
+        Row row[2] = {row_of(item, 0), row_of(item, 1)};
+        ScaleChunk sc_cur[2] = {}, sc_nxt[2] = {};
+        if (item < n_items) sc_nxt[0] = load_scales(row[0], 0), sc_nxt[1] = load_scales(row[1], 0);
+        if (item < n_items && lane == 0) poll((uint32_t)(a_par / kKbPerSlot), (uint32_t)a_par, item);
         __syncwarp();
         bool live = true;
         while (item < n_items && live && !*abort_v) {
             const int next = next_valid_item<MODE>(a, item + gridDim.x, n_items, rbs);
-            const Row next_row = row_of(next);
-            for (int sl = 0; sl < n_slots && live; ++sl, ++w_count) {
-                // the slot's codes have landed (polled under the previous k-block's stores)
-                const int slot = w_count % kWSlots;
-                STAMP(it_count, 0);
-                uint4 code[4];
+            const Row next_row[2] = {row_of(next, 0), row_of(next, 1)};
+            for (int kb = a_par; kb < n_kb; kb += 2) {
+                const uint32_t cnt = kb_base + (uint32_t)kb, wc = w_base_count + (uint32_t)(kb / kKbPerSlot);
+                const int stage = cnt % kStages, slot = wc % kWSlots;
+                STAMP(cnt, 0);
+                if (kb % kKbPerChunk == a_par) {  // this warp's first k-block of a chunk of eight scale groups
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    code[c] = ld_shared_v4(w_base + (uint32_t)(slot * kWSlotBytes) + my_w + (((uint32_t)c ^ my_sw) << 4));
-                    if (!row.valid) code[c] = make_uint4(0u, 0u, 0u, 0u);
+                    for (int h = 0; h < 2; ++h) {
+                        sc_cur[h] = sc_nxt[h];
+                        if (kb - a_par + kKbPerChunk < n_kb) sc_nxt[h] = load_scales(row[h], kb / kKbPerChunk + 1);
+                        else if (next < n_items) sc_nxt[h] = load_scales(next_row[h], 0);
+                    }
                 }
+                // this k-block's codes of both rows (Q4: half of the slot's 64 bytes of a row; Q8: all of them)
+                uint4 code[2][kCodeRegs];
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int c = 0; c < kCodeRegs; ++c) {
+                        const uint32_t chunk = (uint32_t)((BITS == 4 ? (kb & 1) * 2 : 0) + c);
+                        code[h][c] = ld_shared_v4(w_base + (uint32_t)(slot * kWSlotBytes + h * (kWSlotBytes / 2)) + my_w + ((chunk ^ my_sw) << 4));
+                        if (!row[h].valid) code[h][c] = make_uint4(0u, 0u, 0u, 0u);
+                    }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&w_empty[slot]);  // the codes are in registers: the slot may be refilled
-                const int kb0 = sl * kKbPerSlot;
-                if (kb0 % kKbPerChunk == 0) {
-                    sc_cur = sc_nxt;
-                    if (kb0 + kKbPerChunk < n_kb) sc_nxt = load_scales(row, kb0 / kKbPerChunk + 1);
-                    else if (next < n_items) sc_nxt = load_scales(next_row, 0);
-                }
-                const int n_sub = min(kKbPerSlot, n_kb - kb0);
+                STAMP(cnt, 1);
+                PROF_BEGIN();
 #pragma unroll
-                for (int sub = 0; sub < kKbPerSlot; ++sub) {
-                    const int kb = kb0 + sub;
-                    if (sub >= n_sub) break;
-                    const int stage = it_count % kStages;
-                    if (warp == kFirstAWarp) TRACE(0, it_count, 0);
-                    STAMP(it_count, 1);
-                    PROF_BEGIN();
+                for (int h = 0; h < 2; ++h) {
                     __half2 s2[kGroupsPerKb], s16[kGroupsPerKb], m2[kGroupsPerKb];
 #pragma unroll
                     for (int gi = 0; gi < kGroupsPerKb; ++gi) {
                         const int g = ((kb * kBK) / G + gi) & 7;  // group inside the chunk of eight
-                        const float sf = bf16_bits_to_f32(pick16(sc_cur.s, g)), mf = bf16_bits_to_f32(pick16(sc_cur.m, g));
+                        const float sf = bf16_bits_to_f32(pick16(sc_cur[h].s, g)), mf = bf16_bits_to_f32(pick16(sc_cur[h].m, g));
                         s2[gi] = __float2half2_rn(sf), s16[gi] = __float2half2_rn(sf * 0.0625f), m2[gi] = __float2half2_rn(mf);
                     }
                     const uint32_t a_addr = tmem_base + ((uint32_t)(a_quad * 32) << 16) +
-                                            (uint32_t)(kAStageCol0 + stage * kAStageCols + a_half * (kBK / 2));
-                    // this thread's row: 64 codes -> 64 F16 = 32 tensor-memory columns of its lane, two stores of 16
+                                            (uint32_t)(kAStageCol0 + stage * kAStageCols + h * (kBK / 2));
+                    // a row: 64 codes -> 64 F16 = 32 tensor-memory columns of this lane, two stores of 16
 #pragma unroll
                     for (int hc = 0; hc < 2; ++hc) {
                         uint4 d[4];
                         if (BITS == 4) {
-                            const uint4 v = code[sub * 2 + hc];  // 32 codes
+                            const uint4 v = code[h][hc];  // 32 codes
                             const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                             for (int cc = 0; cc < 4; ++cc) {
@@ -529,7 +530,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
                                 d[cc] = dequant_q4_word(w4[cc], s2[gi], s16[gi], m2[gi]);
                             }
                         } else {
-                            const uint4 v0 = code[hc * 2], v1 = code[hc * 2 + 1];  // 2 x 16 codes
+                            const uint4 v0 = code[h][hc * 2], v1 = code[h][hc * 2 + 1];  // 2 x 16 codes
                             const uint32_t w8[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
 #pragma unroll
                             for (int cc = 0; cc < 4; ++cc) {
@@ -539,52 +540,46 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
                         }
                         tc_st16(a_addr + hc * 16, d);
                     }
-                    if (warp == kFirstAWarp) PROF_ADD(1);
-                    STAMP(it_count, 2);
-                    {
-                        PROF_BEGIN();
-                        // under the stores: what the next k-block needs
-                        if (lane == 0) {
-                            const bool slot_ends = sub + 1 >= n_sub;
-                            const bool more = !slot_ends || sl + 1 < n_slots || next < n_items;
-                            if (more) {
-                                if (slot_ends) {
-                                    if (!own_w_thread && warp == kFirstAWarp) top_up(w_count + 1);
-                                    poll_slot(w_count + 1, item);
-                                }
-                                poll_stage(it_count + 1, item);
-                            }
-                        }
-                        if (warp == kFirstAWarp) PROF_ADD(0);
+                    if (h == 0) asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
+                if (warp == kFirstAWarp) PROF_ADD(1);
+                STAMP(cnt, 2);
+                {
+                    PROF_BEGIN();
+                    // under the last stores: what this warp's next k-block needs
+                    if (lane == 0) {
+                        if (kb + 2 < n_kb) poll(w_base_count + (uint32_t)((kb + 2) / kKbPerSlot), cnt + 2, item);
+                        else if (next < n_items) poll(w_base_count + (uint32_t)(n_slots + a_par / kKbPerSlot), kb_base + (uint32_t)(n_kb + a_par), next);
                     }
-                    STAMP(it_count, 3);
-                    {
-                        PROF_BEGIN();
-                        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                        STAMP(it_count, 4);
-                        tc_fence_before();  // orders the stores before the MMA warp's reads across the barrier
-                        __syncwarp();
-                        STAMP(it_count, 5);
-                        if (lane == 0) mbar_arrive(&full_bar[stage]);
-                        STAMP(it_count, 6);
+                    if (warp == kFirstAWarp) PROF_ADD(0);
+                }
+                STAMP(cnt, 3);
+                {
+                    PROF_BEGIN();
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    STAMP(cnt, 4);
+                    tc_fence_before();  // orders the stores before the MMA warp's reads across the barrier
+                    __syncwarp();
+                    tc_fence_after();   // and the next k-block's stores after the MMAs that freed its stage
+                    STAMP(cnt, 5);
+                    if (lane == 0) mbar_arrive(&full_bar[stage]);
+                    STAMP(cnt, 6);
 #if defined(SXB_TC_PROF) || defined(SXB_TC_TRACE)
-                        if (blockIdx.x == 0 && lane == 0 && it_count < 64) g_tc_trace8[warp - kFirstAWarp][it_count] = clock64();
+                    if (blockIdx.x == 0 && lane == 0 && cnt < 64) g_tc_trace8[warp - kFirstAWarp][cnt] = clock64();
 #endif
-                        if (warp == kFirstAWarp) {
-                            TRACE(0, it_count, 1);
-                            PROF_ADD(2);
-                            PROF_COUNT(4);
-                        }
-                    }
-                    ++it_count;
-                    if (*abort_v) {
-                        live = false;
-                        break;
+                    if (warp == kFirstAWarp) {
+                        PROF_ADD(2);
+                        PROF_COUNT(4);
                     }
                 }
+                if (*abort_v) {
+                    live = false;
+                    break;
+                }
             }
+            kb_base += (uint32_t)n_kb, w_base_count += (uint32_t)n_slots;
             item = next;
-            row = next_row;
+            row[0] = next_row[0], row[1] = next_row[1];
         }
     } else if (warp >= kFirstBWarp) {
         // ===================== B producers: activations =====================
