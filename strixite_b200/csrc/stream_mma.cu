@@ -84,6 +84,15 @@ template <int S> __device__ inline uint32_t nibble_pair(uint32_t w) {
     return r;
 }
 
+// Nibbles s and s + 4 of w as the BF16 pair (16 + n_s, 16 + n_{s+4}): the nibble lands in the top four of the seven
+// mantissa bits of 16.0 (0x4180), whose steps are 1/8, so the value is 16 + n exactly - a shift and a lop3, no subtract.
+// The 16s are taken out after the contraction: sum((16 + n) x) = sum(n x) + 16 sum(x), and sum(x) of the group is at hand
+// for the min term anyway.
+template <int S> __device__ inline uint32_t nibble_pair16(uint32_t w) {
+    const uint32_t sh = S == 0 ? (w << 3) : (w >> (4 * S - 3));
+    return (sh & 0x00780078u) | 0x41804180u;
+}
+
 __device__ inline uint32_t times16(uint32_t bf16x2) {
     __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162 *>(&bf16x2);
     v = __hmul2(v, __float2bfloat162_rn(16.f));
@@ -149,11 +158,14 @@ __device__ inline void stage_tile(const uint16_t *__restrict__ x, int K, const i
 
 // One warp: the dots of weight rows rowa / rowb (lane quad g streams both) with the staged tokens.
 // acc[0], acc[1] = row a x tokens 2c, 2c+1;  acc[2], acc[3] = row b x the same tokens.
-template <int BITS, int G>
-__device__ inline void rows_dot(float (&acc)[4], const StreamArgs &a, int64_t rowa, int64_t rowb, bool va, bool vb,
-                                const uint4 *xs, const float *xsum, int lane) {
+// VEC: a step is one quantization group and the row has a multiple of four groups, so the scales and mins of the four
+// steps of a prefetch block are one aligned 8-byte load each (four loads a block instead of sixteen 2-byte ones).
+template <int BITS, int G, bool VEC>
+__device__ inline void rows_dot_impl(float (&acc)[4], const StreamArgs &a, int64_t rowa, int64_t rowb, bool va, bool vb,
+                                     const uint4 *xs, const float *xsum, int lane) {
     using geo = Geo<BITS, G>;
     constexpr int W = geo::kWords, UNITS = geo::kUnits, KI = geo::kStepCodes;
+    static_assert(kPrefetch == 4, "the vector scale path loads four groups at a time");
     const int K = (int)a.K, steps = K / KI, groups = K / G, c = lane & 3;
     const int64_t row_bytes = BITS == 4 ? a.K / 2 : a.K;
     const uint8_t *pa = a.q + rowa * row_bytes + c * geo::kLoadBytes;
@@ -162,20 +174,33 @@ __device__ inline void rows_dot(float (&acc)[4], const StreamArgs &a, int64_t ro
     const uint16_t *sb = a.scale + rowb * groups, *mb = a.minv + rowb * groups;
 
     uint32_t wa[kPrefetch][W], wb[kPrefetch][W];
-    uint16_t qs[kPrefetch][4];
+    uint16_t qs[VEC ? 1 : kPrefetch][4];
+    uint2 qv[2][4];  // VEC: {scale a, min a, scale b, min b} of the block in use and of the next one
     auto fetch = [&](int slot, int step) {
         const bool in = step < steps;
         load_codes<W>(wa[slot], pa + (int64_t)step * 4 * geo::kLoadBytes, in && va);
         load_codes<W>(wb[slot], pb + (int64_t)step * 4 * geo::kLoadBytes, in && vb);
-        const int grp = step / geo::kStepsPerGroup;
-        qs[slot][0] = in && va ? __ldg(sa + grp) : (uint16_t)0;
-        qs[slot][1] = in && va ? __ldg(ma + grp) : (uint16_t)0;
-        qs[slot][2] = in && vb ? __ldg(sb + grp) : (uint16_t)0;
-        qs[slot][3] = in && vb ? __ldg(mb + grp) : (uint16_t)0;
+        if (!VEC) {
+            const int grp = step / geo::kStepsPerGroup;
+            qs[slot][0] = in && va ? __ldg(sa + grp) : (uint16_t)0;
+            qs[slot][1] = in && va ? __ldg(ma + grp) : (uint16_t)0;
+            qs[slot][2] = in && vb ? __ldg(sb + grp) : (uint16_t)0;
+            qs[slot][3] = in && vb ? __ldg(mb + grp) : (uint16_t)0;
+        }
     };
+    auto fetch_scales = [&](uint2 (&dst)[4], int step0) {  // VEC: the four groups step0 .. step0 + 3
+        const bool in = step0 < steps;
+        const uint2 z = make_uint2(0u, 0u);
+        dst[0] = in && va ? __ldg(reinterpret_cast<const uint2 *>(sa + step0)) : z;
+        dst[1] = in && va ? __ldg(reinterpret_cast<const uint2 *>(ma + step0)) : z;
+        dst[2] = in && vb ? __ldg(reinterpret_cast<const uint2 *>(sb + step0)) : z;
+        dst[3] = in && vb ? __ldg(reinterpret_cast<const uint2 *>(mb + step0)) : z;
+    };
+    if (VEC) fetch_scales(qv[0], 0);
 #pragma unroll
     for (int p = 0; p < kPrefetch; ++p) fetch(p, p);
     for (int step0 = 0; step0 < steps; step0 += kPrefetch) {
+        if (VEC) fetch_scales(qv[1], step0 + kPrefetch);
 #pragma unroll
         for (int p = 0; p < kPrefetch; ++p) {
             const int step = step0 + p;
@@ -187,8 +212,8 @@ __device__ inline void rows_dot(float (&acc)[4], const StreamArgs &a, int64_t ro
                     const uint4 bx = xu[v * 32];
                     if (BITS == 4) {
                         const uint32_t x0 = wa[p][v], x1 = wb[p][v];
-                        mma_bf16(d, nibble_pair<0>(x0), nibble_pair<0>(x1), nibble_pair<1>(x0), nibble_pair<1>(x1), bx.x, bx.y);
-                        mma_bf16(d, nibble_pair<2>(x0), nibble_pair<2>(x1), nibble_pair<3>(x0), nibble_pair<3>(x1), bx.z, bx.w);
+                        mma_bf16(d, nibble_pair16<0>(x0), nibble_pair16<0>(x1), nibble_pair16<1>(x0), nibble_pair16<1>(x1), bx.x, bx.y);
+                        mma_bf16(d, nibble_pair16<2>(x0), nibble_pair16<2>(x1), nibble_pair16<3>(x0), nibble_pair16<3>(x1), bx.z, bx.w);
                     } else {
                         const uint32_t bw[4] = {bx.x, bx.y, bx.z, bx.w};
 #pragma unroll
@@ -202,8 +227,15 @@ __device__ inline void rows_dot(float (&acc)[4], const StreamArgs &a, int64_t ro
                     }
                 }
                 const float2 xs2 = *reinterpret_cast<const float2 *>(xsum + step * kTileTokens + 2 * c);
-                const float s_a = bf16_bits_to_f32(qs[p][0]), m_a = bf16_bits_to_f32(qs[p][1]);
-                const float s_b = bf16_bits_to_f32(qs[p][2]), m_b = bf16_bits_to_f32(qs[p][3]);
+                uint16_t q4[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (VEC) q4[i] = (uint16_t)((p < 2 ? qv[0][i].x : qv[0][i].y) >> (16 * (p & 1)));
+                    else q4[i] = qs[p][i];
+                }
+                const float s_a = bf16_bits_to_f32(q4[0]), s_b = bf16_bits_to_f32(q4[2]);
+                float m_a = bf16_bits_to_f32(q4[1]), m_b = bf16_bits_to_f32(q4[3]);
+                if (BITS == 4) m_a = fmaf(-16.f, s_a, m_a), m_b = fmaf(-16.f, s_b, m_b);  // the 16s of nibble_pair16
                 acc[0] = fmaf(s_a, d[0], fmaf(m_a, xs2.x, acc[0]));
                 acc[1] = fmaf(s_a, d[1], fmaf(m_a, xs2.y, acc[1]));
                 acc[2] = fmaf(s_b, d[2], fmaf(m_b, xs2.x, acc[2]));
@@ -211,7 +243,22 @@ __device__ inline void rows_dot(float (&acc)[4], const StreamArgs &a, int64_t ro
             }
             fetch(p, step + kPrefetch);  // refill the slot just consumed
         }
+        if (VEC) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) qv[0][i] = qv[1][i];
+        }
     }
+}
+
+template <int BITS, int G>
+__device__ inline void rows_dot(float (&acc)[4], const StreamArgs &a, int64_t rowa, int64_t rowb, bool va, bool vb,
+                                const uint4 *xs, const float *xsum, int lane) {
+    using geo = Geo<BITS, G>;
+    const int groups = (int)(a.K / G);
+    const bool vec = geo::kStepsPerGroup == 1 && groups % 4 == 0 &&
+                     ((reinterpret_cast<uintptr_t>(a.scale) | reinterpret_cast<uintptr_t>(a.minv)) & 7) == 0;
+    if (vec) rows_dot_impl<BITS, G, true>(acc, a, rowa, rowb, va, vb, xs, xsum, lane);
+    else rows_dot_impl<BITS, G, false>(acc, a, rowa, rowb, va, vb, xs, xsum, lane);
 }
 
 template <int BITS, int G, int MODE, int SRC, typename TOUT>

@@ -15,13 +15,14 @@ pytestmark = pytest.mark.gpu
 FORMATS = [(4, 128), (4, 64), (4, 32), (8, 64), (8, 128), (8, 32)]
 
 
-def assert_bf16_close(got_bits, ref_bits, oracle, what, frac_off=5e-2):
+def assert_bf16_close(got_bits, ref_bits, oracle, what, frac_off=5e-2, ulps=1):
     """Both sides round nearly equal FP32 values to BF16: they agree except where the value sits on a rounding
     boundary (then one BF16 ulp apart), plus the FP32 summation-order noise (3e-5 of the output scale) that matters
-    only for outputs near zero."""
+    only for outputs near zero.  `ulps=2` is for the fused SwiGLU output, which is rounded three times (g and u as
+    stored, silu(g) as stored, their product): one flipped rounding of g or u can move h by two ulps."""
     got, ref = oracle.bf16_to_f32(got_bits).astype(np.float64), oracle.bf16_to_f32(ref_bits).astype(np.float64)
     scale = np.sqrt(np.mean(ref ** 2))
-    tol = np.abs(ref) * 2.0 ** -7 + 3e-5 * scale
+    tol = np.abs(ref) * ulps * 2.0 ** -7 + 3e-5 * scale
     bad = np.abs(got - ref) > tol
     assert not bad.any(), f"{what}: {bad.sum()} elements beyond one BF16 ulp, worst {np.abs(got - ref).max():.3e}"
     frac = (got_bits != ref_bits).mean()
@@ -115,7 +116,7 @@ def test_per_slot_experts(cuda, oracle, bits, G, M, A, E, N, Kd):
         assert list(err.cpu().numpy().view(np.uint32)[:3]) == [1, E + 2, A] == list(err_ref)
         assert np.all(np.isnan(oracle.bf16_to_f32(bits_of(y)[1, 0]))) and np.all(np.isnan(oracle.bf16_to_f32(bits_of(h)[1, 0])))
     assert_bf16_close(bits_of(y)[good], y_ref[good], oracle, "gather")
-    assert_bf16_close(bits_of(h)[good], h_ref[good], oracle, "gather_swiglu", frac_off=1e-2)
+    assert_bf16_close(bits_of(h)[good], h_ref[good], oracle, "gather_swiglu", frac_off=1e-2, ulps=2)
     # combine: h [M, A, K] -> y [M, N]; weights reused as a [E*N, K] down matrix
     hin = oracle.f32_to_bf16(rng.standard_normal((M, A, Kd)).astype(np.float32))
     yc = torch.empty((M, N), dtype=torch.float32, device=cuda)
@@ -173,7 +174,7 @@ def test_grouped_experts_exact_math(cuda, oracle, bits, G, M, A, E, I, d):
     g_ref = oracle.experts_gather(x, gu, E, ids, 0).reshape(M * A, -1)
     h_ref = oracle.experts_gather(x, gu, E, ids, 1).reshape(M * A, -1)
     assert_bf16_close(bits_of(g)[ok], g_ref[ok], oracle, "gather_grouped")
-    assert_bf16_close(bits_of(h)[ok], h_ref[ok], oracle, "gather_grouped_swiglu", frac_off=1e-2)
+    assert_bf16_close(bits_of(h)[ok], h_ref[ok], oracle, "gather_grouped_swiglu", frac_off=1e-2, ulps=2)
     assert np.all(np.isnan(oracle.bf16_to_f32(bits_of(h)[~ok])))
     # combine on the oracle's h so the two sides see identical inputs
     hd = bf16_tensor(h_ref, cuda)
