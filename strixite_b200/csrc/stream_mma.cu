@@ -69,6 +69,13 @@ template <> __device__ inline void load_codes<1>(uint32_t (&w)[1], const uint8_t
     if (pred) asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(w[0]) : "l"(p));
 }
 
+// D = A * B (no accumulator input: the zero operand needs no registers set up).
+__device__ inline void mma_bf16_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
 __device__ inline void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -250,6 +257,88 @@ __device__ inline void rows_dot_impl(float (&acc)[4], const StreamArgs &a, int64
     }
 }
 
+// The common shape, kept lean because the kernel saturates the integer pipe before HBM: a step is one group, the row has
+// a whole number of four-step blocks, scales and mins come by aligned 8-byte loads.  No per-load predicates (a row past
+// the end of the expert is replaced by a row that exists; its sums are dropped by the caller), pointers advance by
+// increments, the last block is peeled so nothing is fetched past the end of a row, and a step's first MMA takes a
+// zero accumulator operand instead of cleared registers.
+template <int BITS, int G>
+__device__ inline void rows_dot_fast(float (&acc)[4], const StreamArgs &a, int64_t rowa, int64_t rowb, const uint4 *xs,
+                                     const float *xsum, int lane) {
+    using geo = Geo<BITS, G>;
+    constexpr int W = geo::kWords, UNITS = geo::kUnits, KI = geo::kStepCodes;
+    constexpr int kBlockBytes = kPrefetch * 4 * geo::kLoadBytes;  // bytes of one row consumed per block of four steps
+    const int K = (int)a.K, blocks = K / (KI * kPrefetch), groups = K / G, c = lane & 3;
+    const int64_t row_bytes = BITS == 4 ? a.K / 2 : a.K;
+    const uint8_t *pa = a.q + rowa * row_bytes + c * geo::kLoadBytes;
+    const uint8_t *pb = a.q + rowb * row_bytes + c * geo::kLoadBytes;
+    const uint2 *sa = reinterpret_cast<const uint2 *>(a.scale + rowa * groups), *ma = reinterpret_cast<const uint2 *>(a.minv + rowa * groups);
+    const uint2 *sb = reinterpret_cast<const uint2 *>(a.scale + rowb * groups), *mb = reinterpret_cast<const uint2 *>(a.minv + rowb * groups);
+    const uint4 *xu = xs + lane;
+    const float *xq = xsum + 2 * c;
+
+    uint32_t wa[kPrefetch][W], wb[kPrefetch][W];
+    uint2 qv[4], qn[4];  // {scale a, min a, scale b, min b} of the block in use / of the next one
+    auto fetch_codes = [&](int p) {  // step p of the block pa / pb point at
+        load_codes<W>(wa[p], pa + p * 4 * geo::kLoadBytes, true);
+        load_codes<W>(wb[p], pb + p * 4 * geo::kLoadBytes, true);
+    };
+    auto fetch_scales = [&](uint2 (&dst)[4]) { dst[0] = __ldg(sa), dst[1] = __ldg(ma), dst[2] = __ldg(sb), dst[3] = __ldg(mb); };
+    auto consume = [&](int p) {
+        float d[4];
+#pragma unroll
+        for (int v = 0; v < UNITS; ++v) {
+            const uint4 bx = xu[(p * UNITS + v) * 32];
+            if (BITS == 4) {
+                const uint32_t x0 = wa[p][v], x1 = wb[p][v];
+                if (v == 0) mma_bf16_first(d, nibble_pair16<0>(x0), nibble_pair16<0>(x1), nibble_pair16<1>(x0), nibble_pair16<1>(x1), bx.x, bx.y);
+                else mma_bf16(d, nibble_pair16<0>(x0), nibble_pair16<0>(x1), nibble_pair16<1>(x0), nibble_pair16<1>(x1), bx.x, bx.y);
+                mma_bf16(d, nibble_pair16<2>(x0), nibble_pair16<2>(x1), nibble_pair16<3>(x0), nibble_pair16<3>(x1), bx.z, bx.w);
+            } else {
+                const uint32_t bw[4] = {bx.x, bx.y, bx.z, bx.w};
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t x0 = wa[p][2 * v + h], x1 = wb[p][2 * v + h];
+                    if (v == 0 && h == 0)
+                        mma_bf16_first(d, nibble_pair<0>(x0), nibble_pair<0>(x1), nibble_pair<1>(x0), nibble_pair<1>(x1), bw[0], times16(bw[0]));
+                    else
+                        mma_bf16(d, nibble_pair<0>(x0), nibble_pair<0>(x1), nibble_pair<1>(x0), nibble_pair<1>(x1), bw[2 * h], times16(bw[2 * h]));
+                    mma_bf16(d, nibble_pair<2>(x0), nibble_pair<2>(x1), nibble_pair<3>(x0), nibble_pair<3>(x1), bw[2 * h + 1],
+                             times16(bw[2 * h + 1]));
+                }
+            }
+        }
+        const float2 xs2 = *reinterpret_cast<const float2 *>(xq + p * kTileTokens);
+        // BF16 bits -> FP32: the upper half of the word as it is, the lower half shifted up
+        auto f32_of = [&](const uint2 &q) { const uint32_t w = p < 2 ? q.x : q.y; return __uint_as_float((p & 1) ? (w & 0xffff0000u) : (w << 16)); };
+        const float s_a = f32_of(qv[0]), s_b = f32_of(qv[2]);
+        float m_a = f32_of(qv[1]), m_b = f32_of(qv[3]);
+        if (BITS == 4) m_a = fmaf(-16.f, s_a, m_a), m_b = fmaf(-16.f, s_b, m_b);  // the 16s of nibble_pair16
+        acc[0] = fmaf(s_a, d[0], fmaf(m_a, xs2.x, acc[0]));
+        acc[1] = fmaf(s_a, d[1], fmaf(m_a, xs2.y, acc[1]));
+        acc[2] = fmaf(s_b, d[2], fmaf(m_b, xs2.x, acc[2]));
+        acc[3] = fmaf(s_b, d[3], fmaf(m_b, xs2.y, acc[3]));
+    };
+
+    fetch_scales(qv);
+#pragma unroll
+    for (int p = 0; p < kPrefetch; ++p) fetch_codes(p);
+    for (int b = 1; b < blocks; ++b) {  // consume block b - 1, fetching block b into the registers it frees
+        pa += kBlockBytes, pb += kBlockBytes, ++sa, ++ma, ++sb, ++mb;
+        fetch_scales(qn);
+#pragma unroll
+        for (int p = 0; p < kPrefetch; ++p) {
+            consume(p);
+            fetch_codes(p);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) qv[i] = qn[i];
+        xu += kPrefetch * UNITS * 32, xq += kPrefetch * kTileTokens;
+    }
+#pragma unroll
+    for (int p = 0; p < kPrefetch; ++p) consume(p);
+}
+
 template <int BITS, int G>
 __device__ inline void rows_dot(float (&acc)[4], const StreamArgs &a, int64_t rowa, int64_t rowb, bool va, bool vb,
                                 const uint4 *xs, const float *xsum, int lane) {
@@ -257,8 +346,13 @@ __device__ inline void rows_dot(float (&acc)[4], const StreamArgs &a, int64_t ro
     const int groups = (int)(a.K / G);
     const bool vec = geo::kStepsPerGroup == 1 && groups % 4 == 0 &&
                      ((reinterpret_cast<uintptr_t>(a.scale) | reinterpret_cast<uintptr_t>(a.minv)) & 7) == 0;
-    if (vec) rows_dot_impl<BITS, G, true>(acc, a, rowa, rowb, va, vb, xs, xsum, lane);
-    else rows_dot_impl<BITS, G, false>(acc, a, rowa, rowb, va, vb, xs, xsum, lane);
+    if (vec && geo::kStepsPerGroup == 1) {
+        // rows past the end of the expert: stream a row that exists instead (the caller drops their sums)
+        const int64_t any = va ? rowa : vb ? rowb : 0;
+        rows_dot_fast<BITS, G>(acc, a, va ? rowa : any, vb ? rowb : any, xs, xsum, lane);
+    } else {
+        rows_dot_impl<BITS, G, false>(acc, a, rowa, rowb, va, vb, xs, xsum, lane);
+    }
 }
 
 template <int BITS, int G, int MODE, int SRC, typename TOUT>
