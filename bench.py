@@ -45,6 +45,7 @@ def parse():
     ap.add_argument("--cpu-tokens", type=int, default=0, help="tokens of the CPU baseline sample (default by workload)")
     ap.add_argument("--experts", type=int, default=0, help="override the expert count (profiling on a small case)")
     ap.add_argument("--tokens", type=int, default=0, help="override the token count (profiling on a small case)")
+    ap.add_argument("--no-graph", action="store_true", help="decode workloads: launch eagerly instead of replaying CUDA graphs")
     ap.add_argument("--seed", type=int, default=0)
     return ap.parse_args()
 
@@ -264,6 +265,33 @@ def run_stack(cfg, args, dev, rank, world, peaks, layers=None, rotate=False):
     for ly in st.layers[:1]:
         ly.check_errors(cfg.name)
 
+    graphs = None
+    if rotate and world == 1 and not args.no_graph:
+        # Decode: a layer is eight short launches, and the gaps between them are a tenth of the step.  Every layer's launch
+        # sequence (all of it goes to the caller's stream through the C ABI) is captured once into a CUDA graph over static
+        # buffers and replayed; the kernels and their arguments are those of the eager path.
+        for l in range(layers):  # every layer eagerly once more: lazy initialisation must not fall inside a capture
+            st.one_layer(l, x_dev)
+        torch.cuda.synchronize()
+        x_dev.copy_(x_loc)
+        graphs = []
+        for l in range(layers):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                y_l = st.one_layer(l, x_dev)
+            graphs.append((g, y_l))
+
+        def device_step():  # noqa: F811  (replaces the eager step above)
+            graphs[counter["i"] % layers][0].replay()
+            counter["i"] += 1
+
+        def e2e_step():  # noqa: F811
+            x_dev.copy_(x_host, non_blocking=True)
+            g, y_l = graphs[counter["i"] % layers]
+            g.replay()
+            counter["i"] += 1
+            y_host.copy_(y_l.to(torch.bfloat16), non_blocking=True)
+
     with ClockSampler(dev.index or 0) as clocks:
         st.events = ([], [])
         ms = timed(device_step, args.steps, args.warmup, dist_on, dev)
@@ -274,6 +302,13 @@ def run_stack(cfg, args, dev, rank, world, peaks, layers=None, rotate=False):
         ev = (ev[0][per_step * args.warmup:], ev[1][per_step * args.warmup:])
         k_ms = kernel_ms(ev)
         e2e_ms = timed(e2e_step, args.steps, 1, dist_on, dev)
+        if graphs is not None:  # the dominant kernel's own time: a few eager layers with events around it
+            st.events = ([], [])
+            for i in range(2 * layers):
+                st.one_layer(i % layers, x_loc)
+            torch.cuda.synchronize()
+            k_ms = kernel_ms((st.events[0][layers:], st.events[1][layers:]))
+            st.events = None
     layer_tokens = cfg.T * (1 if rotate else layers)
     out = dict(
         ms_per_step=ms, value=layer_tokens / (ms * 1e-3), e2e_value=layer_tokens / (e2e_ms * 1e-3), e2e_ms=e2e_ms,
