@@ -69,29 +69,42 @@ template <> __device__ inline void load_codes<1>(uint32_t (&w)[1], const uint8_t
     if (pred) asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(w[0]) : "l"(p));
 }
 
-// D = C + A * B, m16n8k32: A 16 rows x 32 k of unsigned bytes (the codes), B 32 k x 8 columns of signed bytes (one byte
-// plane of the activations), 32-bit integer sums - exact.
-__device__ inline void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+// D = A * B (no accumulator input: the zero operand needs no registers set up).
+__device__ inline void mma_bf16_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+__device__ inline void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-// The same with every accumulator input equal to `c` (no registers to set up for the first MMA of a chain).
-__device__ inline void mma_u8s8_first(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1, int c) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c));
-}
-// Integer sums start from the bit pattern of 1.5 * 2^23: while |sum| < 2^22 the accumulator, read as a float, IS
-// 12582912 + sum exactly, so the conversion to floating point is one subtraction on the FMA pipe, not a conversion
-// instruction.  (A step's sums stay below 128 * 15 * 128 for Q4 and 64 * 255 * 128 = 2.09e6 for Q8.)
-constexpr int kMagicBits = 0x4B400000;
-constexpr float kMagic = 12582912.f;
-__device__ inline float sum_as_f32(int d) { return __int_as_float(d) - kMagic; }
 
-constexpr int kPlanes = 3;
+// Nibbles s and s + 4 of w as the BF16 pair (n_s, n_{s+4}): `(w >> 4s) & 0x000F000F | 0x43004300` is the pair
+// (128 + n_s, 128 + n_{s+4}) exactly (BF16 keeps 8 significant bits), and one packed subtract removes the 128s.
+template <int S> __device__ inline uint32_t nibble_pair(uint32_t w) {
+    uint32_t v = ((w >> (4 * S)) & 0x000F000Fu) | 0x43004300u, r;
+    asm("sub.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(0x43004300u));
+    return r;
+}
+
+// Nibbles s and s + 4 of w as the BF16 pair (16 + n_s, 16 + n_{s+4}): the nibble lands in the top four of the seven
+// mantissa bits of 16.0 (0x4180), whose steps are 1/8, so the value is 16 + n exactly - a shift and a lop3, no subtract.
+// The 16s are taken out after the contraction: sum((16 + n) x) = sum(n x) + 16 sum(x), and sum(x) of the group is at hand
+// for the min term anyway.
+template <int S> __device__ inline uint32_t nibble_pair16(uint32_t w) {
+    const uint32_t sh = S == 0 ? (w << 3) : (w >> (4 * S - 3));
+    return (sh & 0x00780078u) | 0x41804180u;
+}
+
+__device__ inline uint32_t times16(uint32_t bf16x2) {
+    __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162 *>(&bf16x2);
+    v = __hmul2(v, __float2bfloat162_rn(16.f));
+    return *reinterpret_cast<uint32_t *>(&v);
+}
 
 struct StreamArgs {
     const uint16_t *x;  // BF16 activations: x [M, K] (gather / dense) or h [M*A, K] (partial)
@@ -109,207 +122,160 @@ struct StreamArgs {
 
 template <typename T> __device__ inline void store_out(T *p, int64_t i, float v) { store_from_f32(p, i, v); }
 
-// Shared memory of one staged tile (<= 8 tokens), for K codes a row:
-//   planes  [step][chunk][plane][lane] uint2   the B fragments of the integer MMAs
-//   xsum    [step][token] float                sum of the token's activations over the step (for the min term)
-//   xscale  [step][token] float                2^(e - 21): what one unit of the token's fixed-point activations is worth
-//   xmult   [step][token] float                2^-e (staging only)
+// Stages up to 8 activation rows (rows[n] < 0 = none, zeros) into fragment order at xs / xsum.  All threads of the CTA.
 template <int BITS, int G>
-struct TileSmem {
-    using geo = Geo<BITS, G>;
-    __host__ __device__ static size_t plane_bytes(int64_t K) { return (size_t)(K / geo::kStepCodes) * geo::kUnits * kPlanes * 256; }
-    __host__ __device__ static size_t bytes(int64_t K) { return plane_bytes(K) + (size_t)(K / geo::kStepCodes) * kTileTokens * 4 * 3; }
-};
-
-// Stages up to 8 activation rows (rows[n] < 0 = none, zeros) at `base`.  All threads of the CTA.
-//
-// The activations of a (token, step) - a step is at most one quantization group - become 23-bit fixed point relative to
-// the largest of them: X = trunc(x * 2^(21 - e)), e the exponent of the step's largest |x|, so |X| < 2^22 and a BF16 value
-// (8 significant bits) is held exactly unless it is more than 2^14 times smaller than that largest one - what is cut off
-// is below 2^-21 of it, the size of an FP32 rounding of the step's sum.  X is split into three signed bytes
-// (X = P2 * 65536 + P1 * 256 + P0, P0 and P1 in [-128, 127], hence |P2| <= 65: the balanced digits carry upwards, which
-// is why X stops one bit short of 2^23); each byte plane meets the codes in an integer MMA.
-template <int BITS, int G>
-__device__ inline void stage_tile(const uint16_t *__restrict__ x, int K, const int64_t *rows, unsigned char *base) {
+__device__ inline void stage_tile(const uint16_t *__restrict__ x, int K, const int64_t *rows, uint4 *xs, float *xsum) {
     using geo = Geo<BITS, G>;
     constexpr int UNITS = geo::kUnits, KI = geo::kStepCodes, CPL = geo::kCodesPerLane;
     const int units_per_row = K / 8, steps = K / KI;
-    uint2 *planes = reinterpret_cast<uint2 *>(base);
-    float *xsum = reinterpret_cast<float *>(base + TileSmem<BITS, G>::plane_bytes(K));
-    float *xscale = xsum + steps * kTileTokens, *xmult = xscale + steps * kTileTokens;
-    // pass 1: per (step, token) the sum (fixed order), the largest magnitude, finiteness
+    // 8 consecutive k of token n (16 bytes) -> one unit, permuted to match the nibble pairs of the weights.
+    for (int idx = threadIdx.x; idx < kTileTokens * units_per_row; idx += kThreads) {
+        const int n = idx / units_per_row, k8 = idx % units_per_row;
+        const int k = k8 * 8, step = k / KI, rem = k % KI, cc = rem / CPL, v = (rem % CPL) / 8;
+        uint4 src = make_uint4(0u, 0u, 0u, 0u);
+        const int64_t row = rows[n];
+        if (row >= 0) src = *reinterpret_cast<const uint4 *>(x + row * K + k);
+        uint4 dst;
+        if (BITS == 4) {  // [x0 x4 | x1 x5 | x2 x6 | x3 x7]
+            dst.x = __byte_perm(src.x, src.z, 0x5410), dst.y = __byte_perm(src.x, src.z, 0x7632);
+            dst.z = __byte_perm(src.y, src.w, 0x5410), dst.w = __byte_perm(src.y, src.w, 0x7632);
+        } else {  // [x0 x2 | x1 x3 | x4 x6 | x5 x7]
+            dst.x = __byte_perm(src.x, src.y, 0x5410), dst.y = __byte_perm(src.x, src.y, 0x7632);
+            dst.z = __byte_perm(src.z, src.w, 0x5410), dst.w = __byte_perm(src.z, src.w, 0x7632);
+        }
+        xs[(step * UNITS + v) * 32 + n * 4 + cc] = dst;
+    }
+    // sum(x) of every (step, token), in a fixed order.
     for (int idx = threadIdx.x; idx < steps * kTileTokens; idx += kThreads) {
         const int step = idx / kTileTokens, n = idx % kTileTokens;
         const int64_t row = rows[n];
         float sum = 0.f;
-        uint32_t mag = 0u;
         if (row >= 0) {
             const uint4 *p = reinterpret_cast<const uint4 *>(x + row * K + (int64_t)step * KI);
             for (int i = 0; i < KI / 8; ++i) {
                 const uint4 u = p[i];
                 const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    sum += __uint_as_float(w4[j] << 16), sum += __uint_as_float(w4[j] & 0xffff0000u);
-                    mag = max(mag, max(w4[j] & 0x7fffu, (w4[j] >> 16) & 0x7fffu));  // BF16 magnitudes order like their bits
-                }
+                for (int j = 0; j < 4; ++j) sum += __uint_as_float(w4[j] << 16), sum += __uint_as_float(w4[j] & 0xffff0000u);
             }
         }
-        // exponent field of the largest magnitude, kept where both 2^(e - 22) and its inverse are normal floats
-        const int ef = min(max((int)(mag >> 7), 22), 254);
-        const bool finite = (mag >> 7) != 0xffu;
         xsum[idx] = sum;
-        xscale[idx] = finite ? __int_as_float((ef - 21) << 23) : qnan_f32();  // 2^(ef - 127 - 21)
-        xmult[idx] = finite ? __int_as_float((275 - ef) << 23) : 0.f;          // its inverse
     }
-    __syncthreads();
-    // pass 2: 8 consecutive k of token n -> one 8-byte B-fragment entry per plane
-    for (int idx = threadIdx.x; idx < kTileTokens * units_per_row; idx += kThreads) {
-        const int n = idx / units_per_row, k8 = idx % units_per_row;
-        const int k = k8 * 8, step = k / KI, rem = k % KI, cc = rem / CPL, v = (rem % CPL) / 8;
-        const int64_t row = rows[n];
-        int X[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (row >= 0) {
-            const uint4 src = *reinterpret_cast<const uint4 *>(x + row * K + k);
-            const float mult = xmult[step * kTileTokens + n];
-            const uint32_t w4[4] = {src.x, src.y, src.z, src.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                X[2 * j] = __float2int_rz(__uint_as_float(w4[j] << 16) * mult);
-                X[2 * j + 1] = __float2int_rz(__uint_as_float(w4[j] & 0xffff0000u) * mult);
-            }
-        }
-        // fragment order: an MMA's b0 meets the codes of a0, b1 those of a2.  Q4: a0 = the even nibbles of a word of
-        // codes, a2 = the odd ones.  Q8: a0 = the first four codes of the eight, a2 = the other four.
-        int o[8];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            o[i] = BITS == 4 ? X[2 * i] : X[i];
-            o[4 + i] = BITS == 4 ? X[2 * i + 1] : X[4 + i];
-        }
-        uint32_t b[kPlanes][2];
-#pragma unroll
-        for (int pl = 0; pl < kPlanes; ++pl) b[pl][0] = b[pl][1] = 0u;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            int r = o[i];
-#pragma unroll
-            for (int pl = 0; pl < kPlanes; ++pl) {
-                const int byte = (int)(signed char)(r & 0xff);  // balanced digit in [-128, 127]
-                b[pl][i >> 2] |= (uint32_t)(byte & 0xff) << (8 * (i & 3));
-                r = (r - byte) >> 8;
-            }
-        }
-        uint2 *dst = planes + (size_t)((step * UNITS + v) * kPlanes) * 32 + n * 4 + cc;
-#pragma unroll
-        for (int pl = 0; pl < kPlanes; ++pl) dst[pl * 32] = make_uint2(b[pl][0], b[pl][1]);
-    }
-}
-
-// The integer MMAs of one step for this lane: acc-ready sums d[plane][i], i = {row a x token 2c, row a x token 2c+1,
-// row b x token 2c, row b x token 2c+1}.  wa / wb: the lane's codes of rows a / b for the step.
-template <int BITS, int G>
-__device__ inline void step_mmas(int (&d)[kPlanes][4], const uint32_t (&wa)[Geo<BITS, G>::kWords], const uint32_t (&wb)[Geo<BITS, G>::kWords],
-                                 const uint2 *xp /* planes + (step * UNITS) * kPlanes * 32 + lane */) {
-    using geo = Geo<BITS, G>;
-#pragma unroll
-    for (int v = 0; v < geo::kUnits; ++v) {
-        uint32_t a0, a1, a2, a3;
-        if (BITS == 4) {  // a word = 8 nibbles: the even ones as four bytes, the odd ones as four bytes
-            a0 = wa[v] & 0x0f0f0f0fu, a2 = (wa[v] >> 4) & 0x0f0f0f0fu;
-            a1 = wb[v] & 0x0f0f0f0fu, a3 = (wb[v] >> 4) & 0x0f0f0f0fu;
-        } else {          // the bytes are the codes
-            a0 = wa[2 * v], a2 = wa[2 * v + 1];
-            a1 = wb[2 * v], a3 = wb[2 * v + 1];
-        }
-#pragma unroll
-        for (int pl = 0; pl < kPlanes; ++pl) {
-            const uint2 b = xp[(v * kPlanes + pl) * 32];
-            if (v == 0) mma_u8s8_first(d[pl], a0, a1, a2, a3, b.x, b.y, kMagicBits);
-            else mma_u8s8(d[pl], a0, a1, a2, a3, b.x, b.y);
-        }
-    }
-}
-
-// acc += scale * (sum over planes) * 2^e + min * sum(x), for the lane's 2 rows x 2 tokens.
-__device__ inline void step_fold(float (&acc)[4], const int (&d)[kPlanes][4], float s_a, float m_a, float s_b, float m_b, float2 xsc,
-                                 float2 xs2) {
-    float f[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) f[i] = fmaf(sum_as_f32(d[2][i]), 65536.f, fmaf(sum_as_f32(d[1][i]), 256.f, sum_as_f32(d[0][i])));
-    acc[0] = fmaf(s_a * xsc.x, f[0], fmaf(m_a, xs2.x, acc[0]));
-    acc[1] = fmaf(s_a * xsc.y, f[1], fmaf(m_a, xs2.y, acc[1]));
-    acc[2] = fmaf(s_b * xsc.x, f[2], fmaf(m_b, xs2.x, acc[2]));
-    acc[3] = fmaf(s_b * xsc.y, f[3], fmaf(m_b, xs2.y, acc[3]));
 }
 
 // One warp: the dots of weight rows rowa / rowb (lane quad g streams both) with the staged tokens.
-// acc[0], acc[1] = row a x tokens 2c, 2c+1;  acc[2], acc[3] = row b x the same tokens.  Any shape the launcher accepts.
-template <int BITS, int G>
-__device__ inline void rows_dot_any(float (&acc)[4], const StreamArgs &a, int64_t rowa, int64_t rowb, bool va, bool vb,
-                                    const unsigned char *tile, int lane) {
+// acc[0], acc[1] = row a x tokens 2c, 2c+1;  acc[2], acc[3] = row b x the same tokens.
+// VEC: a step is one quantization group and the row has a multiple of four groups, so the scales and mins of the four
+// steps of a prefetch block are one aligned 8-byte load each (four loads a block instead of sixteen 2-byte ones).
+template <int BITS, int G, bool VEC>
+__device__ inline void rows_dot_impl(float (&acc)[4], const StreamArgs &a, int64_t rowa, int64_t rowb, bool va, bool vb,
+                                     const uint4 *xs, const float *xsum, int lane) {
     using geo = Geo<BITS, G>;
     constexpr int W = geo::kWords, UNITS = geo::kUnits, KI = geo::kStepCodes;
+    static_assert(kPrefetch == 4, "the vector scale path loads four groups at a time");
     const int K = (int)a.K, steps = K / KI, groups = K / G, c = lane & 3;
     const int64_t row_bytes = BITS == 4 ? a.K / 2 : a.K;
     const uint8_t *pa = a.q + rowa * row_bytes + c * geo::kLoadBytes;
     const uint8_t *pb = a.q + rowb * row_bytes + c * geo::kLoadBytes;
     const uint16_t *sa = a.scale + rowa * groups, *ma = a.minv + rowa * groups;
     const uint16_t *sb = a.scale + rowb * groups, *mb = a.minv + rowb * groups;
-    const uint2 *planes = reinterpret_cast<const uint2 *>(tile) + lane;
-    const float *xsum = reinterpret_cast<const float *>(tile + TileSmem<BITS, G>::plane_bytes(K)), *xscale = xsum + steps * kTileTokens;
 
     uint32_t wa[kPrefetch][W], wb[kPrefetch][W];
-    uint16_t qs[kPrefetch][4];
+    uint16_t qs[VEC ? 1 : kPrefetch][4];
+    uint2 qv[2][4];  // VEC: {scale a, min a, scale b, min b} of the block in use and of the next one
     auto fetch = [&](int slot, int step) {
         const bool in = step < steps;
         load_codes<W>(wa[slot], pa + (int64_t)step * 4 * geo::kLoadBytes, in && va);
         load_codes<W>(wb[slot], pb + (int64_t)step * 4 * geo::kLoadBytes, in && vb);
-        const int grp = step / geo::kStepsPerGroup;
-        qs[slot][0] = in && va ? __ldg(sa + grp) : (uint16_t)0;
-        qs[slot][1] = in && va ? __ldg(ma + grp) : (uint16_t)0;
-        qs[slot][2] = in && vb ? __ldg(sb + grp) : (uint16_t)0;
-        qs[slot][3] = in && vb ? __ldg(mb + grp) : (uint16_t)0;
+        if (!VEC) {
+            const int grp = step / geo::kStepsPerGroup;
+            qs[slot][0] = in && va ? __ldg(sa + grp) : (uint16_t)0;
+            qs[slot][1] = in && va ? __ldg(ma + grp) : (uint16_t)0;
+            qs[slot][2] = in && vb ? __ldg(sb + grp) : (uint16_t)0;
+            qs[slot][3] = in && vb ? __ldg(mb + grp) : (uint16_t)0;
+        }
     };
+    auto fetch_scales = [&](uint2 (&dst)[4], int step0) {  // VEC: the four groups step0 .. step0 + 3
+        const bool in = step0 < steps;
+        const uint2 z = make_uint2(0u, 0u);
+        dst[0] = in && va ? __ldg(reinterpret_cast<const uint2 *>(sa + step0)) : z;
+        dst[1] = in && va ? __ldg(reinterpret_cast<const uint2 *>(ma + step0)) : z;
+        dst[2] = in && vb ? __ldg(reinterpret_cast<const uint2 *>(sb + step0)) : z;
+        dst[3] = in && vb ? __ldg(reinterpret_cast<const uint2 *>(mb + step0)) : z;
+    };
+    if (VEC) fetch_scales(qv[0], 0);
 #pragma unroll
     for (int p = 0; p < kPrefetch; ++p) fetch(p, p);
     for (int step0 = 0; step0 < steps; step0 += kPrefetch) {
+        if (VEC) fetch_scales(qv[1], step0 + kPrefetch);
 #pragma unroll
         for (int p = 0; p < kPrefetch; ++p) {
             const int step = step0 + p;
             if (step < steps) {
-                int d[kPlanes][4];
-                step_mmas<BITS, G>(d, wa[p], wb[p], planes + (size_t)step * UNITS * kPlanes * 32);
+                float d[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint4 *xu = xs + (size_t)step * UNITS * 32 + lane;
+#pragma unroll
+                for (int v = 0; v < UNITS; ++v) {
+                    const uint4 bx = xu[v * 32];
+                    if (BITS == 4) {
+                        const uint32_t x0 = wa[p][v], x1 = wb[p][v];
+                        mma_bf16(d, nibble_pair16<0>(x0), nibble_pair16<0>(x1), nibble_pair16<1>(x0), nibble_pair16<1>(x1), bx.x, bx.y);
+                        mma_bf16(d, nibble_pair16<2>(x0), nibble_pair16<2>(x1), nibble_pair16<3>(x0), nibble_pair16<3>(x1), bx.z, bx.w);
+                    } else {
+                        const uint32_t bw[4] = {bx.x, bx.y, bx.z, bx.w};
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const uint32_t x0 = wa[p][2 * v + h], x1 = wb[p][2 * v + h];
+                            mma_bf16(d, nibble_pair<0>(x0), nibble_pair<0>(x1), nibble_pair<1>(x0), nibble_pair<1>(x1),
+                                     bw[2 * h], times16(bw[2 * h]));
+                            mma_bf16(d, nibble_pair<2>(x0), nibble_pair<2>(x1), nibble_pair<3>(x0), nibble_pair<3>(x1),
+                                     bw[2 * h + 1], times16(bw[2 * h + 1]));
+                        }
+                    }
+                }
                 const float2 xs2 = *reinterpret_cast<const float2 *>(xsum + step * kTileTokens + 2 * c);
-                const float2 xsc = *reinterpret_cast<const float2 *>(xscale + step * kTileTokens + 2 * c);
-                step_fold(acc, d, bf16_bits_to_f32(qs[p][0]), bf16_bits_to_f32(qs[p][1]), bf16_bits_to_f32(qs[p][2]),
-                          bf16_bits_to_f32(qs[p][3]), xsc, xs2);
+                uint16_t q4[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (VEC) q4[i] = (uint16_t)((p < 2 ? qv[0][i].x : qv[0][i].y) >> (16 * (p & 1)));
+                    else q4[i] = qs[p][i];
+                }
+                const float s_a = bf16_bits_to_f32(q4[0]), s_b = bf16_bits_to_f32(q4[2]);
+                float m_a = bf16_bits_to_f32(q4[1]), m_b = bf16_bits_to_f32(q4[3]);
+                if (BITS == 4) m_a = fmaf(-16.f, s_a, m_a), m_b = fmaf(-16.f, s_b, m_b);  // the 16s of nibble_pair16
+                acc[0] = fmaf(s_a, d[0], fmaf(m_a, xs2.x, acc[0]));
+                acc[1] = fmaf(s_a, d[1], fmaf(m_a, xs2.y, acc[1]));
+                acc[2] = fmaf(s_b, d[2], fmaf(m_b, xs2.x, acc[2]));
+                acc[3] = fmaf(s_b, d[3], fmaf(m_b, xs2.y, acc[3]));
             }
             fetch(p, step + kPrefetch);  // refill the slot just consumed
+        }
+        if (VEC) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) qv[0][i] = qv[1][i];
         }
     }
 }
 
-// The common shape, kept lean because the kernel saturates the integer pipe long before HBM otherwise: a step is one
-// group, the row has a whole number of four-step blocks, scales and mins come by aligned 8-byte loads.  No per-load
-// predicates (a row past the end of the expert is replaced by a row that exists; its sums are dropped by the caller),
-// pointers advance by increments, and the last block is peeled so nothing is fetched past the end of a row.
+// The common shape, kept lean because the kernel saturates the integer pipe before HBM: a step is one group, the row has
+// a whole number of four-step blocks, scales and mins come by aligned 8-byte loads.  No per-load predicates (a row past
+// the end of the expert is replaced by a row that exists; its sums are dropped by the caller), pointers advance by
+// increments, the last block is peeled so nothing is fetched past the end of a row, and a step's first MMA takes a
+// zero accumulator operand instead of cleared registers.
 template <int BITS, int G>
-__device__ inline void rows_dot_fast(float (&acc)[4], const StreamArgs &a, int64_t rowa, int64_t rowb, const unsigned char *tile,
-                                     int lane) {
+__device__ inline void rows_dot_fast(float (&acc)[4], const StreamArgs &a, int64_t rowa, int64_t rowb, const uint4 *xs,
+                                     const float *xsum, int lane) {
     using geo = Geo<BITS, G>;
     constexpr int W = geo::kWords, UNITS = geo::kUnits, KI = geo::kStepCodes;
-    static_assert(kPrefetch == 4, "the scales of a block of four steps are one 8-byte load");
     constexpr int kBlockBytes = kPrefetch * 4 * geo::kLoadBytes;  // bytes of one row consumed per block of four steps
-    const int K = (int)a.K, steps = K / KI, blocks = steps / kPrefetch, groups = K / G, c = lane & 3;
+    const int K = (int)a.K, blocks = K / (KI * kPrefetch), groups = K / G, c = lane & 3;
     const int64_t row_bytes = BITS == 4 ? a.K / 2 : a.K;
     const uint8_t *pa = a.q + rowa * row_bytes + c * geo::kLoadBytes;
     const uint8_t *pb = a.q + rowb * row_bytes + c * geo::kLoadBytes;
     const uint2 *sa = reinterpret_cast<const uint2 *>(a.scale + rowa * groups), *ma = reinterpret_cast<const uint2 *>(a.minv + rowa * groups);
     const uint2 *sb = reinterpret_cast<const uint2 *>(a.scale + rowb * groups), *mb = reinterpret_cast<const uint2 *>(a.minv + rowb * groups);
-    const uint2 *xp = reinterpret_cast<const uint2 *>(tile) + lane;
-    const float *xq = reinterpret_cast<const float *>(tile + TileSmem<BITS, G>::plane_bytes(K)) + 2 * c;  // xsum; xscale follows
-    const int sc_off = steps * kTileTokens;
+    const uint4 *xu = xs + lane;
+    const float *xq = xsum + 2 * c;
 
     uint32_t wa[kPrefetch][W], wb[kPrefetch][W];
     uint2 qv[4], qn[4];  // {scale a, min a, scale b, min b} of the block in use / of the next one
@@ -319,13 +285,39 @@ __device__ inline void rows_dot_fast(float (&acc)[4], const StreamArgs &a, int64
     };
     auto fetch_scales = [&](uint2 (&dst)[4]) { dst[0] = __ldg(sa), dst[1] = __ldg(ma), dst[2] = __ldg(sb), dst[3] = __ldg(mb); };
     auto consume = [&](int p) {
-        int d[kPlanes][4];
-        step_mmas<BITS, G>(d, wa[p], wb[p], xp + (size_t)p * UNITS * kPlanes * 32);
+        float d[4];
+#pragma unroll
+        for (int v = 0; v < UNITS; ++v) {
+            const uint4 bx = xu[(p * UNITS + v) * 32];
+            if (BITS == 4) {
+                const uint32_t x0 = wa[p][v], x1 = wb[p][v];
+                if (v == 0) mma_bf16_first(d, nibble_pair16<0>(x0), nibble_pair16<0>(x1), nibble_pair16<1>(x0), nibble_pair16<1>(x1), bx.x, bx.y);
+                else mma_bf16(d, nibble_pair16<0>(x0), nibble_pair16<0>(x1), nibble_pair16<1>(x0), nibble_pair16<1>(x1), bx.x, bx.y);
+                mma_bf16(d, nibble_pair16<2>(x0), nibble_pair16<2>(x1), nibble_pair16<3>(x0), nibble_pair16<3>(x1), bx.z, bx.w);
+            } else {
+                const uint32_t bw[4] = {bx.x, bx.y, bx.z, bx.w};
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t x0 = wa[p][2 * v + h], x1 = wb[p][2 * v + h];
+                    if (v == 0 && h == 0)
+                        mma_bf16_first(d, nibble_pair<0>(x0), nibble_pair<0>(x1), nibble_pair<1>(x0), nibble_pair<1>(x1), bw[0], times16(bw[0]));
+                    else
+                        mma_bf16(d, nibble_pair<0>(x0), nibble_pair<0>(x1), nibble_pair<1>(x0), nibble_pair<1>(x1), bw[2 * h], times16(bw[2 * h]));
+                    mma_bf16(d, nibble_pair<2>(x0), nibble_pair<2>(x1), nibble_pair<3>(x0), nibble_pair<3>(x1), bw[2 * h + 1],
+                             times16(bw[2 * h + 1]));
+                }
+            }
+        }
         const float2 xs2 = *reinterpret_cast<const float2 *>(xq + p * kTileTokens);
-        const float2 xsc = *reinterpret_cast<const float2 *>(xq + sc_off + p * kTileTokens);
         // BF16 bits -> FP32: the upper half of the word as it is, the lower half shifted up
         auto f32_of = [&](const uint2 &q) { const uint32_t w = p < 2 ? q.x : q.y; return __uint_as_float((p & 1) ? (w & 0xffff0000u) : (w << 16)); };
-        step_fold(acc, d, f32_of(qv[0]), f32_of(qv[1]), f32_of(qv[2]), f32_of(qv[3]), xsc, xs2);
+        const float s_a = f32_of(qv[0]), s_b = f32_of(qv[2]);
+        float m_a = f32_of(qv[1]), m_b = f32_of(qv[3]);
+        if (BITS == 4) m_a = fmaf(-16.f, s_a, m_a), m_b = fmaf(-16.f, s_b, m_b);  // the 16s of nibble_pair16
+        acc[0] = fmaf(s_a, d[0], fmaf(m_a, xs2.x, acc[0]));
+        acc[1] = fmaf(s_a, d[1], fmaf(m_a, xs2.y, acc[1]));
+        acc[2] = fmaf(s_b, d[2], fmaf(m_b, xs2.x, acc[2]));
+        acc[3] = fmaf(s_b, d[3], fmaf(m_b, xs2.y, acc[3]));
     };
 
     fetch_scales(qv);
@@ -341,7 +333,7 @@ __device__ inline void rows_dot_fast(float (&acc)[4], const StreamArgs &a, int64
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) qv[i] = qn[i];
-        xp += kPrefetch * UNITS * kPlanes * 32, xq += kPrefetch * kTileTokens;
+        xu += kPrefetch * UNITS * 32, xq += kPrefetch * kTileTokens;
     }
 #pragma unroll
     for (int p = 0; p < kPrefetch; ++p) consume(p);
@@ -349,17 +341,17 @@ __device__ inline void rows_dot_fast(float (&acc)[4], const StreamArgs &a, int64
 
 template <int BITS, int G>
 __device__ inline void rows_dot(float (&acc)[4], const StreamArgs &a, int64_t rowa, int64_t rowb, bool va, bool vb,
-                                const unsigned char *tile, int lane) {
+                                const uint4 *xs, const float *xsum, int lane) {
     using geo = Geo<BITS, G>;
     const int groups = (int)(a.K / G);
-    const bool lean = geo::kStepsPerGroup == 1 && groups % 4 == 0 &&
-                      ((reinterpret_cast<uintptr_t>(a.scale) | reinterpret_cast<uintptr_t>(a.minv)) & 7) == 0;
-    if (lean) {
+    const bool vec = geo::kStepsPerGroup == 1 && groups % 4 == 0 &&
+                     ((reinterpret_cast<uintptr_t>(a.scale) | reinterpret_cast<uintptr_t>(a.minv)) & 7) == 0;
+    if (vec && geo::kStepsPerGroup == 1) {
         // rows past the end of the expert: stream a row that exists instead (the caller drops their sums)
         const int64_t any = va ? rowa : vb ? rowb : 0;
-        rows_dot_fast<BITS, G>(acc, a, va ? rowa : any, vb ? rowb : any, tile, lane);
+        rows_dot_fast<BITS, G>(acc, a, va ? rowa : any, vb ? rowb : any, xs, xsum, lane);
     } else {
-        rows_dot_any<BITS, G>(acc, a, rowa, rowb, va, vb, tile, lane);
+        rows_dot_impl<BITS, G, false>(acc, a, rowa, rowb, va, vb, xs, xsum, lane);
     }
 }
 
@@ -368,7 +360,7 @@ __global__ void __launch_bounds__(kThreads, 2) stream_kernel(const StreamArgs a)
     using geo = Geo<BITS, G>;
     extern __shared__ __align__(16) unsigned char smem[];
     const int K = (int)a.K, steps = K / geo::kStepCodes;
-    const size_t pass_bytes = TileSmem<BITS, G>::bytes(K);
+    const size_t pass_bytes = (size_t)steps * geo::kUnits * 512 + (size_t)steps * kTileTokens * 4;
     __shared__ int64_t s_row[kTileTokens];  // activation row of each token of the tile, -1 = none
     __shared__ int64_t s_out[kTileTokens];  // output row (slot, or token for dense)
     __shared__ int s_bucket, s_cnt;
@@ -409,7 +401,8 @@ __global__ void __launch_bounds__(kThreads, 2) stream_kernel(const StreamArgs a)
                     s_row[threadIdx.x] = k < a.A ? m * a.A + k : -1;
                 }
                 __syncthreads();
-                stage_tile<BITS, G>(a.x, K, s_row, smem + p * pass_bytes);
+                stage_tile<BITS, G>(a.x, K, s_row, reinterpret_cast<uint4 *>(smem + p * pass_bytes),
+                                    reinterpret_cast<float *>(smem + p * pass_bytes + (size_t)steps * geo::kUnits * 512));
             }
             __syncthreads();
             for (int64_t unit = lo + warp; unit < hi; unit += kWarps) {
@@ -421,7 +414,9 @@ __global__ void __launch_bounds__(kThreads, 2) stream_kernel(const StreamArgs a)
                     const int p = k / kTileTokens, col = k % kTileTokens;
                     const int64_t base = (int64_t)a.ids[m * a.A + k] * a.N;
                     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                    rows_dot<BITS, G>(acc, a, base + ra, base + rb, va, vb, smem + p * pass_bytes, lane);
+                    rows_dot<BITS, G>(acc, a, base + ra, base + rb, va, vb, reinterpret_cast<const uint4 *>(smem + p * pass_bytes),
+                                      reinterpret_cast<const float *>(smem + p * pass_bytes + (size_t)steps * geo::kUnits * 512),
+                                      lane);
                     if (c == col / 2) {  // the lane of the quad that holds this slot's column
                         const float cf = a.coef[m * a.A + k];
                         ta = fmaf(cf, col & 1 ? acc[1] : acc[0], ta);
@@ -470,7 +465,9 @@ __global__ void __launch_bounds__(kThreads, 2) stream_kernel(const StreamArgs a)
         __syncthreads();
         const int bucket = s_bucket, cnt = s_cnt;
         const bool valid = bucket < a.E;  // bucket E: slots with an id outside [0, E) - their outputs become NaN
-        if (valid) stage_tile<BITS, G>(a.x, K, s_row, smem);
+        uint4 *xs = reinterpret_cast<uint4 *>(smem);
+        float *xsum = reinterpret_cast<float *>(smem + (size_t)steps * geo::kUnits * 512);
+        if (valid) stage_tile<BITS, G>(a.x, K, s_row, xs, xsum);
         __syncthreads();
 
         for (int64_t unit = lo + warp; unit < hi; unit += kWarps) {
@@ -486,7 +483,7 @@ __global__ void __launch_bounds__(kThreads, 2) stream_kernel(const StreamArgs a)
                 va = ra < a.N, vb = rb < a.N;
             }
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            if (valid) rows_dot<BITS, G>(acc, a, (int64_t)bucket * a.N + ra, (int64_t)bucket * a.N + rb, va, vb, smem, lane);
+            if (valid) rows_dot<BITS, G>(acc, a, (int64_t)bucket * a.N + ra, (int64_t)bucket * a.N + rb, va, vb, xs, xsum, lane);
             // Epilogue.  Lane (g, c) holds rows ra / rb for tokens 2c and 2c + 1.
 #pragma unroll
             for (int t = 0; t < 2; ++t) {
@@ -563,10 +560,10 @@ int launch_stream(const char *fn, const StreamArgs &a, int64_t est_units, cudaSt
     using geo = Geo<BITS, G>;
     const int64_t steps = a.K / geo::kStepCodes;
     const int64_t passes = SRC == kPerToken ? (a.A + kTileTokens - 1) / kTileTokens : 1;
-    const size_t smem = (size_t)passes * TileSmem<BITS, G>::bytes(a.K);
+    const size_t smem = (size_t)passes * ((size_t)steps * geo::kUnits * 512 + (size_t)steps * kTileTokens * 4);
     SXB_CHECK(smem <= kMaxDynSmem, fn, ": K = ", a.K, SRC == kPerToken ? " x A = " : "", SRC == kPerToken ? a.A : 0, " needs ", smem,
               " bytes of shared memory for one tile's activations, more than ", kMaxDynSmem,
-              " (about K * 24 * ceil(A / 8) bytes for the per-slot combine, K * 24 otherwise; use the grouped form)");
+              " (K * 16 * ceil(A / 8) bytes for the per-slot combine, K * 16 otherwise; use the grouped form)");
     auto kern = stream_kernel<BITS, G, MODE, SRC, TOUT>;
     SXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn,
              ": reserving shared memory");
