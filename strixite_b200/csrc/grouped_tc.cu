@@ -12,20 +12,31 @@
 // tokens costs 80 columns, not a padded 128-row tile.  D[row, token] lives in tensor memory, one row per TMEM lane:
 // the epilogue thread of lane j holds gate row j and up row j of the same tokens, and SwiGLU needs no data movement.
 //
-// One persistent CTA per SM, warp-specialised:
-//   warps 0-3   epilogue: tcgen05.ld of a finished accumulator pair -> SwiGLU / stores, while the next item runs
-//   warp  4     one elected thread issues tcgen05.mma (operands: shared-memory descriptors, K-major, 128-byte swizzle)
-//   warps 5-12  producers.  Thread p owns weight row p of the item: it streams the row's packed codes from global
-//               memory 128 bytes at a time (kept in registers one super-block ahead), dequantizes 64 codes per k-block
-//               with lop3 / packed-half arithmetic and writes the row's 128-byte line of the A tile.  The same
-//               threads gather the tokens' activation rows (16 bytes a chunk), convert BF16 -> F16 and write the B
-//               tile.  Within every group of 8 consecutive k both operands use the order [0 4 1 5 2 6 3 7] (Q4),
-//               the order in which a nibble pair falls out of one lop3, so no element is moved after dequantization.
-// Stages are handed over with mbarriers (producers -> MMA: arrive after fence.proxy.async; MMA -> producers and
-// MMA -> epilogue: tcgen05.commit).  Every wait is bounded: past the limit the CTA raises its abort flag, records
-// {2, item, role} in the status words, drains the tensor pipe and frees its tensor memory before returning.
+// Operands.  A (weights) is read by the MMA from TENSOR MEMORY (the [tmem] form of tcgen05.mma): the producer threads
+// dequantize in registers and tcgen05.st the F16 rows straight into their own TMEM lanes, which needs no proxy fence
+// (shared-memory operands written by threads do, and that fence cost more than the dequantization).  B (activations)
+// is a K-major, 128-byte-swizzled tile in shared memory; with "tile-blocked" activations (sxb_stage_f16_tiles, or the
+// h this kernel's own SwiGLU form writes) the tile of a k-block is ONE contiguous run in global memory and arrives by
+// one cp.async.bulk.  The packed codes come by 2-D tensor copies (64 bytes x 128 rows a box) into a ring in shared
+// memory.  Tensor memory: columns 0-255 the two accumulators, 256-511 four stages of the A operand.
 //
-// No tensor map, no multicast: the operands never come through TMA, so nothing here can touch a peer GPU's memory.
+// One persistent CTA per SM, 16 warps:
+//   warps 0-3   epilogue: tcgen05.ld of the finished accumulators, 16 tokens at a time -> SwiGLU / rounding in
+//               registers -> one store per token straight to global memory (a warp's 32 rows of a token are 64 or 128
+//               contiguous bytes); tensor memory is handed back as soon as the last columns are in registers
+//   warps 4-5   MMA issue, one warp per accumulator (an instruction costs its issuer 60-90 cycles whatever its N);
+//               operands warp-uniform, elect.sync picks the issuing lane; tcgen05.commit frees stages / signals
+//   warps 6-13  weight producers: a lane quadrant has two warps, which split the k-blocks (even / odd); a thread
+//               dequantizes the rows of BOTH accumulators on its lane: lop3 / packed-half arithmetic on 64 codes a
+//               row and k-block.  Within every 8 consecutive k both operands use the order [0 4 1 5 2 6 3 7] (Q4),
+//               the order in which a nibble pair falls out of one lop3, so no element moves after dequantization
+//   warps 14-15 activation producers (one thread issues the bulk copies of tile-blocked activations; the other warp's
+//               lane 0 then runs the ring of weight codes; otherwise both warps gather and convert rows)
+// Stages are handed over with mbarriers (producers -> MMA: arrive after tcgen05.wait::st; copies: complete_tx bytes;
+// MMA -> producers and MMA -> epilogue: tcgen05.commit).  Every wait is bounded: past the limit the CTA raises its abort
+// flag, records {2, item, role} in the status words, drains the tensor pipe and frees its tensor memory before returning.
+//
+// The tensor copies read this GPU's own weight array only, each into the shared memory of the one CTA that issues it.
 
 #include "experts.cuh"
 
@@ -227,7 +238,7 @@ __device__ inline void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, u
                  : "memory");
 }
 
-// One box of a 2-D tensor copy (no multicast), completion counted in bytes on `bar`.  x is a byte offset inside the weight row
+// One box of a 2-D tensor copy, completion counted in bytes on `bar`.  x is a byte offset inside the weight row
 // and always a multiple of 64, as the 16-byte alignment rule of tensor copies requires.
 __device__ inline void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
