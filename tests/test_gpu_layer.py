@@ -137,3 +137,44 @@ def test_layer_tcgen05_c3_prefill(cuda, oracle):
     from strixite_b200 import workloads as W
     err = tc_layer_case(cuda, oracle, W.C3, 48)
     print(f"c3 tcgen05 max-abs error {err:.3e} x RMS")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,T,tc", [("c0", 96, True), ("c0", 4, False), ("c2", 0, False)])
+def test_expert_parallel_shards_add_up(cuda, name, T, tc):
+    """The expert-parallel entry points on ONE GPU: every shard of the experts (2 and 4 shards), run with all tokens and the
+    full router output, yields its partial rows; their sum is the unsharded layer's output up to FP32 summation order."""
+    from dataclasses import replace
+    from strixite_b200 import kernels as K, workloads as W
+    from strixite_b200.kernels import MoeMath
+    from strixite_b200.layer import MoeBuffers, MoeLayer
+    cfg = W.CONFIGS[name]
+    cfg = replace(cfg, shared=False, **({"T": T} if T else {}))
+    math = MoeMath.WmmaF16 if tc else None
+    x = W.activations(cfg, 3, cuda)
+    logits = W.router_logits(x, W.router_weight(cfg, 3, cuda), W.expert_bias(cfg, 3, cuda))
+    # reference: all experts on one rank
+    w = W.make_layer_weights(cfg, 3, cuda)
+    buf = MoeBuffers(cfg.T, cfg.d, cfg.I, cfg.E, cfg.k, cuda, False)
+    full = MoeLayer(w, cfg.E, cfg.k, buf)
+    y_ref = torch.empty((cfg.T, cfg.d), dtype=torch.float32, device=cuda)
+    full.forward(x, logits, y_ref, math=math)
+    torch.cuda.synchronize()
+    full.check_errors(cfg.name)
+    ids, coef = buf.ids[:cfg.T].clone(), buf.coef[:cfg.T].clone()
+    for shards in (2, 4):
+        total = torch.zeros_like(y_ref)
+        n = cfg.E // shards
+        for r in range(shards):
+            wl = W.make_layer_weights(cfg, 3, cuda, e_lo=r * n, e_hi=(r + 1) * n)
+            bl = MoeBuffers(cfg.T, cfg.d, cfg.I, n, cfg.k, cuda, False)
+            bl.ids[:cfg.T].copy_(ids)
+            bl.coef[:cfg.T].copy_(coef)
+            part = MoeLayer(wl, n, cfg.k, bl, E_total=cfg.E, e_lo=r * n)
+            y = torch.empty_like(y_ref)
+            part.run_experts(x, cfg.T, y, part.math_for(cfg.T, math), logits)
+            torch.cuda.synchronize()
+            part.check_errors(f"{cfg.name} shard {r}/{shards}")
+            total += y
+        scale = y_ref.abs().max().item()
+        assert (total - y_ref).abs().max().item() <= 2e-5 * scale, f"{cfg.name}: {shards} shards do not add up to the whole"
