@@ -46,6 +46,7 @@ def parse():
     ap.add_argument("--experts", type=int, default=0, help="override the expert count (profiling on a small case)")
     ap.add_argument("--tokens", type=int, default=0, help="override the token count (profiling on a small case)")
     ap.add_argument("--no-graph", action="store_true", help="decode workloads: launch eagerly instead of replaying CUDA graphs")
+    ap.add_argument("--micro", type=int, default=0, help="micro-batches per rank in expert-parallel runs (default 1)")
     ap.add_argument("--seed", type=int, default=0)
     return ap.parse_args()
 
@@ -124,7 +125,7 @@ class Stack:
     """Resident state of a configuration on this rank: per-layer weights (this rank's experts), router weights, biases,
     the shared workspaces, and the expert-parallel driver."""
 
-    def __init__(self, cfg, layers, seed, dev, rank, world):
+    def __init__(self, cfg, layers, seed, dev, rank, world, micro=0):
         import torch
         from strixite_b200 import workloads as W
         from strixite_b200.ep import Compute, ExpertParallelMoe, shard_bounds
@@ -134,44 +135,60 @@ class Stack:
         self.e_lo, self.e_hi = shard_bounds(cfg.E, world, rank)
         self.t_lo, self.t_hi = shard_bounds(cfg.T, world, rank)
         E_local = self.e_hi - self.e_lo
-        self.buf = MoeBuffers(cfg.T, cfg.d, cfg.I, E_local, cfg.k, dev, cfg.shared and world == 1)
-        self.layers, self.wr, self.bias = [], [], []
+        t = self.t_hi - self.t_lo
+        # micro-batches (expert-parallel runs, --micro): chunks of the rank's rows, each with its own work buffers, so that
+        # one chunk's all-gather / reduce-scatter runs under the other chunk's GEMMs.  Off by default: measured on C4, the
+        # smaller tiles cost the grouped GEMMs more (0.44 -> 0.32 of peak at 8 GPUs) than the overlap returns
+        # (19.7 -> 22.9 ms a step at 8 GPUs, 42.2 -> 48.4 ms at 2).
+        if micro <= 0 or world == 1 or t % micro != 0:
+            micro = 1
+        self.micro = micro
+        Tc = cfg.T // micro
+        self.bufs = [MoeBuffers(Tc, cfg.d, cfg.I, E_local, cfg.k, dev, cfg.shared and world == 1) for _ in range(micro)]
+        self.buf = self.bufs[0]
+        self.layer_sets = [[] for _ in range(micro)]
+        self.wr, self.bias = [], []
         for l in range(layers):
             w = W.make_layer_weights(cfg, seed, dev, layer=l, e_lo=self.e_lo, e_hi=self.e_hi)
-            self.layers.append(MoeLayer(w, E_local, cfg.k, self.buf, E_total=cfg.E, e_lo=self.e_lo))
+            for c in range(micro):
+                self.layer_sets[c].append(MoeLayer(w, E_local, cfg.k, self.bufs[c], E_total=cfg.E, e_lo=self.e_lo))
             self.wr.append(W.router_weight(cfg, seed, dev, layer=l))
             self.bias.append(W.expert_bias(cfg, seed, dev, layer=l))
-        t = self.t_hi - self.t_lo
-        self.ids_loc = torch.empty((t, cfg.k), dtype=torch.int32, device=dev)
-        self.coef_loc = torch.empty((t, cfg.k), dtype=torch.float32, device=dev)
-        self.y_part = torch.empty((cfg.T, cfg.d), dtype=torch.float32, device=dev)
+        self.layers = self.layer_sets[0]
+        tc = t // micro
+        self.ids_loc = [torch.empty((tc, cfg.k), dtype=torch.int32, device=dev) for _ in range(micro)]
+        self.coef_loc = [torch.empty((tc, cfg.k), dtype=torch.float32, device=dev) for _ in range(micro)]
+        self.y_part = [torch.empty((Tc, cfg.d), dtype=torch.float32, device=dev) for _ in range(micro)]
+        self.logits = [None] * micro
         self.router_err = self.buf.router_err
         self.math = None          # None = by token count (tcgen05 from MoeLayer.tc_min_tokens up)
         self.events = None        # (list, list) of CUDA events around the dominant kernel when roofline timing is on
-        self.ep = ExpertParallelMoe(Compute(self._route, self._experts), layers, cfg.T, cfg.d, cfg.k, dev)
+        self.ep = ExpertParallelMoe(Compute(self._route, self._experts, chunked=True), layers, cfg.T, cfg.d, cfg.k, dev, micro=micro)
         self.weight_bytes = sum(ly.w.bytes() for ly in self.layers)
 
-    def _route(self, l, x_loc):
+    def _route(self, l, x_loc, chunk=0):
         from strixite_b200 import kernels as K, workloads as W
         logits = W.router_logits(x_loc, self.wr[l], self.bias[l], tf32=x_loc.shape[0] >= 256)
-        self.logits = logits
+        self.logits[chunk] = logits
         t = x_loc.shape[0]
+        buf = self.bufs[chunk]
         if self.world == 1:
-            ids, coef = self.buf.ids, self.buf.coef
+            ids, coef = buf.ids, buf.coef
         else:
-            ids, coef = self.ids_loc, self.coef_loc
-        K.moe_router(logits, logits.stride(0), t, self.cfg.E, self.cfg.k, None, 1, 0, ids, coef, K.Act.F32, self.router_err)
+            ids, coef = self.ids_loc[chunk], self.coef_loc[chunk]
+        K.moe_router(logits, logits.stride(0), t, self.cfg.E, self.cfg.k, None, 1, 0, ids, coef, K.Act.F32, buf.router_err)
         return ids, coef
 
-    def _experts(self, l, x_all, ids_all, coef_all):
-        layer = self.layers[l]
+    def _experts(self, l, x_all, ids_all, coef_all, chunk=0):
+        layer = self.layer_sets[chunk][l]
+        buf = self.bufs[chunk]
         T = x_all.shape[0]
         if self.world > 1:
-            self.buf.ids.copy_(ids_all)
-            self.buf.coef.copy_(coef_all)
+            buf.ids.copy_(ids_all)
+            buf.coef.copy_(coef_all)
         math = layer.math_for(T, self.math)
-        y = self.y_part[:T]
-        layer.run_experts(x_all, T, y, math, self.logits, events=self.events)
+        y = self.y_part[chunk][:T]
+        layer.run_experts(x_all, T, y, math, self.logits[chunk], events=self.events)
         return y
 
     def step(self, x_loc):
@@ -231,7 +248,7 @@ def run_stack(cfg, args, dev, rank, world, peaks, layers=None, rotate=False):
     from strixite_b200 import kernels as K, workloads as W
 
     layers = layers or args.layers or cfg.layers
-    st = Stack(cfg, layers, args.seed, dev, rank, world)
+    st = Stack(cfg, layers, args.seed, dev, rank, world, micro=getattr(args, "micro", 0))
     t_loc = st.t_hi - st.t_lo
     x_full = W.activations(cfg, args.seed, dev)
     x_loc = x_full[st.t_lo:st.t_hi].contiguous()
@@ -321,7 +338,8 @@ def run_stack(cfg, args, dev, rank, world, peaks, layers=None, rotate=False):
 def roofline_tensor(cfg, res, peaks, world):
     """Dominant kernel of the prefill regime: the grouped gate/up + SwiGLU GEMM, 2 * S * 2I * d flops per launch (this
     rank's share of the slots: S / N on average)."""
-    flops = 2.0 * cfg.T * cfg.k * 2 * cfg.I * cfg.d / world
+    micro = res["stack"].micro  # a launch serves one micro-batch of this rank's slots
+    flops = 2.0 * cfg.T * cfg.k * 2 * cfg.I * cfg.d / world / micro
     if not res["kernel_ms"]:
         return None
     achieved = flops / (res["kernel_ms"] * 1e-3) / 1e12
@@ -329,7 +347,7 @@ def roofline_tensor(cfg, res, peaks, world):
     # DRAM bytes of one launch: an ncu capture of a reduced case (64 experts, 512 tokens) read 328.0 MB against 327.1 MB of
     # codes + scales / mins + tile-blocked activations, a ratio of 1.00; the same sum for this launch, times that ratio.
     ly = res["stack"].layers[0]
-    traffic = 1.003 * (ly.w.gate_up.bytes() + cfg.T * cfg.k / world * cfg.d * 2)
+    traffic = 1.003 * (ly.w.gate_up.bytes() + cfg.T * cfg.k / world / micro * cfg.d * 2)
     return dict(bound="tensor", kernel="grouped_tc_kernel<gate_up+swiglu>", achieved=achieved, peak=peak, unit="TFLOP/s",
                 frac=achieved / peak, peak_source=peaks["source"] + " (sustained bf16)", traffic=traffic,
                 traffic_source="dram bytes of an ncu capture of a reduced case, scaled by algorithmic bytes",
@@ -491,7 +509,7 @@ def main():
         "config": {"workload": cfg.name, "T": cfg.T, "layers": res["layers"], "hidden": cfg.d, "experts": cfg.E,
                    "experts_per_gpu": cfg.E // world, "top_k": cfg.k, "intermediate": cfg.I, "gate_up": f"q{cfg.gu_bits}g{cfg.group(cfg.gu_bits)}",
                    "down": f"q{cfg.dn_bits}g{cfg.group(cfg.dn_bits)}", "shared_expert": cfg.shared, "expert_bias": cfg.bias, "router_projection": "cuBLAS " + ("tf32" if cfg.T // world >= 256 else "fp32") + " (torch.matmul), inside the timed step",
-                   "parallelism": f"ep{world}", "value_is": "T * layers / step time",
+                   "parallelism": f"ep{world}" + (f", {res['stack'].micro} micro-batches a rank" if res["stack"].micro > 1 else ""), "value_is": "T * layers / step time",
                    "l2": "weights resident per step exceed L2 (126 MB): %.1f GB on this rank" % (res["stack"].weight_bytes / 1e9)},
         "clocks": res["clocks"], "gpu_launches": res["launches"],
         "e2e": {"value": res["e2e_value"], "unit": "MoE-layer tokens/s", "h2d_bytes_per_step": res["h2d"],

@@ -11,6 +11,12 @@ Per layer:
     5. residual: x <- bf16(x + y)
 With N = 1 steps 2 and 4 vanish and the kernels are exactly the single-GPU layer's.
 
+Micro-batches.  The rows of a MoE layer stack are independent of one another from the first layer to the last, so a rank may
+cut its rows into `micro` chunks and run each chunk's whole stack as its own sequence of launches on its own stream: while
+one chunk is in its all-gather or reduce-scatter (NVLink, a few SMs), the other chunk's grouped GEMMs have the tensor
+cores.  Every chunk needs its own set of work buffers: the compute callbacks get the chunk number.  Within a layer the
+all-gather of the activations is started before the routing it does not depend on.
+
 The compute steps are injected (`Compute`), so the exchange logic can be exercised on CPU ranks with a stand-in.
 """
 from __future__ import annotations
@@ -26,10 +32,12 @@ import torch.distributed as dist
 class Compute:
     """The per-rank device work of one layer.
     route(layer, x_loc [t, d]) -> (ids [t, k] int32, coef [t, k] float32)
-    experts(layer, x_all [T, d], ids_all [T, k], coef_all [T, k]) -> y_partial [T, d] float32"""
+    experts(layer, x_all [T, d], ids_all [T, k], coef_all [T, k]) -> y_partial [T, d] float32
+    With micro-batches (`chunked = True`) both take the chunk number as a last argument and t, T are a chunk's."""
 
     route: Callable
     experts: Callable
+    chunked: bool = False
 
 
 def shard_bounds(total: int, world: int, rank: int):
@@ -41,7 +49,7 @@ def shard_bounds(total: int, world: int, rank: int):
 
 
 class ExpertParallelMoe:
-    def __init__(self, compute: Compute, n_layers: int, T: int, d: int, k: int, device, group=None):
+    def __init__(self, compute: Compute, n_layers: int, T: int, d: int, k: int, device, group=None, micro: int = 1):
         self.c = compute
         self.layers = n_layers
         self.group = group
@@ -50,34 +58,78 @@ class ExpertParallelMoe:
         self.T, self.d, self.k = T, d, k
         self.t_lo, self.t_hi = shard_bounds(T, self.world, self.rank)
         t = self.t_hi - self.t_lo
+        self.micro = micro if (self.world > 1 and micro > 1 and compute.chunked and t % micro == 0) else 1
+        self.streams = None
         if self.world > 1:
-            self.x_all = torch.empty((T, d), dtype=torch.bfloat16, device=device)
-            self.route_loc = torch.empty((t, 2 * k), dtype=torch.int32, device=device)   # ids | coef bits
-            self.route_all = torch.empty((T, 2 * k), dtype=torch.int32, device=device)
-            self.y_loc = torch.empty((t, d), dtype=torch.float32, device=device)
+            tc, Tc = t // self.micro, T // self.micro
+            self.x_all = [torch.empty((Tc, d), dtype=torch.bfloat16, device=device) for _ in range(self.micro)]
+            self.route_loc = [torch.empty((tc, 2 * k), dtype=torch.int32, device=device) for _ in range(self.micro)]   # ids | coef bits
+            self.route_all = [torch.empty((Tc, 2 * k), dtype=torch.int32, device=device) for _ in range(self.micro)]
+            self.y_loc = [torch.empty((tc, d), dtype=torch.float32, device=device) for _ in range(self.micro)]
 
-    def layer(self, l: int, x_loc: torch.Tensor) -> torch.Tensor:
-        """One layer on this rank's rows; returns y [t, d] float32 (the full sum over all ranks' experts)."""
-        ids, coef = self.c.route(l, x_loc)
+    def _route(self, l, x, chunk):
+        return self.c.route(l, x, chunk) if self.c.chunked else self.c.route(l, x)
+
+    def _experts(self, l, x_all, ids, coef, chunk):
+        return self.c.experts(l, x_all, ids, coef, chunk) if self.c.chunked else self.c.experts(l, x_all, ids, coef)
+
+    def layer(self, l: int, x_loc: torch.Tensor, chunk: int = 0) -> torch.Tensor:
+        """One layer on this rank's rows (of one chunk); returns y [t, d] float32 (the full sum over all ranks' experts)."""
         if self.world == 1:
-            return self.c.experts(l, x_loc, ids, coef)
+            ids, coef = self._route(l, x_loc, chunk)
+            return self._experts(l, x_loc, ids, coef, chunk)
         k = self.k
-        self.route_loc[:, :k] = ids
-        self.route_loc[:, k:] = coef.view(torch.int32)
-        dist.all_gather_into_tensor(self.x_all, x_loc.contiguous(), group=self.group)
-        dist.all_gather_into_tensor(self.route_all, self.route_loc, group=self.group)
-        ids_all = self.route_all[:, :k].contiguous()
-        coef_all = self.route_all[:, k:].contiguous().view(torch.float32)
-        y_part = self.c.experts(l, self.x_all, ids_all, coef_all)
-        dist.reduce_scatter_tensor(self.y_loc, y_part, op=dist.ReduceOp.SUM, group=self.group)
-        return self.y_loc
+        x_all, route_loc, route_all = self.x_all[chunk], self.route_loc[chunk], self.route_all[chunk]
+        gather_x = dist.all_gather_into_tensor(x_all, x_loc.contiguous(), group=self.group, async_op=True)  # under the routing
+        ids, coef = self._route(l, x_loc, chunk)
+        route_loc[:, :k] = ids
+        route_loc[:, k:] = coef.view(torch.int32)
+        gather_r = dist.all_gather_into_tensor(route_all, route_loc, group=self.group, async_op=True)
+        gather_x.wait()
+        gather_r.wait()
+        ids_all = route_all[:, :k].contiguous()
+        coef_all = route_all[:, k:].contiguous().view(torch.float32)
+        y_part = self._experts(l, x_all, ids_all, coef_all, chunk)
+        dist.reduce_scatter_tensor(self.y_loc[chunk], y_part, op=dist.ReduceOp.SUM, group=self.group)
+        return self.y_loc[chunk]
 
     def forward(self, x_loc: torch.Tensor, keep: Optional[List[torch.Tensor]] = None) -> torch.Tensor:
         """The stack: x <- bf16(x + moe_l(x)) for every layer; returns this rank's rows after the last layer."""
-        x = x_loc
+        if self.micro == 1:
+            x = x_loc
+            for l in range(self.layers):
+                y = self.layer(l, x)
+                if keep is not None:
+                    keep.append(y.clone())
+                x = (x.to(torch.float32) + y).to(torch.bfloat16)
+            return x
+        # micro-batches: chunk c's launches go to stream c; layers alternate between the chunks so that one chunk's
+        # collectives are in flight while the other's kernels run
+        cuda = x_loc.is_cuda
+        tc = x_loc.shape[0] // self.micro
+        xs = [x_loc[c * tc:(c + 1) * tc] for c in range(self.micro)]
+        if cuda:
+            if self.streams is None:
+                self.streams = [torch.cuda.Stream(device=x_loc.device) for _ in range(self.micro)]
+            cur = torch.cuda.current_stream()
+            for st in self.streams:
+                st.wait_stream(cur)
         for l in range(self.layers):
-            y = self.layer(l, x)
-            if keep is not None:
-                keep.append(y.clone())
-            x = (x.to(torch.float32) + y).to(torch.bfloat16)
-        return x
+            for c in range(self.micro):
+                if cuda:
+                    with torch.cuda.stream(self.streams[c]):
+                        y = self.layer(l, xs[c], c)
+                        xs[c] = (xs[c].to(torch.float32) + y).to(torch.bfloat16)
+                else:
+                    y = self.layer(l, xs[c], c)
+                    xs[c] = (xs[c].to(torch.float32) + y).to(torch.bfloat16)
+                if keep is not None:
+                    keep.append(y.clone())
+        if cuda:
+            for st in self.streams:
+                cur.wait_stream(st)
+            out = torch.cat(xs)
+            for t in xs:
+                t.record_stream(cur)
+            return out
+        return torch.cat(xs)

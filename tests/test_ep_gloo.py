@@ -66,14 +66,22 @@ def oracle_compute(layers, e_lo, e_hi):
     return Compute(route, experts)
 
 
-def worker(rank, world, port, out_dir, die):
+def chunked(compute):
+    """The same stand-in with the chunk argument of micro-batched runs (it needs no per-chunk buffers)."""
+    from strixite_b200.ep import Compute
+    return Compute(lambda l, x, c: compute.route(l, x), lambda l, xa, i, cf, c: compute.experts(l, xa, i, cf), chunked=True)
+
+
+def worker(rank, world, port, out_dir, die, micro=1):
     sys.path.insert(0, str(ROOT))
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
     from strixite_b200.ep import ExpertParallelMoe, shard_bounds
     x, layers = make_problem()
     e_lo, e_hi = shard_bounds(E, world, rank)
-    ep = ExpertParallelMoe(oracle_compute(layers, e_lo, e_hi), LAYERS, T, D, K_TOP, "cpu")
+    comp = oracle_compute(layers, e_lo, e_hi)
+    ep = ExpertParallelMoe(chunked(comp) if micro > 1 else comp, LAYERS, T, D, K_TOP, "cpu", micro=micro)
+    assert ep.micro == micro
     if die and rank == 1:
         os._exit(0)  # this rank never joins the first collective
     try:
@@ -111,6 +119,19 @@ def test_two_ranks_equal_one_rank(tmp_path, oracle):
     assert got.shape == want.shape
     assert torch.allclose(got.float(), want.float(), rtol=0, atol=2.0 ** -7 * float(want.float().abs().max()))
     assert (got != want).float().mean() < 0.02
+
+
+def test_two_ranks_with_micro_batches_equal_one_rank(tmp_path, oracle):
+    """Each rank's 6 rows as 2 and as 3 chunks: the chunks' stacks are independent, the result is the same rows."""
+    want = single_rank_reference()
+    for micro in (2, 3):
+        out = tmp_path / f"m{micro}"
+        out.mkdir()
+        mp.spawn(worker, args=(2, free_port(), str(out), False, micro), nprocs=2, join=True)
+        got = torch.cat([torch.load(out / f"out{r}.pt") for r in range(2)])
+        assert got.shape == want.shape
+        assert torch.allclose(got.float(), want.float(), rtol=0, atol=2.0 ** -7 * float(want.float().abs().max()))
+        assert (got != want).float().mean() < 0.02
 
 
 def test_a_rank_that_never_joins_is_an_error_not_a_hang(tmp_path, oracle):
