@@ -326,6 +326,9 @@ def run_stack(cfg, args, dev, rank, world, peaks, layers=None, rotate=False):
             torch.cuda.synchronize()
             k_ms = kernel_ms((st.events[0][layers:], st.events[1][layers:]))
             st.events = None
+    ep_timing = st.ep.timing_summary()
+    if ep_timing is not None and rank == 0:
+        print("ep phases, ms per layer (rank 0): " + ", ".join(f"{k} {v:.3f}" for k, v in ep_timing.items()), file=sys.stderr)
     layer_tokens = cfg.T * (1 if rotate else layers)
     out = dict(
         ms_per_step=ms, value=layer_tokens / (ms * 1e-3), e2e_value=layer_tokens / (e2e_ms * 1e-3), e2e_ms=e2e_ms,

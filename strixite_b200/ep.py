@@ -24,6 +24,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Callable, List, Optional
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -60,6 +62,8 @@ class ExpertParallelMoe:
         t = self.t_hi - self.t_lo
         self.micro = micro if (self.world > 1 and micro > 1 and compute.chunked and t % micro == 0) else 1
         self.streams = None
+        # STRIX_EP_TIMING=1: CUDA events around the phases of every layer (rank-local, for tuning the exchange)
+        self.timing = [] if (os.environ.get("STRIX_EP_TIMING") and self.world > 1) else None
         if self.world > 1:
             tc, Tc = t // self.micro, T // self.micro
             self.x_all = [torch.empty((Tc, d), dtype=torch.bfloat16, device=device) for _ in range(self.micro)]
@@ -80,18 +84,43 @@ class ExpertParallelMoe:
             return self._experts(l, x_loc, ids, coef, chunk)
         k = self.k
         x_all, route_loc, route_all = self.x_all[chunk], self.route_loc[chunk], self.route_all[chunk]
+        marks = []
+
+        def mark():
+            if self.timing is not None and x_loc.is_cuda:
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                marks.append(e)
+        mark()
         gather_x = dist.all_gather_into_tensor(x_all, x_loc.contiguous(), group=self.group, async_op=True)  # under the routing
         ids, coef = self._route(l, x_loc, chunk)
         route_loc[:, :k] = ids
         route_loc[:, k:] = coef.view(torch.int32)
+        mark()  # routing issued
         gather_r = dist.all_gather_into_tensor(route_all, route_loc, group=self.group, async_op=True)
         gather_x.wait()
         gather_r.wait()
         ids_all = route_all[:, :k].contiguous()
         coef_all = route_all[:, k:].contiguous().view(torch.float32)
+        mark()  # gathers landed
         y_part = self._experts(l, x_all, ids_all, coef_all, chunk)
+        mark()  # experts issued
         dist.reduce_scatter_tensor(self.y_loc[chunk], y_part, op=dist.ReduceOp.SUM, group=self.group)
+        mark()  # reduce-scatter
+        if marks:
+            self.timing.append(marks)
         return self.y_loc[chunk]
+
+    def timing_summary(self):
+        """Mean milliseconds per layer of (routing, waiting for the gathers, experts, reduce-scatter); needs a device sync."""
+        if not self.timing:
+            return None
+        torch.cuda.synchronize()
+        n = len(self.timing)
+        names = ("route", "gather_wait", "experts", "reduce_scatter")
+        out = {nm: sum(m[i].elapsed_time(m[i + 1]) for m in self.timing) / n for i, nm in enumerate(names)}
+        self.timing.clear()
+        return out
 
     def forward(self, x_loc: torch.Tensor, keep: Optional[List[torch.Tensor]] = None) -> torch.Tensor:
         """The stack: x <- bf16(x + moe_l(x)) for every layer; returns this rank's rows after the last layer."""
