@@ -163,7 +163,8 @@ class Stack:
         self.router_err = self.buf.router_err
         self.math = None          # None = by token count (tcgen05 from MoeLayer.tc_min_tokens up)
         self.events = None        # (list, list) of CUDA events around the dominant kernel when roofline timing is on
-        self.ep = ExpertParallelMoe(Compute(self._route, self._experts, chunked=True), layers, cfg.T, cfg.d, cfg.k, dev, micro=micro)
+        self.ep = ExpertParallelMoe(Compute(self._route, self._experts, chunked=True), layers, cfg.T, cfg.d, cfg.k, dev, micro=micro,
+                                    exchange=os.environ.get("STRIX_EP_EXCHANGE", "reduce_scatter"))
         self.weight_bytes = sum(ly.w.bytes() for ly in self.layers)
 
     def _route(self, l, x_loc, chunk=0):

@@ -51,7 +51,8 @@ def shard_bounds(total: int, world: int, rank: int):
 
 
 class ExpertParallelMoe:
-    def __init__(self, compute: Compute, n_layers: int, T: int, d: int, k: int, device, group=None, micro: int = 1):
+    def __init__(self, compute: Compute, n_layers: int, T: int, d: int, k: int, device, group=None, micro: int = 1,
+                 exchange: str = "reduce_scatter"):
         self.c = compute
         self.layers = n_layers
         self.group = group
@@ -62,6 +63,7 @@ class ExpertParallelMoe:
         t = self.t_hi - self.t_lo
         self.micro = micro if (self.world > 1 and micro > 1 and compute.chunked and t % micro == 0) else 1
         self.streams = None
+        self.exchange = exchange  # how the partial rows come back: "reduce_scatter" (NCCL's) or "a2a" (all-to-all + local sum)
         # STRIX_EP_TIMING=1: CUDA events around the phases of every layer (rank-local, for tuning the exchange)
         self.timing = [] if (os.environ.get("STRIX_EP_TIMING") and self.world > 1) else None
         if self.world > 1:
@@ -70,6 +72,8 @@ class ExpertParallelMoe:
             self.route_loc = [torch.empty((tc, 2 * k), dtype=torch.int32, device=device) for _ in range(self.micro)]   # ids | coef bits
             self.route_all = [torch.empty((Tc, 2 * k), dtype=torch.int32, device=device) for _ in range(self.micro)]
             self.y_loc = [torch.empty((tc, d), dtype=torch.float32, device=device) for _ in range(self.micro)]
+            if exchange == "a2a":
+                self.pieces = [torch.empty((self.world, tc, d), dtype=torch.float32, device=device) for _ in range(self.micro)]
 
     def _route(self, l, x, chunk):
         return self.c.route(l, x, chunk) if self.c.chunked else self.c.route(l, x)
@@ -105,7 +109,14 @@ class ExpertParallelMoe:
         mark()  # gathers landed
         y_part = self._experts(l, x_all, ids_all, coef_all, chunk)
         mark()  # experts issued
-        dist.reduce_scatter_tensor(self.y_loc[chunk], y_part, op=dist.ReduceOp.SUM, group=self.group)
+        if self.exchange == "a2a":
+            # every rank sends each peer that peer's rows of its partial sums directly (all links of the switch at once)
+            # and adds up the N pieces it receives, in rank order
+            pieces = self.pieces[chunk]
+            dist.all_to_all_single(pieces.view(-1), y_part.reshape(-1), group=self.group)
+            torch.sum(pieces, dim=0, out=self.y_loc[chunk])
+        else:
+            dist.reduce_scatter_tensor(self.y_loc[chunk], y_part, op=dist.ReduceOp.SUM, group=self.group)
         mark()  # reduce-scatter
         if marks:
             self.timing.append(marks)

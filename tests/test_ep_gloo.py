@@ -72,7 +72,7 @@ def chunked(compute):
     return Compute(lambda l, x, c: compute.route(l, x), lambda l, xa, i, cf, c: compute.experts(l, xa, i, cf), chunked=True)
 
 
-def worker(rank, world, port, out_dir, die, micro=1):
+def worker(rank, world, port, out_dir, die, micro=1, exchange="reduce_scatter"):
     sys.path.insert(0, str(ROOT))
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
@@ -80,7 +80,7 @@ def worker(rank, world, port, out_dir, die, micro=1):
     x, layers = make_problem()
     e_lo, e_hi = shard_bounds(E, world, rank)
     comp = oracle_compute(layers, e_lo, e_hi)
-    ep = ExpertParallelMoe(chunked(comp) if micro > 1 else comp, LAYERS, T, D, K_TOP, "cpu", micro=micro)
+    ep = ExpertParallelMoe(chunked(comp) if micro > 1 else comp, LAYERS, T, D, K_TOP, "cpu", micro=micro, exchange=exchange)
     assert ep.micro == micro
     if die and rank == 1:
         os._exit(0)  # this rank never joins the first collective
@@ -132,6 +132,15 @@ def test_two_ranks_with_micro_batches_equal_one_rank(tmp_path, oracle):
         assert got.shape == want.shape
         assert torch.allclose(got.float(), want.float(), rtol=0, atol=2.0 ** -7 * float(want.float().abs().max()))
         assert (got != want).float().mean() < 0.02
+
+
+def test_two_ranks_all_to_all_exchange_equals_one_rank(tmp_path, oracle):
+    """The partial rows returned by all-to-all + local sum instead of the reduce-scatter."""
+    want = single_rank_reference()
+    mp.spawn(worker, args=(2, free_port(), str(tmp_path), False, 1, "a2a"), nprocs=2, join=True)
+    got = torch.cat([torch.load(tmp_path / f"out{r}.pt") for r in range(2)])
+    assert torch.allclose(got.float(), want.float(), rtol=0, atol=2.0 ** -7 * float(want.float().abs().max()))
+    assert (got != want).float().mean() < 0.02
 
 
 def test_a_rank_that_never_joins_is_an_error_not_a_hang(tmp_path, oracle):
