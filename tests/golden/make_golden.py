@@ -1,6 +1,6 @@
 """Generates tests/golden/moe_golden.npz.  Run in a container that has the reference checkout:
 
-    make -C oracle all ref REF=/root/reference && python tests/golden/make_golden.py
+    make -C oracle all ref REF=<reference checkout> && python tests/golden/make_golden.py
 
 Quantizer known answers come from the REFERENCE's own formats/q4.cpp / formats/q8.cpp (compiled unchanged by
 oracle/Makefile); router, pack and layer vectors come from the oracle (the reference ships no CPU code and no vectors
