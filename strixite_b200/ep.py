@@ -50,6 +50,13 @@ def shard_bounds(total: int, world: int, rank: int):
     return rank * n, (rank + 1) * n
 
 
+def residual(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """bf16(x + y) with the sum in FP32: one elementwise pass (x BF16, y FP32 in, BF16 out)."""
+    out = torch.empty_like(x)
+    torch.add(x, y, out=out)
+    return out
+
+
 class ExpertParallelMoe:
     def __init__(self, compute: Compute, n_layers: int, T: int, d: int, k: int, device, group=None, micro: int = 1,
                  exchange: str = "reduce_scatter"):
@@ -141,7 +148,7 @@ class ExpertParallelMoe:
                 y = self.layer(l, x)
                 if keep is not None:
                     keep.append(y.clone())
-                x = (x.to(torch.float32) + y).to(torch.bfloat16)
+                x = residual(x, y)
             return x
         # micro-batches: chunk c's launches go to stream c; layers alternate between the chunks so that one chunk's
         # collectives are in flight while the other's kernels run
@@ -159,10 +166,10 @@ class ExpertParallelMoe:
                 if cuda:
                     with torch.cuda.stream(self.streams[c]):
                         y = self.layer(l, xs[c], c)
-                        xs[c] = (xs[c].to(torch.float32) + y).to(torch.bfloat16)
+                        xs[c] = residual(xs[c], y)
                 else:
                     y = self.layer(l, xs[c], c)
-                    xs[c] = (xs[c].to(torch.float32) + y).to(torch.bfloat16)
+                    xs[c] = residual(xs[c], y)
                 if keep is not None:
                     keep.append(y.clone())
         if cuda:
