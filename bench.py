@@ -531,7 +531,7 @@ def main():
         line["achieved_tflops_whole_step"] = algorithmic_flops(cfg, res["layers"], cfg.shared and world == 1) / (res["ms_per_step"] * 1e-3) / 1e12
 
     if rank == 0 and world == 1 and not args.no_cpu:
-        n_tok = args.cpu_tokens or (cfg.T if decode else 192)
+        n_tok = args.cpu_tokens or (cfg.T if decode else 768)
         try:
             cb, _ = cpu_baseline(cfg, res, n_tok, "decode" if decode else "grouped")
             line["cpu_baseline"] = cb
