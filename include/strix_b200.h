@@ -257,6 +257,47 @@ int sxb_stage_f16(const void *x, int64_t M, int64_t K, int bits, void *xh, sxb_s
 int sxb_stage_f16_tiles(const void *x, const void *ws, size_t ws_bytes, int64_t M, int64_t A, int64_t E, int64_t K, int bits,
                         void *xs, sxb_stream_t stream);
 
+/* ---- The whole block as one call ---------------------------------------------------------------------------- */
+
+/* One MoE block: what runtime/qwen4exp.cpp:3143-3217 issues launcher by launcher - router top-k, grouping, gate/up +
+ * SwiGLU, down + combine, the shared expert folded into the combine - as one entry point on one stream.  Every buffer is
+ * the caller's (sizes below; the reference's session buffers, runtime/qwen4exp.cpp:1018-1027,1092-1101); nothing is
+ * allocated and nothing synchronizes.  The rounding points are those of the entry points it calls. */
+typedef struct SxbMoeLayerArgs {
+    int64_t M;                     /* tokens */
+    int64_t E, A;                  /* experts in the weight views; active experts per token */
+    int64_t E_total, e_lo;         /* E_total == E: all experts are here.  Otherwise the views hold experts [e_lo, e_lo + E) of
+                                      E_total (an expert-parallel rank) and y receives this rank's partial sums */
+    const SxbQView *gate_up, *down;/* stacked experts [E * 2I, d] and [E * d, I] */
+    int gate_up_bits, down_bits;   /* 4 or 8 */
+    const SxbQView *shared_gate_up, *shared_down; /* the always-on shared expert [2I, d], [d, I]; NULL, NULL = none */
+    int shared_bits;
+    const void *x;                 /* [M, d] BF16 */
+    const float *logits;           /* [M, logits_ld] FP32 router logits; with a shared expert column E_total is its gate */
+    int64_t logits_ld;
+    void *y;                       /* [M, d] */
+    int out_act;                   /* SXB_ACT_BF16, or SXB_ACT_F32 for the unrounded sums */
+    int math;                      /* SXB_MATH_*; -1 = the tcgen05 kernels from 256 tokens up, the streaming ones below */
+    /* work buffers */
+    int32_t *ids;                  /* [M, A] */
+    float *coef;                   /* [M, A] */
+    void *ws;                      /* sxb_moe_route_workspace_bytes(M, A, E) */
+    size_t ws_bytes;
+    void *h;                       /* [M * A, I] 16-bit */
+    float *partial;                /* [M * A, d] */
+    void *xs;                      /* [M * A, d] F16: tile-blocked activations; tcgen05 path only (else may be NULL) */
+    void *sh_gu, *sh_h;            /* shared expert: [M, 2I] (streaming path only), [M, I], 16-bit */
+    void *sh_y;                    /* shared expert's output [M, d] in y's dtype */
+    int32_t *sh_ids;               /* the rest: tcgen05 path with a shared expert only.  [M] */
+    float *sh_coef;                /* [M] */
+    void *sh_ws;                   /* sxb_moe_route_workspace_bytes(M, 1, 1) */
+    size_t sh_ws_bytes;
+    float *sh_partial;             /* [M, d] */
+    void *sh_xs;                   /* [M, d] F16 */
+    uint32_t *router_err, *expert_err; /* >= 3 words each, zeroed by the caller at session start */
+} SxbMoeLayerArgs;
+int sxb_moe_layer(const SxbMoeLayerArgs *args, sxb_stream_t stream);
+
 /* ---- Quantizers on the device ------------------------------------------------------------------------------- */
 
 /* formats/q4.hpp:32 quantize_q4 / formats/q8.hpp:32 quantize_q8, for weights already on the device: w [N, K] FP32 ->

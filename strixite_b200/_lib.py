@@ -29,6 +29,18 @@ class SxbMoeSharedAdd(C.Structure):
     _fields_ = [("s", vp), ("gate_logit", vp), ("gate_ld", i64), ("gate_index", u32), ("err", vp)]
 
 
+class SxbMoeLayerArgs(C.Structure):
+    """The argument block of sxb_moe_layer (include/strix_b200.h), field for field."""
+
+    _fields_ = [("M", i64), ("E", i64), ("A", i64), ("E_total", i64), ("e_lo", i64),
+                ("gate_up", C.POINTER(SxbQView)), ("down", C.POINTER(SxbQView)), ("gate_up_bits", C.c_int), ("down_bits", C.c_int),
+                ("shared_gate_up", C.POINTER(SxbQView)), ("shared_down", C.POINTER(SxbQView)), ("shared_bits", C.c_int),
+                ("x", vp), ("logits", vp), ("logits_ld", i64), ("y", vp), ("out_act", C.c_int), ("math", C.c_int),
+                ("ids", vp), ("coef", vp), ("ws", vp), ("ws_bytes", sz), ("h", vp), ("partial", vp), ("xs", vp),
+                ("sh_gu", vp), ("sh_h", vp), ("sh_y", vp), ("sh_ids", vp), ("sh_coef", vp), ("sh_ws", vp), ("sh_ws_bytes", sz),
+                ("sh_partial", vp), ("sh_xs", vp), ("router_err", vp), ("expert_err", vp)]
+
+
 QV = C.POINTER(SxbQView)
 SA = C.POINTER(SxbMoeSharedAdd)
 
@@ -54,6 +66,7 @@ SIGNATURES = {
     "sxb_check_expert_error": (C.c_int, [vp, cp]),
     "sxb_report_expert_error": (C.c_int, [C.POINTER(u32), cp]),
     "sxb_quantize": (C.c_int, [vp, i64, i64, i64, C.c_int, vp, vp, vp, vp, vp]),
+    "sxb_moe_layer": (C.c_int, [C.POINTER(SxbMoeLayerArgs), vp]),
 }
 for _b in ("q4", "q8"):
     SIGNATURES[f"sxb_linear_{_b}_experts_gather"] = (C.c_int, [vp, QV, i64, vp, i64, i64, vp, C.c_int, vp, vp])

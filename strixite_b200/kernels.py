@@ -275,3 +275,35 @@ def quantize(w: torch.Tensor, G: int, bits: int, err: Optional[torch.Tensor] = N
     if own and int(err[0].item()) != 0:
         raise Error(1, f"quantize: non-finite weight at [{int(err[1])}, {int(err[2])}]")
     return QDeviceView(q, scale, minv, N, K, G, bits)
+
+
+# ---- the whole block as one call ------------------------------------------------------------------------------
+
+def moe_layer(x, logits, y, gate_up: QDeviceView, down: QDeviceView, E, A, ids, coef, ws, ws_bytes, h, partial, router_err,
+              expert_err, xs=None, math=None, E_total=None, e_lo=0, shared_gate_up: Optional[QDeviceView] = None,
+              shared_down: Optional[QDeviceView] = None, sh_gu=None, sh_h=None, sh_y=None, sh_ids=None, sh_coef=None, sh_ws=None,
+              sh_ws_bytes=0, sh_partial=None, sh_xs=None, stream=None):
+    """sxb_moe_layer: router, grouping, gate/up + SwiGLU, down + combine (+ shared expert) enqueued by one C call.
+    x [M, d] BF16, logits [M, ld] FP32, y [M, d] BF16 or FP32; the rest are the caller's work buffers."""
+    M = x.shape[0]
+    gu, dn = gate_up.c(), down.c()
+    a = _lib.SxbMoeLayerArgs()
+    a.M, a.E, a.A, a.E_total, a.e_lo = M, E, A, (E if E_total is None else E_total), e_lo
+    a.gate_up, a.down, a.gate_up_bits, a.down_bits = C.pointer(gu), C.pointer(dn), gate_up.bits, down.bits
+    keep = [gu, dn]
+    if shared_gate_up is not None:
+        sgu, sdn = shared_gate_up.c(), shared_down.c()
+        keep += [sgu, sdn]
+        a.shared_gate_up, a.shared_down, a.shared_bits = C.pointer(sgu), C.pointer(sdn), shared_gate_up.bits
+    a.x, a.logits, a.logits_ld, a.y = _ptr(x), _ptr(logits), logits.stride(0), _ptr(y)
+    a.out_act = int(Act.F32 if y.dtype == torch.float32 else Act.BF16)
+    a.math = -1 if math is None else int(math)
+    a.ids, a.coef, a.ws, a.ws_bytes, a.h, a.partial = _ptr(ids), _ptr(coef), _ptr(ws), ws_bytes, _ptr(h), _ptr(partial)
+    a.xs = _ptr(xs) if xs is not None else None
+    for name, t in (("sh_gu", sh_gu), ("sh_h", sh_h), ("sh_y", sh_y), ("sh_ids", sh_ids), ("sh_coef", sh_coef), ("sh_ws", sh_ws),
+                    ("sh_partial", sh_partial), ("sh_xs", sh_xs)):
+        setattr(a, name, _ptr(t) if t is not None else None)
+    a.sh_ws_bytes = sh_ws_bytes
+    a.router_err, a.expert_err = _ptr(router_err), _ptr(expert_err)
+    _count(8)
+    _check(_lib.load().sxb_moe_layer(C.byref(a), _stream(stream)))

@@ -178,3 +178,44 @@ def test_expert_parallel_shards_add_up(cuda, name, T, tc):
             total += y
         scale = y_ref.abs().max().item()
         assert (total - y_ref).abs().max().item() <= 2e-5 * scale, f"{cfg.name}: {shards} shards do not add up to the whole"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,T,tc,shared", [("c0", 4, False, False), ("c1", 16, False, True), ("c0", 96, True, False),
+                                               ("c2", 0, False, False), ("c1e", 320, True, True)])
+def test_one_call_layer_equals_the_launch_sequence(cuda, name, T, tc, shared):
+    """sxb_moe_layer (the whole block enqueued by one C call) against the same block issued launcher by launcher:
+    the same kernels with the same arguments, so the outputs are bit-identical (BF16 and FP32 outputs)."""
+    from dataclasses import replace
+    from strixite_b200 import kernels as K, workloads as W
+    from strixite_b200.kernels import MoeMath
+    from strixite_b200.layer import MoeBuffers, MoeLayer
+    cfg = replace(W.C1, E=32, name="c1e") if name == "c1e" else W.CONFIGS[name]
+    cfg = replace(cfg, shared=shared, **({"T": T} if T else {}))
+    math = MoeMath.WmmaF16 if tc else MoeMath.F32
+    x = W.activations(cfg, 5, cuda)
+    logits = W.router_logits(x, W.router_weight(cfg, 5, cuda), W.expert_bias(cfg, 5, cuda))
+    w = W.make_layer_weights(cfg, 5, cuda)
+    buf = MoeBuffers(cfg.T, cfg.d, cfg.I, cfg.E, cfg.k, cuda, shared)
+    layer = MoeLayer(w, cfg.E, cfg.k, buf)
+    b2 = MoeBuffers(cfg.T, cfg.d, cfg.I, cfg.E, cfg.k, cuda, shared)
+    S = cfg.T * cfg.k
+    xs = torch.empty((S, cfg.d), dtype=torch.float16, device=cuda) if tc else None
+    sh_xs = torch.empty((cfg.T, cfg.d), dtype=torch.float16, device=cuda) if (tc and shared) else None
+    for dt in (torch.float32, torch.bfloat16):
+        want = torch.empty((cfg.T, cfg.d), dtype=dt, device=cuda)
+        got = torch.empty_like(want)
+        layer.forward(x, logits, want, math=math)
+        extra = {}
+        if shared:
+            extra = dict(shared_gate_up=w.shared_gate_up, shared_down=w.shared_down, sh_gu=b2.sh_gu, sh_h=b2.sh_h,
+                         sh_y=b2.sh_y32 if dt == torch.float32 else b2.sh_y, sh_ids=b2.sh_ids, sh_coef=b2.sh_coef, sh_ws=b2.sh_ws,
+                         sh_ws_bytes=b2.sh_ws_bytes, sh_partial=b2.sh_partial, sh_xs=sh_xs)
+        K.moe_layer(x, logits, got, w.gate_up, w.down, cfg.E, cfg.k, b2.ids, b2.coef, b2.ws, b2.ws_bytes, b2.h, b2.partial,
+                    b2.router_err, b2.expert_err, xs=xs, math=math, **extra)
+        torch.cuda.synchronize()
+        K.check_router_error(b2.router_err, cfg.name)
+        K.check_expert_error(b2.expert_err, cfg.name)
+        assert torch.equal(b2.ids, buf.ids)
+        assert torch.equal(got.view(torch.int32 if dt == torch.float32 else torch.int16),
+                           want.view(torch.int32 if dt == torch.float32 else torch.int16)), f"{cfg.name} {dt}"
