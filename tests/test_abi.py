@@ -88,3 +88,21 @@ def test_report_errors(lib):
         K.report_router_error([1, 7, 512], "layer 3")
     with pytest.raises(K.Error, match="expert id -1 at slot 42"):
         K.report_expert_error([1, 0xFFFFFFFF, 42], "L0")
+
+
+def test_layer_argument_block_matches_the_header(tmp_path):
+    """The ctypes mirror of SxbMoeLayerArgs against the C compiler's layout of the header's struct: size and every offset."""
+    from strixite_b200 import _lib
+    names = [f[0] for f in _lib.SxbMoeLayerArgs._fields_]
+    src = tmp_path / "layout.c"
+    body = "\n".join(f'    printf("{n} %zu\\n", offsetof(SxbMoeLayerArgs, {n}));' for n in names)
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "strix_b200.h"\nint main(void) {\n'
+                   '    printf("sizeof %zu\\n", sizeof(SxbMoeLayerArgs));\n' + body + "\n    return 0;\n}\n")
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-std=c99", f"-I{ROOT / 'include'}", str(src), "-o", str(exe)], check=True)
+    out = dict(line.split() for line in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines())
+    assert int(out["sizeof"]) == C.sizeof(_lib.SxbMoeLayerArgs)
+    for n in names:
+        assert int(out[n]) == getattr(_lib.SxbMoeLayerArgs, n).offset, n
+    for struct, fields in ((_lib.SxbQView, 6), (_lib.SxbMoeSharedAdd, 5)):
+        assert len(struct._fields_) == fields
