@@ -106,3 +106,19 @@ def test_layer_argument_block_matches_the_header(tmp_path):
         assert int(out[n]) == getattr(_lib.SxbMoeLayerArgs, n).offset, n
     for struct, fields in ((_lib.SxbQView, 6), (_lib.SxbMoeSharedAdd, 5)):
         assert len(struct._fields_) == fields
+
+
+def test_layer_entry_checks_its_argument_block(lib):
+    """sxb_moe_layer refuses a bad argument block before anything is enqueued (no GPU needed)."""
+    from strixite_b200 import _lib
+    assert lib.sxb_moe_layer(None, None) == 1 and "null argument block" in lib.sxb_last_error().decode()
+    a = _lib.SxbMoeLayerArgs()
+    assert lib.sxb_moe_layer(C.byref(a), None) == 1 and "null weight view" in lib.sxb_last_error().decode()
+    gu, dn = _lib.SxbQView(4096, 8192, 12288, 64 * 2 * 128, 256, 128), _lib.SxbQView(4096, 8192, 12288, 64 * 256, 128, 128)
+    a.gate_up, a.down, a.gate_up_bits, a.down_bits = C.pointer(gu), C.pointer(dn), 4, 5
+    assert lib.sxb_moe_layer(C.byref(a), None) == 1 and "weight bits 4 / 5" in lib.sxb_last_error().decode()
+    a.down_bits = 8
+    a.M, a.E, a.A, a.E_total, a.e_lo = 4, 64, 4, 32, 0
+    assert lib.sxb_moe_layer(C.byref(a), None) == 1 and "experts [0, 64) of 32" in lib.sxb_last_error().decode()
+    a.E_total = 64
+    assert lib.sxb_moe_layer(C.byref(a), None) == 1 and "null buffer" in lib.sxb_last_error().decode()
