@@ -188,4 +188,7 @@ inline void swiglu(const void *gu, void *h, int64_t rows, int64_t I, Act act, hi
     b200_detail::check(sxb_swiglu(gu, h, rows, I, b200_detail::act(act), stream));
 }
 
+// No counterpart upstream: the whole block (the call sequence of runtime/qwen4exp.cpp:3143-3217) as one call.
+inline void moe_layer(const SxbMoeLayerArgs &args, hipStream_t stream) { b200_detail::check(sxb_moe_layer(&args, stream)); }
+
 }  // namespace strix::kernels
