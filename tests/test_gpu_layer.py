@@ -140,6 +140,15 @@ def test_layer_tcgen05_c3_prefill(cuda, oracle):
 
 
 @pytest.mark.gpu
+def test_layer_tcgen05_c4_layer(cuda, oracle):
+    """One layer of C4 at full size (T = 16384, Q4 gate/up, Q8 down, Zipf-biased routing: tiles from a few tokens to full)
+    on the tcgen05 path; 24 seeded rows against the oracle."""
+    from strixite_b200 import workloads as W
+    err = tc_layer_case(cuda, oracle, W.C4, 24)
+    print(f"c4 layer tcgen05 max-abs error {err:.3e} x RMS")
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("name,T,tc", [("c0", 96, True), ("c0", 4, False), ("c2", 0, False)])
 def test_expert_parallel_shards_add_up(cuda, name, T, tc):
     """The expert-parallel entry points on ONE GPU: every shard of the experts (2 and 4 shards), run with all tokens and the
