@@ -207,6 +207,38 @@ __device__ inline void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t 
         : "memory");
 }
 
+// One k-block of an accumulator as one instruction group: a non-blocking probe of the NEXT k-block's "operands ready"
+// barrier first, then the four MMAs (k = 16 each; the A columns advance by 8, the B descriptor by 32 bytes), the commit
+// that frees the stage and, for the last k-block of an item, the commit that hands the accumulators over.  The probe's
+// answer is read only after the commits, so its latency passes under their issue; when it says "ready" the next
+// k-block starts without a poll.  Whole-warp call, one elected lane issues.
+__device__ inline bool tc_kblock_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate,
+                                    uint64_t *stage_free, uint64_t *acc_done, uint64_t *next_full, uint32_t next_parity) {
+    uint32_t ready;
+    asm volatile(
+        "{\n\t.reg .pred p, q, r, t, one;\n\t.reg .b32 a1, a2, a3;\n\t.reg .b64 b1, b2, b3;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 r, [%7], %8;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "setp.eq.b32 one, 0, 0;\n\t"
+        "add.u32 a1, %2, 8;\n\tadd.u32 a2, %2, 16;\n\tadd.u32 a3, %2, 24;\n\t"
+        "add.u64 b1, %3, 2;\n\tadd.u64 b2, %3, 4;\n\tadd.u64 b3, %3, 6;\n\t"
+        "elect.sync _|q, 0xffffffff;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [%2], %3, %4, p;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [a1], b1, %4, one;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [a2], b2, %4, one;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [a3], b3, %4, one;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"
+        "setp.ne.b32 t, %9, 0;\n\t"
+        "and.pred t, t, q;\n\t"
+        "@t tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%9];\n\t"
+        "selp.u32 %0, 1, 0, r;\n\t}"
+        : "=r"(ready)
+        : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(smem_u32(stage_free)),
+          "r"(smem_u32(next_full)), "r"(next_parity), "r"(acc_done ? smem_u32(acc_done) : 0u)
+        : "memory");
+    return ready != 0;
+}
+
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart.
 //   bits [0,14) start address >> 4 | [16,30) leading byte offset >> 4 (unused for swizzled K-major: 1)
 //   [32,46) stride byte offset >> 4 (1024 B) | [46,48) descriptor version 1 | [61,64) layout 2 = SWIZZLE_128B
@@ -717,6 +749,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
         const int half = __shfl_sync(0xffffffffu, warp, 0) - kMmaWarp;
         const uint32_t d = tmem_base + (uint32_t)(half * kAccCols);
         uint32_t it_count = 0, acc_count = 0;
+        bool ready = false;  // the probe issued with the previous k-block already saw this one's operands
         for (int item = blockIdx.x; item < n_items && !*abort_v; item += gridDim.x) {
             const ItemInfo it = item_info<MODE>(a, item, rbs);
             if (it.bucket >= a.E) continue;
@@ -737,7 +770,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
                 const uint32_t phase = (it_count / kStages) & 1u;
                 {
                     PROF_BEGIN();
-                    if (lane == 0 && !mbar_wait(&full_bar[stage], phase, abort_v)) raise_abort(item, 3);
+                    if (lane == 0 && !ready && !mbar_wait(&full_bar[stage], phase, abort_v)) raise_abort(item, 3);
                     if (half == 0) {
                         PROF_ADD(5);
                         PROF_COUNT(8);
@@ -750,11 +783,11 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
                 PROF_BEGIN();
                 const uint64_t b_desc = smem_desc(smem_u32(smem + stage * kStageBytes));
                 const uint32_t at = tmem_base + (uint32_t)(kAStageCol0 + stage * kAStageCols + half * (kBK / 2));
-#pragma unroll
-                for (int j = 0; j < kBK / 16; ++j) tc_mma_f16_ts(d, at + j * 8, b_desc + 2 * j, idesc, (kb | j) != 0);
+                static_assert(kBK / 16 == 4, "tc_kblock_ts issues four MMAs");
+                // the stage is freed when these MMAs have read it; the last k-block hands the accumulators to the epilogue
+                ready = tc_kblock_ts(d, at, b_desc, idesc, kb != 0, &empty_bar[stage], kb == n_kb - 1 ? &acc_full[0] : nullptr,
+                                     &full_bar[(it_count + 1) % kStages], ((it_count + 1) / kStages) & 1u);
                 if (half == 0) PROF_ADD(20);
-                tc_commit(&empty_bar[stage]);                 // frees the stage when these MMAs have read it
-                if (kb == n_kb - 1) tc_commit(&acc_full[0]);  // and hands the accumulators to the epilogue
                 if (half == 0) {
                     PROF_ADD(6);
                     TRACE(2, it_count, 1);
