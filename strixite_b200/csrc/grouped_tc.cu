@@ -768,18 +768,28 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
             for (int kb = 0; kb < n_kb; ++kb, ++it_count) {
                 const int stage = it_count % kStages;
                 const uint32_t phase = (it_count / kStages) & 1u;
+                bool failed = false;
                 {
                     PROF_BEGIN();
-                    if (lane == 0 && !ready && !mbar_wait(&full_bar[stage], phase, abort_v)) raise_abort(item, 3);
+                    if (lane == 0 && !ready && !mbar_wait(&full_bar[stage], phase, abort_v)) raise_abort(item, 3), failed = true;
                     if (half == 0) {
                         PROF_ADD(5);
                         PROF_COUNT(8);
                         TRACE(2, it_count, 0);
                     }
                 }
-                __syncwarp();
-                if (*abort_v) break;
-                tc_fence_after();
+                {
+                    // One vote reconverges the warp and tells it whether lane 0's wait gave up (a wait gives up when its
+                    // limit runs out or once another warp has raised the abort flag); the item loop re-reads the flag.
+                    PROF_BEGIN();
+                    if (__any_sync(0xffffffffu, failed)) break;
+                    if (half == 0) PROF_ADD(21);
+                }
+                {
+                    PROF_BEGIN();
+                    tc_fence_after();
+                    if (half == 0) PROF_ADD(22);
+                }
                 PROF_BEGIN();
                 const uint64_t b_desc = smem_desc(smem_u32(smem + stage * kStageBytes));
                 const uint32_t at = tmem_base + (uint32_t)(kAStageCol0 + stage * kAStageCols + half * (kBK / 2));
