@@ -15,8 +15,12 @@ fixed as N grows.
 At N = 1 the line also carries, under "other_workloads", the decode configuration C1 (HBM-bound: achieved GB/s of
 algorithmic bytes) and the single-layer prefill configuration C3 (tensor-bound), each with its own roofline entry.
 
+After the timed region rank 0 pushes a few of its token rows through the CPU oracle, layer by layer with the GPU's own
+layer inputs and logits, and reports the largest error of the stack under "parity" (every N).
+
 --impl reference times the CPU oracle (the restatement of the reference's arithmetic; the reference ships no CPU or
-CUDA implementation of this path) on the host cores, on a bounded sample of the same workload.
+CUDA implementation of this path) on the host cores, on a bounded sample of the same workload - the same sample, from
+the same function, as the "cpu_baseline" leg of the default arm.
 """
 from __future__ import annotations
 
@@ -38,7 +42,7 @@ def parse():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c4", choices=["c1", "c2", "c3", "c4"])
+    ap.add_argument("--workload", default="c4", choices=["c0", "c1", "c2", "c3", "c4"])
     ap.add_argument("--layers", type=int, default=0, help="layers resident (default: the configuration's)")
     ap.add_argument("--no-extra", action="store_true", help="skip the C1 / C3 side measurements at N = 1")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -48,6 +52,9 @@ def parse():
     ap.add_argument("--no-graph", action="store_true", help="decode workloads: launch eagerly instead of replaying CUDA graphs")
     ap.add_argument("--micro", type=int, default=0, help="micro-batches per rank in expert-parallel runs (default 1)")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--parity-rows", type=int, default=32, help="token rows checked against the CPU oracle after the timed region (0 = skip)")
+    ap.add_argument("--planes", type=int, default=3, help="BF16 planes of the FP32 router weight on the tensor-core projection (2 or 3)")
+    ap.add_argument("--math", default="", help="tcgen05 numerics: wmma_f16 (BF16 per-slot dots, the reference's) or wmma_f16_f32p")
     return ap.parse_args()
 
 
@@ -125,7 +132,7 @@ class Stack:
     """Resident state of a configuration on this rank: per-layer weights (this rank's experts), router weights, biases,
     the shared workspaces, and the expert-parallel driver."""
 
-    def __init__(self, cfg, layers, seed, dev, rank, world, micro=0):
+    def __init__(self, cfg, layers, seed, dev, rank, world, micro=0, planes=3):
         import torch
         from strixite_b200 import workloads as W
         from strixite_b200.ep import Compute, ExpertParallelMoe, shard_bounds
@@ -155,12 +162,18 @@ class Stack:
             self.wr.append(W.router_weight(cfg, seed, dev, layer=l))
             self.bias.append(W.expert_bias(cfg, seed, dev, layer=l))
         self.layers = self.layer_sets[0]
+        # The router-logits projection is the library's: the tensor-core form over the weight split into BF16 planes at
+        # load time for prefill-sized batches, the streaming form (the FP32 weight as it is) for decode.
+        from strixite_b200 import kernels as K
+        self.proj_wmma = t // micro >= 128
+        self.planes = [K.router_prepare(w, planes) for w in self.wr] if self.proj_wmma else None
         tc = t // micro
         self.ids_loc = [torch.empty((tc, cfg.k), dtype=torch.int32, device=dev) for _ in range(micro)]
         self.coef_loc = [torch.empty((tc, cfg.k), dtype=torch.float32, device=dev) for _ in range(micro)]
         self.y_part = [torch.empty((Tc, cfg.d), dtype=torch.float32, device=dev) for _ in range(micro)]
-        self.logits = [None] * micro
+        self.logits = [torch.empty((tc, cfg.E + 1), dtype=torch.float32, device=dev) for _ in range(micro)]
         self.router_err = self.buf.router_err
+        self.packed = [False] * micro
         self.math = None          # None = by token count (tcgen05 from MoeLayer.tc_min_tokens up)
         self.events = None        # (list, list) of CUDA events around the dominant kernel when roofline timing is on
         self.ep = ExpertParallelMoe(Compute(self._route, self._experts, chunked=True), layers, cfg.T, cfg.d, cfg.k, dev, micro=micro,
@@ -169,14 +182,17 @@ class Stack:
 
     def _route(self, l, x_loc, chunk=0):
         from strixite_b200 import kernels as K, workloads as W
-        logits = W.router_logits(x_loc, self.wr[l], self.bias[l], tf32=x_loc.shape[0] >= 256)
-        self.logits[chunk] = logits
         t = x_loc.shape[0]
-        buf = self.bufs[chunk]
-        if self.world == 1:
-            ids, coef = buf.ids, buf.coef
+        logits = self.logits[chunk][:t]
+        if self.proj_wmma:
+            K.router_logits_wmma(x_loc, self.planes[l], self.bias[l], logits)
         else:
-            ids, coef = self.ids_loc[chunk], self.coef_loc[chunk]
+            K.router_logits(x_loc, self.wr[l], self.bias[l], logits)
+        buf = self.bufs[chunk]
+        if self.world == 1:  # the layer's own routing (router and pack as one launch for a small batch)
+            self.packed[chunk] = self.layer_sets[chunk][l].route(logits, t)
+            return buf.ids, buf.coef
+        ids, coef = self.ids_loc[chunk], self.coef_loc[chunk]
         K.moe_router(logits, logits.stride(0), t, self.cfg.E, self.cfg.k, None, 1, 0, ids, coef, K.Act.F32, buf.router_err)
         return ids, coef
 
@@ -189,7 +205,7 @@ class Stack:
             buf.coef.copy_(coef_all)
         math = layer.math_for(T, self.math)
         y = self.y_part[chunk][:T]
-        layer.run_experts(x_all, T, y, math, self.logits[chunk], events=self.events)
+        layer.run_experts(x_all, T, y, math, self.logits[chunk], events=self.events, packed=self.packed[chunk] and self.world == 1)
         return y
 
     def step(self, x_loc):
@@ -249,7 +265,13 @@ def run_stack(cfg, args, dev, rank, world, peaks, layers=None, rotate=False):
     from strixite_b200 import kernels as K, workloads as W
 
     layers = layers or args.layers or cfg.layers
-    st = Stack(cfg, layers, args.seed, dev, rank, world, micro=getattr(args, "micro", 0))
+    st = Stack(cfg, layers, args.seed, dev, rank, world, micro=getattr(args, "micro", 0), planes=getattr(args, "planes", 3))
+    if getattr(args, "math", ""):
+        from strixite_b200.kernels import MoeMath
+        st.math_tc = {"wmma_f16": MoeMath.WmmaF16, "wmma_f16_f32p": MoeMath.WmmaF16F32Partials}[args.math]
+        for ls in st.layer_sets:
+            for ly in ls:
+                ly.tc_math = st.math_tc
     t_loc = st.t_hi - st.t_lo
     x_full = W.activations(cfg, args.seed, dev)
     x_loc = x_full[st.t_lo:st.t_hi].contiguous()
@@ -353,7 +375,8 @@ def roofline_tensor(cfg, res, peaks, world):
     ly = res["stack"].layers[0]
     traffic = 1.003 * (ly.w.gate_up.bytes() + cfg.T * cfg.k / world / micro * cfg.d * 2)
     return dict(bound="tensor", kernel="grouped_tc_kernel<gate_up+swiglu>", achieved=achieved, peak=peak, unit="TFLOP/s",
-                frac=achieved / peak, peak_source=peaks["source"] + " (sustained bf16)", traffic=traffic,
+                frac=achieved / peak, peak_source=peaks["source"] + " (sustained bf16)",
+                frac_of_burst=achieved / peaks["tflops_burst"], peak_burst=peaks["tflops_burst"], traffic=traffic,
                 traffic_source="dram bytes of an ncu capture of a reduced case, scaled by algorithmic bytes",
                 flops_per_launch=flops, kernel_ms=res["kernel_ms"])
 
@@ -388,90 +411,156 @@ def decode_bytes_mean(cfg, res):
     return sum(p[0] for p in per_layer) / n, sum(p[1] for p in per_layer) / n, sum(p[2] for p in per_layer) / n
 
 
-def cpu_baseline(cfg, res, n_tokens, semantics):
-    """The oracle on the host cores for a sample of the workload's tokens through layer 0 (rank 0, N = 1)."""
+def config_dict(cfg, layers, world, micro=1, extra=None):
+    """The workload's description, the same keys on every arm."""
+    d = {"workload": cfg.name, "T": cfg.T, "layers": layers, "hidden": cfg.d, "experts": cfg.E, "experts_per_gpu": cfg.E // world,
+         "top_k": cfg.k, "intermediate": cfg.I, "gate_up": f"q{cfg.gu_bits}g{cfg.group(cfg.gu_bits)}",
+         "down": f"q{cfg.dn_bits}g{cfg.group(cfg.dn_bits)}", "shared_expert": cfg.shared, "expert_bias": cfg.bias,
+         "parallelism": f"ep{world}" + (f", {micro} micro-batches a rank" if micro > 1 else ""), "value_is": "T * layers / step time"}
+    d.update(extra or {})
+    return d
+
+
+def semantics_of(cfg, math=None):
+    if cfg.T < 256:
+        return "decode"
+    return "grouped_f32_partials" if (math is not None and int(math) == 6) else "grouped"
+
+
+def cpu_sample(cfg, seed, n_tokens, semantics, dev, repeats=1, warmup=0):
+    """The CPU oracle on the first n_tokens rows of layer 0 of the workload, on all host cores: inputs drawn as the GPU arm
+    draws them (same generators, same seed), router logits formed on the host in float64, the experts those rows pick
+    regenerated and quantized expert by expert.  Returns (seconds per pass, oracle output, cores).  Only the oracle's
+    moe_layer is timed."""
     import numpy as np
-    sys.path.insert(0, str(ROOT / "tests"))
-    from helpers import bits_of
-    from oracle import cpu
-    from test_gpu_layer import oracle_layer_on_touched_experts
-    st = res["stack"]
+    from oracle import check, cpu
     from strixite_b200 import workloads as W
-    x = res["x_full"]
-    logits = W.router_logits(x[:n_tokens], st.wr[0], st.bias[0]).cpu().numpy()
-    xb = bits_of(x[:n_tokens])
-    rows = np.arange(n_tokens)
-    w = st.layers[0].w
-    # time only the oracle's arithmetic: the download of the touched experts happens inside, so run it twice and
-    # time the second pass on warmed page cache... the download dominates nothing: it is excluded by timing the
-    # oracle call through a wrapper that stamps the clock around moe_layer itself.
-    stamps = {}
+    cpu.build(None)
+    x = W.activations(cfg, seed, dev)[:n_tokens]
+    xb = check.bits_of(x)
+    wr = W.router_weight(cfg, seed, dev).cpu().numpy().astype(np.float64)
+    bias = W.expert_bias(cfg, seed, dev).cpu().numpy().astype(np.float64)
+    logits = (cpu.bf16_to_f32(xb).astype(np.float64) @ wr.T + bias).astype(np.float32)
+    shared = None
+    if cfg.shared:
+        import torch
+        def one(which):
+            w32 = W.expert_weight_f32(cfg, seed, dev, which, 0, 0)
+            if torch.device(dev).type == "cuda":
+                from strixite_b200 import kernels as K
+                return check.download(K.quantize(w32, 64, 8), cpu)
+            return cpu.quantize(w32.numpy(), 64, 8)
+        shared = (one("shared_gate_up"), one("shared_down"))
+    times, out = [], None
     real = cpu.moe_layer
 
     def stamped(*a, **k):
         t0 = time.perf_counter()
-        out = real(*a, **k)
-        stamps["s"] = time.perf_counter() - t0
-        return out
+        r = real(*a, **k)
+        times.append(time.perf_counter() - t0)
+        return r
+
+    fetched = {}
+    gen = check.generated_experts(cfg, seed, 0, dev)
+
+    def fetch(which, experts):  # the weights are generated once, outside the timed call, and reused by every pass
+        key = (which, tuple(int(e) for e in experts))
+        if key not in fetched:
+            fetched[key] = gen(which, experts)
+        return fetched[key]
 
     cpu.moe_layer = stamped
     try:
-        ref = oracle_layer_on_touched_experts(cpu, cfg, w, xb, logits, rows, semantics)
+        for _ in range(warmup + repeats):
+            out = check.oracle_layer_with(cpu, cfg, fetch, shared, xb, logits, semantics)
     finally:
         cpu.moe_layer = real
-    return dict(value=n_tokens / stamps["s"], unit="MoE-layer tokens/s", cores=cpu.hardware_threads(), kind="port",
-                sample=f"{n_tokens} tokens of layer 0 of {cfg.name} through the CPU oracle ({semantics} semantics), "
-                       f"{stamps['s']:.2f} s"), ref
+    kept = times[warmup:]
+    return sum(kept) / len(kept), out, cpu.hardware_threads()
+
+
+def cpu_tokens(cfg, args):
+    """Size of the CPU sample: every token of a decode workload, 768 rows of a prefill one (seconds of host work)."""
+    return args.cpu_tokens or (cfg.T if cfg.T <= 64 else 768)
+
+
+def cpu_baseline(cfg, args, dev):
+    n = cpu_tokens(cfg, args)
+    sem = semantics_of(cfg)
+    sec, _, cores = cpu_sample(cfg, args.seed, n, sem, dev)
+    return dict(value=n / sec, unit="MoE-layer tokens/s", cores=cores, kind="port",
+                sample=f"{n} tokens of layer 0 of {cfg.name} through the CPU oracle ({sem} semantics), {sec:.2f} s a pass")
+
+
+def parity_check(cfg, st, x_loc, args, dev, rank):
+    """Rank 0, after the timed region: `rows` of this rank's token rows through the CPU oracle for EVERY layer of the stack,
+    each layer fed the GPU's own input rows and router logits of that layer (so that a rounding difference in one layer
+    does not turn into different routing in the next: the layers are checked one by one, all of them).  Returns the
+    largest max|y - y_ref| / rms(y_ref) over the layers, layer 0's, and whether every layer's router ids are the
+    oracle's for those logits."""
+    import numpy as np
+    import torch
+    from oracle import check, cpu
+    from strixite_b200.ep import residual
+    cpu.build(None)
+    n = min(args.parity_rows, x_loc.shape[0])
+    g = torch.Generator(device="cpu").manual_seed(args.seed + 17)
+    rows = torch.sort(torch.randperm(x_loc.shape[0], generator=g)[:n]).values.to(dev)
+    sem = semantics_of(cfg, st.layers[0].math_for(cfg.T, st.math))
+    rec = []
+    x = x_loc
+    for l in range(st.n_layers):
+        y = st.ep.layer(l, x)
+        ids = st.buf.ids if st.world == 1 else st.ids_loc[0]
+        rec.append((check.bits_of(x[rows]), st.logits[0][rows].cpu().numpy(), ids[rows].cpu().numpy(), y[rows].float().cpu().numpy()))
+        x = residual(x, y)
+    torch.cuda.synchronize()
+    if rank != 0:  # every rank runs the forward (its collectives); rank 0 alone consults the oracle
+        return None
+    worst, first, ids_ok = 0.0, None, True
+    for l, (xb, lg, ids, y) in enumerate(rec):
+        shared = None
+        if cfg.shared:
+            w = st.layers[l].w
+            shared = (check.download(w.shared_gate_up, cpu), check.download(w.shared_down, cpu))
+        ref = check.oracle_layer_with(cpu, cfg, check.generated_experts(cfg, args.seed, l, dev), shared, xb, lg, sem)
+        ids_ok = ids_ok and bool(np.array_equal(ref["ids"], ids))
+        err = check.max_abs_over_rms(y, ref["y_f32"])
+        worst = max(worst, err)
+        if l == 0:
+            first = err
+    return {"rows": int(n), "layers": st.n_layers, "max_abs_over_rms": worst, "layer0": first, "ids_exact": ids_ok,
+            "tolerance": 1e-2, "semantics": sem,
+            "how": "every layer of the stack against the CPU oracle on the GPU's own layer inputs and logits; rank 0's rows"}
 
 
 def run_reference(args):
-    """--impl reference: the CPU oracle on the host cores, same configuration, bounded sample per step."""
+    """--impl reference: the CPU oracle on the host cores, the same bounded sample of the same seeded layer as the default
+    arm's cpu_baseline leg, once per step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    import numpy as np
-    from oracle import cpu
+    import torch
     from strixite_b200 import workloads as W
-    cpu.build(None)
-    cfg = W.CONFIGS[args.workload]
-    n_tok = args.cpu_tokens or (8 if cfg.T > 64 else cfg.T)
-    rng = np.random.default_rng(args.seed)
-    # The sample's experts: quantized on the host by the oracle's quantizer from the same distributions.
-    k, E, d, I = cfg.k, cfg.E, cfg.d, cfg.I
-    x = cpu.f32_to_bf16(rng.standard_normal((n_tok, d)).astype(np.float32))
-    wr = (rng.standard_normal((E + 1, d)) * 0.02).astype(np.float32)
-    logits = (cpu.bf16_to_f32(x) @ wr.T).astype(np.float32)
-    ids, _ = cpu.moe_router(logits, E, k)
-    touched = np.unique(ids)
-    E2 = len(touched)
-    gu = cpu.quantize((rng.standard_normal((E2 * 2 * I, d)) * 0.02).astype(np.float32), cfg.group(cfg.gu_bits), cfg.gu_bits)
-    dn = cpu.quantize((rng.standard_normal((E2 * d, I)) * 0.02).astype(np.float32), cfg.group(cfg.dn_bits), cfg.dn_bits)
-    lw = cpu.LayerWeights(gu, dn)
-    if cfg.shared:
-        lw.shared_gate_up = cpu.quantize((rng.standard_normal((2 * I, d)) * 0.02).astype(np.float32), 64, 8)
-        lw.shared_down = cpu.quantize((rng.standard_normal((d, I)) * 0.02).astype(np.float32), 64, 8)
-    sub = np.full((n_tok, E2 + 1), -1e30, dtype=np.float32)
-    sub[:, :E2] = logits[:, touched]
-    sub[:, E2] = logits[:, E]
-    sem = "grouped" if cfg.T >= 256 else "decode"
-    times = []
-    for i in range(args.warmup + args.steps):
-        t0 = time.perf_counter()
-        cpu.moe_layer(x, sub, lw, E2, k, semantics=sem)
-        if i >= args.warmup:
-            times.append(time.perf_counter() - t0)
-    s = sum(times) / len(times)
-    value = n_tok / s
+    cfg = W.c2_config(args.seed) if args.workload == "c2" else W.CONFIGS[args.workload]
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if torch.cuda.is_available() else torch.device("cpu")
+    n_tok = cpu_tokens(cfg, args)
+    if dev.type == "cpu" and not args.cpu_tokens:
+        n_tok = min(n_tok, 16)  # no GPU to draw and quantize the experts on: keep the host-side generation short
+    sem = semantics_of(cfg)
+    sec, _, cores = cpu_sample(cfg, args.seed, n_tok, sem, dev, repeats=args.steps, warmup=min(args.warmup, 1))
+    value = n_tok / sec
     unit = "MoE-layer tokens/s"
+    layers = args.layers or (8 if cfg.T <= 64 else cfg.layers)
     print(json.dumps({
         "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": value, "unit": unit, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": s * 1e3, "higher_is_better": True, "scaling": "strong",
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f64 accumulate, bf16 activations", "data": "synthetic",
-        "config": {"workload": cfg.name, "T": cfg.T, "hidden": d, "experts": E, "top_k": k, "intermediate": I,
-                   "gate_up": f"q{cfg.gu_bits}", "down": f"q{cfg.dn_bits}"},
-        "cpu_baseline": {"value": value, "unit": unit, "cores": cpu.hardware_threads(), "kind": "port",
-                         "sample": f"{n_tok} tokens through one layer per step (the reference has no CPU or CUDA "
-                                   f"implementation of this path; this is the CPU oracle restating its arithmetic)"},
+        "config": config_dict(cfg, layers, max(1, args.gpus)),
+        "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port",
+                         "sample": f"{n_tok} tokens of layer 0 of {cfg.name} through the CPU oracle ({sem} semantics) per step, "
+                                   f"{sec:.2f} s a pass (the reference has no CPU or CUDA implementation of this path; this is "
+                                   f"the CPU oracle restating its arithmetic)"},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -503,22 +592,35 @@ def main():
         cfg = replace(cfg, E=args.experts or cfg.E, T=args.tokens or cfg.T, name=cfg.name + "_reduced")
     decode = cfg.T <= 64
 
+    if cfg.shared and world > 1:
+        raise SystemExit(f"{cfg.name} has a shared expert, which is not sharded: run it on one GPU (the expert-parallel workload is c4)")
     res = run_stack(cfg, args, dev, rank, world, peaks, layers=(8 if decode else None), rotate=decode)
+    st = res["stack"]
     line = {
         "metric": "moe_layer_tokens_per_s", "value": res["value"], "unit": "MoE-layer tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f16 x f16 -> f32 (tcgen05), bf16 activations" if not decode
         else "bf16 x int4/int8 codes -> f32 (mma.sync), bf16 activations",
         "data": "synthetic",
-        "config": {"workload": cfg.name, "T": cfg.T, "layers": res["layers"], "hidden": cfg.d, "experts": cfg.E,
-                   "experts_per_gpu": cfg.E // world, "top_k": cfg.k, "intermediate": cfg.I, "gate_up": f"q{cfg.gu_bits}g{cfg.group(cfg.gu_bits)}",
-                   "down": f"q{cfg.dn_bits}g{cfg.group(cfg.dn_bits)}", "shared_expert": cfg.shared, "expert_bias": cfg.bias, "router_projection": "cuBLAS " + ("tf32" if cfg.T // world >= 256 else "fp32") + " (torch.matmul), inside the timed step",
-                   "parallelism": f"ep{world}" + (f", {res['stack'].micro} micro-batches a rank" if res["stack"].micro > 1 else ""), "value_is": "T * layers / step time",
-                   "l2": "weights resident per step exceed L2 (126 MB): %.1f GB on this rank" % (res["stack"].weight_bytes / 1e9)},
+        "config": config_dict(cfg, res["layers"], world, st.micro),
+        "details": {
+            "router_projection": ("sxb_router_logits_wmma (tcgen05, FP32 weight as %d BF16 planes)" % args.planes) if st.proj_wmma
+            else "sxb_router_logits (streaming, FP32 weight)",
+            "residual": "sxb_residual_add",
+            "l2": "weights resident per step exceed L2 (126 MB): %.1f GB on this rank" % (st.weight_bytes / 1e9)},
         "clocks": res["clocks"], "gpu_launches": res["launches"],
         "e2e": {"value": res["e2e_value"], "unit": "MoE-layer tokens/s", "h2d_bytes_per_step": res["h2d"],
                 "d2h_bytes_per_step": res["d2h"], "ms_per_step": res["e2e_ms"]},
     }
+    if args.parity_rows > 0:
+        try:
+            par = parity_check(cfg, st, res["x_full"][st.t_lo:st.t_hi].contiguous(), args, dev, rank)
+        except Exception as e:  # a checker failure must not lose the measured line; it is reported as such
+            par = {"rows": 0, "error": f"{type(e).__name__}: {e}"}
+            if world > 1:
+                raise
+        if par is not None:
+            line["parity"] = par
     if decode:
         b, U, gu_b = decode_bytes_mean(cfg, res)
         line["roofline"] = dict(bound="hbm", kernel="whole layer", achieved=b / (res["ms_per_step"] * 1e-3) / 1e9,
@@ -531,14 +633,12 @@ def main():
         line["achieved_tflops_whole_step"] = algorithmic_flops(cfg, res["layers"], cfg.shared and world == 1) / (res["ms_per_step"] * 1e-3) / 1e12
 
     if rank == 0 and world == 1 and not args.no_cpu:
-        n_tok = args.cpu_tokens or (cfg.T if decode else 768)
         try:
-            cb, _ = cpu_baseline(cfg, res, n_tok, "decode" if decode else "grouped")
-            line["cpu_baseline"] = cb
+            line["cpu_baseline"] = cpu_baseline(cfg, args, dev)
         except Exception as e:  # the baseline is a reported extra: never lose the GPU line to it
             line["cpu_baseline"] = {"value": None, "unit": "MoE-layer tokens/s", "cores": None, "kind": "port",
                                     "sample": f"failed: {type(e).__name__}: {e}"}
-    del res
+    del res, st
 
     if rank == 0 and world == 1 and not args.no_extra and args.workload == "c4":
         extra = {}
@@ -549,6 +649,11 @@ def main():
             r = run_stack(c, args, dev, 0, 1, peaks, layers=(8 if dec else 1), rotate=dec)
             e = {"tokens_per_s": r["value"], "ms_per_step": r["ms_per_step"], "e2e_tokens_per_s": r["e2e_value"],
                  "gpu_launches": r["launches"], "clocks": r["clocks"]}
+            if args.parity_rows > 0:
+                try:
+                    e["parity"] = parity_check(c, r["stack"], r["x_full"], args, dev, 0)
+                except Exception as ex:
+                    e["parity"] = {"rows": 0, "error": f"{type(ex).__name__}: {ex}"}
             if dec:
                 b, U, gu_b = decode_bytes_mean(c, r)
                 gbs = b / (r["ms_per_step"] * 1e-3) / 1e9

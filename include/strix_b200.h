@@ -64,15 +64,19 @@ enum {
  *                             scale / min applied per group in FP32, FP32 accumulation (the reference's
  *                             "exact weights" semantics; only the summation order differs from its FP32 kernels);
  *   WMMA_F16 and its kinds    activations as F16, weights dequantized to F16 (code * scale + min, one rounding),
- *                             FP32 accumulation in tensor memory on tcgen05 tensor cores.  Narrow / Wide / Wide256
- *                             are accepted for source compatibility and select the same kernel. */
+ *                             FP32 accumulation in tensor memory on tcgen05 tensor cores, the combine's per-slot dots
+ *                             stored as BF16 (kernels/moe_grouped.hip:47-57).  Narrow / Wide / Wide256 are accepted
+ *                             for source compatibility and select the same kernel. */
 enum {
     SXB_MATH_F32 = 0,
     SXB_MATH_WMMA_BF16 = 1,
     SXB_MATH_WMMA_F16 = 2,
     SXB_MATH_WMMA_F16_NARROW = 3,
     SXB_MATH_WMMA_F16_WIDE = 4,
-    SXB_MATH_WMMA_F16_WIDE256 = 5
+    SXB_MATH_WMMA_F16_WIDE256 = 5,
+    /* Not in the reference: WMMA_F16 with the combine's per-slot dots kept in FP32.  The reference's matrix-unit path
+     * - and SXB_MATH_WMMA_F16 .. WIDE256 here - round them to BF16 (kernels/moe_grouped.hip:47-57). */
+    SXB_MATH_WMMA_F16_F32_PARTIALS = 6
 };
 
 /* runtime/q4_device.hpp:14-19 (Q4DeviceView) and runtime/q8_device.hpp:13-18 (Q8DeviceView): a non-owning view of
@@ -125,6 +129,32 @@ int sxb_moe_shared_add_inject(void *y, const void *s, const float *gate_logit, i
                               uint32_t gate_index, void *x, const float *w_in, int64_t H, int act, uint32_t *err,
                               sxb_stream_t stream);
 
+/* ---- Router-logits projection (the step before the router) and residual add (the step after the block) --------- */
+
+/* kernels/linear.hpp:22-27  linear_bf16w: y [M, N] = x [M, K] * W^T, W [N, K] raw BF16 bits, FP32 accumulation, one rounding;
+ * BF16 x, out_act BF16 or F32 (the router logits stay FP32: runtime/qwen4exp.cpp:3149-3155).  One pass over W for all
+ * tokens: the decode form.  K % 8 == 0; x and w 16-byte aligned. */
+int sxb_linear_bf16w(const void *x, const uint16_t *w, void *y, int64_t M, int64_t N, int64_t K, int act, int out_act,
+                     sxb_stream_t stream);
+/* No counterpart in the reference (whose router weight is BF16 and has no bias).  The same projection for the router:
+ * logits [M, ld >= N] FP32 = x [M, K] BF16 * W^T + bias, W [N, K] FP32 (w_act = SXB_ACT_F32) or BF16 bits, bias [N] FP32
+ * or NULL.  Streaming form (decode). */
+int sxb_router_logits(const void *x, const void *w, int w_act, const float *bias, int64_t M, int64_t N, int64_t K, float *logits,
+                      int64_t ld, sxb_stream_t stream);
+/* kernels/linear_wmma.hpp:29-30  linear_bf16w_wmma: the multi-token form on the tensor cores (tcgen05 here).  The weight
+ * is prepared once, at load time: sxb_router_prepare splits W [N, K] into `planes` BF16 planes [planes][Npad][K] (Npad = N
+ * rounded up to 128; sxb_router_planes_bytes gives the size) - one plane for a BF16 weight; for an FP32 weight two planes
+ * carry 16 bits of it, three all 24 - and the GEMM sums the exact BF16 products of x with every plane in FP32.  With
+ * planes = 1, planes_in may be the BF16 weight [N, K] itself, unprepared.
+ * K % 64 == 0.  A wait that ran out is reported by sxb_check_dense_status. */
+size_t sxb_router_planes_bytes(int64_t N, int64_t K, int planes);
+int sxb_router_prepare(const void *w, int w_act, int64_t N, int64_t K, int planes, void *planes_out, sxb_stream_t stream);
+int sxb_router_logits_wmma(const void *x, const void *planes_in, int planes, const float *bias, int64_t M, int64_t N, int64_t K,
+                           float *logits, int64_t ld, sxb_stream_t stream);
+/* The single-stream case of kernels/hc.hpp:52-54 hc_inject (weight 1): out [n] BF16 = bf16(x + y), x BF16, y F32 or BF16
+ * (y_act); out may be x itself.  n % 8 == 0. */
+int sxb_residual_add(const void *x, const void *y, int y_act, void *out, int64_t n, sxb_stream_t stream);
+
 /* ---- Pack (grouping of slots by expert) --------------------------------------------------------------------- */
 
 /* kernels/moe_grouped.hpp:48  moe_route_workspace_bytes.  Returns 0 and sets the error message on bad arguments.
@@ -136,6 +166,13 @@ size_t sxb_moe_route_workspace_bytes(int64_t M, int64_t A, int64_t E);
  * slot order, so the whole workspace is reproducible.  1 <= A <= 64, 1 <= E <= 1023, M*A <= 2^20. */
 int sxb_moe_group_routes(const int32_t *ids, int64_t M, int64_t A, int64_t E, void *ws, size_t ws_bytes, uint32_t *err,
                          sxb_stream_t stream);
+/* No counterpart in the reference (two launches there).  sxb_moe_router (FP32 logits, no shared slot) and
+ * sxb_moe_group_routes[_ep] as ONE launch of one CTA, for batches of at most 2048 slots (M * k): the decode step's
+ * routing.  E_local == E_total: all experts are here (e_lo = 0); otherwise the expert-parallel pack.  Same words out as
+ * the two calls. */
+int sxb_moe_route_small(const float *logits, int64_t ld, int64_t M, int64_t E_total, int64_t k, int64_t e_lo, int64_t E_local,
+                        int32_t *ids, float *coef, void *ws, size_t ws_bytes, uint32_t *router_err, uint32_t *expert_err,
+                        sxb_stream_t stream);
 /* No counterpart in the reference.  The tcgen05 grouped kernels bound every device-side wait; one that runs out writes
  * {2, work item, role} into words 5..7 of the workspace header (zeroed by every pack) and the kernel returns.  This
  * reads the header back (it synchronizes, like sxb_check_expert_error) and returns SXB_ERR_DATA if that happened. */
@@ -150,12 +187,35 @@ int sxb_moe_group_routes_ep(const int32_t *ids, int64_t M, int64_t A, int64_t E_
  * out[3] = tile8_bucket, out[4] = tile8_start, out[5] = tile128_bucket, out[6] = tile128_start, out[7] = total words. */
 int sxb_route_layout(int64_t M, int64_t A, int64_t E, int64_t out[8]);
 
+/* No counterpart in the reference.  Bound of every device-side wait of the tcgen05 kernels for the launches that follow
+ * (process-wide; default 2 s, minimum 1 us).  A wait that runs out ends its kernel with the status words set. */
+int sxb_set_wait_limit(uint64_t nanoseconds);
+/* Test hook, no counterpart in the reference: slot >= 0 makes CTA 0 of the following tcgen05 launches leave that fill of
+ * its weight-code ring out, so a bounded wait runs out and the kernel's give-up path runs; -1 (the default) = off. */
+int sxb_test_skip_ring_slot(int slot);
+
 /* ---- Dense quantized linear --------------------------------------------------------------------------------- */
 
 /* kernels/linear_q4.hpp:26,30  linear_q4:  y [M, N] = x [M, K] * dequant(W)^T.  out_act == act, or BF16 x -> F32 y. */
 int sxb_linear_q4(const void *x, const SxbQView *w, void *y, int64_t M, int act, int out_act, sxb_stream_t stream);
 /* kernels/linear_q8.hpp:13-14  linear_q8. */
 int sxb_linear_q8(const void *x, const SxbQView *w, void *y, int64_t M, int act, int out_act, sxb_stream_t stream);
+
+/* kernels/linear_wmma.hpp:23,26  linear_q4_wmma / linear_q8_wmma: the multi-token dense projection on the tensor cores,
+ * here the tcgen05 grouped kernel run as one group with the result written by its epilogue (no pack, no scratch).
+ * Numerics of this library's WMMA_F16 path: x as F16, weights f16(code * scale + min), FP32 accumulation, one rounding.
+ * act SXB_ACT_BF16, or SXB_ACT_F16_TILED for x staged by sxb_stage_f16_tiles with a null workspace; out_act BF16 or F32.
+ * K % 128 == 0, N % 16 == 0. */
+int sxb_linear_q4_wmma(const void *x, const SxbQView *w, void *y, int64_t M, int act, int out_act, sxb_stream_t stream);
+int sxb_linear_q8_wmma(const void *x, const SxbQView *w, void *y, int64_t M, int act, int out_act, sxb_stream_t stream);
+/* No counterpart in the reference (which runs linear_q8_wmma, then swiglu): w = [gate | up] rows, h [M, N/2] =
+ * silu(g) * u from the FP32 accumulators, rounded once; h_f16 as for the grouped SwiGLU gather (3 / 4: tile-blocked for a
+ * Q4 / Q8 down projection, then pass act = SXB_ACT_F16_TILED to sxb_linear_q*_wmma). */
+int sxb_linear_q4_wmma_swiglu(const void *x, const SxbQView *w, void *h, int64_t M, int act, int h_f16, sxb_stream_t stream);
+int sxb_linear_q8_wmma_swiglu(const void *x, const SxbQView *w, void *h, int64_t M, int act, int h_f16, sxb_stream_t stream);
+/* No counterpart in the reference.  The dense tcgen05 projections have no workspace to record a wait that ran out in;
+ * the record lives inside the library, one per device.  Reads it back (synchronizes), clears it, SXB_ERR_DATA if set. */
+int sxb_check_dense_status(const char *what);
 
 /* kernels/swiglu.hpp:21  swiglu: gu [rows, 2I] = [gate | up] -> h [rows, I]; BF16: h = bf16(bf16(silu(g)) * u). */
 int sxb_swiglu(const void *gu, void *h, int64_t rows, int64_t I, int act, sxb_stream_t stream);
@@ -203,8 +263,9 @@ int sxb_linear_q4_experts_gather_grouped_swiglu(const void *x, const SxbQView *w
                                                 size_t ws_bytes, int64_t M, int64_t A, void *h, int act, int math,
                                                 sxb_stream_t stream, int h_f16);
 /* kernels/moe_grouped.hpp:88-91  linear_q4_experts_combine_grouped.  partial: M*A*N FP32 scratch owned by the caller
- * (the per-slot dots); y[m, :] = sum_a fma(coef[m, a], partial[m*A + a, :]) in slot order, one rounding, optionally
- * + sigmoid(gate) * s (shared).  out_act as for sxb_linear_q4_experts_combine. */
+ * (the per-slot dots; with a WMMA_F16 math they are stored as BF16 in the first half of it, as the reference does);
+ * y[m, :] = sum_a fma(coef[m, a], partial[m*A + a, :]) in slot order, one rounding, optionally + sigmoid(gate) * s
+ * (shared).  out_act as for sxb_linear_q4_experts_combine. */
 int sxb_linear_q4_experts_combine_grouped(const void *h, const SxbQView *w, int64_t E, const int32_t *ids,
                                           const float *coef, const void *ws, size_t ws_bytes, float *partial,
                                           int64_t M, int64_t A, void *y, int act, int out_act, int math,
@@ -212,9 +273,11 @@ int sxb_linear_q4_experts_combine_grouped(const void *h, const SxbQView *w, int6
 /* No counterpart in the reference.  sxb_linear_q4_experts_combine_grouped for callers that cannot supply `partial`: an
  * engine whose memory plan left no spare device memory, or a decode loop that must not call cudaMalloc (it synchronizes
  * the device).  The per-slot dots go to a 16 MiB array inside the library image instead; x / h / y stay the caller's.
- * Refuses M * A * N > 4 Mi floats (4,194,304) with SXB_ERR_CHECK.  Allocates nothing.  The first call on a device looks the
- * array's address up (a blocking runtime call): make it before any stream capture.  Every call on a device shares the
- * array: calls that overlap on the GPU race. */
+ * Refuses M * A * N > 4 Mi floats (4,194,304) with SXB_ERR_CHECK.  Calls no allocator.  The 16 MiB are taken when the CUDA
+ * runtime loads this part of the library on a device - with its default lazy loading, inside the FIRST call on that
+ * device, which also looks the array's address up (a blocking runtime call): make one small call per device before the
+ * host sizes its memory plan and before any stream capture.  The address is kept per device for the life of the process (a
+ * cudaDeviceReset invalidates it).  Every call on a device shares the array: calls that overlap on the GPU race. */
 int sxb_linear_q4_experts_combine_grouped_noalloc(const void *h, const SxbQView *w, int64_t E, const int32_t *ids,
                                                   const float *coef, const void *ws, size_t ws_bytes, int64_t M, int64_t A,
                                                   void *y, int act, int out_act, int math, sxb_stream_t stream,
@@ -252,6 +315,7 @@ int sxb_stage_f16(const void *x, int64_t M, int64_t K, int bits, void *xh, sxb_s
  * receives, for every slot position pos of the slot order and every k-block kb of 64, the 128-byte F16 line of token
  * slots[pos] / A at byte (kb * S + pos) * 128, swizzled for its place in its 128-slot tile, so that a tile's operand of a
  * k-block is one contiguous run and reaches shared memory with a single bulk copy.  xs: caller-owned, M*A*K*2 bytes.
+ * ws == NULL (with A = E = 1): the rows of a dense projection in their own order, for sxb_linear_q*_wmma[_swiglu].
  * Pass act = SXB_ACT_F16_TILED to the grouped gather.  The SwiGLU gather writes h in the same form with h_f16 = 3 (Q4
  * down) or 4 (Q8 down); pass the same h_f16 to the combine. */
 int sxb_stage_f16_tiles(const void *x, const void *ws, size_t ws_bytes, int64_t M, int64_t A, int64_t E, int64_t K, int bits,
@@ -273,7 +337,8 @@ typedef struct SxbMoeLayerArgs {
     const SxbQView *shared_gate_up, *shared_down; /* the always-on shared expert [2I, d], [d, I]; NULL, NULL = none */
     int shared_bits;
     const void *x;                 /* [M, d] BF16 */
-    const float *logits;           /* [M, logits_ld] FP32 router logits; with a shared expert column E_total is its gate */
+    const float *logits;           /* [M, logits_ld] FP32 router logits; with a shared expert column E_total is its gate.
+                                      NULL: ids and coef already hold the routes and no router runs */
     int64_t logits_ld;
     void *y;                       /* [M, d] */
     int out_act;                   /* SXB_ACT_BF16, or SXB_ACT_F32 for the unrounded sums */
@@ -288,12 +353,12 @@ typedef struct SxbMoeLayerArgs {
     void *xs;                      /* [M * A, d] F16: tile-blocked activations; tcgen05 path only (else may be NULL) */
     void *sh_gu, *sh_h;            /* shared expert: [M, 2I] (streaming path only), [M, I], 16-bit */
     void *sh_y;                    /* shared expert's output [M, d] in y's dtype */
-    int32_t *sh_ids;               /* the rest: tcgen05 path with a shared expert only.  [M] */
-    float *sh_coef;                /* [M] */
-    void *sh_ws;                   /* sxb_moe_route_workspace_bytes(M, 1, 1) */
+    int32_t *sh_ids;               /* unused (kept for layout compatibility): the shared expert's prefill form is a dense */
+    float *sh_coef;                /* tcgen05 projection and needs no routes, workspace or scratch; may be NULL */
+    void *sh_ws;
     size_t sh_ws_bytes;
-    float *sh_partial;             /* [M, d] */
-    void *sh_xs;                   /* [M, d] F16 */
+    float *sh_partial;
+    void *sh_xs;                   /* [M, d] F16: tcgen05 path with a shared expert only */
     uint32_t *router_err, *expert_err; /* >= 3 words each, zeroed by the caller at session start */
 } SxbMoeLayerArgs;
 int sxb_moe_layer(const SxbMoeLayerArgs *args, sxb_stream_t stream);

@@ -61,7 +61,7 @@ namespace strix::kernels {
 static_assert(sizeof(Q4DeviceView) == sizeof(SxbQView) && sizeof(Q8DeviceView) == sizeof(SxbQView),
               "SxbQView must keep Q4DeviceView's / Q8DeviceView's layout");
 
-enum class MoeMath { F32, WmmaBf16, WmmaF16, WmmaF16Narrow, WmmaF16Wide, WmmaF16Wide256 };
+enum class MoeMath { F32, WmmaBf16, WmmaF16, WmmaF16Narrow, WmmaF16Wide, WmmaF16Wide256, WmmaF16F32Partials /* not upstream */ };
 constexpr int64_t kMoeMaxExperts = 1023;
 constexpr int64_t kMoeMaxSlots = 1 << 20;
 
@@ -182,6 +182,28 @@ inline void linear_q4_experts_combine(const void *h, const Q4DeviceView &w, int6
 }
 inline void check_expert_error(const uint32_t *err, const char *what) { b200_detail::check(sxb_check_expert_error(err, what)); }
 inline void report_expert_error(const uint32_t e[3], const char *what) { b200_detail::check(sxb_report_expert_error(e, what)); }
+
+// kernels/linear_wmma.hpp: the multi-token projections on the tensor cores
+inline void linear_q4_wmma(const void *x, const Q4DeviceView &w, void *y, int64_t M, Act act, Act out_act, hipStream_t stream) {
+    b200_detail::check(sxb_linear_q4_wmma(x, b200_detail::view(w), y, M, b200_detail::act(act), b200_detail::act(out_act), stream));
+}
+inline void linear_q8_wmma(const void *x, const Q8DeviceView &w, void *y, int64_t M, Act act, Act out_act, hipStream_t stream) {
+    b200_detail::check(sxb_linear_q8_wmma(x, b200_detail::view(w), y, M, b200_detail::act(act), b200_detail::act(out_act), stream));
+}
+// kernels/linear.hpp: BF16-weight projections (the router logits: BF16 x -> F32 y)
+inline void linear_bf16w(const void *x, const uint16_t *w, void *y, int64_t M, int64_t N, int64_t K, Act act, Act out_act,
+                         hipStream_t stream) {
+    b200_detail::check(sxb_linear_bf16w(x, w, y, M, N, K, b200_detail::act(act), b200_detail::act(out_act), stream));
+}
+inline void linear_bf16w(const void *x, const uint16_t *w, void *y, int64_t M, int64_t N, int64_t K, Act act, hipStream_t stream) {
+    linear_bf16w(x, w, y, M, N, K, act, act, stream);
+}
+// kernels/linear_wmma.hpp:29-30 - here for the router's dtype pair (BF16 x -> F32 y): a BF16 weight is its own single plane
+inline void linear_bf16w_wmma(const void *x, const uint16_t *w, void *y, int64_t M, int64_t N, int64_t K, Act act, Act out_act,
+                              hipStream_t stream) {
+    if (act != Act::BF16 || out_act != Act::F32) throw Error("linear_bf16w_wmma: BF16 x -> F32 y only");
+    b200_detail::check(sxb_router_logits_wmma(x, w, 1, nullptr, M, N, K, static_cast<float *>(y), N, stream));
+}
 
 // kernels/swiglu.hpp
 inline void swiglu(const void *gu, void *h, int64_t rows, int64_t I, Act act, hipStream_t stream) {

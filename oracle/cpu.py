@@ -6,6 +6,7 @@ TEST INFRASTRUCTURE: the checker, never the thing measured or shipped.  BF16 dat
 from __future__ import annotations
 
 import ctypes as C
+import os
 import pathlib
 import subprocess
 from dataclasses import dataclass
@@ -21,9 +22,21 @@ i64, vp = C.c_int64, C.c_void_p
 F32, BF16 = 0, 1
 
 
-def build(reference: Optional[str] = "/root/reference") -> None:
-    """Compiles the oracle, and the reference quantizers when the reference checkout is present."""
+def reference_checkout() -> Optional[str]:
+    """Where the reference's sources lie on this machine: $STRIX_REFERENCE_DIR, else a `reference` directory beside the
+    repository; None when neither holds formats/q4.cpp (the GPU hosts: only the prebuilt library travels there)."""
+    for cand in (os.environ.get("STRIX_REFERENCE_DIR"), str(HERE.parent.parent / "reference")):
+        if cand and pathlib.Path(cand, "formats", "q4.cpp").exists():
+            return cand
+    return None
+
+
+def build(reference: Optional[str] = "") -> None:
+    """Compiles the oracle, and the reference quantizers when a reference checkout is found ("" = look for one,
+    None = do not)."""
     subprocess.run(["make", "-C", str(HERE), "all"], check=True, capture_output=True)
+    if reference == "":
+        reference = reference_checkout()
     if reference and pathlib.Path(reference, "formats", "q4.cpp").exists():
         subprocess.run(["make", "-C", str(HERE), "ref", f"REF={reference}"], check=True, capture_output=True)
 
@@ -177,9 +190,10 @@ def swiglu(gu: np.ndarray) -> np.ndarray:
 
 
 def experts_gather(x: np.ndarray, w: QWeight, E: int, ids: np.ndarray, swiglu_mode: int = 0,
-                   err: Optional[np.ndarray] = None, threads: int = 0, w_f16: bool = False) -> np.ndarray:
+                   err: Optional[np.ndarray] = None, threads: int = 0, w_f16: bool = False, x_f16: int = 0) -> np.ndarray:
     """swiglu_mode 0: y [M, A, N]; 1: h [M, A, N/2] with the decode rounding points; 2: one rounding (grouped F16).
-    w_f16: weights as the matrix-unit path's F16 operand, f16(code * f16(scale) + f16(min))."""
+    w_f16: weights as the matrix-unit path's F16 operand, f16(code * f16(scale) + f16(min)).
+    x_f16: activations staged as F16: 0 kept as they are, 1 to nearest, 2 toward zero (the reference's staging)."""
     x = np.ascontiguousarray(x)
     ids = np.ascontiguousarray(ids, dtype=np.int32)
     M, A = ids.shape
@@ -189,13 +203,15 @@ def experts_gather(x: np.ndarray, w: QWeight, E: int, ids: np.ndarray, swiglu_mo
     lib().orc_experts_gather(_p(x), C.c_int(_act_of(x)), _p(np.ascontiguousarray(w.q)),
                              _p(np.ascontiguousarray(w.scale)), _p(np.ascontiguousarray(w.minv)), i64(w.N), i64(w.K),
                              i64(w.G), C.c_int(w.bits), i64(E), _p(ids), i64(M), i64(A), _p(y), C.c_int(swiglu_mode),
-                             _p(err), C.c_int(threads), C.c_int(int(w_f16)))
+                             _p(err), C.c_int(threads), C.c_int(int(w_f16)), C.c_int(int(x_f16)))
     return y
 
 
 def experts_combine(h: np.ndarray, w: QWeight, E: int, ids: np.ndarray, coef: np.ndarray, out_act: Optional[int] = None,
-                    err: Optional[np.ndarray] = None, threads: int = 0, want_partial: bool = False, w_f16: bool = False):
-    """h [M, A, K] -> y [M, N] (and the per-slot dots [M*A, N] FP32 when asked)."""
+                    err: Optional[np.ndarray] = None, threads: int = 0, want_partial: bool = False, w_f16: bool = False,
+                    x_f16: int = 0, partial_bf16: bool = False):
+    """h [M, A, K] -> y [M, N] (and the per-slot dots [M*A, N] FP32 when asked).  partial_bf16: the per-slot dots are
+    rounded to BF16 before the weighted sum (the reference's matrix-unit path, kernels/moe_grouped.hip:47-57)."""
     h = np.ascontiguousarray(h)
     ids = np.ascontiguousarray(ids, dtype=np.int32)
     coef = np.ascontiguousarray(coef, dtype=np.float32)
@@ -208,7 +224,7 @@ def experts_combine(h: np.ndarray, w: QWeight, E: int, ids: np.ndarray, coef: np
     lib().orc_experts_combine(_p(h), C.c_int(act), _p(np.ascontiguousarray(w.q)), _p(np.ascontiguousarray(w.scale)),
                               _p(np.ascontiguousarray(w.minv)), i64(w.N), i64(w.K), i64(w.G), C.c_int(w.bits), i64(E),
                               _p(ids), _p(coef), i64(M), i64(A), _p(y), C.c_int(out_act), _p(partial), _p(err),
-                              C.c_int(threads), C.c_int(int(w_f16)))
+                              C.c_int(threads), C.c_int(int(w_f16)), C.c_int(int(x_f16)), C.c_int(int(partial_bf16)))
     return (y, partial) if want_partial else y
 
 
@@ -254,28 +270,36 @@ def moe_layer(x: np.ndarray, logits: np.ndarray, w: LayerWeights, E: int, k: int
     separate.  x [T, d] BF16 bits, logits [T, E + 1] float32 (column E = the shared gate).
     semantics "decode": the per-slot / vector-unit kernels' numerics - FP32 dequantized weights, g and u rounded as
         stored, h = bf16(bf16(silu(g)) * u) (kernels/linear_q4.hip:268-274);
-    semantics "grouped": the matrix-unit path's numerics served from 6 tokens up - weights as F16 operands
-        f16(code * scale + min), h = bf16(silu(g) * u) from the unrounded accumulators (kernels/moe_grouped.hpp:29-38,
-        kernels/moe_grouped.hip:508-524); per-slot partials stay FP32 here (the reference rounds them to BF16).
+    semantics "grouped": the matrix-unit path's numerics served from 6 tokens up - activations staged as F16 toward
+        zero (kernels/moe_grouped.hip:29-32), weights as F16 operands f16(code * scale + min), h = bf16(silu(g) * u)
+        from the unrounded accumulators (kernels/moe_grouped.hpp:29-38, kernels/moe_grouped.hip:508-524), every
+        per-slot dot of the down projection rounded to BF16 before the weighted sum (kernels/moe_grouped.hip:47-57);
+    semantics "grouped_f32_partials": the same with the activations staged to nearest and the per-slot dots kept in
+        FP32 - a variant kept to measure what the BF16 partials cost.
     Returns dict(ids, coef, h, y_routed_f32, y_f32, y_bf16)."""
+    if semantics not in ("decode", "grouped", "grouped_f32_partials"):
+        raise ValueError(f"unknown semantics {semantics!r}")
     ids, coef = moe_router(logits, E, k)
     f16 = semantics != "decode"
-    h = experts_gather(x, w.gate_up, E, ids, swiglu_mode=2 if f16 else 1, threads=threads, w_f16=f16)
-    y_routed = experts_combine(h, w.down, E, ids, coef, out_act=F32, threads=threads, w_f16=f16)
+    xm = 0 if not f16 else (2 if semantics == "grouped" else 1)
+    pb = semantics == "grouped"
+    h = experts_gather(x, w.gate_up, E, ids, swiglu_mode=2 if f16 else 1, threads=threads, w_f16=f16, x_f16=xm)
+    y_routed = experts_combine(h, w.down, E, ids, coef, out_act=F32, threads=threads, w_f16=f16, x_f16=xm, partial_bf16=pb)
     out = dict(ids=ids, coef=coef, h=h, y_routed_f32=y_routed)
     if w.shared_gate_up is not None:
-        if f16:  # the shared expert through the same matrix-unit numerics: one "expert" every token is routed to
+        if f16:  # the shared expert through the same matrix-unit numerics as a dense projection (linear_q8_wmma)
             zero = np.zeros((x.shape[0], 1), dtype=np.int32)
-            hs = experts_gather(x, w.shared_gate_up, 1, zero, swiglu_mode=2, threads=threads, w_f16=True)[:, 0]
+            hs = experts_gather(x, w.shared_gate_up, 1, zero, swiglu_mode=2, threads=threads, w_f16=True, x_f16=xm)[:, 0]
         else:
             hs = swiglu(linear_q(x, w.shared_gate_up, threads=threads))
         s = linear_q(hs, w.shared_down, threads=threads, w_f16=f16)
         gate = np.ascontiguousarray(logits[:, E], dtype=np.float32)
         s32 = linear_q(hs, w.shared_down, out_act=F32, threads=threads, w_f16=f16)
         out["shared_s"], out["shared_s_f32"] = s, s32
-        # FP32 view: nothing after h is rounded - the routed sum and the shared expert's output stay FP32, so the
-        # comparison is not at the mercy of one BF16 rounding of s or y falling the other way (one such flip of an
-        # s near 1 is 4e-3, the size of the whole tolerance).  BF16 view: the reference's roundings of s, y, y + g s.
+        # FP32 view: nothing after h is rounded except what the path itself rounds (the BF16 per-slot dots of
+        # "grouped") - the routed sum and the shared expert's output stay FP32, so the comparison is not at the mercy
+        # of one BF16 rounding of s or y falling the other way (one such flip of an s near 1 is 4e-3, the size of the
+        # whole tolerance).  BF16 view: the reference's roundings of s, y, y + g s.
         out["y_f32"] = moe_shared_add(y_routed, s32, gate, E)
         out["y_bf16"] = moe_shared_add(f32_to_bf16(y_routed), s, gate, E)
     else:

@@ -8,7 +8,7 @@
 // reference's device code is pinned only for the quantizers (checked bit-for-bit against
 // the reference's own formats/q4.cpp and formats/q8.cpp compiled by oracle/Makefile);
 // for router / pack / expert math parity is "unpinned": it rests on the header prose and
-// kernel sources cited below.
+// kernel sources cited below.  PARITY UNPINNED for those parts.
 //
 // Conventions: BF16 values travel as raw uint16_t bits; "act" 0 = F32, 1 = BF16
 // (kernels/norm.hpp:20).  Expert weights are stacked [E*N, K] (kernels/linear_q4.hpp:32-35).
@@ -113,6 +113,17 @@ uint16_t double_to_f16_bits(double v) {
     return sign | (uint16_t)(((exp + 15) << 10) | (q & 0x3FF));
 }
 inline float round_f16(double v) { return (float)f16_bits_to_double(double_to_f16_bits(v)); }
+// Round toward zero to binary16: the largest-magnitude F16 value not beyond v (what the reference's staging of BF16
+// activations does, kernels/moe_grouped.hip:29-32; exact for BF16 inputs in F16's normal range either way).
+inline float trunc_f16(double v) {
+    const double r = f16_bits_to_double(double_to_f16_bits(v));
+    if (std::isnan(r) || std::fabs(r) <= std::fabs(v)) return (float)r;
+    if (std::isinf(r)) return std::signbit(v) ? -65504.0f : 65504.0f;  // nearest rounded past the largest finite value
+    const uint16_t bits = double_to_f16_bits(v);
+    return (float)f16_bits_to_double((uint16_t)(bits - 1));  // one step toward zero (same sign, smaller magnitude)
+}
+// Activation staging of the matrix-unit path: mode 0 keeps the value, 1 rounds to F16 (nearest even), 2 toward zero.
+inline float stage_f16(float v, int mode) { return mode == 0 ? v : mode == 1 ? round_f16(v) : trunc_f16(v); }
 
 // One dequantized row.
 //   f16 == false: the FP32 values of formats/q4.cpp:121-134 / formats/q8.cpp:117-127 - code * scale, then + min, each
@@ -324,14 +335,16 @@ void orc_swiglu(const void *gu, void *h, int64_t rows, int64_t I, int act) {
 //   swiglu_mode 2 (grouped matrix-unit semantics, kernels/moe_grouped.hip:508-524):
 //                 h = stored(silu(g_f32) * u_f32), one rounding.
 //   w_f16: the weights are the matrix-unit path's F16 operand (see dequant_row) instead of the FP32 dequantization.
+//   x_f16: the activations as that path stages them: 0 as they are, 1 F16 to nearest, 2 F16 toward zero
+//          (kernels/moe_grouped.hip:29-32).
 // An id outside [0, E): err = {1, id, slot}, that slot's outputs NaN.
 void orc_experts_gather(const void *x, int act, const uint8_t *q, const uint16_t *scale, const uint16_t *minv,
                         int64_t Ntot, int64_t K, int64_t G, int bits, int64_t E, const int32_t *ids, int64_t M,
-                        int64_t A, void *y, int swiglu_mode, uint32_t *err, int threads, int w_f16) {
+                        int64_t A, void *y, int swiglu_mode, uint32_t *err, int threads, int w_f16, int x_f16) {
     const QView w{q, scale, minv, Ntot, K, G, bits};
     const int64_t N = Ntot / E, S = M * A, I = N / 2, out_cols = swiglu_mode ? I : N;
     std::vector<float> xf((size_t)(M * K));
-    for (int64_t i = 0; i < M * K; ++i) xf[(size_t)i] = load_act(x, i, act);
+    for (int64_t i = 0; i < M * K; ++i) xf[(size_t)i] = stage_f16(load_act(x, i, act), x_f16);
     std::vector<std::vector<int64_t>> b;
     bucket_slots(ids, S, E, b);
     for (int64_t s : b[(size_t)E]) {
@@ -369,15 +382,17 @@ void orc_experts_gather(const void *x, int act, const uint8_t *q, const uint16_t
 //   y[m, :] = sum_a coef[m, a] * (h[m, a, :] * W[ids[m, a]]^T), one rounding at the store.
 // Each per-slot dot is formed in double and cast to FP32; the sum over a runs in slot order
 // in double.  partial_out (optional, [M*A, N] FP32) receives the per-slot dots
-// (kernels/moe_grouped.hpp:84-87).  Any invalid id of a token: err, its whole y row NaN.
+// (kernels/moe_grouped.hpp:84-87).  partial_bf16: every per-slot dot is rounded to BF16 before the sum, as the
+// reference's matrix-unit path stores them (kernels/moe_grouped.hip:47-57); x_f16 as in orc_experts_gather.
+// Any invalid id of a token: err, its whole y row NaN.
 void orc_experts_combine(const void *h, int act, const uint8_t *q, const uint16_t *scale, const uint16_t *minv,
                          int64_t Ntot, int64_t K, int64_t G, int bits, int64_t E, const int32_t *ids,
                          const float *coef, int64_t M, int64_t A, void *y, int out_act, float *partial_out,
-                         uint32_t *err, int threads, int w_f16) {
+                         uint32_t *err, int threads, int w_f16, int x_f16, int partial_bf16) {
     const QView w{q, scale, minv, Ntot, K, G, bits};
     const int64_t N = Ntot / E, S = M * A;
     std::vector<float> hf((size_t)(S * K));
-    for (int64_t i = 0; i < S * K; ++i) hf[(size_t)i] = load_act(h, i, act);
+    for (int64_t i = 0; i < S * K; ++i) hf[(size_t)i] = stage_f16(load_act(h, i, act), x_f16);
     std::vector<float> local;
     float *partial = partial_out;
     if (!partial) {
@@ -398,7 +413,10 @@ void orc_experts_combine(const void *h, int act, const uint8_t *q, const uint16_
         std::vector<float> row((size_t)K);
         for (int64_t n = blk * kRowBlock; n < std::min(N, (blk + 1) * kRowBlock); ++n) {
             dequant_row(w, e * N + n, row.data(), w_f16 != 0);
-            for (int64_t s : slots) partial[s * N + n] = (float)dot_f32(&hf[(size_t)(s * K)], row.data(), K);
+            for (int64_t s : slots) {
+                const float p = (float)dot_f32(&hf[(size_t)(s * K)], row.data(), K);
+                partial[s * N + n] = partial_bf16 ? bf16_to_f32(f32_to_bf16(p)) : p;  // kernels/moe_grouped.hip:47-57
+            }
         }
     });
     parallel_for(M, threads, [&](int64_t m) {

@@ -9,10 +9,7 @@ import ctypes as C
 import pathlib
 
 _PKG = pathlib.Path(__file__).resolve().parent
-import os
-
-# STRIX_B200_LIB: load another build of the same library (e.g. one compiled with development counters).
-LIB_PATH = pathlib.Path(os.environ.get("STRIX_B200_LIB") or _PKG / "libstrix_b200.so")
+LIB_PATH = _PKG / "libstrix_b200.so"
 
 i64, i32, u32, sz, vp, cp = C.c_int64, C.c_int32, C.c_uint32, C.c_size_t, C.c_void_p, C.c_char_p
 
@@ -67,6 +64,20 @@ SIGNATURES = {
     "sxb_report_expert_error": (C.c_int, [C.POINTER(u32), cp]),
     "sxb_quantize": (C.c_int, [vp, i64, i64, i64, C.c_int, vp, vp, vp, vp, vp]),
     "sxb_moe_layer": (C.c_int, [C.POINTER(SxbMoeLayerArgs), vp]),
+    "sxb_set_wait_limit": (C.c_int, [C.c_uint64]),
+    "sxb_test_skip_ring_slot": (C.c_int, [C.c_int]),
+    "sxb_check_dense_status": (C.c_int, [cp]),
+    "sxb_linear_q4_wmma": (C.c_int, [vp, QV, vp, i64, C.c_int, C.c_int, vp]),
+    "sxb_linear_q8_wmma": (C.c_int, [vp, QV, vp, i64, C.c_int, C.c_int, vp]),
+    "sxb_linear_q4_wmma_swiglu": (C.c_int, [vp, QV, vp, i64, C.c_int, C.c_int, vp]),
+    "sxb_linear_q8_wmma_swiglu": (C.c_int, [vp, QV, vp, i64, C.c_int, C.c_int, vp]),
+    "sxb_linear_bf16w": (C.c_int, [vp, vp, vp, i64, i64, i64, C.c_int, C.c_int, vp]),
+    "sxb_router_logits": (C.c_int, [vp, vp, C.c_int, vp, i64, i64, i64, vp, i64, vp]),
+    "sxb_router_planes_bytes": (sz, [i64, i64, C.c_int]),
+    "sxb_router_prepare": (C.c_int, [vp, C.c_int, i64, i64, C.c_int, vp, vp]),
+    "sxb_router_logits_wmma": (C.c_int, [vp, vp, C.c_int, vp, i64, i64, i64, vp, i64, vp]),
+    "sxb_residual_add": (C.c_int, [vp, vp, C.c_int, vp, i64, vp]),
+    "sxb_moe_route_small": (C.c_int, [vp, i64, i64, i64, i64, i64, i64, vp, vp, vp, sz, vp, vp, vp]),
 }
 for _b in ("q4", "q8"):
     SIGNATURES[f"sxb_linear_{_b}_experts_gather"] = (C.c_int, [vp, QV, i64, vp, i64, i64, vp, C.c_int, vp, vp])

@@ -18,7 +18,12 @@ int stream_combine_slots(const char *fn, const void *h, const SxbQView *w, int64
                          sxb_stream_t stream);
 int combine_reduce(const char *fn, const float *partial, const int32_t *ids, const float *coef, int64_t M, int64_t A,
                    int64_t E_total, int64_t e_lo, int64_t E_local, int64_t N, void *y, int out_act,
-                   const SxbMoeSharedAdd *shared, int s_act, sxb_stream_t stream);
+                   const SxbMoeSharedAdd *shared, int s_act, bool partial_bf16, sxb_stream_t stream);
+// grouped.cu: the grouped down projection + combine behind every public combine entry (checks, dispatch on math, reduce).
+template <int BITS>
+int combine_grouped(const char *fn, const void *h, const SxbQView *w, int64_t E_view, const int32_t *ids, const float *coef,
+                    const void *ws, size_t ws_bytes, float *partial, int64_t M, int64_t A, void *y, int act, int out_act,
+                    int math, sxb_stream_t stream, const SxbMoeSharedAdd *shared, int h_f16, int64_t E_total, int64_t e_lo);
 
 // grouped_tc.cu - tcgen05 kernels (F16 operands, FP32 accumulation in tensor memory).
 template <int BITS>
@@ -26,9 +31,24 @@ int tc_gather_grouped(const char *fn, const void *x, const SxbQView *w, int64_t 
                       int64_t M, int64_t A, void *y, int act, bool swiglu, int h_f16, sxb_stream_t stream);
 template <int BITS>
 int tc_partial_grouped(const char *fn, const void *h, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes,
-                       int64_t M, int64_t A, float *partial, int act, int h_f16, sxb_stream_t stream);
+                       int64_t M, int64_t A, float *partial, int act, int h_f16, bool partial_bf16, sxb_stream_t stream);
+// Dense projection on the same kernel (out_kind 0 BF16, 1 FP32, 2 fused SwiGLU; x_kind 0 BF16, 3 tile-blocked F16).
+template <int BITS>
+int tc_dense(const char *fn, const void *x, const SxbQView *w, void *y, int64_t M, int x_kind, int out_kind, int h_f16,
+             uint32_t *status, sxb_stream_t stream);
+// f32act.cu - Act::F32 activations: the plain FP32 correctness path.  ids / ws both null: a dense projection.
+template <int BITS>
+int f32_gather(const char *fn, const void *x, const SxbQView *w, int64_t E, const int32_t *ids, const void *ws, int64_t M, int64_t A,
+               void *y, bool swiglu, int row_div, uint32_t *err, sxb_stream_t stream);
+template <int BITS>
+int f32_combine(const char *fn, const void *h, const SxbQView *w, int64_t E, const int32_t *ids, const float *coef, int64_t M,
+                int64_t A, void *y, uint32_t *err, sxb_stream_t stream);
+// route_pack.cu: SXB_ERR_DATA with the message for the status words {2, work item, role} of a wait that ran out.
+int tc_status_error(const char *what, const uint32_t e[3]);
 
-inline bool math_is_f16(int math) { return math >= SXB_MATH_WMMA_F16 && math <= SXB_MATH_WMMA_F16_WIDE256; }
-inline bool math_ok(int math) { return math >= SXB_MATH_F32 && math <= SXB_MATH_WMMA_F16_WIDE256; }
+inline bool math_is_f16(int math) { return math >= SXB_MATH_WMMA_F16 && math <= SXB_MATH_WMMA_F16_F32_PARTIALS; }
+inline bool math_ok(int math) { return math >= SXB_MATH_F32 && math <= SXB_MATH_WMMA_F16_F32_PARTIALS; }
+// The reference's matrix-unit path stores the combine's per-slot dots as BF16 (kernels/moe_grouped.hip:47-57).
+inline bool math_bf16_partials(int math) { return math >= SXB_MATH_WMMA_F16 && math <= SXB_MATH_WMMA_F16_WIDE256; }
 
 }  // namespace sxb

@@ -15,9 +15,11 @@ int gather_grouped(const char *fn, const void *x, const SxbQView *w, int64_t E, 
     SXB_CHECK(!h_f16 || (act != SXB_ACT_F32 && math_is_f16(math)), fn,
               ": F16 h needs BF16 activations and a WMMA_F16 math, got ", act_name(act), " math ", math);
     SXB_CHECK((act != SXB_ACT_F16_STAGED && act != SXB_ACT_F16_TILED) || math_is_f16(math), fn, ": staged F16 activations need a WMMA_F16 math");
-    if (math_is_f16(math)) return tc_gather_grouped<BITS>(fn, x, w, E, ws, ws_bytes, M, A, y, act, swiglu, h_f16, stream);
+    if (math_is_f16(math) && act != SXB_ACT_F32) return tc_gather_grouped<BITS>(fn, x, w, E, ws, ws_bytes, M, A, y, act, swiglu, h_f16, stream);
     return stream_gather_grouped<BITS>(fn, x, w, E, ws, ws_bytes, M, A, y, act, swiglu, stream);
 }
+
+}  // namespace
 
 template <int BITS>
 int combine_grouped(const char *fn, const void *h, const SxbQView *w, int64_t E_view, const int32_t *ids, const float *coef,
@@ -37,14 +39,23 @@ int combine_grouped(const char *fn, const void *h, const SxbQView *w, int64_t E_
               " with activations ", act_name(act), " unsupported (same dtype, or F32)");
     SXB_CHECK(apart(partial, M * A * N * 4, h, M * A * w->K * act_bytes(act)), fn, ": partial overlaps h");
     SXB_CHECK(apart(y, M * N * act_bytes(out_act), h, M * A * w->K * act_bytes(act)), fn, ": y overlaps h");
-    int rc = math_is_f16(math)
-                 ? tc_partial_grouped<BITS>(fn, h, w, E_view, ws, ws_bytes, M, A, partial, act, h_f16, stream)
+    // FP32 activations take the plain FP32 path whatever the math (the F16 kinds are defined for BF16 activations)
+    const bool tc = math_is_f16(math) && act != SXB_ACT_F32;
+    const bool pb = tc && math_bf16_partials(math);
+    int rc = tc
+                 ? tc_partial_grouped<BITS>(fn, h, w, E_view, ws, ws_bytes, M, A, partial, act, h_f16, pb, stream)
                  : stream_partial_grouped<BITS>(fn, h, w, E_view, ws, ws_bytes, M, A, partial, act, stream);
     if (rc) return rc;
-    return combine_reduce(fn, partial, ids, coef, M, A, E_total, e_lo, E_view, N, y, out_act, shared, out_act, stream);
+    return combine_reduce(fn, partial, ids, coef, M, A, E_total, e_lo, E_view, N, y, out_act, shared, out_act, pb, stream);
 }
 
-}  // namespace
+template int combine_grouped<4>(const char *, const void *, const SxbQView *, int64_t, const int32_t *, const float *, const void *,
+                                size_t, float *, int64_t, int64_t, void *, int, int, int, sxb_stream_t, const SxbMoeSharedAdd *,
+                                int, int64_t, int64_t);
+template int combine_grouped<8>(const char *, const void *, const SxbQView *, int64_t, const int32_t *, const float *, const void *,
+                                size_t, float *, int64_t, int64_t, void *, int, int, int, sxb_stream_t, const SxbMoeSharedAdd *,
+                                int, int64_t, int64_t);
+
 }  // namespace sxb
 
 using namespace sxb;

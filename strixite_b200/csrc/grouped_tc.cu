@@ -39,24 +39,7 @@
 // The tensor copies read this GPU's own weight array only, each into the shared memory of the one CTA that issues it.
 
 #include "experts.cuh"
-
-#include <cuda.h>  // CUtensorMap and its enums only; the encoder is looked up through the runtime, nothing links libcuda
-#include <cuda_bf16.h>
-#include <cuda_fp16.h>
-
-#if defined(SXB_TC_PROF) || defined(SXB_TC_TRACE)
-__device__ unsigned long long g_tc_prof[32];
-__device__ long long g_tc_trace[4][64][2];  // role (A, B, MMA, -), k-block index of CTA 0, two timestamps
-__device__ long long g_tc_trace8[8][64];    // arrival time of every A warp, per k-block of CTA 0
-__device__ long long g_tc_stamp[64][8];     // fine-grained stamps of the first A warp, per k-block of CTA 0
-#define STAMP(idx, which) \
-    do { if (blockIdx.x == 0 && (warp & 3) == (kFirstAWarp & 3) && lane == 0 && (idx) < 64) g_tc_stamp[idx][which] = clock64(); } while (0)
-#define TRACE(role, idx, which) \
-    do { if (blockIdx.x == 0 && lane == 0 && (idx) < 64) g_tc_trace[role][idx][which] = clock64(); } while (0)
-#else
-#define TRACE(role, idx, which) do {} while (0)
-#define STAMP(idx, which) do {} while (0)
-#endif
+#include "tc_ptx.cuh"
 
 namespace sxb {
 namespace {
@@ -83,22 +66,9 @@ constexpr int kAStageCol0 = 2 * kAccCols, kAStageCols = 2 * (kBK / 2);
 // rows, as two boxes of 128 rows.
 constexpr int kWSlots = 4;
 constexpr int kWSlotBytes = kAThreads * 64;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any legitimate wait
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any legitimate wait (the default bound)
 
 enum TcMode { kTcGather = 0, kTcSwiglu = 1, kTcPartial = 2 };
-
-// Optional cycle accounting per warp role (development builds only: -DSXB_TC_PROF).  CTA 0, lane 0 of one warp per role.
-#ifdef SXB_TC_PROF
-#define PROF_BEGIN() const long long prof_t0_ = clock64()
-#define PROF_ADD(slot) \
-    do { if (blockIdx.x == 0 && lane == 0) atomicAdd(&g_tc_prof[slot], (unsigned long long)(clock64() - prof_t0_)); } while (0)
-#define PROF_COUNT(slot) \
-    do { if (blockIdx.x == 0 && lane == 0) atomicAdd(&g_tc_prof[slot], 1ull); } while (0)
-#else
-#define PROF_BEGIN() do {} while (0)
-#define PROF_ADD(slot) do {} while (0)
-#define PROF_COUNT(slot) do {} while (0)
-#endif
 
 struct TcArgs {
     const uint16_t *x;  // activations: BF16 or F16 bits, see x_kind
@@ -114,174 +84,11 @@ struct TcArgs {
     int out_f16;  // SwiGLU output h: 0 BF16, 1 F16 bits of its BF16 rounding, 2 the same in the Q4 operand's k order,
                   // 3 / 4 tile-blocked for a Q4 / Q8 down operand
     uint32_t *status;  // >= 3 words: {2, item, role} on a wait that ran out
+    int64_t dense_M;   // > 0: a dense projection - no grouping workspace, one group holding rows 0 .. dense_M - 1 in order
+    int partial_bf16;  // kTcPartial: the per-slot dots are stored as BF16 bits (N * 2 bytes a slot), not FP32
+    unsigned long long wait_limit_ns;  // bound of every device-side wait
+    int test_skip_slot;  // >= 0: CTA 0 never issues ring slot number test_skip_slot, so a wait runs out (tests only)
 };
-
-// ---- PTX wrappers ----------------------------------------------------------------------------------------------
-__device__ inline uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ inline void mbar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ inline void mbar_arrive(uint64_t *bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ inline bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ inline unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-// Bounded wait.  False when the CTA is aborting or the limit ran out (then the caller raises the abort itself).
-// The common case must stay cheap: the first polls touch nothing but the barrier; the abort flag and the (slow to read)
-// global timer are consulted only once a wait has lasted thousands of polls.
-__device__ inline bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
-    unsigned long long t0 = 0;
-    for (uint32_t spins = 0;; ++spins) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spins & 4095u) == 4095u) {
-            if (*abort_flag) return false;
-            const unsigned long long now = global_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) return false;
-        }
-    }
-}
-__device__ inline void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ inline void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ inline void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-// Executed by a whole (converged) warp; elect.sync picks the lane that issues - the same one every time for a full mask,
-// so the commits track the MMAs of the lane that issued them.
-__device__ inline void tc_commit(uint64_t *bar) {
-    asm volatile(
-        "{\n\t.reg .pred q;\n\t"
-        "elect.sync _|q, 0xffffffff;\n\t"
-        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar))
-        : "memory");
-}
-// 16 consecutive columns of this thread's TMEM lane from each of two addresses, one wait for both.
-__device__ inline void tc_ld16x2(uint32_t taddr0, uint32_t taddr1, float (&v0)[16], float (&v1)[16]) {
-    uint32_t r[16], q[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr0));
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3]), "=r"(q[4]), "=r"(q[5]), "=r"(q[6]), "=r"(q[7]), "=r"(q[8]),
-          "=r"(q[9]), "=r"(q[10]), "=r"(q[11]), "=r"(q[12]), "=r"(q[13]), "=r"(q[14]), "=r"(q[15])
-        : "r"(taddr1));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v0[i] = __uint_as_float(r[i]), v1[i] = __uint_as_float(q[i]);
-}
-// silu on the special-function unit: ex2 and a reciprocal, a few ulp of FP32 - far inside the BF16 rounding that follows.
-__device__ inline float silu_fast(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
-
-// 16 consecutive columns of this thread's TMEM lane, written from registers.
-__device__ inline void tc_st16(uint32_t taddr, const uint4 (&d)[4]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
-        "r"(d[0].x), "r"(d[0].y), "r"(d[0].z), "r"(d[0].w), "r"(d[1].x), "r"(d[1].y), "r"(d[1].z), "r"(d[1].w), "r"(d[2].x),
-        "r"(d[2].y), "r"(d[2].z), "r"(d[2].w), "r"(d[3].x), "r"(d[3].y), "r"(d[3].z), "r"(d[3].w)
-        : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem]: the A operand (128 rows x 16 k of F16, two per 32-bit column) read from tensor memory.
-// Whole-warp call, one elected lane issues (see tc_commit).
-__device__ inline void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "elect.sync _|q, 0xffffffff;\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-// One k-block of an accumulator as one instruction group: a non-blocking probe of the NEXT k-block's "operands ready"
-// barrier first, then the four MMAs (k = 16 each; the A columns advance by 8, the B descriptor by 32 bytes), the commit
-// that frees the stage and, for the last k-block of an item, the commit that hands the accumulators over.  The probe's
-// answer is read only after the commits, so its latency passes under their issue; when it says "ready" the next
-// k-block starts without a poll.  Whole-warp call, one elected lane issues.
-__device__ inline bool tc_kblock_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate,
-                                    uint64_t *stage_free, uint64_t *acc_done, uint64_t *next_full, uint32_t next_parity) {
-    uint32_t ready;
-    asm volatile(
-        "{\n\t.reg .pred p, q, r, t, one;\n\t.reg .b32 a1, a2, a3;\n\t.reg .b64 b1, b2, b3;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 r, [%7], %8;\n\t"
-        "setp.ne.b32 p, %5, 0;\n\t"
-        "setp.eq.b32 one, 0, 0;\n\t"
-        "add.u32 a1, %2, 8;\n\tadd.u32 a2, %2, 16;\n\tadd.u32 a3, %2, 24;\n\t"
-        "add.u64 b1, %3, 2;\n\tadd.u64 b2, %3, 4;\n\tadd.u64 b3, %3, 6;\n\t"
-        "elect.sync _|q, 0xffffffff;\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [%2], %3, %4, p;\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [a1], b1, %4, one;\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [a2], b2, %4, one;\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f16 [%1], [a3], b3, %4, one;\n\t"
-        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"
-        "setp.ne.b32 t, %9, 0;\n\t"
-        "and.pred t, t, q;\n\t"
-        "@t tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%9];\n\t"
-        "selp.u32 %0, 1, 0, r;\n\t}"
-        : "=r"(ready)
-        : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(smem_u32(stage_free)),
-          "r"(smem_u32(next_full)), "r"(next_parity), "r"(acc_done ? smem_u32(acc_done) : 0u)
-        : "memory");
-    return ready != 0;
-}
-
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart.
-//   bits [0,14) start address >> 4 | [16,30) leading byte offset >> 4 (unused for swizzled K-major: 1)
-//   [32,46) stride byte offset >> 4 (1024 B) | [46,48) descriptor version 1 | [61,64) layout 2 = SWIZZLE_128B
-__device__ inline uint64_t smem_desc(uint32_t addr) {
-    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-// Instruction descriptor for kind::f16: D FP32 (bits [4,6) = 1), A and B F16 (formats 0), both K-major,
-// N >> 3 at bits [17,23), M >> 4 at bits [24,29).
-__device__ inline uint32_t instr_desc(int n_cols) { return (1u << 4) | ((uint32_t)(n_cols >> 3) << 17) | ((128u >> 4) << 24); }
-
-__device__ inline uint32_t h2_as_u32(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
-__device__ inline __half2 u32_as_h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
-
-// Byte offset of 16-byte chunk c of row r inside a K-major, 128-byte-swizzled tile.
-__device__ inline uint32_t swz(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
-
-// Tile-blocked activations: rows live at their position `pos` in the pack's slot order, k-block-major, each row's 128-byte
-// line of a k-block already swizzled for its place n = pos - tile_start in the tile.  The B operand of (tile, k-block) is
-// then ONE contiguous run of cnt * 128 bytes at byte offset (kb * S + tile_start) * 128: a single bulk copy.
-__device__ inline int64_t tiled_offset(int64_t S, int kb, int64_t pos, int n, int c) {
-    return ((int64_t)kb * S + pos) * 128 + ((c ^ (n & 7)) << 4);
-}
-__device__ inline void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ inline void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint64_t *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
-                 "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
-
-// One box of a 2-D tensor copy, completion counted in bytes on `bar`.  x is a byte offset inside the weight row
-// and always a multiple of 64, as the 16-byte alignment rule of tensor copies requires.
-__device__ inline void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-                 "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ inline uint4 ld_shared_v4(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
 
 // Eight activations (one 16-byte chunk of BF16 or F16) -> F16 in the operand's k order.
 template <int BITS>
@@ -349,6 +156,11 @@ __device__ inline ItemInfo item_info(const TcArgs &a, int item, int rbs) {
     ItemInfo it;
     const int tile = item / rbs;
     it.rb = item % rbs;
+    if (a.dense_M > 0) {  // dense projection: tile t holds rows 128 t .. of the one group
+        it.bucket = 0, it.start = tile * kMaxTileTokens;
+        it.cnt = (int)min((int64_t)kMaxTileTokens, a.dense_M - it.start);
+        return it;
+    }
     it.bucket = a.ws[a.L.t128_bucket + tile];
     it.start = a.ws[a.L.t128_start + tile];
     it.cnt = min(kMaxTileTokens, a.ws[a.L.offsets + it.bucket + 1] - it.start);
@@ -358,6 +170,7 @@ __device__ inline ItemInfo item_info(const TcArgs &a, int item, int rbs) {
 // Next item of this CTA (stride gridDim.x) at or after `item` whose bucket is a real expert.
 template <int MODE>
 __device__ inline int next_valid_item(const TcArgs &a, int item, int n_items, int rbs) {
+    if (a.dense_M > 0) return item;
     while (item < n_items && a.ws[a.L.t128_bucket + item / rbs] >= a.E) item += gridDim.x;
     return item;
 }
@@ -376,7 +189,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int K = (int)a.K, n_kb = K / kBK, groups = K / G;
     const int rbs = row_blocks<MODE>(a);
-    const int n_items = a.ws[3] * rbs;
+    const int n_items = (a.dense_M > 0 ? (int)((a.dense_M + kMaxTileTokens - 1) / kMaxTileTokens) : a.ws[3]) * rbs;
+    // slot (row of the output / of h) at position pos of the slot order; a dense projection's rows are in their own order
+    auto slot_at = [&](int pos) -> int { return a.dense_M > 0 ? pos : a.ws[a.L.slots + pos]; };
     volatile int *abort_v = &abort_flag;
 
     if (threadIdx.x == 0) {
@@ -415,7 +230,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
     uint32_t issued = 0;
     auto issue_one = [&]() -> bool {
         const int slot = issued % kWSlots;
-        if (issued >= (uint32_t)kWSlots && !mbar_wait(&w_empty[slot], ((issued / kWSlots) & 1u) ^ 1u, abort_v)) {
+        if (issued >= (uint32_t)kWSlots && !mbar_wait(&w_empty[slot], ((issued / kWSlots) & 1u) ^ 1u, abort_v, a.wait_limit_ns)) {
             raise_abort(is_item, 6);
             return false;
         }
@@ -425,9 +240,13 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
             else is_y0 = (int)(it.bucket * a.N + (int64_t)it.rb * kAThreads), is_y1 = is_y0 + 128;
         }
         const uint32_t dst = w_base + (uint32_t)(slot * kWSlotBytes);
-        mbar_expect_tx(&w_full[slot], (uint32_t)kWSlotBytes);
-        tma_load_2d(dst, &wmap, is_slot * 64, is_y0, &w_full[slot]);
-        tma_load_2d(dst + kWSlotBytes / 2, &wmap, is_slot * 64, is_y1, &w_full[slot]);
+        // test hook: CTA 0 leaves one slot unfilled (neither the byte count nor the copies), so that its consumers' wait
+        // runs out at the launch's limit and the abort path is exercised without anything faulting
+        if (!(blockIdx.x == 0 && (int)issued == a.test_skip_slot)) {
+            mbar_expect_tx(&w_full[slot], (uint32_t)kWSlotBytes);
+            tma_load_2d(dst, &wmap, is_slot * 64, is_y0, &w_full[slot]);
+            tma_load_2d(dst + kWSlotBytes / 2, &wmap, is_slot * 64, is_y1, &w_full[slot]);
+        }
         ++issued;
         if (++is_slot == n_slots) is_slot = 0, is_item = next_valid_item<MODE>(a, is_item + gridDim.x, n_items, rbs);
         return true;
@@ -504,8 +323,8 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
         // lane 0: the codes of slot number wc have landed and the stage of k-block number cnt is free
         auto poll = [&](uint32_t wc, uint32_t cnt, int it_for_status) {
             if (!own_w_thread && warp == kFirstAWarp) top_up(wc);
-            if (!mbar_wait(&w_full[wc % kWSlots], (wc / kWSlots) & 1u, abort_v)) raise_abort(it_for_status, 7);
-            else if (!mbar_wait(&empty_bar[cnt % kStages], ((cnt / kStages) & 1u) ^ 1u, abort_v)) raise_abort(it_for_status, 1);
+            if (!mbar_wait(&w_full[wc % kWSlots], (wc / kWSlots) & 1u, abort_v, a.wait_limit_ns)) raise_abort(it_for_status, 7);
+            else if (!mbar_wait(&empty_bar[cnt % kStages], ((cnt / kStages) & 1u) ^ 1u, abort_v, a.wait_limit_ns)) raise_abort(it_for_status, 1);
         };
 
         // This warp's k-blocks of an item: kb = a_par, a_par + 2, ...; k-block kb lives in slot kb / kKbPerSlot.
@@ -526,7 +345,6 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
             for (int kb = a_par; kb < n_kb; kb += 2) {
                 const uint32_t cnt = kb_base + (uint32_t)kb, wc = w_base_count + (uint32_t)(kb / kKbPerSlot);
                 const int stage = cnt % kStages, slot = wc % kWSlots;
-                STAMP(cnt, 0);
                 if (kb % kKbPerChunk == a_par) {  // this warp's first k-block of a chunk of eight scale groups
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
@@ -547,8 +365,6 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
                     }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&w_empty[slot]);  // the codes are in registers: the slot may be refilled
-                STAMP(cnt, 1);
-                PROF_BEGIN();
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     __half2 s2[kGroupsPerKb], s16[kGroupsPerKb], m2[kGroupsPerKb];
@@ -585,34 +401,20 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
                     }
                     if (h == 0) asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 }
-                if (warp == kFirstAWarp) PROF_ADD(1);
-                STAMP(cnt, 2);
                 {
-                    PROF_BEGIN();
                     // under the last stores: what this warp's next k-block needs
                     if (lane == 0) {
                         if (kb + 2 < n_kb) poll(w_base_count + (uint32_t)((kb + 2) / kKbPerSlot), cnt + 2, item);
                         else if (next < n_items) poll(w_base_count + (uint32_t)(n_slots + a_par / kKbPerSlot), kb_base + (uint32_t)(n_kb + a_par), next);
                     }
-                    if (warp == kFirstAWarp) PROF_ADD(0);
                 }
-                STAMP(cnt, 3);
                 {
-                    PROF_BEGIN();
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                    STAMP(cnt, 4);
                     tc_fence_before();  // orders the stores before the MMA warp's reads across the barrier
                     __syncwarp();
                     tc_fence_after();   // and the next k-block's stores after the MMAs that freed its stage
-                    STAMP(cnt, 5);
                     if (lane == 0) mbar_arrive(&full_bar[stage]);
-                    STAMP(cnt, 6);
-#if defined(SXB_TC_PROF) || defined(SXB_TC_TRACE)
-                    if (blockIdx.x == 0 && lane == 0 && cnt < 64) g_tc_trace8[warp - kFirstAWarp][cnt] = clock64();
-#endif
                     if (warp == kFirstAWarp) {
-                        PROF_ADD(2);
-                        PROF_COUNT(4);
                     }
                 }
                 if (*abort_v) {
@@ -643,11 +445,10 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
                     const unsigned char *src = reinterpret_cast<const unsigned char *>(a.x) + (int64_t)it.start * 128;
                     for (int kb = 0; kb < n_kb; ++kb, ++it_count) {
                         const int stage = it_count % kStages;
-                        if (!mbar_wait(&empty_bar[stage], ((it_count / kStages) & 1u) ^ 1u, abort_v)) {
+                        if (!mbar_wait(&empty_bar[stage], ((it_count / kStages) & 1u) ^ 1u, abort_v, a.wait_limit_ns)) {
                             raise_abort(item, 5);
                             break;
                         }
-                        TRACE(1, it_count, 0);
                         mbar_expect_tx(&full_bar[stage], bytes);
                         bulk_g2s(smem_u32(smem + stage * kStageBytes), src + (int64_t)kb * a.L.S * 128, bytes, &full_bar[stage]);
                     }
@@ -665,7 +466,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
             const int n_mine = min(max(it.cnt - bw * kRowsPerWarp, 0), kRowsPerWarp);
             __syncwarp();
             for (int n = lane; n < n_mine; n += 32) {
-                const int64_t slot = a.ws[a.L.slots + it.start + bw * kRowsPerWarp + n];
+                const int64_t slot = slot_at(it.start + bw * kRowsPerWarp + n);
                 row_off[n] = (MODE == kTcPartial ? slot : slot / a.A) * a.K;
             }
             __syncwarp();
@@ -677,22 +478,16 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
                     // hand over k-block kb - kBAhead first: its group is the oldest of the kBAhead still pending, and the
                     // MMA warp must not have to wait for this warp's next free stage to learn that it has landed
                     if (kb >= kBAhead) {
-                        PROF_BEGIN();
                         asm volatile("cp.async.wait_group %0;" ::"n"(kBAhead - 1) : "memory");
                         fence_proxy_async();
-                        if (bw == 0) PROF_ADD(14);
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&full_bar[(it_count + kb - kBAhead) % kStages]);
-                        if (bw == 0) TRACE(1, it_count + kb - kBAhead, 1);
                     }
                     if (kb < n_kb) {
                         const uint32_t cnt = it_count + kb;
                         const int stage = cnt % kStages;
                         {
-                            PROF_BEGIN();
-                            if (lane == 0 && !mbar_wait(&empty_bar[stage], ((cnt / kStages) & 1u) ^ 1u, abort_v)) raise_abort(item, 5);
-                            if (bw == 0) PROF_ADD(12);
-                            if (bw == 0) TRACE(1, cnt, 0);
+                            if (lane == 0 && !mbar_wait(&empty_bar[stage], ((cnt / kStages) & 1u) ^ 1u, abort_v, a.wait_limit_ns)) raise_abort(item, 5);
                         }
                         __syncwarp();
                         if (*abort_v) {
@@ -717,7 +512,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
                 for (int kb = 0; kb < n_kb && live; ++kb) {
                     const uint32_t cnt = it_count + kb;
                     const int stage = cnt % kStages;
-                    if (lane == 0 && !mbar_wait(&empty_bar[stage], ((cnt / kStages) & 1u) ^ 1u, abort_v)) raise_abort(item, 5);
+                    if (lane == 0 && !mbar_wait(&empty_bar[stage], ((cnt / kStages) & 1u) ^ 1u, abort_v, a.wait_limit_ns)) raise_abort(item, 5);
                     __syncwarp();
                     if (*abort_v) {
                         live = false;
@@ -756,9 +551,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
             const uint32_t acc_phase = acc_count & 1u;
             ++acc_count;
             {
-                PROF_BEGIN();
-                if (lane == 0 && !mbar_wait(&acc_empty[0], acc_phase ^ 1u, abort_v)) raise_abort(item, 2);
-                if (half == 0) PROF_ADD(7);
+                if (lane == 0 && !mbar_wait(&acc_empty[0], acc_phase ^ 1u, abort_v, a.wait_limit_ns)) raise_abort(item, 2);
             }
             __syncwarp();
             if (*abort_v) break;
@@ -770,43 +563,32 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
                 const uint32_t phase = (it_count / kStages) & 1u;
                 bool failed = false;
                 {
-                    PROF_BEGIN();
-                    if (lane == 0 && !ready && !mbar_wait(&full_bar[stage], phase, abort_v)) raise_abort(item, 3), failed = true;
+                    if (lane == 0 && !ready && !mbar_wait(&full_bar[stage], phase, abort_v, a.wait_limit_ns)) raise_abort(item, 3), failed = true;
                     if (half == 0) {
-                        PROF_ADD(5);
-                        PROF_COUNT(8);
-                        TRACE(2, it_count, 0);
                     }
                 }
                 {
                     // One vote reconverges the warp and tells it whether lane 0's wait gave up (a wait gives up when its
                     // limit runs out or once another warp has raised the abort flag); the item loop re-reads the flag.
-                    PROF_BEGIN();
                     if (__any_sync(0xffffffffu, failed)) break;
-                    if (half == 0) PROF_ADD(21);
                 }
                 {
-                    PROF_BEGIN();
                     tc_fence_after();
-                    if (half == 0) PROF_ADD(22);
                 }
-                PROF_BEGIN();
                 const uint64_t b_desc = smem_desc(smem_u32(smem + stage * kStageBytes));
                 const uint32_t at = tmem_base + (uint32_t)(kAStageCol0 + stage * kAStageCols + half * (kBK / 2));
                 static_assert(kBK / 16 == 4, "tc_kblock_ts issues four MMAs");
                 // the stage is freed when these MMAs have read it; the last k-block hands the accumulators to the epilogue
                 ready = tc_kblock_ts(d, at, b_desc, idesc, kb != 0, &empty_bar[stage], kb == n_kb - 1 ? &acc_full[0] : nullptr,
                                      &full_bar[(it_count + 1) % kStages], ((it_count + 1) / kStages) & 1u);
-                if (half == 0) PROF_ADD(20);
                 if (half == 0) {
-                    PROF_ADD(6);
-                    TRACE(2, it_count, 1);
                 }
             }
         }
         // Drain: every MMA issued by this CTA has completed before tensor memory is released.
+        // (this wait does not give up when the CTA is aborting: tensor memory must not be released under an MMA)
         tc_commit(&drain_bar);
-        if (lane == 0) mbar_wait(&drain_bar, 0u, abort_v);
+        if (lane == 0) mbar_wait(&drain_bar, 0u, nullptr, a.wait_limit_ns);
         __syncwarp();
     } else {
         // ===================== epilogue =====================
@@ -841,34 +623,30 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
             } else {
                 const int64_t r = (int64_t)it.rb * kAThreads + r_loc;
                 row_ok = r < a.N;  // N is a multiple of 16: the second accumulator's row r + 128 is checked on its own
-                elem_off = r * (MODE == kTcPartial ? 4 : 2);
+                elem_off = r * (MODE == kTcPartial && !a.partial_bf16 ? 4 : 2);
             }
             const bool row1_ok = MODE != kTcSwiglu && (int64_t)it.rb * kAThreads + 128 + r_loc < a.N;
             // Slot of token n of the tile (lanes 0..15 fetch the 16 tokens of a pass, one pass ahead; nothing may depend
             // on the loaded value before the next pass, or the in-order issue would stall this pass's stores behind it).
-            auto token_slot = [&](int n) -> int { return (tiled_out || n >= it.cnt) ? 0 : a.ws[a.L.slots + it.start + n]; };
+            auto token_slot = [&](int n) -> int { return (tiled_out || n >= it.cnt) ? 0 : slot_at(it.start + n); };
             // Offset of a token's output row / line, in 16-byte units.
             auto token_off = [&](int n, int slot) -> uint32_t {
                 if (tiled_out) return (uint32_t)(it.start + n) * 8u;
-                return (uint32_t)(((int64_t)slot * (MODE == kTcSwiglu ? I * 2 : a.N * (MODE == kTcPartial ? 4 : 2))) >> 4);
+                return (uint32_t)(((int64_t)slot * (MODE == kTcSwiglu ? I * 2 : a.N * (MODE == kTcPartial && !a.partial_bf16 ? 4 : 2))) >> 4);
             };
             int slot_nxt = lane < 16 ? token_slot(lane) : 0;
             if (valid) {
                 const uint32_t acc_phase = acc_count & 1u;
                 ++acc_count;
                 {
-                    PROF_BEGIN();
-                    if (lane == 0 && !mbar_wait(&acc_full[0], acc_phase, abort_v)) raise_abort(item, 4);
+                    if (lane == 0 && !mbar_wait(&acc_full[0], acc_phase, abort_v, a.wait_limit_ns)) raise_abort(item, 4);
                     if (warp == 0) {
-                        PROF_ADD(9);
-                        PROF_COUNT(11);
                     }
                 }
                 __syncwarp();
                 if (*abort_v) break;
                 tc_fence_after();
             }
-            PROF_BEGIN();
             unsigned char *out = static_cast<unsigned char *>(a.out) + elem_off;
             for (int c0 = 0; c0 < it.cnt; c0 += 16) {
                 float g[16], u[16];
@@ -895,19 +673,31 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
                         const uint16_t hv = h_as_f16 ? __half_as_ushort(__float2half_rn(bf16_bits_to_f32(b))) : b;
                         const uint32_t sw = tiled_out ? ((xor_chunk ^ (uint32_t)(t & 7)) << 4) : 0u;
                         if (row_ok && t < live) *reinterpret_cast<uint16_t *>(out + off + sw) = hv;
-                    } else if (MODE == kTcPartial) {
+                    } else if (MODE == kTcPartial && !a.partial_bf16) {
                         if (row_ok && t < live) *reinterpret_cast<float *>(out + off) = g[t];
                         if (row1_ok && t < live) *reinterpret_cast<float *>(out + off + 512) = u[t];
-                    } else {
+                    } else {  // BF16 rows: the plain gather's y, or the per-slot dots as kernels/moe_grouped.hip:47-57 stores them
                         if (row_ok && t < live) *reinterpret_cast<uint16_t *>(out + off) = __bfloat16_as_ushort(__float2bfloat16_rn(g[t]));
                         if (row1_ok && t < live) *reinterpret_cast<uint16_t *>(out + off + 256) = __bfloat16_as_ushort(__float2bfloat16_rn(u[t]));
                     }
                 }
             }
-            if (warp == 0) PROF_ADD(10);
         }
     }
 
+    // An aborting CTA must not return under copies it issued into its own shared memory (which may go to the next CTA):
+    // the thread that ran the ring of weight codes waits, bounded, for the last fill of every slot; the activation copies
+    // complete on barriers that also count thread arrivals, so their issuer lets a generous time pass instead.
+    if (*abort_v) {
+        for (int sl = 0; sl < kWSlots && issued > 0; ++sl) {
+            if (issued <= (uint32_t)sl) continue;
+            const uint32_t last = ((issued - 1 - (uint32_t)sl) / kWSlots) * kWSlots + (uint32_t)sl;
+            if (blockIdx.x == 0 && (int)last == a.test_skip_slot) continue;  // the test hook's slot was never filled
+            mbar_wait(&w_full[sl], (last / kWSlots) & 1u, nullptr, 1000000ull);
+        }
+        if (warp == kFirstBWarp && lane == 0 && a.x_kind == 3)
+            for (const unsigned long long t0 = global_ns(); global_ns() - t0 < 50000ull;) {}
+    }
     tc_fence_before();
     __syncthreads();
     if (warp == kMmaWarp) {
@@ -930,16 +720,17 @@ __global__ void __launch_bounds__(256) stage_f16_kernel(const uint4 *__restrict_
 template <int BITS>
 __global__ void __launch_bounds__(256) stage_tiles_kernel(const uint16_t *__restrict__ x, const int32_t *__restrict__ ws,
                                                           RouteWords L, int64_t A, int64_t K, unsigned char *__restrict__ xs) {
-    const int n_tiles = ws[3], chunks_per_row = (int)(K / 8);
+    // ws == nullptr: a dense projection's rows, in their own order (L.S rows, tile t = rows 128 t ..)
+    const int n_tiles = ws ? ws[3] : (int)((L.S + kMaxTileTokens - 1) / kMaxTileTokens), chunks_per_row = (int)(K / 8);
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        const int bucket = ws[L.t128_bucket + tile], start = ws[L.t128_start + tile];
-        const int cnt = min(kMaxTileTokens, ws[L.offsets + bucket + 1] - start);
+        const int bucket = ws ? ws[L.t128_bucket + tile] : 0, start = ws ? ws[L.t128_start + tile] : tile * kMaxTileTokens;
+        const int cnt = ws ? min(kMaxTileTokens, ws[L.offsets + bucket + 1] - start) : (int)min((int64_t)kMaxTileTokens, L.S - start);
         if (bucket >= L.E) continue;
         // a warp takes one row at a time: its 32 lanes read 512 contiguous bytes of the token's activations per step,
         // four steps in flight
         const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
         for (int n = warp; n < cnt; n += warps) {
-            const int64_t tok = ws[L.slots + start + n] / A;
+            const int64_t tok = ws ? ws[L.slots + start + n] / A : start + n;
             const uint4 *src = reinterpret_cast<const uint4 *>(x + tok * K);
             for (int k8 = lane; k8 < chunks_per_row; k8 += 128) {
                 uint4 v[4];
@@ -980,34 +771,26 @@ int check_tc(const char *fn, const void *x, const SxbQView *w, int64_t E, const 
 
 // Tensor map over the packed codes of a stacked weight, seen as bytes [rows, row_bytes]: boxes of 64 bytes x 128 rows,
 // 16-byte chunks swizzled in the 64-byte mode so that 32 threads reading 32 consecutive rows hit every bank once.
-// Rows past the end of the weight read as zero.  The encoder is a host-side computation of the driver library, found
-// through the runtime.
-using TensorMapEncode = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                     const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+// Rows past the end of the weight read as zero.
 int weight_tensor_map(const char *fn, const uint8_t *q, int64_t rows, int64_t row_bytes, CUtensorMap *map) {
-    static TensorMapEncode encode = [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &found) != cudaSuccess ||
-            found != cudaDriverEntryPointSuccess)
-            p = nullptr;
-        return reinterpret_cast<TensorMapEncode>(p);
-    }();
-    SXB_CHECK(encode != nullptr, fn, ": the driver offers no cuTensorMapEncodeTiled");
-    const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows}, strides[1] = {(cuuint64_t)row_bytes};
-    const cuuint32_t box[2] = {64u, 128u}, elem[2] = {1u, 1u};
-    const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(q), dims, strides, box, elem,
-                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    SXB_CHECK(rc == CUDA_SUCCESS, fn, ": tensor map over ", rows, " rows of ", row_bytes, " bytes refused (CUresult ", (int)rc, ")");
-    return SXB_OK;
+    return tensor_map_2d(fn, q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)row_bytes, (uint64_t)rows, (uint64_t)row_bytes, 64u, 128u,
+                         CU_TENSOR_MAP_SWIZZLE_64B, map);
 }
 
-// The status words of a launch live in the grouping workspace's header (words 5..7, zeroed by the pack).
+// Knobs of the bounded waits, set through sxb_set_wait_limit / sxb_test_skip_ring_slot and read by every later launch of
+// the calling process (plain globals: the library's callers drive it from one thread at a time).
+unsigned long long g_wait_limit_ns = kWaitLimitNs;
+int g_test_skip_slot = -1;
+
+// Status words of the launches that have no grouping workspace to hold them (dense projections, the router-logits GEMM):
+// one set per device, inside the library.
+__device__ uint32_t g_dense_status[4];
+
+// The status words of a grouped launch live in the grouping workspace's header (words 5..7, zeroed by the pack).
 template <int BITS, int MODE>
-int launch_tc(const char *fn, const TcArgs &a, int64_t G, cudaStream_t st) {
+int launch_tc(const char *fn, TcArgs a, int64_t G, cudaStream_t st) {
     const size_t smem = (size_t)kStages * kStageBytes + (size_t)kWSlots * kWSlotBytes + 1024;
+    a.wait_limit_ns = g_wait_limit_ns, a.test_skip_slot = g_test_skip_slot;
     CUtensorMap wmap;
     if (int rc = weight_tensor_map(fn, a.q, a.E * a.N, BITS == 4 ? a.K / 2 : a.K, &wmap)) return rc;
     auto go = [&](auto kern) -> int {
@@ -1024,6 +807,41 @@ int launch_tc(const char *fn, const TcArgs &a, int64_t G, cudaStream_t st) {
 }
 
 }  // namespace
+
+unsigned long long wait_limit_ns() { return g_wait_limit_ns; }
+
+int library_status_words(const char *fn, uint32_t **out) {
+    void *p = nullptr;
+    SXB_CUDA(cudaGetSymbolAddress(&p, g_dense_status), fn, ": address of the library's status words");
+    *out = static_cast<uint32_t *>(p);
+    return SXB_OK;
+}
+
+// A 2-D tiled tensor map over row-major data [outer, inner] of `elem_bytes`-byte elements.  The encoder is a host-side
+// computation of the driver library, found through the runtime (nothing links libcuda).  Out-of-range parts of a box read
+// as zero.
+int tensor_map_2d(const char *fn, const void *base, CUtensorMapDataType dtype, int elem_bytes, uint64_t inner, uint64_t outer,
+                  uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle, CUtensorMap *map) {
+    using TensorMapEncode = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                         const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                         CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static TensorMapEncode encode = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &found) != cudaSuccess ||
+            found != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<TensorMapEncode>(p);
+    }();
+    SXB_CHECK(encode != nullptr, fn, ": the driver offers no cuTensorMapEncodeTiled");
+    (void)elem_bytes;
+    const cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer}, strides[1] = {(cuuint64_t)row_stride_bytes};
+    const cuuint32_t box[2] = {box_inner, box_outer}, elem[2] = {1u, 1u};
+    const CUresult rc = encode(map, dtype, 2, const_cast<void *>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    SXB_CHECK(rc == CUDA_SUCCESS, fn, ": tensor map over ", outer, " rows of ", row_stride_bytes, " bytes refused (CUresult ", (int)rc, ")");
+    return SXB_OK;
+}
 
 template <int BITS>
 int tc_gather_grouped(const char *fn, const void *x, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes, int64_t M,
@@ -1046,7 +864,7 @@ int tc_gather_grouped(const char *fn, const void *x, const SxbQView *w, int64_t 
 
 template <int BITS>
 int tc_partial_grouped(const char *fn, const void *h, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes, int64_t M,
-                       int64_t A, float *partial, int act, int h_f16, sxb_stream_t stream) {
+                       int64_t A, float *partial, int act, int h_f16, bool partial_bf16, sxb_stream_t stream) {
     SXB_CHECK((h_f16 != 2 && h_f16 != 3) || BITS == 4, fn, ": h_f16 = ", h_f16, " (the Q4 operand's k order) with a Q8 down weight");
     SXB_CHECK(h_f16 != 4 || BITS == 8, fn, ": h_f16 = 4 (tile-blocked, natural k order) with a Q4 down weight");
     if (int rc = check_tc(fn, h, w, E, ws, ws_bytes, M, A, partial, act)) return rc;
@@ -1054,11 +872,46 @@ int tc_partial_grouped(const char *fn, const void *h, const SxbQView *w, int64_t
     TcArgs a{};
     a.x = static_cast<const uint16_t *>(h), a.q = w->q, a.scale = w->scale, a.minv = w->minv;
     a.N = N, a.K = w->K, a.A = A, a.E = E, a.ws = static_cast<const int32_t *>(ws), a.L = route_words(M, A, E);
-    a.out = partial, a.x_kind = h_f16 >= 3 ? 3 : h_f16, a.out_f16 = 0;
+    a.out = partial, a.x_kind = h_f16 >= 3 ? 3 : h_f16, a.out_f16 = 0, a.partial_bf16 = partial_bf16;
     a.status = reinterpret_cast<uint32_t *>(const_cast<void *>(ws)) + 5;
     auto st = static_cast<cudaStream_t>(stream);
     if (int rc = launch_tc<BITS, kTcPartial>(fn, a, w->G, st)) return rc;
     SXB_CHECK_LAUNCH(fn, " tcgen05 partial M=", M, " A=", A, " E=", E, " N=", N, " K=", w->K, " G=", w->G);
+    return SXB_OK;
+}
+
+// A dense projection y [M, N] = x [M, K] * dequant(W)^T on the same kernel: one group, rows in their own order, no
+// workspace, and the result written by the epilogue itself (kernels/linear_wmma.hip:69-113).
+//   out_kind 0: y BF16;  1: y FP32;  2: W = [gate | up] rows and the output is h = silu(g) * u [M, N / 2], stored as h_f16 says
+//   x_kind 0: x BF16 [M, K];  3: x tile-blocked F16 (sxb_stage_f16_tiles with a null workspace)
+// status: where a wait that ran out is recorded; null = the library's own words (sxb_check_dense_status).
+template <int BITS>
+int tc_dense(const char *fn, const void *x, const SxbQView *w, void *y, int64_t M, int x_kind, int out_kind, int h_f16,
+             uint32_t *status, sxb_stream_t stream) {
+    SXB_CHECK(x != nullptr && y != nullptr && w != nullptr, fn, ": null pointer (x=", x, ", y=", y, ")");
+    SXB_CHECK(w->q != nullptr && w->scale != nullptr && w->minv != nullptr, fn, ": null weight pointer");
+    SXB_CHECK(w->G == 32 || w->G == 64 || w->G == 128, fn, ": group size ", w->G, " unsupported (32, 64 or 128)");
+    SXB_CHECK(w->K >= 128 && w->K % 128 == 0 && w->K <= (1 << 24), fn, ": K = ", w->K, ", the tcgen05 kernels need a multiple of 128");
+    SXB_CHECK(M >= 1 && M <= kMoeMaxSlots, fn, ": M (rows of x) = ", M, ", expected 1..", kMoeMaxSlots);
+    SXB_CHECK(w->N >= 16 && w->N % 16 == 0 && w->N <= 0x7fffffff, fn, ": N = ", w->N, " must be a multiple of 16");
+    SXB_CHECK(aligned16(w->q) && aligned16(x) && aligned16(y), fn, ": codes, x and y must be 16-byte aligned");
+    SXB_CHECK(out_kind != 2 || w->N % 2 == 0, fn, ": [gate | up] rows: N = ", w->N, " must be even");
+    const int64_t out_bytes = out_kind == 2 ? M * (w->N / 2) * 2 : M * w->N * (out_kind == 1 ? 4 : 2);
+    SXB_CHECK(apart(x, M * w->K * 2, y, out_bytes), fn, ": output y [", y, ", +", out_bytes, " B) overlaps input x [", x, ", +",
+              M * w->K * 2, " B)");
+    if (status == nullptr)
+        if (int rc = library_status_words(fn, &status)) return rc;
+    TcArgs a{};
+    a.x = static_cast<const uint16_t *>(x), a.q = w->q, a.scale = w->scale, a.minv = w->minv;
+    a.N = w->N, a.K = w->K, a.A = 1, a.E = 1, a.ws = nullptr, a.L = RouteWords{};
+    a.L.S = M, a.L.E = 1;
+    a.out = y, a.x_kind = x_kind, a.out_f16 = out_kind == 2 ? h_f16 : 0, a.partial_bf16 = 0, a.dense_M = M, a.status = status;
+    auto st = static_cast<cudaStream_t>(stream);
+    int rc = out_kind == 2   ? launch_tc<BITS, kTcSwiglu>(fn, a, w->G, st)
+             : out_kind == 1 ? launch_tc<BITS, kTcPartial>(fn, a, w->G, st)
+                             : launch_tc<BITS, kTcGather>(fn, a, w->G, st);
+    if (rc) return rc;
+    SXB_CHECK_LAUNCH(fn, " tcgen05 dense M=", M, " N=", w->N, " K=", w->K, " G=", w->G, " out_kind=", out_kind);
     return SXB_OK;
 }
 
@@ -1067,25 +920,79 @@ template int tc_gather_grouped<4>(const char *, const void *, const SxbQView *, 
 template int tc_gather_grouped<8>(const char *, const void *, const SxbQView *, int64_t, const void *, size_t, int64_t, int64_t,
                                   void *, int, bool, int, sxb_stream_t);
 template int tc_partial_grouped<4>(const char *, const void *, const SxbQView *, int64_t, const void *, size_t, int64_t, int64_t,
-                                   float *, int, int, sxb_stream_t);
+                                   float *, int, int, bool, sxb_stream_t);
 template int tc_partial_grouped<8>(const char *, const void *, const SxbQView *, int64_t, const void *, size_t, int64_t, int64_t,
-                                   float *, int, int, sxb_stream_t);
+                                   float *, int, int, bool, sxb_stream_t);
+template int tc_dense<4>(const char *, const void *, const SxbQView *, void *, int64_t, int, int, int, uint32_t *, sxb_stream_t);
+template int tc_dense<8>(const char *, const void *, const SxbQView *, void *, int64_t, int, int, int, uint32_t *, sxb_stream_t);
 
 }  // namespace sxb
+
+using namespace sxb;
+
+extern "C" int sxb_set_wait_limit(uint64_t nanoseconds) {
+    SXB_CHECK(nanoseconds >= 1000ull, "set_wait_limit: ", nanoseconds, " ns is below the minimum of 1000");
+    g_wait_limit_ns = nanoseconds;
+    return SXB_OK;
+}
+extern "C" int sxb_test_skip_ring_slot(int slot) {
+    g_test_skip_slot = slot;
+    return SXB_OK;
+}
+extern "C" int sxb_check_dense_status(const char *what) {
+    uint32_t e[4] = {0, 0, 0, 0};
+    SXB_CUDA(cudaMemcpyFromSymbol(e, g_dense_status, sizeof(e)), "check_dense_status: reading the status words");
+    if (e[0] == 0) return SXB_OK;
+    const uint32_t zero[4] = {0, 0, 0, 0};
+    SXB_CUDA(cudaMemcpyToSymbol(g_dense_status, zero, sizeof(zero)), "check_dense_status: clearing the status words");
+    return tc_status_error(what, e);
+}
+
+// kernels/linear_wmma.hip:69-113 (linear_q4_wmma / linear_q8_wmma): argument rules and dtype pairs of the reference's
+// launchers (x 16-byte aligned, y apart from x, out_act == act or BF16 x -> F32 y), BF16 activations only.
+namespace {
+template <int BITS>
+int linear_wmma(const char *fn, const void *x, const SxbQView *w, void *y, int64_t M, int act, int out_act, sxb_stream_t stream) {
+    SXB_CHECK(act == SXB_ACT_BF16 || act == SXB_ACT_F16_TILED, fn, ": BF16 activations (or tile-blocked F16 ones) only, got ", act);
+    SXB_CHECK(out_act == SXB_ACT_BF16 || out_act == SXB_ACT_F32, fn, ": output dtype ", out_act, " unsupported (BF16 or F32)");
+    return tc_dense<BITS>(fn, x, w, y, M, act == SXB_ACT_F16_TILED ? 3 : 0, out_act == SXB_ACT_F32 ? 1 : 0, 0, nullptr, stream);
+}
+template <int BITS>
+int linear_wmma_swiglu(const char *fn, const void *x, const SxbQView *w, void *h, int64_t M, int act, int h_f16, sxb_stream_t stream) {
+    SXB_CHECK(act == SXB_ACT_BF16 || act == SXB_ACT_F16_TILED, fn, ": BF16 activations (or tile-blocked F16 ones) only, got ", act);
+    SXB_CHECK(h_f16 >= 0 && h_f16 <= 4, fn, ": h_f16 = ", h_f16, ", expected 0..4");
+    return tc_dense<BITS>(fn, x, w, h, M, act == SXB_ACT_F16_TILED ? 3 : 0, 2, h_f16, nullptr, stream);
+}
+}  // namespace
+extern "C" int sxb_linear_q4_wmma(const void *x, const SxbQView *w, void *y, int64_t M, int act, int out_act, sxb_stream_t stream) {
+    return linear_wmma<4>("linear_q4_wmma", x, w, y, M, act, out_act, stream);
+}
+extern "C" int sxb_linear_q8_wmma(const void *x, const SxbQView *w, void *y, int64_t M, int act, int out_act, sxb_stream_t stream) {
+    return linear_wmma<8>("linear_q8_wmma", x, w, y, M, act, out_act, stream);
+}
+extern "C" int sxb_linear_q4_wmma_swiglu(const void *x, const SxbQView *w, void *h, int64_t M, int act, int h_f16, sxb_stream_t stream) {
+    return linear_wmma_swiglu<4>("linear_q4_wmma_swiglu", x, w, h, M, act, h_f16, stream);
+}
+extern "C" int sxb_linear_q8_wmma_swiglu(const void *x, const SxbQView *w, void *h, int64_t M, int act, int h_f16, sxb_stream_t stream) {
+    return linear_wmma_swiglu<8>("linear_q8_wmma_swiglu", x, w, h, M, act, h_f16, stream);
+}
 
 extern "C" int sxb_stage_f16_tiles(const void *x, const void *ws, size_t ws_bytes, int64_t M, int64_t A, int64_t E, int64_t K,
                                    int bits, void *xs, sxb_stream_t stream) {
     using namespace sxb;
-    SXB_CHECK(x != nullptr && ws != nullptr && xs != nullptr, "stage_f16_tiles: null pointer (x=", x, ", ws=", ws, ", xs=", xs, ")");
+    SXB_CHECK(x != nullptr && xs != nullptr, "stage_f16_tiles: null pointer (x=", x, ", xs=", xs, ")");
     SXB_CHECK(M >= 1 && A >= 1 && A <= 64 && E >= 1 && E <= kMoeMaxExperts && M * A <= kMoeMaxSlots, "stage_f16_tiles: M = ", M,
               ", A = ", A, ", E = ", E);
+    SXB_CHECK(ws != nullptr || (A == 1 && E == 1), "stage_f16_tiles: a null workspace means a dense projection's rows (A = E = 1), got A = ",
+              A, ", E = ", E);
     SXB_CHECK(K >= 64 && K % 64 == 0, "stage_f16_tiles: K = ", K, " must be a multiple of 64 (one 128-byte line per k-block)");
     SXB_CHECK(bits == 4 || bits == 8, "stage_f16_tiles: k order of a ", bits, "-bit operand unsupported (4 or 8)");
-    SXB_CHECK(ws_bytes >= (size_t)route_words(M, A, E).total * 4, "stage_f16_tiles: workspace of ", ws_bytes, " bytes, needs ",
-              route_words(M, A, E).total * 4);
+    SXB_CHECK(ws == nullptr || ws_bytes >= (size_t)route_words(M, A, E).total * 4, "stage_f16_tiles: workspace of ", ws_bytes,
+              " bytes, needs ", route_words(M, A, E).total * 4);
     SXB_CHECK(aligned16(x) && aligned16(xs), "stage_f16_tiles: x and xs must be 16-byte aligned");
-    const RouteWords L = route_words(M, A, E);
-    const unsigned blocks = (unsigned)std::min<int64_t>(L.T128max, (int64_t)sm_count() * 4);
+    RouteWords L = route_words(M, A, E);
+    const int64_t tiles = ws ? L.T128max : (M + kMaxTileTokens - 1) / kMaxTileTokens;
+    const unsigned blocks = (unsigned)std::min<int64_t>(tiles, (int64_t)sm_count() * 4);
     auto st = static_cast<cudaStream_t>(stream);
     if (bits == 4)
         stage_tiles_kernel<4><<<blocks, 256, 0, st>>>((const uint16_t *)x, (const int32_t *)ws, L, A, K, (unsigned char *)xs);
@@ -1094,31 +1001,6 @@ extern "C" int sxb_stage_f16_tiles(const void *x, const void *ws, size_t ws_byte
     SXB_CHECK_LAUNCH("stage_f16_tiles M=", M, " A=", A, " K=", K, " bits=", bits);
     return SXB_OK;
 }
-
-#if defined(SXB_TC_PROF) || defined(SXB_TC_TRACE)
-extern "C" __attribute__((visibility("default"))) int sxb_debug_tc_stamp(long long *out) {
-    cudaMemcpyFromSymbol(out, g_tc_stamp, sizeof(long long) * 64 * 8);
-    return 0;
-}
-extern "C" __attribute__((visibility("default"))) int sxb_debug_tc_trace8(long long *out) {
-    cudaMemcpyFromSymbol(out, g_tc_trace8, sizeof(long long) * 8 * 64);
-    return 0;
-}
-extern "C" __attribute__((visibility("default"))) int sxb_debug_tc_trace(long long *out) {
-    cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(long long) * 4 * 64 * 2);
-    return 0;
-}
-extern "C" __attribute__((visibility("default"))) int sxb_debug_tc_prof(unsigned long long *out, int reset) {
-    cudaMemcpyFromSymbol(out, g_tc_prof, sizeof(unsigned long long) * 32);
-    if (reset) {
-        unsigned long long z[32] = {};
-        cudaMemcpyToSymbol(g_tc_prof, z, sizeof(z));
-        static long long zt[4 * 64 * 2] = {};
-        cudaMemcpyToSymbol(g_tc_trace, zt, sizeof(zt));
-    }
-    return 0;
-}
-#endif
 
 extern "C" int sxb_stage_f16(const void *x, int64_t M, int64_t K, int bits, void *xh, sxb_stream_t stream) {
     using namespace sxb;

@@ -3,15 +3,10 @@
 // always-on shared expert folded into the combine.  Everything goes to the caller's stream through the library's own
 // entry points; nothing is allocated, nothing synchronizes.
 
-#include "common.cuh"
+#include "experts.cuh"
 
 namespace sxb {
 namespace {
-
-__global__ void fill_shared_routes(int32_t *ids, float *coef, int64_t n) {
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) ids[i] = 0, coef[i] = 1.f;
-}
 
 int linear_dense(int bits, const void *x, const SxbQView *w, void *y, int64_t M, int act, int out_act, sxb_stream_t st) {
     return bits == 4 ? sxb_linear_q4(x, w, y, M, act, out_act, st) : sxb_linear_q8(x, w, y, M, act, out_act, st);
@@ -55,7 +50,8 @@ extern "C" int sxb_moe_layer(const SxbMoeLayerArgs *a, sxb_stream_t stream) {
     const bool shared = a->shared_gate_up != nullptr;
     SXB_CHECK(shared == (a->shared_down != nullptr), fn, ": the shared expert needs both of its weights");
     SXB_CHECK(!(shared && ep), fn, ": the shared expert is not sharded: run it on one rank, outside the expert-parallel call");
-    SXB_CHECK(a->x != nullptr && a->logits != nullptr && a->y != nullptr && a->ids != nullptr && a->coef != nullptr &&
+    SXB_CHECK(a->logits != nullptr || !shared, fn, ": the shared expert's gate is a column of the logits: logits must not be null");
+    SXB_CHECK(a->x != nullptr && a->y != nullptr && a->ids != nullptr && a->coef != nullptr &&
                   a->ws != nullptr && a->h != nullptr && a->partial != nullptr && a->router_err != nullptr && a->expert_err != nullptr,
               fn, ": null buffer");
     SXB_CHECK(a->out_act == SXB_ACT_BF16 || a->out_act == SXB_ACT_F32, fn, ": output dtype ", a->out_act);
@@ -67,10 +63,20 @@ extern "C" int sxb_moe_layer(const SxbMoeLayerArgs *a, sxb_stream_t stream) {
     SXB_CHECK(!tc || a->xs != nullptr, fn, ": the tcgen05 path needs the tile-blocked activation buffer xs (M * A * d F16)");
     auto st = static_cast<cudaStream_t>(stream);
 
-    // router (kernels/moe_router.hpp:38-40): top-k of the first E_total logits; a shared expert's gate is column E_total
-    if (int rc = sxb_moe_router(a->logits, a->logits_ld, M, a->E_total, A, nullptr, 1, 0, a->ids, a->coef, SXB_ACT_F32,
-                                a->router_err, stream))
-        return rc;
+    // router (kernels/moe_router.hpp:38-40): top-k of the first E_total logits; a shared expert's gate is column E_total.
+    // logits == NULL: ids and coef already hold the routes (an expert-parallel rank receives them from the tokens' owners)
+    // A small batch (decode) routes and packs in one launch.
+    bool packed = false;
+    if (a->logits != nullptr && !ep && M * A <= 2048) {
+        if (int rc = sxb_moe_route_small(a->logits, a->logits_ld, M, a->E_total, A, 0, E, a->ids, a->coef, a->ws, a->ws_bytes,
+                                         a->router_err, a->expert_err, stream))
+            return rc;
+        packed = true;
+    } else if (a->logits != nullptr) {
+        if (int rc = sxb_moe_router(a->logits, a->logits_ld, M, a->E_total, A, nullptr, 1, 0, a->ids, a->coef, SXB_ACT_F32,
+                                    a->router_err, stream))
+            return rc;
+    }
 
     // the shared expert as dense projections (runtime/qwen4exp.cpp:3163-3168), in y's dtype
     if (shared) {
@@ -81,25 +87,26 @@ extern "C" int sxb_moe_layer(const SxbMoeLayerArgs *a, sxb_stream_t stream) {
             if (int rc = sxb_swiglu(a->sh_gu, a->sh_h, M, I, SXB_ACT_BF16, stream)) return rc;
             if (int rc = linear_dense(a->shared_bits, a->sh_h, a->shared_down, a->sh_y, M, SXB_ACT_BF16, a->out_act, stream)) return rc;
         } else {
-            // the same grouped kernels with one "expert" that every token is routed to
-            SXB_CHECK(a->sh_ids != nullptr && a->sh_coef != nullptr && a->sh_ws != nullptr && a->sh_partial != nullptr && a->sh_xs != nullptr,
-                      fn, ": null shared-expert buffer for the tcgen05 path");
-            fill_shared_routes<<<(unsigned)((M + 255) / 256), 256, 0, st>>>(a->sh_ids, a->sh_coef, M);
-            SXB_CHECK_LAUNCH(fn, " shared routes M=", M);
-            if (int rc = sxb_moe_group_routes(a->sh_ids, M, 1, 1, a->sh_ws, a->sh_ws_bytes, a->expert_err, stream)) return rc;
-            if (int rc = sxb_stage_f16_tiles(a->x, a->sh_ws, a->sh_ws_bytes, M, 1, 1, d, a->shared_bits, a->sh_xs, stream)) return rc;
+            // dense projections on the tcgen05 kernel (kernels/linear_wmma.hip:69-113), SwiGLU fused into the first;
+            // a wait that ran out is recorded in the routed experts' workspace header, like theirs
+            SXB_CHECK(a->sh_xs != nullptr, fn, ": null shared-expert buffer sh_xs for the tcgen05 path");
+            uint32_t *status = reinterpret_cast<uint32_t *>(a->ws) + 5;
+            if (int rc = sxb_stage_f16_tiles(a->x, nullptr, 0, M, 1, 1, d, a->shared_bits, a->sh_xs, stream)) return rc;
             const int hf = a->shared_bits == 4 ? 3 : 4;
-            if (int rc = gather_swiglu(a->shared_bits, a->sh_xs, a->shared_gate_up, 1, a->sh_ws, a->sh_ws_bytes, M, 1, a->sh_h,
-                                       SXB_ACT_F16_TILED, math, stream, hf))
-                return rc;
-            if (int rc = combine(a->shared_bits, a->sh_h, a->shared_down, 1, a->sh_ids, a->sh_coef, a->sh_ws, a->sh_ws_bytes,
-                                 a->sh_partial, M, 1, a->sh_y, a->out_act, math, stream, nullptr, hf))
-                return rc;
+            const int of = a->out_act == SXB_ACT_F32 ? 1 : 0;
+            int rc = a->shared_bits == 4
+                         ? tc_dense<4>(fn, a->sh_xs, a->shared_gate_up, a->sh_h, M, 3, 2, hf, status, stream)
+                         : tc_dense<8>(fn, a->sh_xs, a->shared_gate_up, a->sh_h, M, 3, 2, hf, status, stream);
+            if (rc) return rc;
+            rc = a->shared_bits == 4 ? tc_dense<4>(fn, a->sh_h, a->shared_down, a->sh_y, M, 3, of, 0, status, stream)
+                                     : tc_dense<8>(fn, a->sh_h, a->shared_down, a->sh_y, M, 3, of, 0, status, stream);
+            if (rc) return rc;
         }
     }
 
     // pack (kernels/moe_grouped.hpp:53-54)
-    if (ep) {
+    if (packed) {
+    } else if (ep) {
         if (int rc = sxb_moe_group_routes_ep(a->ids, M, A, a->E_total, a->e_lo, E, a->ws, a->ws_bytes, a->expert_err, stream)) return rc;
     } else {
         if (int rc = sxb_moe_group_routes(a->ids, M, A, E, a->ws, a->ws_bytes, a->expert_err, stream)) return rc;

@@ -14,9 +14,13 @@
 // Limits and rules
 //   * M * A * N <= kNoAllocFloats (4 Mi floats = 16 MiB; e.g. 100 tokens x 10 slots x 4096 columns).  Larger calls are
 //     refused with an error; use the caller-scratch entry point for them.
-//   * Every GPU that loads the library carries the 16 MiB until the process exits.
-//   * The first call on a device performs the address lookup (a blocking runtime call): make it before any stream
-//     capture begins.
+//   * The 16 MiB are taken on a device when the CUDA runtime loads this part of the library there, and held until the
+//     process exits.  With the runtime's default lazy loading that moment is the FIRST CALL of this entry point on the
+//     device (which also loads the combine's kernels): a host that plans its device memory to the last byte makes one
+//     small call per device BEFORE it sizes that plan, or the first call of a decode step can fail for lack of memory.
+//   * That first call also performs the address lookup (a blocking runtime call): make it before any stream capture.
+//   * The looked-up address is kept per device ordinal for the life of the process; cudaDeviceReset, or driving the
+//     same device through another context, invalidates it.
 //   * All calls on a device share the one array and it keeps the last call's contents.  Nothing in it needs to start
 //     at zero - every word a call reads was written by that same call - but two calls that overlap on the GPU (two
 //     streams, or two host threads) race on it.  Serialize them.
@@ -61,22 +65,13 @@ extern "C" int sxb_linear_q4_experts_combine_grouped_noalloc(const void *h, cons
                                                              int64_t A, void *y, int act, int out_act, int math,
                                                              sxb_stream_t stream, const SxbMoeSharedAdd *shared, int h_f16) {
     const char *fn = "linear_q4_experts_combine_grouped_noalloc";
-    SXB_CHECK(math_ok(math), fn, ": unknown math ", math);
-    SXB_CHECK(h_f16 >= 0 && h_f16 <= 4, fn, ": h_f16 = ", h_f16, ", expected 0..4");
-    SXB_CHECK(!h_f16 || (act == SXB_ACT_BF16 && math_is_f16(math)), fn, ": F16 h needs BF16 activations and a WMMA_F16 math");
-    SXB_CHECK(h != nullptr && w != nullptr && ids != nullptr && coef != nullptr && y != nullptr && ws != nullptr, fn,
-              ": null pointer (h=", h, ", ids=", (const void *)ids, ", coef=", (const void *)coef, ", y=", y, ", ws=", ws, ")");
-    SXB_CHECK(E >= 1 && w->N >= 1 && w->N % E == 0, fn, ": weight has ", w->N, " rows for E = ", E, " experts");
+    SXB_CHECK(w != nullptr && E >= 1 && w->N >= 1 && w->N % E == 0, fn, ": weight has ", w ? w->N : 0, " rows for E = ", E, " experts");
     SXB_CHECK(M >= 1 && A >= 1, fn, ": M = ", M, ", A = ", A, ", both must be >= 1");
     const int64_t N = w->N / E;
     SXB_CHECK(M * A <= kNoAllocFloats / N, fn, ": M * A * N = ", M, " * ", A, " * ", N, " per-slot dots exceed the built-in scratch of ",
               kNoAllocFloats, " floats (16 MiB); call linear_q4_experts_combine_grouped with caller-owned scratch instead");
-    SXB_CHECK(act_ok(out_act) && (out_act == act || out_act == SXB_ACT_F32), fn, ": output dtype ", act_name(out_act),
-              " with activations ", act_name(act), " unsupported (same dtype, or F32)");
     float *partial = nullptr;
     if (int rc = partial_scratch(&partial)) return rc;
-    int rc = math_is_f16(math) ? tc_partial_grouped<4>(fn, h, w, E, ws, ws_bytes, M, A, partial, act, h_f16, stream)
-                               : stream_partial_grouped<4>(fn, h, w, E, ws, ws_bytes, M, A, partial, act, stream);
-    if (rc) return rc;
-    return combine_reduce(fn, partial, ids, coef, M, A, E, 0, E, N, y, out_act, shared, out_act, stream);
+    // from here on the caller-scratch entry point's own code: the same checks (pointers, dtypes, overlaps), the same kernels
+    return combine_grouped<4>(fn, h, w, E, ids, coef, ws, ws_bytes, partial, M, A, y, act, out_act, math, stream, shared, h_f16, E, 0);
 }

@@ -11,6 +11,7 @@
 //   bases / tile lists, and a scatter in which every warp places its own segment in order.
 
 #include "route_pack.cuh"
+#include "router_token.cuh"
 
 namespace sxb {
 namespace {
@@ -114,9 +115,9 @@ __device__ inline void warp_place(const int32_t *ids, int s0, int s1, int e_lo, 
     }
 }
 
-__global__ void __launch_bounds__(kPackThreads)
-    pack_small_kernel(const int32_t *__restrict__ ids, RouteWords L, int E_total, int e_lo, bool ep, int32_t *ws,
-                      uint32_t *err) {
+// The whole pack of a small batch by one CTA of kPackThreads threads.
+__device__ void pack_small_body(const int32_t *__restrict__ ids, const RouteWords &L, int E_total, int e_lo, bool ep, int32_t *ws,
+                                uint32_t *err) {
     __shared__ int cnt[kPackThreads], scanbuf[33], tile_first[2 * 1025];
     __shared__ int first_bad;
     const int t = threadIdx.x, S = (int)L.S, E = (int)L.E;
@@ -136,6 +137,28 @@ __global__ void __launch_bounds__(kPackThreads)
     if (t <= E) cnt[t] = ws[L.offsets + t];  // cnt becomes the bucket cursors
     __syncthreads();
     if (t < 32) warp_place(ids, 0, S, e_lo, E, cnt, ws + L.slots);
+}
+
+__global__ void __launch_bounds__(kPackThreads)
+    pack_small_kernel(const int32_t *__restrict__ ids, RouteWords L, int E_total, int e_lo, bool ep, int32_t *ws,
+                      uint32_t *err) {
+    pack_small_body(ids, L, E_total, e_lo, ep, ws, err);
+}
+
+// Router and pack of a small batch (decode: a few dozen tokens) as ONE launch of one CTA: every warp routes tokens
+// (route_token), the CTA then packs the slots it has just written.  Same words out as moe_router + moe_group_routes.
+template <int NV>
+__global__ void __launch_bounds__(kPackThreads)
+    route_small_kernel(const float *__restrict__ logits, int64_t ld, int M, int E_total, int k, int32_t *__restrict__ ids,
+                       float *__restrict__ coef, RouteWords L, int e_lo, bool ep, int32_t *ws, uint32_t *router_err,
+                       uint32_t *expert_err) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int m = warp; m < M; m += kPackThreads / 32)
+        route_token<float, NV>(logits + (int64_t)m * ld, lane, m, E_total, k, nullptr, 1, 0, ids + (int64_t)m * k,
+                               coef + (int64_t)m * k, k, router_err);
+    __threadfence_block();
+    __syncthreads();  // the ids written above are read by other threads of this CTA below
+    pack_small_body(ids, L, E_total, e_lo, ep, ws, expert_err);
 }
 
 // Large S, launch 1: histogram of every 1024-slot segment (one warp each) into scratch [nseg][E + 1], and the
@@ -252,6 +275,23 @@ RouteWords route_words(int64_t M, int64_t A, int64_t E) {
 
 using namespace sxb;
 
+namespace sxb {
+// {2, work item, role}: the record of a device-side wait of the tcgen05 kernels that ran out (grouped_tc.cu).
+int tc_status_error(const char *what, const uint32_t e[3]) {
+    static const char *roles[] = {"an unknown role",
+                                  "a weight producer waiting for a free operand stage",
+                                  "an MMA warp waiting for free accumulators",
+                                  "an MMA warp waiting for a filled operand stage",
+                                  "the epilogue waiting for the accumulators",
+                                  "the activation copy thread waiting for a free operand stage",
+                                  "the weight-code copy thread waiting for a free ring slot",
+                                  "a weight producer waiting for its packed codes"};
+    last_error() = cat(what ? what : "", ": a tcgen05 kernel gave up a wait at work item ", e[1], " (",
+                       roles[e[2] >= 1 && e[2] <= 7 ? e[2] : 0], "); its outputs are incomplete");
+    return SXB_ERR_DATA;
+}
+}  // namespace sxb
+
 extern "C" {
 
 size_t sxb_moe_route_workspace_bytes(int64_t M, int64_t A, int64_t E) {
@@ -277,11 +317,8 @@ int sxb_check_grouped_status(const void *ws, const char *what) {
     int32_t head[8];
     SXB_CUDA(cudaMemcpy(head, ws, sizeof(head), cudaMemcpyDeviceToHost), "reading the workspace header for ", what);
     if (head[5] == 0) return SXB_OK;
-    static const char *roles[] = {"?", "a producer waiting for a free stage", "the MMA warp waiting for free accumulators",
-                                  "the MMA warp waiting for a filled stage", "the epilogue waiting for the accumulators"};
-    last_error() = cat(what, ": a tcgen05 grouped kernel gave up a wait at work item ", head[6], " (",
-                       roles[head[7] >= 1 && head[7] <= 4 ? head[7] : 0], "); its outputs are incomplete");
-    return SXB_ERR_DATA;
+    const uint32_t e[3] = {(uint32_t)head[5], (uint32_t)head[6], (uint32_t)head[7]};
+    return tc_status_error(what, e);
 }
 
 int sxb_moe_group_routes(const int32_t *ids, int64_t M, int64_t A, int64_t E, void *ws, size_t ws_bytes, uint32_t *err,
@@ -292,6 +329,34 @@ int sxb_moe_group_routes(const int32_t *ids, int64_t M, int64_t A, int64_t E, vo
 int sxb_moe_group_routes_ep(const int32_t *ids, int64_t M, int64_t A, int64_t E_total, int64_t e_lo, int64_t E_local,
                             void *ws, size_t ws_bytes, uint32_t *err, sxb_stream_t stream) {
     return group_routes("moe_group_routes_ep", ids, M, A, E_total, e_lo, E_local, true, ws, ws_bytes, err, stream);
+}
+
+int sxb_moe_route_small(const float *logits, int64_t ld, int64_t M, int64_t E_total, int64_t k, int64_t e_lo, int64_t E_local,
+                        int32_t *ids, float *coef, void *ws, size_t ws_bytes, uint32_t *router_err, uint32_t *expert_err,
+                        sxb_stream_t stream) {
+    const char *fn = "moe_route_small";
+    SXB_CHECK(logits != nullptr && ids != nullptr && coef != nullptr && ws != nullptr && router_err != nullptr && expert_err != nullptr,
+              fn, ": null pointer");
+    SXB_CHECK(E_total >= 1 && E_total <= 1024 && k >= 1 && k <= E_total && k <= 32 && ld >= E_total, fn, ": E = ", E_total, ", k = ", k,
+              ", ld = ", ld, " (E 1..1024, k 1..min(E, 32), ld >= E)");
+    SXB_CHECK(M >= 1 && M * k <= kSmallSlots, fn, ": M * k = ", M * k, " slots, this one-CTA form takes at most ", kSmallSlots,
+              " (use moe_router + moe_group_routes)");
+    SXB_CHECK(E_local >= 1 && E_local <= kMoeMaxExperts && e_lo >= 0 && e_lo + E_local <= E_total, fn, ": experts [", e_lo, ", ",
+              e_lo + E_local, ") outside [0, ", E_total, ")");
+    const bool ep = E_local != E_total;
+    const RouteWords L = route_words(M, k, E_local);
+    SXB_CHECK(ws_bytes >= (size_t)L.total * 4, fn, ": workspace of ", ws_bytes, " bytes, needs ", L.total * 4);
+    auto st = static_cast<cudaStream_t>(stream);
+    auto *w = static_cast<int32_t *>(ws);
+#define SXB_ROUTE_SMALL(NV) \
+    route_small_kernel<NV><<<1, kPackThreads, 0, st>>>(logits, ld, (int)M, (int)E_total, (int)k, ids, coef, L, (int)e_lo, ep, w, router_err, expert_err)
+    if (E_total <= 128) SXB_ROUTE_SMALL(4);
+    else if (E_total <= 256) SXB_ROUTE_SMALL(8);
+    else if (E_total <= 512) SXB_ROUTE_SMALL(16);
+    else SXB_ROUTE_SMALL(32);
+#undef SXB_ROUTE_SMALL
+    SXB_CHECK_LAUNCH(fn, " M=", M, " E=", E_total, " k=", k);
+    return SXB_OK;
 }
 
 }  // extern "C"

@@ -8,9 +8,8 @@
 // lanes that hold it - instead of five shuffle/compare steps on (value, index) pairs.  Only the lane that owned the
 // pick rescans its registers.
 
-#include "common.cuh"
+#include "router_token.cuh"
 
-#include <climits>
 #include <mutex>
 
 namespace sxb {
@@ -66,13 +65,6 @@ constexpr int64_t kMaxExperts = 1024;
 constexpr int64_t kMaxTopK = 32;
 constexpr int64_t kMaxTokens = 0x7fffffff;
 
-// Order-preserving map float -> uint32 (finite values and infinities): a < b  <=>  key(a) < key(b).
-// -0 is folded onto +0 first, so the two compare equal as they do as floats.
-__device__ inline uint32_t order_key(float v) {
-    const uint32_t u = __float_as_uint(v + 0.0f);
-    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-}
-
 template <typename T, int NV>
 __global__ void __launch_bounds__(kLanes *kTokensPerCta)
     router_kernel(const T *__restrict__ logits, int64_t ld, int64_t M, int E, int k, const T *__restrict__ shared,
@@ -81,77 +73,7 @@ __global__ void __launch_bounds__(kLanes *kTokensPerCta)
     const int lane = threadIdx.x % kLanes;
     const int64_t m = (int64_t)blockIdx.x * kTokensPerCta + threadIdx.x / kLanes;
     if (m >= M) return;  // whole warps leave together
-    const T *row = logits + m * ld;
-
-    uint32_t key[NV];
-    float val[NV];
-    int bad = INT_MAX;  // smallest index of a non-finite logit (E = the shared gate)
-#pragma unroll
-    for (int j = 0; j < NV; ++j) {
-        const int e = lane + j * kLanes;
-        const float x = e < E ? load_as_f32(row, e) : -INFINITY;
-        val[j] = x;
-        key[j] = e < E ? order_key(x) : 0u;  // 0 sorts below every real key (key(-inf) = 0x007fffff)
-        if (e < E && !isfinite(x)) bad = min(bad, e);
-    }
-    float sl = 0.f;
-    if (shared != nullptr) {
-        sl = load_as_f32(shared, m * shared_ld);
-        if (!isfinite(sl)) bad = min(bad, E);
-    }
-    bad = __reduce_min_sync(0xffffffffu, bad);
-    int32_t *id_row = ids + m * A;
-    float *coef_row = coef + m * A;
-    if (bad != INT_MAX) {
-        if (lane == 0) raise_error(err, (uint32_t)m, (uint32_t)bad);
-        for (int a = lane; a < A; a += kLanes) {
-            id_row[a] = -1;
-            coef_row[a] = qnan_f32();
-        }
-        return;
-    }
-
-    // This lane's best: ascending scan with a strict > keeps the lower index on a tie.
-    uint32_t lk;
-    int li, lj;
-    auto lane_best = [&] {
-        lk = 0u, li = INT_MAX, lj = -1;
-#pragma unroll
-        for (int j = 0; j < NV; ++j)
-            if (key[j] > lk) lk = key[j], li = lane + j * kLanes, lj = j;
-    };
-    lane_best();
-    float my_v = 0.f, top = 0.f;
-    int my_i = -1;
-    for (int r = 0; r < k; ++r) {
-        const uint32_t best_key = __reduce_max_sync(0xffffffffu, lk);
-        const int best_i = __reduce_min_sync(0xffffffffu, lk == best_key ? li : INT_MAX);
-        const int owner = best_i % kLanes;
-        float bv = 0.f;
-        if (lane == owner) {
-#pragma unroll
-            for (int j = 0; j < NV; ++j)
-                if (j == lj) bv = val[j], key[j] = 0u;  // static register indices only
-            lane_best();
-        }
-        bv = __shfl_sync(0xffffffffu, bv, owner);
-        if (r == 0) top = bv;
-        if (lane == r) my_v = bv, my_i = best_i;
-    }
-
-    // Softmax over the k picks; the sum is the reference's 32-lane xor butterfly, so equal exps give equal sums.
-    const float ex = lane < k ? expf(my_v - top) : 0.f;
-    float sum = ex;
-#pragma unroll
-    for (int off = kLanes / 2; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-    if (lane < k) {
-        id_row[lane] = my_i;
-        coef_row[lane] = ex / sum;
-    }
-    if (shared != nullptr && lane == 0) {
-        id_row[k] = shared_id;
-        coef_row[k] = 1.0f / (1.0f + expf(-sl));
-    }
+    route_token<T, NV>(logits + m * ld, lane, m, E, k, shared, shared_ld, shared_id, ids + m * A, coef + m * A, A, err);
 }
 
 constexpr int kAddThreads = 256;

@@ -509,7 +509,8 @@ __global__ void __launch_bounds__(kThreads, 2) stream_kernel(const StreamArgs a)
 // Four columns a thread.  A token with an id outside [0, E_total) gets a NaN row.  Slots of experts outside
 // [e_lo, e_lo + E_local) - other ranks' in expert-parallel runs - are skipped.  SH folds the shared expert's gated add:
 // y = stored(sum) + sigmoid(gate) * s, the arithmetic of moe_shared_add on the stored y.
-template <typename TOUT, typename TS, bool SH>
+// PBF16: the per-slot dots are BF16 bits, N * 2 bytes a slot (kernels/moe_grouped.hip:47-57), read from the same buffer.
+template <typename TOUT, typename TS, bool SH, bool PBF16>
 __global__ void __launch_bounds__(256)
     combine_reduce_kernel(const float *__restrict__ partial, const int32_t *__restrict__ ids, const float *__restrict__ coef,
                           int64_t M, int64_t A, int64_t E_total, int64_t e_lo, int64_t E_local, int64_t N,
@@ -525,7 +526,14 @@ __global__ void __launch_bounds__(256)
         ok = ok && id >= 0 && id < E_total;
         if (id < e_lo || id >= e_lo + E_local) continue;
         const float cf = coef[m * A + k];
-        const float4 p = *reinterpret_cast<const float4 *>(partial + (m * A + k) * N + n);
+        float4 p;
+        if constexpr (PBF16) {
+            const uint2 b = *reinterpret_cast<const uint2 *>(reinterpret_cast<const uint16_t *>(partial) + (m * A + k) * N + n);
+            p.x = __uint_as_float(b.x << 16), p.y = __uint_as_float(b.x & 0xffff0000u);
+            p.z = __uint_as_float(b.y << 16), p.w = __uint_as_float(b.y & 0xffff0000u);
+        } else {
+            p = *reinterpret_cast<const float4 *>(partial + (m * A + k) * N + n);
+        }
         v[0] = fmaf(cf, p.x, v[0]), v[1] = fmaf(cf, p.y, v[1]), v[2] = fmaf(cf, p.z, v[2]), v[3] = fmaf(cf, p.w, v[3]);
     }
     if (!ok) v[0] = v[1] = v[2] = v[3] = qnan_f32();
@@ -599,9 +607,13 @@ int linear_impl(const char *fn, const void *x, const SxbQView *w, void *y, int64
     if (int rc = check_view(fn, w)) return rc;
     SXB_CHECK(M >= 1 && M <= 65535ll * 8, fn, ": M (rows of x) = ", M, ", expected 1..", 65535ll * 8);
     SXB_CHECK(aligned16(x), fn, ": x ", x, " must be 16-byte aligned for vector loads");
-    if (int rc = need_bf16(fn, act)) return rc;
-    SXB_CHECK(out_act == act || out_act == SXB_ACT_F32, fn, ": output dtype ", act_name(out_act), " with input ",
+    SXB_CHECK(act_ok(act) && (out_act == act || out_act == SXB_ACT_F32), fn, ": output dtype ", act_name(out_act), " with input ",
               act_name(act), " unsupported (same dtype, or BF16 -> F32)");
+    if (act == SXB_ACT_F32) {
+        SXB_CHECK(apart(x, M * w->K * 4, y, M * w->N * 4), fn, ": output y overlaps input x");
+        return f32_gather<BITS>(fn, x, w, 1, nullptr, nullptr, M, 1, y, false, 1, nullptr, stream);
+    }
+    if (int rc = need_bf16(fn, act)) return rc;
     SXB_CHECK(apart(x, M * w->K * 2, y, M * w->N * act_bytes(out_act)), fn, ": output y [", y, ", +",
               M * w->N * act_bytes(out_act), " B) overlaps input x [", x, ", +", M * w->K * 2, " B)");
     StreamArgs a{};
@@ -632,6 +644,10 @@ int experts_slots_impl(const char *fn, const void *x, const SxbQView *w, int64_t
     if (int rc = check_experts(fn, x, w, E, M, A, y)) return rc;
     SXB_CHECK(ids != nullptr && err != nullptr, fn, ": null pointer (ids=", (const void *)ids, ", err=", (const void *)err, ")");
     SXB_CHECK(M >= 1 && M <= 65535, fn, ": M (tokens) = ", M, ", expected 1..65535");
+    if (act == SXB_ACT_F32) {
+        SXB_CHECK(apart(x, M * w->K * 4, y, M * A * (swiglu ? w->N / E / 2 : w->N / E) * 4), fn, ": output overlaps input");
+        return f32_gather<BITS>(fn, x, w, E, ids, nullptr, M, A, y, swiglu, (int)A, err, stream);
+    }
     if (int rc = need_bf16(fn, act)) return rc;
     const int64_t N = w->N / E;
     SXB_CHECK(!swiglu || N % 2 == 0, fn, ": SwiGLU gather needs an even row count per expert ([gate | up]), got ", N);
@@ -667,6 +683,10 @@ template <int BITS>
 int stream_gather_grouped(const char *fn, const void *x, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes,
                           int64_t M, int64_t A, void *y, int act, bool swiglu, sxb_stream_t stream) {
     if (int rc = check_grouped(fn, x, w, E, M, A, ws, ws_bytes, y)) return rc;
+    if (act == SXB_ACT_F32) {
+        SXB_CHECK(apart(x, M * w->K * 4, y, M * A * (swiglu ? w->N / E / 2 : w->N / E) * 4), fn, ": output overlaps input x");
+        return f32_gather<BITS>(fn, x, w, E, nullptr, ws, M, A, y, swiglu, (int)A, nullptr, stream);
+    }
     if (int rc = need_bf16(fn, act)) return rc;
     const int64_t N = w->N / E;
     SXB_CHECK(!swiglu || N % 2 == 0, fn, ": gate_up has ", N, " rows an expert, expected an even count (gate rows then up rows)");
@@ -688,6 +708,7 @@ template <int BITS>
 int stream_partial_grouped(const char *fn, const void *h, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes,
                            int64_t M, int64_t A, float *partial, int act, sxb_stream_t stream) {
     if (int rc = check_grouped(fn, h, w, E, M, A, ws, ws_bytes, partial)) return rc;
+    if (act == SXB_ACT_F32) return f32_gather<BITS>(fn, h, w, E, nullptr, ws, M, A, partial, false, 1, nullptr, stream);
     if (int rc = need_bf16(fn, act)) return rc;
     const int64_t N = w->N / E;
     StreamArgs a{};
@@ -710,9 +731,13 @@ int stream_combine_slots(const char *fn, const void *h, const SxbQView *w, int64
     if (int rc = check_experts(fn, h, w, E, M, A, y)) return rc;
     SXB_CHECK(ids != nullptr && err != nullptr, fn, ": null pointer (ids=", (const void *)ids, ", err=", (const void *)err, ")");
     SXB_CHECK(M >= 1 && M <= 65535, fn, ": M (tokens) = ", M, ", expected 1..65535");
-    if (int rc = need_bf16(fn, act)) return rc;
-    SXB_CHECK(out_act == act || out_act == SXB_ACT_F32, fn, ": output dtype ", act_name(out_act), " with activations ",
+    SXB_CHECK(act_ok(act) && (out_act == act || out_act == SXB_ACT_F32), fn, ": output dtype ", act_name(out_act), " with activations ",
               act_name(act), " unsupported (same dtype, or F32)");
+    if (act == SXB_ACT_F32) {
+        SXB_CHECK(apart(h, M * A * w->K * 4, y, M * (w->N / E) * 4), fn, ": output y overlaps input h");
+        return f32_combine<BITS>(fn, h, w, E, ids, coef, M, A, y, err, stream);
+    }
+    if (int rc = need_bf16(fn, act)) return rc;
     const int64_t N = w->N / E;
     SXB_CHECK(apart(h, M * A * w->K * 2, y, M * N * act_bytes(out_act)), fn, ": output y overlaps input h");
     StreamArgs a{};
@@ -743,7 +768,7 @@ template int stream_partial_grouped<8>(const char *, const void *, const SxbQVie
 
 int combine_reduce(const char *fn, const float *partial, const int32_t *ids, const float *coef, int64_t M, int64_t A,
                    int64_t E_total, int64_t e_lo, int64_t E_local, int64_t N, void *y, int out_act,
-                   const SxbMoeSharedAdd *shared, int s_act, sxb_stream_t stream) {
+                   const SxbMoeSharedAdd *shared, int s_act, bool partial_bf16, sxb_stream_t stream) {
     SXB_CHECK(partial != nullptr && ids != nullptr && coef != nullptr && y != nullptr, fn, ": null pointer (partial=",
               (const void *)partial, ", ids=", (const void *)ids, ", coef=", (const void *)coef, ", y=", y, ")");
     SXB_CHECK(N % 4 == 0 && aligned16(partial), fn, ": N = ", N, " must be a multiple of 4 and partial 16-byte aligned");
@@ -762,11 +787,16 @@ int combine_reduce(const char *fn, const float *partial, const int32_t *ids, con
     const int64_t gld = shared ? shared->gate_ld : 0;
     const uint32_t gi = shared ? shared->gate_index : 0;
     uint32_t *err = shared ? shared->err : nullptr;
-#define SXB_REDUCE(TOUT, TS, SH)                                                                                        \
-    combine_reduce_kernel<TOUT, TS, SH><<<blocks, 256, 0, st>>>(partial, ids, coef, M, A, E_total, e_lo, E_local, N,   \
-                                                                static_cast<TOUT *>(y),                                \
-                                                                static_cast<const TS *>(shared ? shared->s : nullptr), \
-                                                                gl, gld, gi, err)
+#define SXB_REDUCE_P(TOUT, TS, SH, PB)                                                                                  \
+    combine_reduce_kernel<TOUT, TS, SH, PB><<<blocks, 256, 0, st>>>(partial, ids, coef, M, A, E_total, e_lo, E_local, N, \
+                                                                    static_cast<TOUT *>(y),                              \
+                                                                    static_cast<const TS *>(shared ? shared->s : nullptr), \
+                                                                    gl, gld, gi, err)
+#define SXB_REDUCE(TOUT, TS, SH)                          \
+    do {                                                  \
+        if (partial_bf16) SXB_REDUCE_P(TOUT, TS, SH, true); \
+        else SXB_REDUCE_P(TOUT, TS, SH, false);            \
+    } while (0)
     if (out_act == SXB_ACT_F32) {
         if (!shared) SXB_REDUCE(float, float, false);
         else if (s_act == SXB_ACT_F32) SXB_REDUCE(float, float, true);
@@ -777,6 +807,7 @@ int combine_reduce(const char *fn, const float *partial, const int32_t *ids, con
         else SXB_REDUCE(uint16_t, uint16_t, true);
     }
 #undef SXB_REDUCE
+#undef SXB_REDUCE_P
     SXB_CHECK_LAUNCH(fn, " reduce M=", M, " A=", A, " N=", N, shared ? " +shared" : "");
     return SXB_OK;
 }

@@ -51,9 +51,14 @@ def shard_bounds(total: int, world: int, rank: int):
 
 
 def residual(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
-    """bf16(x + y) with the sum in FP32: one elementwise pass (x BF16, y FP32 in, BF16 out)."""
+    """bf16(x + y) with the sum in FP32: one elementwise pass (x BF16, y FP32 in, BF16 out) - the library's kernel on a
+    GPU, torch's on the CPU ranks of the plumbing tests."""
     out = torch.empty_like(x)
-    torch.add(x, y, out=out)
+    if x.is_cuda:
+        from . import kernels as K
+        K.residual_add(x, y, out)
+    else:
+        torch.add(x, y, out=out)
     return out
 
 
@@ -166,12 +171,14 @@ class ExpertParallelMoe:
                 if cuda:
                     with torch.cuda.stream(self.streams[c]):
                         y = self.layer(l, xs[c], c)
+                        if keep is not None:
+                            keep.append(y.clone())  # on the chunk's stream: y is overwritten by its next layer there
                         xs[c] = residual(xs[c], y)
                 else:
                     y = self.layer(l, xs[c], c)
+                    if keep is not None:
+                        keep.append(y.clone())
                     xs[c] = residual(xs[c], y)
-                if keep is not None:
-                    keep.append(y.clone())
         if cuda:
             for st in self.streams:
                 cur.wait_stream(st)

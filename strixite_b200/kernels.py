@@ -43,6 +43,7 @@ class MoeMath(enum.IntEnum):  # kernels/moe_grouped.hpp:39
     WmmaF16Narrow = 3
     WmmaF16Wide = 4
     WmmaF16Wide256 = 5
+    WmmaF16F32Partials = 6  # not in the reference: WmmaF16 with the combine's per-slot dots kept in FP32
 
 
 LAUNCHES = 0  # kernels of this library launched through this module (the benchmark's gpu_launches)
@@ -130,6 +131,79 @@ def moe_shared_add_inject(y, s, gate_logit, gate_ld, M, N, gate_index, x, w_in, 
                                                  _ptr(w_in), H, int(act), _ptr(err), _stream(stream)))
 
 
+# ---- kernels/linear.hpp, kernels/linear_wmma.hpp: the router-logits projection; the residual add ----------------
+
+def linear_bf16w(x, w, y, M, N, K, act, out_act=None, stream=None):
+    _check(_lib.load().sxb_linear_bf16w(_ptr(x), _ptr(w), _ptr(y), M, N, K, int(act), int(act if out_act is None else out_act),
+                                        _stream(stream)))
+
+
+def _w_act(w) -> int:
+    return int(Act.F32 if w.dtype == torch.float32 else Act.BF16)
+
+
+def router_logits(x, w, bias, logits, stream=None):
+    """logits [M, ld] FP32 = x [M, K] BF16 * w [N, K]^T (FP32 or BF16) + bias [N]: the streaming (decode) form."""
+    M, K = x.shape
+    N = w.shape[0]
+    _check(_lib.load().sxb_router_logits(_ptr(x), _ptr(w), _w_act(w), _ptr(bias), M, N, K, _ptr(logits), logits.stride(0),
+                                         _stream(stream)))
+
+
+@dataclass
+class RouterPlanes:
+    """A router weight prepared for the tensor-core projection: `planes` BF16 planes [planes][Npad][K]."""
+
+    data: torch.Tensor
+    planes: int
+    N: int
+    K: int
+
+
+def router_prepare(w: torch.Tensor, planes: Optional[int] = None, stream=None) -> RouterPlanes:
+    """Splits w [N, K] (FP32: 3 planes carry every bit of it, 2 planes 16 bits; BF16: 1 plane) once, at load time."""
+    N, K = w.shape
+    if planes is None:
+        planes = 3 if w.dtype == torch.float32 else 1
+    nbytes = _lib.load().sxb_router_planes_bytes(N, K, planes)
+    if nbytes == 0:
+        _check(1)
+    data = torch.empty(nbytes // 2, dtype=torch.int16, device=w.device)
+    _check(_lib.load().sxb_router_prepare(_ptr(w), _w_act(w), N, K, planes, _ptr(data), _stream(stream)))
+    return RouterPlanes(data, planes, N, K)
+
+
+def router_logits_wmma(x, rp: RouterPlanes, bias, logits, stream=None):
+    """The same projection on the tcgen05 tensor cores (prefill)."""
+    M = x.shape[0]
+    _check(_lib.load().sxb_router_logits_wmma(_ptr(x), _ptr(rp.data), rp.planes, _ptr(bias), M, rp.N, rp.K, _ptr(logits),
+                                              logits.stride(0), _stream(stream)))
+
+
+def residual_add(x, y, out, stream=None):
+    """out = bf16(x + y); x, out BF16 (out may be x), y FP32 or BF16."""
+    _check(_lib.load().sxb_residual_add(_ptr(x), _ptr(y), int(Act.F32 if y.dtype == torch.float32 else Act.BF16), _ptr(out),
+                                        x.numel(), _stream(stream)))
+
+
+def check_dense_status(what: str):
+    _check(_lib.load().sxb_check_dense_status(what.encode()))
+
+
+def set_wait_limit(ns: int):
+    _check(_lib.load().sxb_set_wait_limit(int(ns)))
+
+
+def linear_qw_wmma(x, w: QDeviceView, y, M, act, out_act=None, stream=None):
+    fn = getattr(_lib.load(), f"sxb_linear_{_b(w)}_wmma")
+    _check(fn(_ptr(x), C.byref(w.c()), _ptr(y), M, int(act), int(Act.BF16 if out_act is None else out_act), _stream(stream)))
+
+
+def linear_qw_wmma_swiglu(x, w: QDeviceView, h, M, act, h_f16=0, stream=None):
+    fn = getattr(_lib.load(), f"sxb_linear_{_b(w)}_wmma_swiglu")
+    _check(fn(_ptr(x), C.byref(w.c()), _ptr(h), M, int(act), int(h_f16), _stream(stream)))
+
+
 # ---- kernels/moe_grouped.hpp ----------------------------------------------------------------------------------
 
 def moe_route_workspace_bytes(M, A, E) -> int:
@@ -149,6 +223,12 @@ def route_layout(M, A, E) -> dict:
 def moe_group_routes(ids, M, A, E, ws, ws_bytes, err, stream=None):
     _count(2 if M * A > 2048 else 0)  # the multi-CTA pack is three launches
     _check(_lib.load().sxb_moe_group_routes(_ptr(ids), M, A, E, _ptr(ws), ws_bytes, _ptr(err), _stream(stream)))
+
+
+def moe_route_small(logits, ld, M, E_total, k, e_lo, E_local, ids, coef, ws, ws_bytes, router_err, expert_err, stream=None):
+    """moe_router + moe_group_routes[_ep] as one launch of one CTA (M * k <= 2048 slots)."""
+    _check(_lib.load().sxb_moe_route_small(_ptr(logits), ld, M, E_total, k, e_lo, E_local, _ptr(ids), _ptr(coef), _ptr(ws),
+                                           ws_bytes, _ptr(router_err), _ptr(expert_err), _stream(stream)))
 
 
 def check_grouped_status(ws, what: str):
@@ -295,7 +375,7 @@ def moe_layer(x, logits, y, gate_up: QDeviceView, down: QDeviceView, E, A, ids, 
         sgu, sdn = shared_gate_up.c(), shared_down.c()
         keep += [sgu, sdn]
         a.shared_gate_up, a.shared_down, a.shared_bits = C.pointer(sgu), C.pointer(sdn), shared_gate_up.bits
-    a.x, a.logits, a.logits_ld, a.y = _ptr(x), _ptr(logits), logits.stride(0), _ptr(y)
+    a.x, a.logits, a.logits_ld, a.y = _ptr(x), _ptr(logits), (logits.stride(0) if logits is not None else 0), _ptr(y)
     a.out_act = int(Act.F32 if y.dtype == torch.float32 else Act.BF16)
     a.math = -1 if math is None else int(math)
     a.ids, a.coef, a.ws, a.ws_bytes, a.h, a.partial = _ptr(ids), _ptr(coef), _ptr(ws), ws_bytes, _ptr(h), _ptr(partial)

@@ -57,14 +57,8 @@ class MoeBuffers:
         self.router_err = torch.zeros(4, dtype=torch.int32, device=dev)
         self.expert_err = torch.zeros(4, dtype=torch.int32, device=dev)
         if shared:
-            self.sh_ids = torch.zeros((T, 1), dtype=torch.int32, device=dev)
-            self.sh_coef = torch.ones((T, 1), dtype=torch.float32, device=dev)
-            self.sh_ws_bytes = K.moe_route_workspace_bytes(T, 1, 1)
-            self.sh_ws = torch.empty(self.sh_ws_bytes // 4, dtype=torch.int32, device=dev)
-            self.sh_ws_tokens = -1
             self.sh_gu = torch.empty((T, 2 * I), dtype=torch.bfloat16, device=dev)
             self.sh_h = torch.empty((T, I), dtype=torch.bfloat16, device=dev)
-            self.sh_partial = torch.empty((T, d), dtype=torch.float32, device=dev)
             self.sh_y = torch.empty((T, d), dtype=torch.bfloat16, device=dev)
             self.sh_y32 = torch.empty((T, d), dtype=torch.float32, device=dev)
 
@@ -74,6 +68,8 @@ class MoeLayer:
     weight views and return their partial sum of y (see `ep.ExpertParallelMoe`)."""
 
     tc_min_tokens = 256
+    tc_math = MoeMath.WmmaF16   # the tcgen05 path's numerics: the reference's (BF16 per-slot dots); WmmaF16F32Partials keeps them FP32
+    small_slots = 2048          # up to this many slots the router and the pack are one launch (sxb_moe_route_small)
 
     def __init__(self, weights: MoeWeights, n_experts: int, top_k: int, buffers: MoeBuffers, E_total: Optional[int] = None,
                  e_lo: int = 0):
@@ -91,12 +87,18 @@ class MoeLayer:
     def math_for(self, T: int, math: Optional[MoeMath]) -> MoeMath:
         if math is not None:
             return math
-        return MoeMath.WmmaF16 if T >= self.tc_min_tokens else MoeMath.F32
+        return self.tc_math if T >= self.tc_min_tokens else MoeMath.F32
 
-    def route(self, logits: torch.Tensor, T: int):
-        """moe_router on logits [T, ld] FP32 (column E_total = the shared gate when ld > E_total)."""
+    def route(self, logits: torch.Tensor, T: int) -> bool:
+        """moe_router on logits [T, ld] FP32 (column E_total = the shared gate when ld > E_total).  For a small batch the
+        pack rides in the same launch; returns whether it did."""
         b = self.buf
+        if T * self.k <= self.small_slots and not self.ep:
+            K.moe_route_small(logits, logits.stride(0), T, self.E_total, self.k, 0, self.E, b.ids, b.coef, b.ws, b.ws_bytes,
+                              b.router_err, b.expert_err)
+            return True
         K.moe_router(logits, logits.stride(0), T, self.E_total, self.k, None, 1, 0, b.ids, b.coef, Act.F32, b.router_err)
+        return False
 
     def shared_expert(self, x: torch.Tensor, T: int, math: MoeMath, out: torch.Tensor):
         """The always-on shared expert as dense projections -> out [T, d] (runtime/qwen4exp.cpp:3163-3168): BF16 as the
@@ -108,25 +110,23 @@ class MoeLayer:
             K.swiglu(b.sh_gu, b.sh_h, T, self.I, Act.BF16)
             K.linear_qw(b.sh_h, w.shared_down, out, T, Act.BF16, out_act)
             return
-        # Prefill: the same tcgen05 grouped kernels with one "expert" that every token is routed to.
-        if b.sh_ws_tokens != T:
-            K.moe_group_routes(b.sh_ids, T, 1, 1, b.sh_ws, b.sh_ws_bytes, b.expert_err)
-            b.sh_ws_tokens = T
+        # Prefill: dense projections on the tcgen05 kernel (kernels/linear_wmma.hip:69-113), SwiGLU fused into the first
         if b.tiled_x_sh is None:
             b.tiled_x_sh = torch.empty((b.max_tokens, self.d), dtype=torch.float16, device=x.device)
-        K.stage_f16_tiles(x, b.sh_ws, b.sh_ws_bytes, T, 1, 1, self.d, w.shared_gate_up.bits, b.tiled_x_sh)
+        K.stage_f16_tiles(x, None, 0, T, 1, 1, self.d, w.shared_gate_up.bits, b.tiled_x_sh)
         hf = 3 if w.shared_down.bits == 4 else 4
-        K.linear_qw_experts_gather_grouped_swiglu(b.tiled_x_sh, w.shared_gate_up, 1, b.sh_ws, b.sh_ws_bytes, T, 1, b.sh_h,
-                                                  Act.F16_TILED, math, h_f16=hf)
-        K.linear_qw_experts_combine_grouped(b.sh_h, w.shared_down, 1, b.sh_ids, b.sh_coef, b.sh_ws, b.sh_ws_bytes,
-                                            b.sh_partial, T, 1, out, Act.BF16, math, out_act=out_act, h_f16=hf)
+        K.linear_qw_wmma_swiglu(b.tiled_x_sh, w.shared_gate_up, b.sh_h, T, Act.F16_TILED, h_f16=hf)
+        K.linear_qw_wmma(b.sh_h, w.shared_down, out, T, Act.F16_TILED, out_act)
 
     def experts(self, x: torch.Tensor, T: int, y: torch.Tensor, math: MoeMath, gate_logit=None, gate_ld: int = 0,
-                shared_out: Optional[torch.Tensor] = None, events=None, before_combine=None):
-        """pack -> gate/up + SwiGLU -> down + combine into y [T, d] (BF16 or FP32), ids / coef already in the buffers."""
+                shared_out: Optional[torch.Tensor] = None, events=None, before_combine=None, packed: bool = False):
+        """pack -> gate/up + SwiGLU -> down + combine into y [T, d] (BF16 or FP32), ids / coef already in the buffers
+        (packed: the workspace too)."""
         b, w, A = self.buf, self.w, self.k
         out_act = Act.F32 if y.dtype == torch.float32 else Act.BF16
-        if self.ep:
+        if packed:
+            pass
+        elif self.ep:
             K.moe_group_routes_ep(b.ids, T, A, self.E_total, self.e_lo, self.E, b.ws, b.ws_bytes, b.expert_err)
         else:
             K.moe_group_routes(b.ids, T, A, self.E, b.ws, b.ws_bytes, b.expert_err)
@@ -166,20 +166,24 @@ class MoeLayer:
         T = x.shape[0]
         assert T <= self.buf.max_tokens and x.dtype == torch.bfloat16 and logits.dtype == torch.float32
         math = self.math_for(T, math)
-        self.route(logits, T)
-        return self.run_experts(x, T, y, math, logits)
+        packed = self.route(logits, T)
+        return self.run_experts(x, T, y, math, logits, packed=packed)
 
-    def run_experts(self, x: torch.Tensor, T: int, y: torch.Tensor, math: MoeMath, logits: torch.Tensor, events=None):
+    def run_experts(self, x: torch.Tensor, T: int, y: torch.Tensor, math: MoeMath, logits: torch.Tensor, events=None,
+                    packed: bool = False):
         """Everything after the router: shared expert, pack, routed experts, combine (+ gated shared add)."""
-        if self.w.shared_gate_up is None or self.ep:
-            self.experts(x, T, y, math, events=events)
+        if self.ep and self.w.shared_gate_up is not None:
+            raise K.Error(1, "an expert-parallel rank's layer holds no shared expert: the shared expert is not sharded - run "
+                             "it on the tokens' owner, outside the expert-parallel layer")
+        if self.w.shared_gate_up is None:
+            self.experts(x, T, y, math, events=events, packed=packed)
             return y
         b = self.buf
         sh = b.sh_y32 if y.dtype == torch.float32 else b.sh_y
         gate = logits.data_ptr() + 4 * self.E_total
         if K_is_f16(math):
             self.shared_expert(x, T, math, sh)
-            self.experts(x, T, y, math, gate_logit=gate, gate_ld=logits.stride(0), shared_out=sh, events=events)
+            self.experts(x, T, y, math, gate_logit=gate, gate_ld=logits.stride(0), shared_out=sh, events=events, packed=packed)
             return y
         # Decode: the shared expert's three small launches run on a second stream under the routed experts' weight
         # streaming (they leave most SMs idle on their own) and are joined just before the combine that adds them.
@@ -193,7 +197,7 @@ class MoeLayer:
             self.shared_expert(x, T, math, sh)
             b.ev_join.record(b.side_stream)
         self.experts(x, T, y, math, gate_logit=gate, gate_ld=logits.stride(0), shared_out=sh, events=events,
-                     before_combine=lambda: cur.wait_event(b.ev_join))
+                     before_combine=lambda: cur.wait_event(b.ev_join), packed=packed)
         return y
 
     def check_errors(self, what: str = "moe layer"):
@@ -201,6 +205,7 @@ class MoeLayer:
         K.check_router_error(self.buf.router_err, what)
         K.check_expert_error(self.buf.expert_err, what)
         K.check_grouped_status(self.buf.ws, what)
+        K.check_dense_status(what)  # the shared expert's dense tcgen05 projections record here
 
 
 def K_is_f16(math: MoeMath) -> bool:

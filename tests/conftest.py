@@ -31,8 +31,7 @@ def golden():
 @pytest.fixture(scope="session")
 def lib():
     from strixite_b200 import build, _lib
-    if not _lib.LIB_PATH.exists():
-        build.build()
+    build.build()  # incremental: a library older than its sources would fail at load with a missing symbol
     return _lib.load()
 
 

@@ -78,7 +78,7 @@ def layer_case(rng):
     out = {"layer.x": x, "layer.logits": logits}
     for name, w in [("gu", gu), ("dn", dn), ("sgu", sgu), ("sdn", sdn)]:
         out[f"layer.{name}.q"], out[f"layer.{name}.scale"], out[f"layer.{name}.minv"] = w.q, w.scale, w.minv
-    for sem in ("decode", "grouped"):
+    for sem in ("decode", "grouped", "grouped_f32_partials"):
         r = cpu.moe_layer(x, logits, cpu.LayerWeights(gu, dn, sgu, sdn), E, k, semantics=sem, threads=1)
         out[f"layer.{sem}.ids"], out[f"layer.{sem}.coef"] = r["ids"], r["coef"]
         out[f"layer.{sem}.h"], out[f"layer.{sem}.y_f32"], out[f"layer.{sem}.y_bf16"] = r["h"], r["y_f32"], r["y_bf16"]

@@ -2,14 +2,8 @@
 import numpy as np
 import torch
 
+from oracle.check import bits_of, download, max_abs_over_rms, oracle_layer_on_touched_experts, rms  # noqa: F401
 from strixite_b200.kernels import QDeviceView
-
-
-def bits_of(t: torch.Tensor) -> np.ndarray:
-    """A BF16 (or int16 bit) tensor as numpy uint16."""
-    if t.dtype == torch.bfloat16:
-        t = t.view(torch.int16)
-    return t.detach().cpu().numpy().view(np.uint16)
 
 
 def bf16_tensor(bits: np.ndarray, device) -> torch.Tensor:
@@ -22,20 +16,6 @@ def upload(w, device) -> QDeviceView:
     s = torch.from_numpy(np.ascontiguousarray(w.scale).view(np.int16)).to(device)
     m = torch.from_numpy(np.ascontiguousarray(w.minv).view(np.int16)).to(device)
     return QDeviceView(q, s, m, w.N, w.K, w.G, w.bits)
-
-
-def download(v: QDeviceView, cpu_mod):
-    return cpu_mod.QWeight(v.q.cpu().numpy(), v.scale.cpu().numpy().view(np.uint16),
-                           v.minv.cpu().numpy().view(np.uint16), v.N, v.K, v.G, v.bits)
-
-
-def rms(a: np.ndarray) -> float:
-    return float(np.sqrt(np.mean(np.square(a.astype(np.float64)))))
-
-
-def max_abs_over_rms(got: np.ndarray, ref: np.ndarray) -> float:
-    """The acceptance metric of the layer outputs: max |got - ref| / rms(ref); the bar is 1e-2."""
-    return float(np.max(np.abs(got.astype(np.float64) - ref.astype(np.float64)))) / max(rms(ref), 1e-30)
 
 
 def bf16_ulps(a_bits: np.ndarray, b_bits: np.ndarray) -> np.ndarray:

@@ -42,6 +42,14 @@ def test_shim_compiles(tmp_path):
                     str(src)], check=True)
 
 
+def test_cxx_host_links_against_the_library(lib, tmp_path):
+    """tests/cpp/call_block.cpp - the reference's call block through the C++ shim - compiles and links against
+    libstrix_b200.so (it is run, and its output compared, by the GPU tests)."""
+    from helpers_cpp import build_call_block
+    exe = build_call_block(tmp_path)
+    assert exe.exists()
+
+
 def test_preconditions_fail_before_any_launch(lib):
     from strixite_b200 import kernels as K
     with pytest.raises(K.Error, match="null pointer"):
@@ -77,8 +85,8 @@ def test_weight_view_checks(lib):
     assert "M (rows of x) = 0" in call(M=0)[1]
     rc, msg = call(q=0)
     assert rc == 1 and "null weight pointer" in msg
-    rc = lib.sxb_linear_q4(1 << 20, C.byref(_lib.SxbQView(4096, 8192, 12288, 64, 256, 128)), 1 << 24, 4, 0, 0, None)
-    assert rc == 1 and "FP32 activations are not implemented" in lib.sxb_last_error().decode()
+    rc = lib.sxb_linear_q4(1 << 20, C.byref(_lib.SxbQView(4096, 8192, 12288, 64, 256, 128)), 1 << 24, 4, 0, 1, None)
+    assert rc == 1 and "output dtype BF16 with input F32 unsupported" in lib.sxb_last_error().decode()
 
 
 def test_report_errors(lib):

@@ -7,37 +7,11 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import bits_of, download, max_abs_over_rms
+from helpers import bits_of, download, max_abs_over_rms, oracle_layer_on_touched_experts
 
 pytestmark = pytest.mark.gpu
 
 TOL = 1e-2  # max |y - y_ref| <= TOL * rms(y_ref), the path's stated tolerance
-
-
-def oracle_layer_on_touched_experts(oracle, cfg, w, x_bits, logits, rows, semantics, threads=0):
-    """Runs the oracle on the token subset `rows`, downloading only the experts those tokens are routed to (the
-    stacked matrices of the large configurations are gigabytes; rows are independent)."""
-    ids, _ = oracle.moe_router(logits[rows], cfg.E, cfg.k)
-    touched = np.unique(ids)
-    remap = -np.ones(cfg.E, dtype=np.int64)
-    remap[touched] = np.arange(len(touched))
-    n_gu, n_dn = 2 * cfg.I, cfg.d
-    def take(view, n):
-        idx = torch.from_numpy(np.concatenate([np.arange(e * n, (e + 1) * n) for e in touched])).to(view.q.device)
-        return oracle.QWeight(view.q[idx].cpu().numpy(), view.scale[idx].cpu().numpy().view(np.uint16),
-                              view.minv[idx].cpu().numpy().view(np.uint16), len(touched) * n, view.K, view.G, view.bits)
-    lw = oracle.LayerWeights(take(w.gate_up, n_gu), take(w.down, n_dn))
-    if w.shared_gate_up is not None:
-        lw.shared_gate_up, lw.shared_down = download(w.shared_gate_up, oracle), download(w.shared_down, oracle)
-    # the oracle routes on the original logits; present it logits whose columns are the touched experts only
-    E2 = len(touched)
-    sub = np.full((len(rows), E2 + 1), -1e30, dtype=np.float32)
-    sub[:, :E2] = logits[rows][:, touched]
-    sub[:, E2] = logits[rows][:, cfg.E]
-    out = oracle.moe_layer(x_bits[rows], sub, lw, E2, cfg.k, semantics=semantics, threads=threads)
-    assert np.array_equal(touched[out["ids"]], ids)  # same picks through the remapping
-    out["ids"] = ids
-    return out
 
 
 def run_layer(cfg, seed, dev, math=None):
@@ -109,43 +83,95 @@ def test_layer_rows_do_not_depend_on_batch(cuda):
         start += n
 
 
-def tc_layer_case(cuda, oracle, cfg, n_check, seed=0):
-    """Runs the layer on the tcgen05 path and checks `n_check` seeded token rows against the oracle's matrix-unit
-    semantics (rows are independent, so a subset is a valid check of the full-size run)."""
+def edge_rows(buf, cfg):
+    """Token rows that sit at the edges of the pack: the first and the last slot of the fullest and of the emptiest
+    non-empty expert, and the first slot of a partly filled 128-slot tile."""
+    from strixite_b200 import kernels as K
+    L = K.route_layout(cfg.T, cfg.k, cfg.E)
+    ws = buf.ws.cpu().numpy()
+    off = ws[L["offsets"]:L["offsets"] + cfg.E + 2].astype(np.int64)
+    slots = ws[L["slots"]:L["slots"] + cfg.T * cfg.k]
+    cnt = np.diff(off)[: cfg.E]
+    live = np.nonzero(cnt)[0]
+    hot, cold = live[np.argmax(cnt[live])], live[np.argmin(cnt[live])]
+    pos = [off[hot], off[hot + 1] - 1, off[cold], off[cold + 1] - 1]
+    ragged = [e for e in live if cnt[e] % 128 != 0 and cnt[e] > 128]
+    if ragged:
+        e = ragged[0]
+        pos += [off[e] + (cnt[e] // 128) * 128, off[e + 1] - 1]
+    return sorted({int(slots[p]) // cfg.k for p in pos}), int(cnt[hot]), int(cnt[cold])
+
+
+def tc_layer_case(cuda, oracle, cfg, n_check, seed=0, math=None):
+    """Runs the layer on the tcgen05 path and checks `n_check` seeded token rows - the pack's edge rows among them -
+    against the oracle's matrix-unit semantics (rows are independent, so a subset is a valid check of the full-size
+    run).  Returns (error vs the reference's numerics, error vs the FP32-partials variant, the two variants' distance)."""
     from strixite_b200.kernels import MoeMath
-    w, x, logits, buf, y32, ybf = run_layer(cfg, seed, cuda, math=MoeMath.WmmaF16)
-    rows = np.sort(np.random.default_rng(seed).choice(cfg.T, size=min(n_check, cfg.T), replace=False))
+    math = MoeMath.WmmaF16 if math is None else math
+    w, x, logits, buf, y32, ybf = run_layer(cfg, seed, cuda, math=math)
+    edges, hot, cold = edge_rows(buf, cfg)
+    rnd = [int(r) for r in np.random.default_rng(seed).permutation(cfg.T) if int(r) not in set(edges)]
+    rows = np.array(sorted(edges + rnd[: max(0, min(n_check, cfg.T) - len(edges))]))
     xb, lg = bits_of(x), logits.cpu().numpy()
     ref = oracle_layer_on_touched_experts(oracle, cfg, w, xb, lg, rows, "grouped")
+    alt = oracle_layer_on_touched_experts(oracle, cfg, w, xb, lg, rows, "grouped_f32_partials")
     assert np.array_equal(buf.ids.cpu().numpy()[rows], ref["ids"]), "router ids must be bit-exact"
-    err = max_abs_over_rms(y32.cpu().numpy()[rows], ref["y_f32"])
-    assert err <= TOL, f"{cfg.name}: max-abs error {err:.3e} x RMS exceeds the path's tolerance {TOL}"
-    return err
+    got = y32.cpu().numpy()[rows]
+    err_ref, err_alt = max_abs_over_rms(got, ref["y_f32"]), max_abs_over_rms(got, alt["y_f32"])
+    dist = max_abs_over_rms(ref["y_f32"], alt["y_f32"])
+    print(f"{cfg.name} {math.name}: {len(rows)} rows (fullest expert {hot} slots, emptiest {cold}); max-abs error / RMS "
+          f"{err_ref:.3e} vs the reference's numerics (BF16 per-slot dots), {err_alt:.3e} vs FP32 per-slot dots; "
+          f"the two oracle variants differ by {dist:.3e}")
+    want = err_ref if math != MoeMath.WmmaF16F32Partials else err_alt
+    assert want <= TOL, f"{cfg.name}: max-abs error {want:.3e} x RMS exceeds the path's tolerance {TOL}"
+    return err_ref, err_alt, dist
 
 
 def test_layer_tcgen05_small(cuda, oracle):
-    """C0's layer (Q8 experts, no shared expert) with enough tokens for every expert to be hit, all rows checked."""
+    """C0's layer (Q8 experts, no shared expert) with enough tokens for every expert to be hit, all rows checked, both
+    forms of the per-slot dots."""
     from dataclasses import replace
     from strixite_b200 import workloads as W
+    from strixite_b200.kernels import MoeMath
     cfg = replace(W.C0, T=96, name="c0_t96")
     tc_layer_case(cuda, oracle, cfg, 96)
+    tc_layer_case(cuda, oracle, cfg, 96, math=MoeMath.WmmaF16F32Partials)
 
 
 def test_layer_tcgen05_c3_prefill(cuda, oracle):
-    """C3 at full size (T = 4096, 512 Q4 experts + Q8 shared expert) on the tcgen05 path; 48 seeded rows against the
-    oracle, plus a full-size property: rows computed in the big batch equal the same rows computed in a small batch."""
+    """C3 at full size (T = 4096, 512 Q4 experts + Q8 shared expert) on the tcgen05 path; 512 rows against the oracle,
+    the pack's edge rows among them."""
     from strixite_b200 import workloads as W
-    err = tc_layer_case(cuda, oracle, W.C3, 48)
-    print(f"c3 tcgen05 max-abs error {err:.3e} x RMS")
+    tc_layer_case(cuda, oracle, W.C3, 512)
+
+
+def test_layer_tcgen05_rows_do_not_depend_on_batch(cuda):
+    """A full-size property of the tcgen05 path: rows computed in the big batch (C3, T = 4096) equal, bit for bit, the same
+    rows computed as a batch of their own (320 of them: other tiles, other tile fill, same per-row arithmetic)."""
+    from strixite_b200 import workloads as W
+    from strixite_b200.kernels import MoeMath
+    from strixite_b200.layer import MoeBuffers, MoeLayer
+    cfg = W.C3
+    w = W.make_layer_weights(cfg, 0, cuda)
+    x = W.activations(cfg, 0, cuda)
+    logits = W.router_logits(x, W.router_weight(cfg, 0, cuda), W.expert_bias(cfg, 0, cuda))
+    layer = MoeLayer(w, cfg.E, cfg.k, MoeBuffers(cfg.T, cfg.d, cfg.I, cfg.E, cfg.k, cuda, cfg.shared))
+    y_all = torch.empty((cfg.T, cfg.d), dtype=torch.float32, device=cuda)
+    layer.forward(x, logits, y_all, math=MoeMath.WmmaF16)
+    sel = torch.arange(100, 100 + 320, device=cuda)
+    y_sub = torch.empty((320, cfg.d), dtype=torch.float32, device=cuda)
+    layer.forward(x[sel].contiguous(), logits[sel].contiguous(), y_sub, math=MoeMath.WmmaF16)
+    torch.cuda.synchronize()
+    layer.check_errors(cfg.name)
+    assert torch.equal(y_sub, y_all[sel])
 
 
 @pytest.mark.gpu
 def test_layer_tcgen05_c4_layer(cuda, oracle):
     """One layer of C4 at full size (T = 16384, Q4 gate/up, Q8 down, Zipf-biased routing: tiles from a few tokens to full)
-    on the tcgen05 path; 24 seeded rows against the oracle."""
+    on the tcgen05 path; 256 rows against the oracle, the pack's edge rows among them."""
     from strixite_b200 import workloads as W
-    err = tc_layer_case(cuda, oracle, W.C4, 24)
-    print(f"c4 layer tcgen05 max-abs error {err:.3e} x RMS")
+    tc_layer_case(cuda, oracle, W.C4, 256)
 
 
 @pytest.mark.gpu
@@ -218,8 +244,7 @@ def test_one_call_layer_equals_the_launch_sequence(cuda, name, T, tc, shared):
         extra = {}
         if shared:
             extra = dict(shared_gate_up=w.shared_gate_up, shared_down=w.shared_down, sh_gu=b2.sh_gu, sh_h=b2.sh_h,
-                         sh_y=b2.sh_y32 if dt == torch.float32 else b2.sh_y, sh_ids=b2.sh_ids, sh_coef=b2.sh_coef, sh_ws=b2.sh_ws,
-                         sh_ws_bytes=b2.sh_ws_bytes, sh_partial=b2.sh_partial, sh_xs=sh_xs)
+                         sh_y=b2.sh_y32 if dt == torch.float32 else b2.sh_y, sh_xs=sh_xs)
         K.moe_layer(x, logits, got, w.gate_up, w.down, cfg.E, cfg.k, b2.ids, b2.coef, b2.ws, b2.ws_bytes, b2.h, b2.partial,
                     b2.router_err, b2.expert_err, xs=xs, math=math, **extra)
         torch.cuda.synchronize()

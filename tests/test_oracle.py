@@ -92,7 +92,7 @@ def test_layer_golden(oracle, golden):
         return oracle.QWeight(golden[f"layer.{name}.q"], golden[f"layer.{name}.scale"], golden[f"layer.{name}.minv"], N, K, G, bits)
     w = oracle.LayerWeights(qw("gu", E * 128, 128, 64, 4), qw("dn", E * 128, 64, 32, 8), qw("sgu", 128, 128, 64, 8),
                             qw("sdn", 128, 64, 64, 8))
-    for sem in ("decode", "grouped"):
+    for sem in ("decode", "grouped", "grouped_f32_partials"):
         r = oracle.moe_layer(golden["layer.x"], golden["layer.logits"], w, E, k, semantics=sem, threads=2)
         assert np.array_equal(r["ids"], golden[f"layer.{sem}.ids"])
         assert np.array_equal(r["h"], golden[f"layer.{sem}.h"])
