@@ -342,7 +342,7 @@ typedef struct SxbMoeLayerArgs {
     int64_t logits_ld;
     void *y;                       /* [M, d] */
     int out_act;                   /* SXB_ACT_BF16, or SXB_ACT_F32 for the unrounded sums */
-    int math;                      /* SXB_MATH_*; -1 = the tcgen05 kernels from 256 tokens up, the streaming ones below */
+    int math;                      /* SXB_MATH_*; -1 = the tcgen05 kernels (FP32 per-slot dots) from 256 tokens up, the streaming ones below */
     /* work buffers */
     int32_t *ids;                  /* [M, A] */
     float *coef;                   /* [M, A] */

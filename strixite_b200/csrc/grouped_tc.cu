@@ -68,7 +68,9 @@ constexpr int kWSlots = 4;
 constexpr int kWSlotBytes = kAThreads * 64;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any legitimate wait (the default bound)
 
-enum TcMode { kTcGather = 0, kTcSwiglu = 1, kTcPartial = 2 };
+// kTcPartialBf16: kTcPartial with the per-slot dots stored as BF16 bits (N * 2 bytes a slot) - for the epilogue it is the
+// plain gather's store on h rows.  A mode of its own, so that the per-token store code of every mode stays one short form.
+enum TcMode { kTcGather = 0, kTcSwiglu = 1, kTcPartial = 2, kTcPartialBf16 = 3 };
 
 struct TcArgs {
     const uint16_t *x;  // activations: BF16 or F16 bits, see x_kind
@@ -85,7 +87,6 @@ struct TcArgs {
                   // 3 / 4 tile-blocked for a Q4 / Q8 down operand
     uint32_t *status;  // >= 3 words: {2, item, role} on a wait that ran out
     int64_t dense_M;   // > 0: a dense projection - no grouping workspace, one group holding rows 0 .. dense_M - 1 in order
-    int partial_bf16;  // kTcPartial: the per-slot dots are stored as BF16 bits (N * 2 bytes a slot), not FP32
     unsigned long long wait_limit_ns;  // bound of every device-side wait
     int test_skip_slot;  // >= 0: CTA 0 never issues ring slot number test_skip_slot, so a wait runs out (tests only)
 };
@@ -467,7 +468,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
             __syncwarp();
             for (int n = lane; n < n_mine; n += 32) {
                 const int64_t slot = slot_at(it.start + bw * kRowsPerWarp + n);
-                row_off[n] = (MODE == kTcPartial ? slot : slot / a.A) * a.K;
+                row_off[n] = (MODE == kTcPartial || MODE == kTcPartialBf16 ? slot : slot / a.A) * a.K;
             }
             __syncwarp();
             bool live = true;
@@ -623,7 +624,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
             } else {
                 const int64_t r = (int64_t)it.rb * kAThreads + r_loc;
                 row_ok = r < a.N;  // N is a multiple of 16: the second accumulator's row r + 128 is checked on its own
-                elem_off = r * (MODE == kTcPartial && !a.partial_bf16 ? 4 : 2);
+                elem_off = r * (MODE == kTcPartial ? 4 : 2);
             }
             const bool row1_ok = MODE != kTcSwiglu && (int64_t)it.rb * kAThreads + 128 + r_loc < a.N;
             // Slot of token n of the tile (lanes 0..15 fetch the 16 tokens of a pass, one pass ahead; nothing may depend
@@ -632,7 +633,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
             // Offset of a token's output row / line, in 16-byte units.
             auto token_off = [&](int n, int slot) -> uint32_t {
                 if (tiled_out) return (uint32_t)(it.start + n) * 8u;
-                return (uint32_t)(((int64_t)slot * (MODE == kTcSwiglu ? I * 2 : a.N * (MODE == kTcPartial && !a.partial_bf16 ? 4 : 2))) >> 4);
+                return (uint32_t)(((int64_t)slot * (MODE == kTcSwiglu ? I * 2 : a.N * (MODE == kTcPartial ? 4 : 2))) >> 4);
             };
             int slot_nxt = lane < 16 ? token_slot(lane) : 0;
             if (valid) {
@@ -673,7 +674,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_tc_kernel(const TcArgs a,
                         const uint16_t hv = h_as_f16 ? __half_as_ushort(__float2half_rn(bf16_bits_to_f32(b))) : b;
                         const uint32_t sw = tiled_out ? ((xor_chunk ^ (uint32_t)(t & 7)) << 4) : 0u;
                         if (row_ok && t < live) *reinterpret_cast<uint16_t *>(out + off + sw) = hv;
-                    } else if (MODE == kTcPartial && !a.partial_bf16) {
+                    } else if (MODE == kTcPartial) {
                         if (row_ok && t < live) *reinterpret_cast<float *>(out + off) = g[t];
                         if (row1_ok && t < live) *reinterpret_cast<float *>(out + off + 512) = u[t];
                     } else {  // BF16 rows: the plain gather's y, or the per-slot dots as kernels/moe_grouped.hip:47-57 stores them
@@ -872,10 +873,10 @@ int tc_partial_grouped(const char *fn, const void *h, const SxbQView *w, int64_t
     TcArgs a{};
     a.x = static_cast<const uint16_t *>(h), a.q = w->q, a.scale = w->scale, a.minv = w->minv;
     a.N = N, a.K = w->K, a.A = A, a.E = E, a.ws = static_cast<const int32_t *>(ws), a.L = route_words(M, A, E);
-    a.out = partial, a.x_kind = h_f16 >= 3 ? 3 : h_f16, a.out_f16 = 0, a.partial_bf16 = partial_bf16;
+    a.out = partial, a.x_kind = h_f16 >= 3 ? 3 : h_f16, a.out_f16 = 0;
     a.status = reinterpret_cast<uint32_t *>(const_cast<void *>(ws)) + 5;
     auto st = static_cast<cudaStream_t>(stream);
-    if (int rc = launch_tc<BITS, kTcPartial>(fn, a, w->G, st)) return rc;
+    if (int rc = partial_bf16 ? launch_tc<BITS, kTcPartialBf16>(fn, a, w->G, st) : launch_tc<BITS, kTcPartial>(fn, a, w->G, st)) return rc;
     SXB_CHECK_LAUNCH(fn, " tcgen05 partial M=", M, " A=", A, " E=", E, " N=", N, " K=", w->K, " G=", w->G);
     return SXB_OK;
 }
@@ -905,7 +906,7 @@ int tc_dense(const char *fn, const void *x, const SxbQView *w, void *y, int64_t 
     a.x = static_cast<const uint16_t *>(x), a.q = w->q, a.scale = w->scale, a.minv = w->minv;
     a.N = w->N, a.K = w->K, a.A = 1, a.E = 1, a.ws = nullptr, a.L = RouteWords{};
     a.L.S = M, a.L.E = 1;
-    a.out = y, a.x_kind = x_kind, a.out_f16 = out_kind == 2 ? h_f16 : 0, a.partial_bf16 = 0, a.dense_M = M, a.status = status;
+    a.out = y, a.x_kind = x_kind, a.out_f16 = out_kind == 2 ? h_f16 : 0, a.dense_M = M, a.status = status;
     auto st = static_cast<cudaStream_t>(stream);
     int rc = out_kind == 2   ? launch_tc<BITS, kTcSwiglu>(fn, a, w->G, st)
              : out_kind == 1 ? launch_tc<BITS, kTcPartial>(fn, a, w->G, st)

@@ -58,7 +58,7 @@ extern "C" int sxb_moe_layer(const SxbMoeLayerArgs *a, sxb_stream_t stream) {
     const int64_t M = a->M, A = a->A, E = a->E, d = a->gate_up->K, I = a->gate_up->N / E / 2;
     SXB_CHECK(a->gate_up->N == E * 2 * I && a->down->N == E * d && a->down->K == I, fn, ": gate_up [", a->gate_up->N, ", ",
               a->gate_up->K, "] and down [", a->down->N, ", ", a->down->K, "] do not describe ", E, " experts");
-    const int math = a->math >= 0 ? a->math : (M >= 256 ? SXB_MATH_WMMA_F16 : SXB_MATH_F32);
+    const int math = a->math >= 0 ? a->math : (M >= 256 ? SXB_MATH_WMMA_F16_F32_PARTIALS : SXB_MATH_F32);
     const bool tc = math >= SXB_MATH_WMMA_F16;
     SXB_CHECK(!tc || a->xs != nullptr, fn, ": the tcgen05 path needs the tile-blocked activation buffer xs (M * A * d F16)");
     auto st = static_cast<cudaStream_t>(stream);

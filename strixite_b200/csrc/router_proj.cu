@@ -25,8 +25,8 @@ namespace {
 
 // ---- streaming form ------------------------------------------------------------------------------------------
 
-constexpr int kStreamWarps = 8;
-constexpr int kTokChunk = 8;
+constexpr int kStreamWarps = 4;   // warps of a CTA: each takes a quarter of the row's k range
+constexpr int kTokChunk = 16;     // tokens whose sums a lane keeps in registers at a time
 
 __device__ inline void load_w8(const float *p, float (&w)[8]) {
     const float4 a = __ldg(reinterpret_cast<const float4 *>(p)), b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
@@ -39,29 +39,37 @@ __device__ inline void load_w8(const uint16_t *p, float (&w)[8]) {
     for (int i = 0; i < 4; ++i) w[2 * i] = __uint_as_float(u[i] << 16), w[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
 }
 
-// y[m, n] = sum_k x[m, k] * w[n, k] (+ bias[n]); one warp per row n, tokens eight at a time, lanes strided over k in
-// runs of eight; the sum of a (token, row) pair is formed in a fixed order (per lane ascending k, then an xor butterfly).
+// y[m, n] = sum_k x[m, k] * w[n, k] (+ bias[n]).  One CTA per weight row n: its bytes are streamed once, every warp a
+// contiguous quarter of the k range in runs of eight per lane, all loads of a run independent of one another; a lane keeps
+// the sums of 16 tokens.  The sum of a (token, row) pair is formed in a fixed order: per lane ascending k, an xor butterfly
+// inside the warp, then the four warps' parts in warp order.
 template <typename TW, typename TOUT>
 __global__ void __launch_bounds__(32 * kStreamWarps)
     logits_stream_kernel(const uint16_t *__restrict__ x, const TW *__restrict__ w, const float *__restrict__ bias, int64_t M,
                          int64_t N, int64_t K, TOUT *__restrict__ y, int64_t ld) {
-    const int lane = threadIdx.x & 31;
-    const int64_t n = (int64_t)blockIdx.x * kStreamWarps + (threadIdx.x >> 5);
-    if (n >= N) return;
+    __shared__ float part[kStreamWarps][kTokChunk];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t n = blockIdx.x;
     const TW *wr = w + n * K;
     const float b = bias ? bias[n] : 0.f;
+    // this warp's k range: a quarter of the row, rounded to the 256 k a warp covers per step
+    const int64_t steps = (K + 255) / 256, per = (steps + kStreamWarps - 1) / kStreamWarps;
+    const int64_t k_lo = (int64_t)warp * per * 256, k_hi = min(K, k_lo + per * 256);
     for (int64_t m0 = 0; m0 < M; m0 += kTokChunk) {
+        const int live = (int)min((int64_t)kTokChunk, M - m0);
         float acc[kTokChunk];
 #pragma unroll
         for (int t = 0; t < kTokChunk; ++t) acc[t] = 0.f;
-        for (int64_t k = lane * 8; k < K; k += 256) {
+        for (int64_t k = k_lo + lane * 8; k < k_hi; k += 256) {
             float wv[8];
             load_w8(wr + k, wv);
+            uint4 xv[kTokChunk];
+#pragma unroll
+            for (int t = 0; t < kTokChunk; ++t)
+                xv[t] = t < live ? __ldg(reinterpret_cast<const uint4 *>(x + (m0 + t) * K + k)) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
             for (int t = 0; t < kTokChunk; ++t) {
-                if (m0 + t >= M) break;
-                const uint4 xv = __ldg(reinterpret_cast<const uint4 *>(x + (m0 + t) * K + k));
-                const uint32_t u[4] = {xv.x, xv.y, xv.z, xv.w};
+                const uint32_t u[4] = {xv[t].x, xv[t].y, xv[t].z, xv[t].w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     acc[t] = fmaf(__uint_as_float(u[i] << 16), wv[2 * i], acc[t]);
@@ -73,8 +81,16 @@ __global__ void __launch_bounds__(32 * kStreamWarps)
         for (int t = 0; t < kTokChunk; ++t) {
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], off);
-            if (lane == 0 && m0 + t < M) store_from_f32(y, (m0 + t) * ld + n, acc[t] + b);
+            if (lane == 0) part[warp][t] = acc[t];
         }
+        __syncthreads();
+        if (threadIdx.x < live) {
+            float v = part[0][threadIdx.x];
+#pragma unroll
+            for (int wq = 1; wq < kStreamWarps; ++wq) v += part[wq][threadIdx.x];
+            store_from_f32(y, (m0 + threadIdx.x) * ld + n, v + b);
+        }
+        __syncthreads();
     }
 }
 
@@ -324,7 +340,7 @@ int check_proj(const char *fn, const void *x, const void *w, const void *y, int6
 template <typename TOUT>
 int launch_stream_logits(const char *fn, const void *x, const void *w, int w_act, const float *bias, int64_t M, int64_t N, int64_t K,
                          TOUT *y, int64_t ld, cudaStream_t st) {
-    const unsigned blocks = (unsigned)((N + kStreamWarps - 1) / kStreamWarps);
+    const unsigned blocks = (unsigned)N;  // one CTA per weight row
     if (w_act == SXB_ACT_F32)
         logits_stream_kernel<float, TOUT><<<blocks, 32 * kStreamWarps, 0, st>>>((const uint16_t *)x, (const float *)w, bias, M, N, K, y, ld);
     else

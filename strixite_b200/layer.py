@@ -68,7 +68,10 @@ class MoeLayer:
     weight views and return their partial sum of y (see `ep.ExpertParallelMoe`)."""
 
     tc_min_tokens = 256
-    tc_math = MoeMath.WmmaF16   # the tcgen05 path's numerics: the reference's (BF16 per-slot dots); WmmaF16F32Partials keeps them FP32
+    # The tcgen05 path's numerics.  WmmaF16F32Partials keeps the combine's per-slot dots in FP32; WmmaF16 rounds them to
+    # BF16 as the reference's served path does, which by itself moves an output by up to ~2e-2 of the output RMS
+    # (measured on the Zipf-routed stack) - beyond the 1e-2 this path is held to - and measured no faster here.
+    tc_math = MoeMath.WmmaF16F32Partials
     small_slots = 2048          # up to this many slots the router and the pack are one launch (sxb_moe_route_small)
 
     def __init__(self, weights: MoeWeights, n_experts: int, top_k: int, buffers: MoeBuffers, E_total: Optional[int] = None,

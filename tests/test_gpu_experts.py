@@ -313,12 +313,32 @@ def test_grouped_experts_tcgen05(cuda, oracle, bits, G, M, A, E, I, d):
             hd = hd.float().to(torch.float16)
         if f16 == 2:
             hd = hd.view(M * A, I // 8, 8)[:, :, PERM].reshape(M * A, I).contiguous()
+        # FP32 per-slot dots (this library's extra math kind): tight against the oracle
         partial = torch.zeros((M * A, d), dtype=torch.float32, device=cuda)
         y = torch.empty((M, d), dtype=torch.float32, device=cuda)
-        K.linear_qw_experts_combine_grouped(hd, dnd, E, idd, cfd, ws, nbytes, partial, M, A, y, K.Act.BF16, K.MoeMath.WmmaF16,
-                                            out_act=K.Act.F32, h_f16=f16)
+        K.linear_qw_experts_combine_grouped(hd, dnd, E, idd, cfd, ws, nbytes, partial, M, A, y, K.Act.BF16,
+                                            K.MoeMath.WmmaF16F32Partials, out_act=K.Act.F32, h_f16=f16)
         torch.cuda.synchronize()
         K.check_grouped_status(ws, "tcgen05 combine")
         assert max_abs_over_rms(partial.cpu().numpy()[ok], p_ref[ok]) < 3e-5
         assert max_abs_over_rms(y.cpu().numpy()[rows], y_ref[rows]) < 3e-5
         assert np.all(np.isnan(y.cpu().numpy()[5]))
+        # BF16 per-slot dots (the reference's WMMA_F16, kernels/moe_grouped.hip:47-57): the stored dots are the BF16 rounding
+        # of the same sums - equal to the oracle's rounding except where a sum sits on a rounding boundary (one ulp) - and
+        # y is the slot-order sum of exactly those stored values
+        pb = torch.zeros((M * A, d), dtype=torch.float32, device=cuda)
+        yb = torch.empty((M, d), dtype=torch.float32, device=cuda)
+        K.linear_qw_experts_combine_grouped(hd, dnd, E, idd, cfd, ws, nbytes, pb, M, A, yb, K.Act.BF16, K.MoeMath.WmmaF16,
+                                            out_act=K.Act.F32, h_f16=f16)
+        torch.cuda.synchronize()
+        got_p = bits_of(pb.view(torch.bfloat16).reshape(-1)[: M * A * d].view(M * A, d))
+        want_p = oracle.f32_to_bf16(p_ref)
+        gp, wp = oracle.bf16_to_f32(got_p[ok]).astype(np.float64), oracle.bf16_to_f32(want_p[ok]).astype(np.float64)
+        p_rms = float(np.sqrt(np.mean(wp ** 2)))
+        assert np.all(np.abs(gp - wp) <= 2.0 ** -7 * np.abs(wp) + 3e-5 * p_rms)  # one BF16 ulp, or FP32 summation noise near zero
+        assert (got_p[ok] != want_p[ok]).mean() < 0.01
+        stored = oracle.bf16_to_f32(got_p).astype(np.float64).reshape(M, A, d)
+        y_from_stored = np.einsum("ma,mad->md", coef.astype(np.float64), np.where(np.isnan(stored), 0, stored))
+        assert max_abs_over_rms(yb.cpu().numpy()[rows], y_from_stored[rows]) < 3e-6
+        y_ref_b = oracle.experts_combine(h_ref.reshape(M, A, I), dn, E, ids, coef, out_act=oracle.F32, w_f16=True, partial_bf16=True)
+        assert max_abs_over_rms(yb.cpu().numpy()[rows], y_ref_b[rows]) < 1e-2

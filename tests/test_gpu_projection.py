@@ -51,8 +51,10 @@ def test_router_logits_streaming(cuda, oracle, M, N, K, w_bf16):
 @pytest.mark.parametrize("M,N,K,planes,w_bf16", [(4096, 513, 4096, 3, False), (300, 513, 1024, 2, False), (1000, 129, 512, 1, True),
                                                    (128, 64, 256, 3, False)])
 def test_router_logits_tcgen05(cuda, oracle, M, N, K, planes, w_bf16):
-    """The tensor-core projection: three planes reproduce the FP32 weight exactly (error = FP32 summation only), two planes
-    keep 16 bits of it, one plane is a BF16 weight."""
+    """The tensor-core projection: three planes reproduce the FP32 weight exactly, two planes keep 16 bits of it, one plane
+    is a BF16 weight.  What is left is the tensor cores' FP32 accumulation, which is not IEEE summation (the reference says
+    the same of its matrix units, kernels/wmma.hpp:10-11): measured 1.3e-5 of the largest logit over K = 4096 x 3 planes,
+    held to 3e-5 here (the streaming form, plain FP32 FMAs, is held to 1e-5)."""
     from strixite_b200 import kernels as Kn
     rng = np.random.default_rng(M + N + planes)
     xb = oracle.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
@@ -73,7 +75,7 @@ def test_router_logits_tcgen05(cuda, oracle, M, N, K, planes, w_bf16):
     want = logits_f64(oracle, xb, w, bias)
     got = out.cpu().numpy()
     assert np.all(np.isnan(got[:, N:]))
-    tol = 1e-5 if planes != 2 else 4e-5
+    tol = 3e-5 if planes != 2 else 6e-5
     assert np.max(np.abs(got[:, :N] - want)) <= tol * np.max(np.abs(want)), np.max(np.abs(got[:, :N] - want)) / np.max(np.abs(want))
     if w_bf16 and planes == 1:  # the unprepared BF16 weight as its own plane
         out2 = torch.empty((M, N), dtype=torch.float32, device=cuda)
@@ -82,7 +84,7 @@ def test_router_logits_tcgen05(cuda, oracle, M, N, K, planes, w_bf16):
         assert np.max(np.abs(out2.cpu().numpy() - plain)) <= 1e-5 * np.max(np.abs(plain))
 
 
-@pytest.mark.parametrize("M,E,k,shards", [(16, 512, 10, 1), (64, 512, 10, 1), (7, 64, 4, 1), (200, 1024, 10, 1), (16, 512, 10, 4)])
+@pytest.mark.parametrize("M,E,k,shards", [(16, 512, 10, 1), (64, 512, 10, 1), (7, 64, 4, 1), (200, 1000, 10, 1), (16, 512, 10, 4)])
 def test_route_small_equals_router_then_pack(cuda, M, E, k, shards):
     """sxb_moe_route_small writes the same ids, coef and workspace, word for word, as moe_router + moe_group_routes[_ep]."""
     from strixite_b200 import kernels as Kn
