@@ -54,6 +54,10 @@ def parse():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--parity-rows", type=int, default=32, help="token rows checked against the CPU oracle after the timed region (0 = skip)")
     ap.add_argument("--planes", type=int, default=3, help="BF16 planes of the FP32 router weight on the tensor-core projection (2 or 3)")
+    ap.add_argument("--ep", default="native", choices=["native", "torch"],
+                    help="expert-parallel driver: the library's C entry point sxb_moe_layer_ep, or torch.distributed (strixite_b200/ep.py)")
+    ap.add_argument("--return-path", dest="return_path", type=int, default=1,
+                    help="native driver, rows back to their owners: 0 NCCL reduce-scatter, 1 peer stores of FP32 pieces, 2 of BF16 pieces")
     ap.add_argument("--math", default="", help="tcgen05 numerics: wmma_f16 (BF16 per-slot dots, the reference's) or wmma_f16_f32p")
     return ap.parse_args()
 
@@ -132,7 +136,7 @@ class Stack:
     """Resident state of a configuration on this rank: per-layer weights (this rank's experts), router weights, biases,
     the shared workspaces, and the expert-parallel driver."""
 
-    def __init__(self, cfg, layers, seed, dev, rank, world, micro=0, planes=3):
+    def __init__(self, cfg, layers, seed, dev, rank, world, micro=0, planes=3, ep_impl="native", return_path=1):
         import torch
         from strixite_b200 import workloads as W
         from strixite_b200.ep import Compute, ExpertParallelMoe, shard_bounds
@@ -177,8 +181,59 @@ class Stack:
         self.math = None          # None = by token count (tcgen05 from MoeLayer.tc_min_tokens up)
         self.events = None        # (list, list) of CUDA events around the dominant kernel when roofline timing is on
         self.ep = ExpertParallelMoe(Compute(self._route, self._experts, chunked=True), layers, cfg.T, cfg.d, cfg.k, dev, micro=micro,
-                                    exchange=os.environ.get("STRIX_EP_EXCHANGE", "reduce_scatter"))
+                                    exchange="reduce_scatter")
         self.weight_bytes = sum(ly.w.bytes() for ly in self.layers)
+        # Expert-parallel runs go through the library's C entry point (sxb_moe_layer_ep: NCCL gathers, this rank's experts,
+        # the rows' way back by peer stores or reduce-scatter); --ep torch keeps the torch.distributed driver of ep.py.
+        self.native = None
+        if world > 1 and ep_impl == "native" and micro == 1:
+            import torch.distributed as dist
+            box = [K.ep_unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(box, src=0)
+            self.native = K.EpContext(box[0], world, rank, cfg.T, cfg.d, cfg.k, return_path)
+            self.y_loc = torch.empty((t, cfg.d), dtype=torch.float32, device=dev)
+
+    def layer(self, l, x_loc):
+        """One layer on this rank's rows -> y [t, d] FP32."""
+        if self.native is None:
+            return self.ep.layer(l, x_loc)
+        from strixite_b200 import kernels as K
+        t = x_loc.shape[0]
+        logits = self.logits[0][:t]
+        if self.proj_wmma:
+            K.router_logits_wmma(x_loc, self.planes[l], self.bias[l], logits)
+        else:
+            K.router_logits(x_loc, self.wr[l], self.bias[l], logits)
+        ly, b = self.layers[l], self.buf
+        if b.tiled_x is None:
+            b.tiled_x = torch_empty_f16((b.max_tokens * self.cfg.k, self.cfg.d), self.dev)
+        self.native.layer(x_loc, logits, self.y_loc, ly.w.gate_up, ly.w.down, ly.E, self.cfg.E, self.e_lo, self.cfg.k, b.ids, b.coef,
+                          b.ws, b.ws_bytes, b.h, b.partial, b.router_err, b.expert_err, xs=b.tiled_x,
+                          math=ly.math_for(self.cfg.T, self.math))
+        return self.y_loc
+
+    def forward(self, x_loc):
+        """The stack: x <- bf16(x + moe_l(x)) for every layer."""
+        if self.native is None:
+            return self.ep.forward(x_loc)
+        from strixite_b200.ep import residual
+        x = x_loc
+        for l in range(self.n_layers):
+            x = residual(x, self.layer(l, x))
+        return x
+
+    def local_ids(self):
+        """The router ids of this rank's own rows after a layer call."""
+        if self.world == 1:
+            return self.buf.ids
+        return self.buf.ids[self.t_lo:self.t_hi] if self.native is not None else self.ids_loc[0]
+
+    def local_slots(self):
+        """Slots this rank's experts served in the last layer call (the pack's offsets: the overflow bucket starts there)."""
+        from strixite_b200 import kernels as K
+        E_local = self.e_hi - self.e_lo
+        L = K.route_layout(self.cfg.T, self.cfg.k, E_local)
+        return int(self.buf.ws[L["offsets"] + E_local].item())
 
     def _route(self, l, x_loc, chunk=0):
         from strixite_b200 import kernels as K, workloads as W
@@ -209,10 +264,15 @@ class Stack:
         return y
 
     def step(self, x_loc):
-        return self.ep.forward(x_loc)
+        return self.forward(x_loc)
 
     def one_layer(self, l, x_loc):
-        return self.ep.layer(l, x_loc)
+        return self.layer(l, x_loc)
+
+
+def torch_empty_f16(shape, dev):
+    import torch
+    return torch.empty(shape, dtype=torch.float16, device=dev)
 
 
 def algorithmic_flops(cfg, layers, shared):
@@ -265,7 +325,8 @@ def run_stack(cfg, args, dev, rank, world, peaks, layers=None, rotate=False):
     from strixite_b200 import kernels as K, workloads as W
 
     layers = layers or args.layers or cfg.layers
-    st = Stack(cfg, layers, args.seed, dev, rank, world, micro=getattr(args, "micro", 0), planes=getattr(args, "planes", 3))
+    st = Stack(cfg, layers, args.seed, dev, rank, world, micro=getattr(args, "micro", 0), planes=getattr(args, "planes", 3),
+               ep_impl=getattr(args, "ep", "native"), return_path=getattr(args, "return_path", 1))
     if getattr(args, "math", ""):
         from strixite_b200.kernels import MoeMath
         st.math_tc = {"wmma_f16": MoeMath.WmmaF16, "wmma_f16_f32p": MoeMath.WmmaF16F32Partials}[args.math]
@@ -349,21 +410,61 @@ def run_stack(cfg, args, dev, rank, world, peaks, layers=None, rotate=False):
             torch.cuda.synchronize()
             k_ms = kernel_ms((st.events[0][layers:], st.events[1][layers:]))
             st.events = None
-    ep_timing = st.ep.timing_summary()
-    if ep_timing is not None and rank == 0:
-        print("ep phases, ms per layer (rank 0): " + ", ".join(f"{k} {v:.3f}" for k, v in ep_timing.items()), file=sys.stderr)
+    ep_info = None
+    if world > 1:
+        # per rank: the phases of a layer (ms, mean over one more pass of the stack) and the slots its experts served
+        if st.native is not None:
+            st.native.set_timing(True)
+            st.step(x_loc)
+            phases = st.native.timing()
+            st.native.set_timing(False)
+        else:
+            st.ep.timing = []
+            st.step(x_loc)
+            phases = st.ep.timing_summary() or {}
+            st.ep.timing = None
+        slots, x_l = [], x_loc
+        from strixite_b200.ep import residual
+        for l in range(layers):
+            y_l = st.layer(l, x_l)
+            slots.append(st.local_slots())
+            x_l = residual(x_l, y_l)
+        mine = {"rank": rank, "phases_ms": phases, "slots_per_layer": slots}
+        gathered = [None] * world
+        dist.all_gather_object(gathered, mine)
+        ep_info = gathered
     layer_tokens = cfg.T * (1 if rotate else layers)
     out = dict(
         ms_per_step=ms, value=layer_tokens / (ms * 1e-3), e2e_value=layer_tokens / (e2e_ms * 1e-3), e2e_ms=e2e_ms,
         h2d=x_host.numel() * 2 * world, d2h=y_host.numel() * 2 * world, launches=launches_per_step, clocks=clocks.summary(),
-        kernel_ms=k_ms, layers=layers, stack=st, x_full=x_full,
+        kernel_ms=k_ms, layers=layers, stack=st, x_full=x_full, ep_info=ep_info,
     )
     return out
+
+
+def roofline_ep(cfg, res, peaks, world):
+    """Expert-parallel runs: every rank's own expert phase (pack, activation staging, gate/up + SwiGLU, down, combine - the
+    CUDA events of sxb_moe_layer_ep around it) against the flops of the slots that rank's experts served."""
+    per_rank = []
+    for info in res["ep_info"]:
+        ms = info["phases_ms"].get("experts")
+        slots = sum(info["slots_per_layer"]) / max(1, len(info["slots_per_layer"]))
+        flops = 2.0 * slots * 3 * cfg.I * cfg.d
+        per_rank.append({"rank": info["rank"], "slots_per_layer": slots, "experts_ms": ms,
+                         "tflops": (flops / (ms * 1e-3) / 1e12) if ms else None})
+    mine = per_rank[0]
+    peak = peaks["tflops_sustained"]
+    return dict(bound="tensor", kernel="experts phase of sxb_moe_layer_ep (pack, staging, gate/up + SwiGLU, down, combine), rank 0",
+                achieved=mine["tflops"], peak=peak, unit="TFLOP/s", frac=(mine["tflops"] / peak) if mine["tflops"] else None,
+                peak_source=peaks["source"] + " (sustained bf16)", traffic=None, per_rank=per_rank,
+                flops_per_launch=2.0 * mine["slots_per_layer"] * 3 * cfg.I * cfg.d, kernel_ms=mine["experts_ms"])
 
 
 def roofline_tensor(cfg, res, peaks, world):
     """Dominant kernel of the prefill regime: the grouped gate/up + SwiGLU GEMM, 2 * S * 2I * d flops per launch (this
     rank's share of the slots: S / N on average)."""
+    if world > 1 and res.get("ep_info") and res["ep_info"][0]["phases_ms"].get("experts"):
+        return roofline_ep(cfg, res, peaks, world)
     micro = res["stack"].micro  # a launch serves one micro-batch of this rank's slots
     flops = 2.0 * cfg.T * cfg.k * 2 * cfg.I * cfg.d / world / micro
     if not res["kernel_ms"]:
@@ -510,8 +611,8 @@ def parity_check(cfg, st, x_loc, args, dev, rank):
     rec = []
     x = x_loc
     for l in range(st.n_layers):
-        y = st.ep.layer(l, x)
-        ids = st.buf.ids if st.world == 1 else st.ids_loc[0]
+        y = st.layer(l, x)
+        ids = st.local_ids()
         rec.append((check.bits_of(x[rows]), st.logits[0][rows].cpu().numpy(), ids[rows].cpu().numpy(), y[rows].float().cpu().numpy()))
         x = residual(x, y)
     torch.cuda.synchronize()
@@ -612,6 +713,10 @@ def main():
         "e2e": {"value": res["e2e_value"], "unit": "MoE-layer tokens/s", "h2d_bytes_per_step": res["h2d"],
                 "d2h_bytes_per_step": res["d2h"], "ms_per_step": res["e2e_ms"]},
     }
+    if res.get("ep_info"):
+        line["expert_parallel"] = {"driver": "sxb_moe_layer_ep" if st.native is not None else "torch.distributed (ep.py)",
+                                   "return_path": {0: "nccl reduce-scatter (fp32)", 1: "peer stores, fp32 pieces", 2: "peer stores, bf16 pieces"}[args.return_path]
+                                   if st.native is not None else st.ep.exchange, "per_rank": res["ep_info"]}
     if args.parity_rows > 0:
         try:
             par = parity_check(cfg, st, res["x_full"][st.t_lo:st.t_hi].contiguous(), args, dev, rank)

@@ -363,6 +363,34 @@ typedef struct SxbMoeLayerArgs {
 } SxbMoeLayerArgs;
 int sxb_moe_layer(const SxbMoeLayerArgs *args, sxb_stream_t stream);
 
+/* ---- Expert parallelism (no counterpart in the reference, which drives one GPU) ------------------------------- */
+
+/* One process per GPU; rank r of `world` holds experts [r E / world, (r + 1) E / world) of every layer and owns the token
+ * rows [r T / world, (r + 1) T / world).  sxb_moe_layer_ep runs one layer on the rank's rows: all-gather of the activations
+ * and of the routes (NCCL), this rank's experts on all T rows, and the rows' way back to their owners:
+ *   return_path 0  the partial rows [T, d] FP32 through ncclReduceScatter (sum);
+ *   return_path 1  every row stored, as the rank's piece, straight into its owner's receive buffer through peer-mapped
+ *                  pointers (plain stores from the combine kernel), the owner adds its `world` pieces in rank order (FP32);
+ *   return_path 2  the same with BF16 pieces (half the bytes on the links; one more rounding per piece).
+ * libnccl.so.2 is opened at run time, not linked.  sxb_ep_unique_id: rank 0 makes the communicator's id and the host sends
+ * the 128 bytes to the other ranks by its own means.  sxb_ep_create (collective, synchronizes) builds the communicator,
+ * allocates the rank's exchange buffers ONCE (device memory: T*d*2 bytes of gathered activations, plus T*d*4 (paths 0, 1) or
+ * T*d*2 (path 2)) and maps the peers' receive buffers (CUDA IPC).  The per-layer call allocates nothing and uses the
+ * caller's stream plus one stream of the library's for the activation gather. */
+typedef struct SxbEp SxbEp;
+int sxb_ep_unique_id(uint8_t id[128]);
+int sxb_ep_create(const uint8_t id[128], int world, int rank, int64_t T, int64_t d, int64_t A, int return_path, SxbEp **out);
+int sxb_ep_destroy(SxbEp *ep);
+/* args as for sxb_moe_layer with: M = the rank's rows t = T / world; x [t, d], logits [t, ld] and y [t, d] the rank's rows
+ * (y = the full sums over every rank's experts, FP32 or BF16); E, e_lo, E_total the rank's experts; no shared expert (it is
+ * not sharded: run it on the rows' owner).  The work buffers ids, coef, ws, h, partial, xs are sized for all T rows. */
+int sxb_moe_layer_ep(SxbEp *ep, const SxbMoeLayerArgs *args, sxb_stream_t stream);
+/* Phase timing for tuning: on = 1 records CUDA events at the phase boundaries of the following calls; sxb_ep_timing
+ * (synchronizes) returns the mean milliseconds a layer of {routing + route gather, wait for the activations, experts issued,
+ * exchange back, sum of the pieces} over the last `*layers` (at most 64) calls. */
+int sxb_ep_set_timing(SxbEp *ep, int on);
+int sxb_ep_timing(SxbEp *ep, float ms[5], int *layers);
+
 /* ---- Quantizers on the device ------------------------------------------------------------------------------- */
 
 /* formats/q4.hpp:32 quantize_q4 / formats/q8.hpp:32 quantize_q8, for weights already on the device: w [N, K] FP32 ->

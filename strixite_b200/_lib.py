@@ -77,6 +77,12 @@ SIGNATURES = {
     "sxb_router_prepare": (C.c_int, [vp, C.c_int, i64, i64, C.c_int, vp, vp]),
     "sxb_router_logits_wmma": (C.c_int, [vp, vp, C.c_int, vp, i64, i64, i64, vp, i64, vp]),
     "sxb_residual_add": (C.c_int, [vp, vp, C.c_int, vp, i64, vp]),
+    "sxb_ep_unique_id": (C.c_int, [vp]),
+    "sxb_ep_create": (C.c_int, [vp, C.c_int, C.c_int, i64, i64, i64, C.c_int, C.POINTER(vp)]),
+    "sxb_ep_destroy": (C.c_int, [vp]),
+    "sxb_moe_layer_ep": (C.c_int, [vp, C.POINTER(SxbMoeLayerArgs), vp]),
+    "sxb_ep_set_timing": (C.c_int, [vp, C.c_int]),
+    "sxb_ep_timing": (C.c_int, [vp, C.POINTER(C.c_float), C.POINTER(C.c_int)]),
     "sxb_moe_route_small": (C.c_int, [vp, i64, i64, i64, i64, i64, i64, vp, vp, vp, sz, vp, vp, vp]),
 }
 for _b in ("q4", "q8"):

@@ -5,6 +5,16 @@
 
 namespace sxb {
 
+// Where an expert-parallel rank's combine writes: row m of the T token rows belongs to rank m / t, and goes - as this
+// rank's piece of it - to row (rank * t + m % t) of that rank's receive buffer [world][t][N], through a peer mapping
+// (plain stores; the owner sums the pieces in rank order).
+struct PeerOut {
+    void *base[8];
+    int world, rank;
+    int64_t t;
+    int bf16;  // pieces stored as BF16 instead of FP32
+};
+
 // stream_mma.cu - exact-product kernels (mma.sync on integer codes, FP32 scale / min per group).
 template <int BITS>
 int stream_gather_grouped(const char *fn, const void *x, const SxbQView *w, int64_t E, const void *ws, size_t ws_bytes,
@@ -18,12 +28,16 @@ int stream_combine_slots(const char *fn, const void *h, const SxbQView *w, int64
                          sxb_stream_t stream);
 int combine_reduce(const char *fn, const float *partial, const int32_t *ids, const float *coef, int64_t M, int64_t A,
                    int64_t E_total, int64_t e_lo, int64_t E_local, int64_t N, void *y, int out_act,
-                   const SxbMoeSharedAdd *shared, int s_act, bool partial_bf16, sxb_stream_t stream);
+                   const SxbMoeSharedAdd *shared, int s_act, bool partial_bf16, sxb_stream_t stream,
+                   const PeerOut *peer = nullptr);
 // grouped.cu: the grouped down projection + combine behind every public combine entry (checks, dispatch on math, reduce).
 template <int BITS>
 int combine_grouped(const char *fn, const void *h, const SxbQView *w, int64_t E_view, const int32_t *ids, const float *coef,
                     const void *ws, size_t ws_bytes, float *partial, int64_t M, int64_t A, void *y, int act, int out_act,
-                    int math, sxb_stream_t stream, const SxbMoeSharedAdd *shared, int h_f16, int64_t E_total, int64_t e_lo);
+                    int math, sxb_stream_t stream, const SxbMoeSharedAdd *shared, int h_f16, int64_t E_total, int64_t e_lo,
+                    const PeerOut *peer = nullptr);
+// layer.cu: sxb_moe_layer; with `peer` the combine's rows go to their owners' receive buffers instead of y.
+int moe_layer_impl(const SxbMoeLayerArgs *a, sxb_stream_t stream, const PeerOut *peer);
 
 // grouped_tc.cu - tcgen05 kernels (F16 operands, FP32 accumulation in tensor memory).
 template <int BITS>

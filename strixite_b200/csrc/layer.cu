@@ -26,32 +26,32 @@ int combine(int bits, const void *h, const SxbQView *w, int64_t E, const int32_t
 }
 int combine_ep(int bits, const void *h, const SxbQView *w, int64_t E, int64_t E_total, int64_t e_lo, const int32_t *ids,
                const float *coef, const void *ws, size_t ws_bytes, float *partial, int64_t M, int64_t A, void *y, int out_act,
-               int math, sxb_stream_t st, int h_f16) {
-    return bits == 4 ? sxb_linear_q4_experts_combine_grouped_ep(h, w, E, E_total, e_lo, ids, coef, ws, ws_bytes, partial, M, A, y,
-                                                                SXB_ACT_BF16, out_act, math, st, h_f16)
-                     : sxb_linear_q8_experts_combine_grouped_ep(h, w, E, E_total, e_lo, ids, coef, ws, ws_bytes, partial, M, A, y,
-                                                                SXB_ACT_BF16, out_act, math, st, h_f16);
+               int math, sxb_stream_t st, int h_f16, const PeerOut *peer) {
+    const char *fn = "moe_layer (expert-parallel combine)";
+    return bits == 4 ? combine_grouped<4>(fn, h, w, E, ids, coef, ws, ws_bytes, partial, M, A, y, SXB_ACT_BF16, out_act, math, st,
+                                          nullptr, h_f16, E_total, e_lo, peer)
+                     : combine_grouped<8>(fn, h, w, E, ids, coef, ws, ws_bytes, partial, M, A, y, SXB_ACT_BF16, out_act, math, st,
+                                          nullptr, h_f16, E_total, e_lo, peer);
 }
 
 }  // namespace
-}  // namespace sxb
 
-extern "C" int sxb_moe_layer(const SxbMoeLayerArgs *a, sxb_stream_t stream) {
-    using namespace sxb;
+int moe_layer_impl(const SxbMoeLayerArgs *a, sxb_stream_t stream, const PeerOut *peer) {
     const char *fn = "moe_layer";
     SXB_CHECK(a != nullptr, fn, ": null argument block");
     SXB_CHECK(a->gate_up != nullptr && a->down != nullptr, fn, ": null weight view");
     SXB_CHECK((a->gate_up_bits == 4 || a->gate_up_bits == 8) && (a->down_bits == 4 || a->down_bits == 8), fn, ": weight bits ",
               a->gate_up_bits, " / ", a->down_bits, ", expected 4 or 8");
     SXB_CHECK(a->M >= 1 && a->E >= 1 && a->A >= 1, fn, ": M = ", a->M, ", E = ", a->E, ", A = ", a->A);
-    const bool ep = a->E_total != a->E;
+    // a peer output makes even a single rank take the expert-parallel forms of the pack and the combine
+    const bool ep = a->E_total != a->E || peer != nullptr;
     SXB_CHECK(a->E_total >= a->E && a->e_lo >= 0 && a->e_lo + a->E <= a->E_total, fn, ": experts [", a->e_lo, ", ", a->e_lo + a->E,
               ") of ", a->E_total);
     const bool shared = a->shared_gate_up != nullptr;
     SXB_CHECK(shared == (a->shared_down != nullptr), fn, ": the shared expert needs both of its weights");
     SXB_CHECK(!(shared && ep), fn, ": the shared expert is not sharded: run it on one rank, outside the expert-parallel call");
     SXB_CHECK(a->logits != nullptr || !shared, fn, ": the shared expert's gate is a column of the logits: logits must not be null");
-    SXB_CHECK(a->x != nullptr && a->y != nullptr && a->ids != nullptr && a->coef != nullptr &&
+    SXB_CHECK(a->x != nullptr && (a->y != nullptr || peer != nullptr) && a->ids != nullptr && a->coef != nullptr &&
                   a->ws != nullptr && a->h != nullptr && a->partial != nullptr && a->router_err != nullptr && a->expert_err != nullptr,
               fn, ": null buffer");
     SXB_CHECK(a->out_act == SXB_ACT_BF16 || a->out_act == SXB_ACT_F32, fn, ": output dtype ", a->out_act);
@@ -124,7 +124,7 @@ extern "C" int sxb_moe_layer(const SxbMoeLayerArgs *a, sxb_stream_t stream) {
     // down + combine (+ gated shared add) (kernels/moe_grouped.hpp:88-91)
     if (ep)
         return combine_ep(a->down_bits, a->h, a->down, E, a->E_total, a->e_lo, a->ids, a->coef, a->ws, a->ws_bytes, a->partial, M, A,
-                          a->y, a->out_act, math, stream, hf);
+                          a->y, a->out_act, math, stream, hf, peer);
     SxbMoeSharedAdd sh{};
     if (shared) {
         sh.s = a->sh_y, sh.gate_logit = a->logits + a->E_total, sh.gate_ld = a->logits_ld, sh.gate_index = (uint32_t)a->E_total;
@@ -133,3 +133,7 @@ extern "C" int sxb_moe_layer(const SxbMoeLayerArgs *a, sxb_stream_t stream) {
     return combine(a->down_bits, a->h, a->down, E, a->ids, a->coef, a->ws, a->ws_bytes, a->partial, M, A, a->y, a->out_act, math,
                    stream, shared ? &sh : nullptr, hf);
 }
+
+}  // namespace sxb
+
+extern "C" int sxb_moe_layer(const SxbMoeLayerArgs *a, sxb_stream_t stream) { return sxb::moe_layer_impl(a, stream, nullptr); }

@@ -549,6 +549,47 @@ __global__ void __launch_bounds__(256)
     for (int j = 0; j < 4; ++j) store_from_f32(y, i + j, v[j]);
 }
 
+// The same reduce for an expert-parallel rank whose rows go to their owners: no shared add, FP32 sums; the four columns
+// are stored, as this rank's piece, into the owner's receive buffer through its peer mapping (16 or 8 bytes a store).
+template <bool PBF16, bool OUT_BF16>
+__global__ void __launch_bounds__(256)
+    combine_reduce_peer_kernel(const float *__restrict__ partial, const int32_t *__restrict__ ids, const float *__restrict__ coef,
+                               int64_t M, int64_t A, int64_t E_total, int64_t e_lo, int64_t E_local, int64_t N, const PeerOut peer) {
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= M * N) return;
+    const int64_t m = i / N, n = i % N;
+    bool ok = true;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int64_t k = 0; k < A; ++k) {
+        const int32_t id = ids[m * A + k];
+        ok = ok && id >= 0 && id < E_total;
+        if (id < e_lo || id >= e_lo + E_local) continue;
+        const float cf = coef[m * A + k];
+        float4 p;
+        if constexpr (PBF16) {
+            const uint2 b = *reinterpret_cast<const uint2 *>(reinterpret_cast<const uint16_t *>(partial) + (m * A + k) * N + n);
+            p.x = __uint_as_float(b.x << 16), p.y = __uint_as_float(b.x & 0xffff0000u);
+            p.z = __uint_as_float(b.y << 16), p.w = __uint_as_float(b.y & 0xffff0000u);
+        } else {
+            p = *reinterpret_cast<const float4 *>(partial + (m * A + k) * N + n);
+        }
+        v[0] = fmaf(cf, p.x, v[0]), v[1] = fmaf(cf, p.y, v[1]), v[2] = fmaf(cf, p.z, v[2]), v[3] = fmaf(cf, p.w, v[3]);
+    }
+    if (!ok) v[0] = v[1] = v[2] = v[3] = qnan_f32();
+    const int owner = (int)(m / peer.t);
+    const int64_t at = (((int64_t)peer.rank * peer.t + m % peer.t) * N + n);
+    if constexpr (OUT_BF16) {
+        uint2 o;
+        o.x = (uint32_t)f32_to_bf16_bits(v[0]) | ((uint32_t)f32_to_bf16_bits(v[1]) << 16);
+        o.y = (uint32_t)f32_to_bf16_bits(v[2]) | ((uint32_t)f32_to_bf16_bits(v[3]) << 16);
+        *reinterpret_cast<uint2 *>(static_cast<uint16_t *>(peer.base[owner]) + at) = o;
+    } else {
+        *reinterpret_cast<float4 *>(static_cast<float *>(peer.base[owner]) + at) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    // no fence here: the stores have been performed when the kernel has completed, and the rank signals its peers only by
+    // work enqueued behind this kernel on the same stream
+}
+
 int check_view(const char *fn, const SxbQView *w) {
     SXB_CHECK(w != nullptr, fn, ": null weight view");
     SXB_CHECK(w->q != nullptr && w->scale != nullptr && w->minv != nullptr, fn, ": null weight pointer (q=",
@@ -768,7 +809,26 @@ template int stream_partial_grouped<8>(const char *, const void *, const SxbQVie
 
 int combine_reduce(const char *fn, const float *partial, const int32_t *ids, const float *coef, int64_t M, int64_t A,
                    int64_t E_total, int64_t e_lo, int64_t E_local, int64_t N, void *y, int out_act,
-                   const SxbMoeSharedAdd *shared, int s_act, bool partial_bf16, sxb_stream_t stream) {
+                   const SxbMoeSharedAdd *shared, int s_act, bool partial_bf16, sxb_stream_t stream, const PeerOut *peer) {
+    if (peer != nullptr) {
+        SXB_CHECK(partial != nullptr && ids != nullptr && coef != nullptr, fn, ": null pointer");
+        SXB_CHECK(shared == nullptr && N % 4 == 0 && aligned16(partial), fn, ": peer output takes no shared add; N = ", N);
+        SXB_CHECK(peer->world >= 1 && peer->world <= 8 && peer->t >= 1 && M == peer->t * peer->world, fn, ": ", M, " rows over ",
+                  peer->world, " ranks of ", peer->t);
+        const unsigned blocks = (unsigned)((M * N / 4 + 255) / 256);
+        auto st = static_cast<cudaStream_t>(stream);
+#define SXB_PEER(PB, OB) combine_reduce_peer_kernel<PB, OB><<<blocks, 256, 0, st>>>(partial, ids, coef, M, A, E_total, e_lo, E_local, N, *peer)
+        if (partial_bf16) {
+            if (peer->bf16) SXB_PEER(true, true);
+            else SXB_PEER(true, false);
+        } else {
+            if (peer->bf16) SXB_PEER(false, true);
+            else SXB_PEER(false, false);
+        }
+#undef SXB_PEER
+        SXB_CHECK_LAUNCH(fn, " reduce to peers M=", M, " A=", A, " N=", N);
+        return SXB_OK;
+    }
     SXB_CHECK(partial != nullptr && ids != nullptr && coef != nullptr && y != nullptr, fn, ": null pointer (partial=",
               (const void *)partial, ", ids=", (const void *)ids, ", coef=", (const void *)coef, ", y=", y, ")");
     SXB_CHECK(N % 4 == 0 && aligned16(partial), fn, ": N = ", N, " must be a multiple of 4 and partial 16-byte aligned");

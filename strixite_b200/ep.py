@@ -24,8 +24,6 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Callable, List, Optional
 
-import os
-
 import torch
 import torch.distributed as dist
 
@@ -76,8 +74,8 @@ class ExpertParallelMoe:
         self.micro = micro if (self.world > 1 and micro > 1 and compute.chunked and t % micro == 0) else 1
         self.streams = None
         self.exchange = exchange  # how the partial rows come back: "reduce_scatter" (NCCL's) or "a2a" (all-to-all + local sum)
-        # STRIX_EP_TIMING=1: CUDA events around the phases of every layer (rank-local, for tuning the exchange)
-        self.timing = [] if (os.environ.get("STRIX_EP_TIMING") and self.world > 1) else None
+        # set to a list to record CUDA events around the phases of every layer (rank-local; see timing_summary)
+        self.timing = None
         if self.world > 1:
             tc, Tc = t // self.micro, T // self.micro
             self.x_all = [torch.empty((Tc, d), dtype=torch.bfloat16, device=device) for _ in range(self.micro)]

@@ -359,12 +359,8 @@ def quantize(w: torch.Tensor, G: int, bits: int, err: Optional[torch.Tensor] = N
 
 # ---- the whole block as one call ------------------------------------------------------------------------------
 
-def moe_layer(x, logits, y, gate_up: QDeviceView, down: QDeviceView, E, A, ids, coef, ws, ws_bytes, h, partial, router_err,
-              expert_err, xs=None, math=None, E_total=None, e_lo=0, shared_gate_up: Optional[QDeviceView] = None,
-              shared_down: Optional[QDeviceView] = None, sh_gu=None, sh_h=None, sh_y=None, sh_ids=None, sh_coef=None, sh_ws=None,
-              sh_ws_bytes=0, sh_partial=None, sh_xs=None, stream=None):
-    """sxb_moe_layer: router, grouping, gate/up + SwiGLU, down + combine (+ shared expert) enqueued by one C call.
-    x [M, d] BF16, logits [M, ld] FP32, y [M, d] BF16 or FP32; the rest are the caller's work buffers."""
+def _layer_args(x, logits, y, gate_up, down, E, A, ids, coef, ws, ws_bytes, h, partial, router_err, expert_err, xs, math, E_total,
+                e_lo, shared_gate_up, shared_down, sh_gu, sh_h, sh_y, sh_xs):
     M = x.shape[0]
     gu, dn = gate_up.c(), down.c()
     a = _lib.SxbMoeLayerArgs()
@@ -380,10 +376,61 @@ def moe_layer(x, logits, y, gate_up: QDeviceView, down: QDeviceView, E, A, ids, 
     a.math = -1 if math is None else int(math)
     a.ids, a.coef, a.ws, a.ws_bytes, a.h, a.partial = _ptr(ids), _ptr(coef), _ptr(ws), ws_bytes, _ptr(h), _ptr(partial)
     a.xs = _ptr(xs) if xs is not None else None
-    for name, t in (("sh_gu", sh_gu), ("sh_h", sh_h), ("sh_y", sh_y), ("sh_ids", sh_ids), ("sh_coef", sh_coef), ("sh_ws", sh_ws),
-                    ("sh_partial", sh_partial), ("sh_xs", sh_xs)):
+    for name, t in (("sh_gu", sh_gu), ("sh_h", sh_h), ("sh_y", sh_y), ("sh_xs", sh_xs)):
         setattr(a, name, _ptr(t) if t is not None else None)
-    a.sh_ws_bytes = sh_ws_bytes
     a.router_err, a.expert_err = _ptr(router_err), _ptr(expert_err)
+    return a, keep
+
+
+def moe_layer(x, logits, y, gate_up: QDeviceView, down: QDeviceView, E, A, ids, coef, ws, ws_bytes, h, partial, router_err,
+              expert_err, xs=None, math=None, E_total=None, e_lo=0, shared_gate_up: Optional[QDeviceView] = None,
+              shared_down: Optional[QDeviceView] = None, sh_gu=None, sh_h=None, sh_y=None, sh_xs=None, stream=None):
+    """sxb_moe_layer: router, grouping, gate/up + SwiGLU, down + combine (+ shared expert) enqueued by one C call.
+    x [M, d] BF16, logits [M, ld] FP32 (None: ids / coef already hold the routes), y [M, d] BF16 or FP32; the rest are the
+    caller's work buffers."""
+    a, keep = _layer_args(x, logits, y, gate_up, down, E, A, ids, coef, ws, ws_bytes, h, partial, router_err, expert_err, xs, math,
+                          E_total, e_lo, shared_gate_up, shared_down, sh_gu, sh_h, sh_y, sh_xs)
     _count(8)
     _check(_lib.load().sxb_moe_layer(C.byref(a), _stream(stream)))
+
+
+# ---- expert parallelism over the C ABI (no counterpart in the reference) ------------------------------------------
+
+def ep_unique_id() -> bytes:
+    buf = (C.c_uint8 * 128)()
+    _check(_lib.load().sxb_ep_unique_id(buf))
+    return bytes(buf)
+
+
+class EpContext:
+    """A rank's expert-parallel context (sxb_ep_create): NCCL communicator, exchange buffers, peer mappings.
+    return_path: 0 reduce-scatter, 1 peer stores of FP32 pieces, 2 of BF16 pieces."""
+
+    def __init__(self, unique_id: bytes, world: int, rank: int, T: int, d: int, A: int, return_path: int = 1):
+        self.handle = C.c_void_p()
+        idb = (C.c_uint8 * 128).from_buffer_copy(unique_id)
+        _check(_lib.load().sxb_ep_create(idb, world, rank, T, d, A, return_path, C.byref(self.handle)))
+        self.world, self.rank, self.T, self.return_path = world, rank, T, return_path
+
+    def layer(self, x_loc, logits_loc, y_loc, gate_up: QDeviceView, down: QDeviceView, E_local, E_total, e_lo, A, ids, coef, ws,
+              ws_bytes, h, partial, router_err, expert_err, xs=None, math=None, stream=None):
+        """sxb_moe_layer_ep on this rank's rows; ids / coef / ws / h / partial / xs are sized for all T rows."""
+        a, keep = _layer_args(x_loc, logits_loc, y_loc, gate_up, down, E_local, A, ids, coef, ws, ws_bytes, h, partial, router_err,
+                              expert_err, xs, math, E_total, e_lo, None, None, None, None, None, None)
+        _count(9)
+        _check(_lib.load().sxb_moe_layer_ep(self.handle, C.byref(a), _stream(stream)))
+
+    def set_timing(self, on: bool):
+        _check(_lib.load().sxb_ep_set_timing(self.handle, int(on)))
+
+    def timing(self) -> dict:
+        ms = (C.c_float * 5)()
+        n = C.c_int()
+        _check(_lib.load().sxb_ep_timing(self.handle, ms, C.byref(n)))
+        names = ("route", "gather_wait", "experts", "return", "sum")
+        return {"layers": n.value, **{k: float(v) for k, v in zip(names, ms)}}
+
+    def close(self):
+        if self.handle:
+            _lib.load().sxb_ep_destroy(self.handle)
+            self.handle = C.c_void_p()
