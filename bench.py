@@ -58,6 +58,8 @@ def parse():
                     help="expert-parallel driver: the library's C entry point sxb_moe_layer_ep, or torch.distributed (strixite_b200/ep.py)")
     ap.add_argument("--return-path", dest="return_path", type=int, default=1,
                     help="native driver, rows back to their owners: 0 NCCL reduce-scatter, 1 peer stores of FP32 pieces, 2 of BF16 pieces")
+    ap.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
+                    help="expert-parallel runs: experts dealt to ranks by calibrated load, or expert e on rank e // (E / N)")
     ap.add_argument("--math", default="", help="tcgen05 numerics: wmma_f16 (BF16 per-slot dots, the reference's) or wmma_f16_f32p")
     return ap.parse_args()
 
@@ -136,7 +138,7 @@ class Stack:
     """Resident state of a configuration on this rank: per-layer weights (this rank's experts), router weights, biases,
     the shared workspaces, and the expert-parallel driver."""
 
-    def __init__(self, cfg, layers, seed, dev, rank, world, micro=0, planes=3, ep_impl="native", return_path=1):
+    def __init__(self, cfg, layers, seed, dev, rank, world, micro=0, planes=3, ep_impl="native", return_path=1, placement="balanced"):
         import torch
         from strixite_b200 import workloads as W
         from strixite_b200.ep import Compute, ExpertParallelMoe, shard_bounds
@@ -158,13 +160,16 @@ class Stack:
         self.bufs = [MoeBuffers(Tc, cfg.d, cfg.I, E_local, cfg.k, dev, cfg.shared and world == 1) for _ in range(micro)]
         self.buf = self.bufs[0]
         self.layer_sets = [[] for _ in range(micro)]
-        self.wr, self.bias = [], []
+        self.wr, self.bias, self.order = [], [], []
         for l in range(layers):
-            w = W.make_layer_weights(cfg, seed, dev, layer=l, e_lo=self.e_lo, e_hi=self.e_hi)
+            order = W.expert_placement(cfg, seed, dev, l, world, placement)  # which expert sits where (identity on one GPU)
+            w = W.make_layer_weights(cfg, seed, dev, layer=l, e_lo=self.e_lo, e_hi=self.e_hi, order=order)
             for c in range(micro):
                 self.layer_sets[c].append(MoeLayer(w, E_local, cfg.k, self.bufs[c], E_total=cfg.E, e_lo=self.e_lo))
-            self.wr.append(W.router_weight(cfg, seed, dev, layer=l))
-            self.bias.append(W.expert_bias(cfg, seed, dev, layer=l))
+            wr, bias = W.placed_router(cfg, seed, dev, l, order)
+            self.wr.append(wr)
+            self.bias.append(bias)
+            self.order.append(order)
         self.layers = self.layer_sets[0]
         # The router-logits projection is the library's: the tensor-core form over the weight split into BF16 planes at
         # load time for prefill-sized batches, the streaming form (the FP32 weight as it is) for decode.
@@ -322,11 +327,13 @@ def run_stack(cfg, args, dev, rank, world, peaks, layers=None, rotate=False):
     """Times a configuration.  rotate: a step runs ONE layer, cycling through the resident layers so consecutive steps
     never find their weights in L2 (decode); otherwise a step runs the whole stack."""
     import torch
+    import torch.distributed as dist
     from strixite_b200 import kernels as K, workloads as W
 
     layers = layers or args.layers or cfg.layers
     st = Stack(cfg, layers, args.seed, dev, rank, world, micro=getattr(args, "micro", 0), planes=getattr(args, "planes", 3),
-               ep_impl=getattr(args, "ep", "native"), return_path=getattr(args, "return_path", 1))
+               ep_impl=getattr(args, "ep", "native"), return_path=getattr(args, "return_path", 1),
+               placement=getattr(args, "placement", "balanced"))
     if getattr(args, "math", ""):
         from strixite_b200.kernels import MoeMath
         st.math_tc = {"wmma_f16": MoeMath.WmmaF16, "wmma_f16_f32p": MoeMath.WmmaF16F32Partials}[args.math]
@@ -624,7 +631,7 @@ def parity_check(cfg, st, x_loc, args, dev, rank):
         if cfg.shared:
             w = st.layers[l].w
             shared = (check.download(w.shared_gate_up, cpu), check.download(w.shared_down, cpu))
-        ref = check.oracle_layer_with(cpu, cfg, check.generated_experts(cfg, args.seed, l, dev), shared, xb, lg, sem)
+        ref = check.oracle_layer_with(cpu, cfg, check.generated_experts(cfg, args.seed, l, dev, st.order[l]), shared, xb, lg, sem)
         ids_ok = ids_ok and bool(np.array_equal(ref["ids"], ids))
         err = check.max_abs_over_rms(y, ref["y_f32"])
         worst = max(worst, err)
@@ -716,7 +723,7 @@ def main():
     if res.get("ep_info"):
         line["expert_parallel"] = {"driver": "sxb_moe_layer_ep" if st.native is not None else "torch.distributed (ep.py)",
                                    "return_path": {0: "nccl reduce-scatter (fp32)", 1: "peer stores, fp32 pieces", 2: "peer stores, bf16 pieces"}[args.return_path]
-                                   if st.native is not None else st.ep.exchange, "per_rank": res["ep_info"]}
+                                   if st.native is not None else st.ep.exchange, "placement": args.placement, "per_rank": res["ep_info"]}
     if args.parity_rows > 0:
         try:
             par = parity_check(cfg, st, res["x_full"][st.t_lo:st.t_hi].contiguous(), args, dev, rank)

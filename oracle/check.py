@@ -77,11 +77,12 @@ def oracle_layer_on_touched_experts(oracle, cfg, w, x_bits, logits, rows, semant
     return oracle_layer_with(oracle, cfg, fetch, shared, x_bits[rows], logits[rows], semantics, threads)
 
 
-def generated_experts(cfg, seed, layer, device):
+def generated_experts(cfg, seed, layer, device, order=None):
     """fetch() for oracle_layer_with that REGENERATES the asked experts of a synthetic layer instead of downloading them
     (strixite_b200.workloads draws every expert from its own seeded generator): any rank can check rows routed to experts
     it does not hold.  Quantized on the device when there is one (bit-identical to the reference's quantizer), else by the
-    oracle's quantizer on the host."""
+    oracle's quantizer on the host.  order: the experts' placement (position p holds expert order[p]; the ids asked for
+    are positions)."""
     import torch
     from strixite_b200 import workloads as W
 
@@ -90,7 +91,7 @@ def generated_experts(cfg, seed, layer, device):
         G = cfg.group(bits)
         parts = []
         for e in experts:
-            w32 = W.expert_weight_f32(cfg, seed, device, which, int(e), layer)
+            w32 = W.expert_weight_f32(cfg, seed, device, which, int(e) if order is None else int(order[int(e)]), layer)
             if torch.device(device).type == "cuda":
                 from strixite_b200 import kernels as K
                 parts.append(download(K.quantize(w32, G, bits), cpu))

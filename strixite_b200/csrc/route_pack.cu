@@ -193,11 +193,19 @@ __global__ void __launch_bounds__(kPackThreads)
     const int b = threadIdx.x, E = (int)L.E;
     int total = 0;
     if (b <= E) {
+        // sixteen segments at a time: the loads of a chunk are independent of one another (a chain of dependent
+        // read-modify-writes over 160 segments was most of this launch)
         int32_t *col = ws + L.scratch + b;
-        for (int seg = 0; seg < L.nseg; ++seg) {
-            const int c = col[(int64_t)seg * (E + 1)];
-            col[(int64_t)seg * (E + 1)] = total;
-            total += c;
+        const int64_t stride = E + 1;
+        for (int seg0 = 0; seg0 < L.nseg; seg0 += 16) {
+            int c[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) c[i] = seg0 + i < L.nseg ? col[(int64_t)(seg0 + i) * stride] : 0;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                if (seg0 + i < L.nseg) col[(int64_t)(seg0 + i) * stride] = total;
+                total += c[i];
+            }
         }
     }
     int bad = 0x7fffffff;

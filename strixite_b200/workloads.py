@@ -103,9 +103,41 @@ def expert_weight_f32(cfg: MoeConfig, seed: int, device, which: str, expert: int
     return torch.randn(shape, generator=gen(seed, f"{which}.{layer}.{expert}", device), device=device) * 0.02
 
 
-def make_layer_weights(cfg: MoeConfig, seed: int, device, layer: int = 0, e_lo: int = 0, e_hi: Optional[int] = None):
+def expert_placement(cfg: MoeConfig, seed: int, device, layer: int, world: int, mode: str = "balanced", calib_tokens: int = 4096):
+    """Which expert sits where in an expert-parallel run: a list `order` of the E expert ids, rank r holding the experts
+    order[r E / world : (r + 1) E / world] (every rank the same number).  Relabelling experts this way changes nothing
+    in the model: the router weight's rows and the experts move together.
+      "contiguous": expert e at position e.
+      "balanced":   by observed load, as a serving engine places experts from its routing statistics: a calibration batch
+                    (other activations than the measured ones: seed + 1000) is routed once, an expert's cost is the
+                    128-token tiles it fills, and experts are dealt, heaviest first, to the least loaded rank that still
+                    has room.  With a Zipf-skewed router the contiguous split leaves one rank 1.5-1.9x the mean load."""
+    if world == 1 or mode == "contiguous":
+        return list(range(cfg.E))
+    x = activations(cfg, seed + 1000, device, T=calib_tokens).float()
+    logits = x @ router_weight(cfg, seed, device, layer).t() + expert_bias(cfg, seed, device, layer)
+    ids = logits[:, : cfg.E].topk(cfg.k, dim=1).indices.reshape(-1)
+    cnt = torch.bincount(ids, minlength=cfg.E).cpu().double() * (cfg.T / calib_tokens)
+    cost = torch.ceil(cnt / 128.0) + 1e-3 * cnt
+    cap = cfg.E // world
+    load, members = [0.0] * world, [[] for _ in range(world)]
+    for e in sorted(range(cfg.E), key=lambda i: (-float(cost[i]), i)):
+        r = min((r for r in range(world) if len(members[r]) < cap), key=lambda r: (load[r], r))
+        members[r].append(e)
+        load[r] += float(cost[e])
+    return [e for r in range(world) for e in sorted(members[r])]
+
+
+def placed_router(cfg: MoeConfig, seed: int, device, layer: int, order):
+    """Router weight [E + 1, d] and bias [E + 1] with their expert rows in placement order (row E, the shared gate, last)."""
+    rows = torch.tensor(list(order) + [cfg.E], device=device)
+    return router_weight(cfg, seed, device, layer)[rows].contiguous(), expert_bias(cfg, seed, device, layer)[rows].contiguous()
+
+
+def make_layer_weights(cfg: MoeConfig, seed: int, device, layer: int = 0, e_lo: int = 0, e_hi: Optional[int] = None, order=None):
     """Draws and quantizes one layer's experts [e_lo, e_hi) on the device (FP32 never leaves it), expert by expert so
-    that a rank holding a slice of the experts gets the same bytes as a rank holding them all.
+    that a rank holding a slice of the experts gets the same bytes as a rank holding them all.  order: the expert at
+    position p is expert order[p] (expert_placement); None = in their own order.
     Returns strixite_b200.layer.MoeWeights with the experts stacked along N."""
     from . import kernels as K
     from .layer import MoeWeights
@@ -119,7 +151,8 @@ def make_layer_weights(cfg: MoeConfig, seed: int, device, layer: int = 0, e_lo: 
         s = torch.empty((n * rows, cols // G), dtype=torch.int16, device=device)
         m = torch.empty((n * rows, cols // G), dtype=torch.int16, device=device)
         err = torch.zeros(4, dtype=torch.int32, device=device)
-        for i, e in enumerate(range(e_lo, e_hi)):
+        for i, pos in enumerate(range(e_lo, e_hi)):
+            e = pos if order is None else order[pos]
             v = K.quantize(expert_weight_f32(cfg, seed, device, which, e, layer), G, bits, err=err)
             q[i * rows:(i + 1) * rows] = v.q
             s[i * rows:(i + 1) * rows] = v.scale
