@@ -60,6 +60,8 @@ def parse():
                     help="native driver, rows back to their owners: 0 NCCL reduce-scatter, 1 peer stores of FP32 pieces, 2 of BF16 pieces")
     ap.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
                     help="expert-parallel runs: experts dealt to ranks by calibrated load, or expert e on rank e // (E / N)")
+    ap.add_argument("--stage", default="tiles", choices=["tiles", "rows"],
+                    help="tcgen05 gate/up activations: gathered once into the tile-blocked form, or converted once and gathered per tile")
     ap.add_argument("--math", default="", help="tcgen05 numerics: wmma_f16 (BF16 per-slot dots, the reference's) or wmma_f16_f32p")
     return ap.parse_args()
 
@@ -334,6 +336,10 @@ def run_stack(cfg, args, dev, rank, world, peaks, layers=None, rotate=False):
     st = Stack(cfg, layers, args.seed, dev, rank, world, micro=getattr(args, "micro", 0), planes=getattr(args, "planes", 3),
                ep_impl=getattr(args, "ep", "native"), return_path=getattr(args, "return_path", 1),
                placement=getattr(args, "placement", "balanced"))
+    if getattr(args, "stage", "tiles") == "rows":
+        for ls in st.layer_sets:
+            for ly in ls:
+                ly.stage_rows = True
     if getattr(args, "math", ""):
         from strixite_b200.kernels import MoeMath
         st.math_tc = {"wmma_f16": MoeMath.WmmaF16, "wmma_f16_f32p": MoeMath.WmmaF16F32Partials}[args.math]

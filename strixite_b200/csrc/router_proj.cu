@@ -25,8 +25,9 @@ namespace {
 
 // ---- streaming form ------------------------------------------------------------------------------------------
 
-constexpr int kStreamWarps = 4;   // warps of a CTA: each takes a quarter of the row's k range
-constexpr int kTokChunk = 16;     // tokens whose sums a lane keeps in registers at a time
+constexpr int kStreamWarps = 8;   // warps of a CTA = weight rows it takes at a time
+constexpr int kTokChunk = 16;     // tokens whose activations sit in shared memory (and whose sums a lane keeps)
+constexpr int kStreamKTile = 4096;  // k range staged at a time: 16 tokens x 4096 x 2 bytes = 128 KB of shared memory
 
 __device__ inline void load_w8(const float *p, float (&w)[8]) {
     const float4 a = __ldg(reinterpret_cast<const float4 *>(p)), b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
@@ -39,41 +40,58 @@ __device__ inline void load_w8(const uint16_t *p, float (&w)[8]) {
     for (int i = 0; i < 4; ++i) w[2 * i] = __uint_as_float(u[i] << 16), w[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
 }
 
-// y[m, n] = sum_k x[m, k] * w[n, k] (+ bias[n]).  One CTA per weight row n: its bytes are streamed once, every warp a
-// contiguous quarter of the k range in runs of eight per lane, all loads of a run independent of one another; a lane keeps
-// the sums of 16 tokens.  The sum of a (token, row) pair is formed in a fixed order: per lane ascending k, an xor butterfly
-// inside the warp, then the four warps' parts in warp order.
+// y[m, n] = sum_k x[m, k] * w[n, k] (+ bias[n]).  A CTA stages the activations of 16 tokens in shared memory once and its
+// eight warps then stream one weight row each against them (lanes strided over k in runs of eight: a row's bytes are
+// read once, by 16-byte loads that are independent of one another), so the activations cross L2 once per eight rows.
+// The sum of a (token, row) pair is formed in a fixed order: per lane ascending k, then an xor butterfly.
 template <typename TW, typename TOUT>
 __global__ void __launch_bounds__(32 * kStreamWarps)
     logits_stream_kernel(const uint16_t *__restrict__ x, const TW *__restrict__ w, const float *__restrict__ bias, int64_t M,
                          int64_t N, int64_t K, TOUT *__restrict__ y, int64_t ld) {
-    __shared__ float part[kStreamWarps][kTokChunk];
+    extern __shared__ __align__(16) unsigned char xs_raw[];
+    uint4 *xs = reinterpret_cast<uint4 *>(xs_raw);  // [kTokChunk][kt / 8] chunks of eight BF16
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int64_t n = blockIdx.x;
-    const TW *wr = w + n * K;
-    const float b = bias ? bias[n] : 0.f;
-    // this warp's k range: a quarter of the row, rounded to the 256 k a warp covers per step
-    const int64_t steps = (K + 255) / 256, per = (steps + kStreamWarps - 1) / kStreamWarps;
-    const int64_t k_lo = (int64_t)warp * per * 256, k_hi = min(K, k_lo + per * 256);
+    const int64_t n = (int64_t)blockIdx.x * kStreamWarps + warp;
+    const bool row_ok = n < N;
+    const TW *wr = w + (row_ok ? n : 0) * K;
+    const float b = (row_ok && bias) ? bias[n] : 0.f;
     for (int64_t m0 = 0; m0 < M; m0 += kTokChunk) {
         const int live = (int)min((int64_t)kTokChunk, M - m0);
         float acc[kTokChunk];
 #pragma unroll
         for (int t = 0; t < kTokChunk; ++t) acc[t] = 0.f;
-        for (int64_t k = k_lo + lane * 8; k < k_hi; k += 256) {
-            float wv[8];
-            load_w8(wr + k, wv);
-            uint4 xv[kTokChunk];
+        for (int64_t k0 = 0; k0 < K; k0 += kStreamKTile) {
+            const int kt = (int)min((int64_t)kStreamKTile, K - k0), chunks = kt / 8;
+            __syncthreads();  // every warp is done with the previous tile
+            for (int i = threadIdx.x; i < kTokChunk * chunks; i += 32 * kStreamWarps) {
+                const int t = i / chunks, c = i % chunks;
+                xs[i] = t < live ? __ldg(reinterpret_cast<const uint4 *>(x + (m0 + t) * K + k0) + c) : make_uint4(0u, 0u, 0u, 0u);
+            }
+            __syncthreads();
+            if (row_ok) {
+                // four runs of the row in flight at a time: their loads are issued before any of them is consumed
+                for (int c0 = lane; c0 < chunks; c0 += 4 * 32) {
+                    float wv[4][8];
 #pragma unroll
-            for (int t = 0; t < kTokChunk; ++t)
-                xv[t] = t < live ? __ldg(reinterpret_cast<const uint4 *>(x + (m0 + t) * K + k)) : make_uint4(0u, 0u, 0u, 0u);
+                    for (int j = 0; j < 4; ++j) {
+                        const int c = c0 + 32 * j;
+                        if (c < chunks) load_w8(wr + k0 + (int64_t)c * 8, wv[j]);
+                    }
 #pragma unroll
-            for (int t = 0; t < kTokChunk; ++t) {
-                const uint32_t u[4] = {xv[t].x, xv[t].y, xv[t].z, xv[t].w};
+                    for (int j = 0; j < 4; ++j) {
+                        const int c = c0 + 32 * j;
+                        if (c >= chunks) break;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    acc[t] = fmaf(__uint_as_float(u[i] << 16), wv[2 * i], acc[t]);
-                    acc[t] = fmaf(__uint_as_float(u[i] & 0xffff0000u), wv[2 * i + 1], acc[t]);
+                        for (int t = 0; t < kTokChunk; ++t) {
+                            const uint4 xv = xs[t * chunks + c];
+                            const uint32_t u[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                acc[t] = fmaf(__uint_as_float(u[i] << 16), wv[j][2 * i], acc[t]);
+                                acc[t] = fmaf(__uint_as_float(u[i] & 0xffff0000u), wv[j][2 * i + 1], acc[t]);
+                            }
+                        }
+                    }
                 }
             }
         }
@@ -81,16 +99,8 @@ __global__ void __launch_bounds__(32 * kStreamWarps)
         for (int t = 0; t < kTokChunk; ++t) {
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], off);
-            if (lane == 0) part[warp][t] = acc[t];
+            if (lane == 0 && row_ok && t < live) store_from_f32(y, (m0 + t) * ld + n, acc[t] + b);
         }
-        __syncthreads();
-        if (threadIdx.x < live) {
-            float v = part[0][threadIdx.x];
-#pragma unroll
-            for (int wq = 1; wq < kStreamWarps; ++wq) v += part[wq][threadIdx.x];
-            store_from_f32(y, (m0 + threadIdx.x) * ld + n, v + b);
-        }
-        __syncthreads();
     }
 }
 
@@ -340,11 +350,17 @@ int check_proj(const char *fn, const void *x, const void *w, const void *y, int6
 template <typename TOUT>
 int launch_stream_logits(const char *fn, const void *x, const void *w, int w_act, const float *bias, int64_t M, int64_t N, int64_t K,
                          TOUT *y, int64_t ld, cudaStream_t st) {
-    const unsigned blocks = (unsigned)N;  // one CTA per weight row
-    if (w_act == SXB_ACT_F32)
-        logits_stream_kernel<float, TOUT><<<blocks, 32 * kStreamWarps, 0, st>>>((const uint16_t *)x, (const float *)w, bias, M, N, K, y, ld);
-    else
-        logits_stream_kernel<uint16_t, TOUT><<<blocks, 32 * kStreamWarps, 0, st>>>((const uint16_t *)x, (const uint16_t *)w, bias, M, N, K, y, ld);
+    const unsigned blocks = (unsigned)((N + kStreamWarps - 1) / kStreamWarps);
+    const size_t smem = (size_t)kTokChunk * std::min<int64_t>(K, kStreamKTile) * 2;
+    if (w_act == SXB_ACT_F32) {
+        auto kern = logits_stream_kernel<float, TOUT>;
+        SXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn, ": reserving shared memory");
+        kern<<<blocks, 32 * kStreamWarps, smem, st>>>((const uint16_t *)x, (const float *)w, bias, M, N, K, y, ld);
+    } else {
+        auto kern = logits_stream_kernel<uint16_t, TOUT>;
+        SXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn, ": reserving shared memory");
+        kern<<<blocks, 32 * kStreamWarps, smem, st>>>((const uint16_t *)x, (const uint16_t *)w, bias, M, N, K, y, ld);
+    }
     SXB_CHECK_LAUNCH(fn, " M=", M, " N=", N, " K=", K);
     return SXB_OK;
 }

@@ -257,26 +257,14 @@ __device__ inline void rows_dot_impl(float (&acc)[4], const StreamArgs &a, int64
     }
 }
 
-// A warp's weights in flight: the codes of four steps of rows a / b and the scales / mins of that block.  The state
-// outlives a call of rows_dot_fast: while a warp consumes the LAST block of one unit it already fetches the first block of
-// its next unit, so the stream of loads does not drain at every unit boundary (a down projection's unit is only two
-// blocks long: without this, half of its time is the ramp).
-template <int BITS, int G>
-struct Pipe {
-    uint32_t wa[kPrefetch][Geo<BITS, G>::kWords], wb[kPrefetch][Geo<BITS, G>::kWords];
-    uint2 qv[4];  // {scale a, min a, scale b, min b} of the block in the registers
-    bool primed;  // the first block of the coming unit is already in flight
-};
-
 // The common shape, kept lean because the kernel saturates the integer pipe before HBM: a step is one group, the row has
 // a whole number of four-step blocks, scales and mins come by aligned 8-byte loads.  No per-load predicates (a row past
 // the end of the expert is replaced by a row that exists; its sums are dropped by the caller), pointers advance by
-// increments, and a step's first MMA takes a zero accumulator operand instead of cleared registers.  has_next: the warp's
-// next unit streams the rows next_delta below these (same expert, same tile of tokens, all of them inside the expert);
-// its first block is fetched into the registers the last block of this unit frees.
+// increments, the last block is peeled so nothing is fetched past the end of a row, and a step's first MMA takes a
+// zero accumulator operand instead of cleared registers.
 template <int BITS, int G>
 __device__ inline void rows_dot_fast(float (&acc)[4], const StreamArgs &a, int64_t rowa, int64_t rowb, const uint4 *xs,
-                                     const float *xsum, int lane, Pipe<BITS, G> &pipe, bool has_next, int next_delta) {
+                                     const float *xsum, int lane) {
     using geo = Geo<BITS, G>;
     constexpr int W = geo::kWords, UNITS = geo::kUnits, KI = geo::kStepCodes;
     constexpr int kBlockBytes = kPrefetch * 4 * geo::kLoadBytes;  // bytes of one row consumed per block of four steps
@@ -289,10 +277,11 @@ __device__ inline void rows_dot_fast(float (&acc)[4], const StreamArgs &a, int64
     const uint4 *xu = xs + lane;
     const float *xq = xsum + 2 * c;
 
-    uint2 qn[4];  // scales / mins of the next block
+    uint32_t wa[kPrefetch][W], wb[kPrefetch][W];
+    uint2 qv[4], qn[4];  // {scale a, min a, scale b, min b} of the block in use / of the next one
     auto fetch_codes = [&](int p) {  // step p of the block pa / pb point at
-        load_codes<W>(pipe.wa[p], pa + p * 4 * geo::kLoadBytes, true);
-        load_codes<W>(pipe.wb[p], pb + p * 4 * geo::kLoadBytes, true);
+        load_codes<W>(wa[p], pa + p * 4 * geo::kLoadBytes, true);
+        load_codes<W>(wb[p], pb + p * 4 * geo::kLoadBytes, true);
     };
     auto fetch_scales = [&](uint2 (&dst)[4]) { dst[0] = __ldg(sa), dst[1] = __ldg(ma), dst[2] = __ldg(sb), dst[3] = __ldg(mb); };
     auto consume = [&](int p) {
@@ -301,7 +290,7 @@ __device__ inline void rows_dot_fast(float (&acc)[4], const StreamArgs &a, int64
         for (int v = 0; v < UNITS; ++v) {
             const uint4 bx = xu[(p * UNITS + v) * 32];
             if (BITS == 4) {
-                const uint32_t x0 = pipe.wa[p][v], x1 = pipe.wb[p][v];
+                const uint32_t x0 = wa[p][v], x1 = wb[p][v];
                 if (v == 0) mma_bf16_first(d, nibble_pair16<0>(x0), nibble_pair16<0>(x1), nibble_pair16<1>(x0), nibble_pair16<1>(x1), bx.x, bx.y);
                 else mma_bf16(d, nibble_pair16<0>(x0), nibble_pair16<0>(x1), nibble_pair16<1>(x0), nibble_pair16<1>(x1), bx.x, bx.y);
                 mma_bf16(d, nibble_pair16<2>(x0), nibble_pair16<2>(x1), nibble_pair16<3>(x0), nibble_pair16<3>(x1), bx.z, bx.w);
@@ -309,7 +298,7 @@ __device__ inline void rows_dot_fast(float (&acc)[4], const StreamArgs &a, int64
                 const uint32_t bw[4] = {bx.x, bx.y, bx.z, bx.w};
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const uint32_t x0 = pipe.wa[p][2 * v + h], x1 = pipe.wb[p][2 * v + h];
+                    const uint32_t x0 = wa[p][2 * v + h], x1 = wb[p][2 * v + h];
                     if (v == 0 && h == 0)
                         mma_bf16_first(d, nibble_pair<0>(x0), nibble_pair<0>(x1), nibble_pair<1>(x0), nibble_pair<1>(x1), bw[0], times16(bw[0]));
                     else
@@ -322,8 +311,8 @@ __device__ inline void rows_dot_fast(float (&acc)[4], const StreamArgs &a, int64
         const float2 xs2 = *reinterpret_cast<const float2 *>(xq + p * kTileTokens);
         // BF16 bits -> FP32: the upper half of the word as it is, the lower half shifted up
         auto f32_of = [&](const uint2 &q) { const uint32_t w = p < 2 ? q.x : q.y; return __uint_as_float((p & 1) ? (w & 0xffff0000u) : (w << 16)); };
-        const float s_a = f32_of(pipe.qv[0]), s_b = f32_of(pipe.qv[2]);
-        float m_a = f32_of(pipe.qv[1]), m_b = f32_of(pipe.qv[3]);
+        const float s_a = f32_of(qv[0]), s_b = f32_of(qv[2]);
+        float m_a = f32_of(qv[1]), m_b = f32_of(qv[3]);
         if (BITS == 4) m_a = fmaf(-16.f, s_a, m_a), m_b = fmaf(-16.f, s_b, m_b);  // the 16s of nibble_pair16
         acc[0] = fmaf(s_a, d[0], fmaf(m_a, xs2.x, acc[0]));
         acc[1] = fmaf(s_a, d[1], fmaf(m_a, xs2.y, acc[1]));
@@ -331,11 +320,9 @@ __device__ inline void rows_dot_fast(float (&acc)[4], const StreamArgs &a, int64
         acc[3] = fmaf(s_b, d[3], fmaf(m_b, xs2.y, acc[3]));
     };
 
-    if (!pipe.primed) {
-        fetch_scales(pipe.qv);
+    fetch_scales(qv);
 #pragma unroll
-        for (int p = 0; p < kPrefetch; ++p) fetch_codes(p);
-    }
+    for (int p = 0; p < kPrefetch; ++p) fetch_codes(p);
     for (int b = 1; b < blocks; ++b) {  // consume block b - 1, fetching block b into the registers it frees
         pa += kBlockBytes, pb += kBlockBytes, ++sa, ++ma, ++sb, ++mb;
         fetch_scales(qn);
@@ -345,49 +332,24 @@ __device__ inline void rows_dot_fast(float (&acc)[4], const StreamArgs &a, int64
             fetch_codes(p);
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) pipe.qv[i] = qn[i];
+        for (int i = 0; i < 4; ++i) qv[i] = qn[i];
         xu += kPrefetch * UNITS * 32, xq += kPrefetch * kTileTokens;
     }
-    // the last block; nothing is fetched past the end of a row: the freed registers take the next unit's first block
-    if (has_next) {
-        const int64_t nexta = rowa + next_delta, nextb = rowb + next_delta;
-        pa = a.q + nexta * row_bytes + c * geo::kLoadBytes, pb = a.q + nextb * row_bytes + c * geo::kLoadBytes;
-        sa = reinterpret_cast<const uint2 *>(a.scale + nexta * groups), ma = reinterpret_cast<const uint2 *>(a.minv + nexta * groups);
-        sb = reinterpret_cast<const uint2 *>(a.scale + nextb * groups), mb = reinterpret_cast<const uint2 *>(a.minv + nextb * groups);
-        fetch_scales(qn);
 #pragma unroll
-        for (int p = 0; p < kPrefetch; ++p) {
-            consume(p);
-            fetch_codes(p);
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) pipe.qv[i] = qn[i];
-    } else {
-#pragma unroll
-        for (int p = 0; p < kPrefetch; ++p) consume(p);
-    }
-    pipe.primed = has_next;
+    for (int p = 0; p < kPrefetch; ++p) consume(p);
 }
 
-// Whether the lean form applies to this weight (uniform over a launch).
-template <int BITS, int G>
-__device__ inline bool fast_shape(const StreamArgs &a) {
-    using geo = Geo<BITS, G>;
-    const int groups = (int)(a.K / G);
-    return geo::kStepsPerGroup == 1 && groups % 4 == 0 &&
-           ((reinterpret_cast<uintptr_t>(a.scale) | reinterpret_cast<uintptr_t>(a.minv)) & 7) == 0;
-}
-
-// One unit of a warp.  has_next / next_delta: see rows_dot_fast (ignored by the general form).
 template <int BITS, int G>
 __device__ inline void rows_dot(float (&acc)[4], const StreamArgs &a, int64_t rowa, int64_t rowb, bool va, bool vb,
-                                const uint4 *xs, const float *xsum, int lane, Pipe<BITS, G> &pipe, bool has_next = false,
-                                int next_delta = 0) {
+                                const uint4 *xs, const float *xsum, int lane) {
     using geo = Geo<BITS, G>;
-    if (geo::kStepsPerGroup == 1 && fast_shape<BITS, G>(a)) {
+    const int groups = (int)(a.K / G);
+    const bool vec = geo::kStepsPerGroup == 1 && groups % 4 == 0 &&
+                     ((reinterpret_cast<uintptr_t>(a.scale) | reinterpret_cast<uintptr_t>(a.minv)) & 7) == 0;
+    if (vec && geo::kStepsPerGroup == 1) {
         // rows past the end of the expert: stream a row that exists instead (the caller drops their sums)
         const int64_t any = va ? rowa : vb ? rowb : 0;
-        rows_dot_fast<BITS, G>(acc, a, va ? rowa : any, vb ? rowb : any, xs, xsum, lane, pipe, has_next && va && vb, next_delta);
+        rows_dot_fast<BITS, G>(acc, a, va ? rowa : any, vb ? rowb : any, xs, xsum, lane);
     } else {
         rows_dot_impl<BITS, G, false>(acc, a, rowa, rowb, va, vb, xs, xsum, lane);
     }
@@ -452,11 +414,9 @@ __global__ void __launch_bounds__(kThreads, 2) stream_kernel(const StreamArgs a)
                     const int p = k / kTileTokens, col = k % kTileTokens;
                     const int64_t base = (int64_t)a.ids[m * a.A + k] * a.N;
                     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                    Pipe<BITS, G> pipe;
-                    pipe.primed = false;
                     rows_dot<BITS, G>(acc, a, base + ra, base + rb, va, vb, reinterpret_cast<const uint4 *>(smem + p * pass_bytes),
                                       reinterpret_cast<const float *>(smem + p * pass_bytes + (size_t)steps * geo::kUnits * 512),
-                                      lane, pipe);
+                                      lane);
                     if (c == col / 2) {  // the lane of the quad that holds this slot's column
                         const float cf = a.coef[m * a.A + k];
                         ta = fmaf(cf, col & 1 ? acc[1] : acc[0], ta);
@@ -510,10 +470,6 @@ __global__ void __launch_bounds__(kThreads, 2) stream_kernel(const StreamArgs a)
         if (valid) stage_tile<BITS, G>(a.x, K, s_row, xs, xsum);
         __syncthreads();
 
-        Pipe<BITS, G> pipe;
-        pipe.primed = false;
-        constexpr int kUnitRows = MODE == kSwiglu ? 8 : 16;  // rows a unit advances both streamed rows by
-        const int64_t last_full = MODE == kSwiglu ? I / 8 : a.N / 16;  // units below this one have all their rows
         for (int64_t unit = lo + warp; unit < hi; unit += kWarps) {
             const int64_t u = unit - tile * units_per_tile;
             // The two weight rows this lane streams, as rows inside the expert, and where their results go.
@@ -526,12 +482,8 @@ __global__ void __launch_bounds__(kThreads, 2) stream_kernel(const StreamArgs a)
                 ra = u * 16 + g, rb = ra + 8;
                 va = ra < a.N, vb = rb < a.N;
             }
-            // the warp's next unit of this tile, when all of its rows exist: its first block rides under this unit's last
-            const bool has_next = unit + kWarps < hi && u + kWarps < last_full;
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            if (valid)
-                rows_dot<BITS, G>(acc, a, (int64_t)bucket * a.N + ra, (int64_t)bucket * a.N + rb, va, vb, xs, xsum, lane, pipe, has_next,
-                                  kUnitRows * kWarps);
+            if (valid) rows_dot<BITS, G>(acc, a, (int64_t)bucket * a.N + ra, (int64_t)bucket * a.N + rb, va, vb, xs, xsum, lane);
             // Epilogue.  Lane (g, c) holds rows ra / rb for tokens 2c and 2c + 1.
 #pragma unroll
             for (int t = 0; t < 2; ++t) {

@@ -72,6 +72,8 @@ class MoeLayer:
     # BF16 as the reference's served path does, which by itself moves an output by up to ~2e-2 of the output RMS
     # (measured on the Zipf-routed stack) - beyond the 1e-2 this path is held to - and measured no faster here.
     tc_math = MoeMath.WmmaF16F32Partials
+    stage_rows = False          # tcgen05 path: True = x converted once to F16 rows (sxb_stage_f16) and gathered per tile by the
+                                # kernel's copy warps; False = x gathered once into the tile-blocked form (sxb_stage_f16_tiles)
     small_slots = 2048          # up to this many slots the router and the pack are one launch (sxb_moe_route_small)
 
     def __init__(self, weights: MoeWeights, n_experts: int, top_k: int, buffers: MoeBuffers, E_total: Optional[int] = None,
@@ -142,9 +144,14 @@ class MoeLayer:
             # x gathered into the tile-blocked F16 form once; every row block of every tile then bulk-copies its operand
             if b.tiled_x is None:
                 b.tiled_x = torch.empty((b.max_tokens * A, self.d), dtype=torch.float16, device=x.device)
-            K.stage_f16_tiles(x, b.ws, b.ws_bytes, T, A, self.E, self.d, w.gate_up.bits, b.tiled_x)
-            K.linear_qw_experts_gather_grouped_swiglu(b.tiled_x, w.gate_up, self.E, b.ws, b.ws_bytes, T, A, b.h,
-                                                      Act.F16_TILED, math, h_f16=hf)
+            if self.stage_rows:
+                K.stage_f16(x, T, self.d, w.gate_up.bits, b.tiled_x)
+                K.linear_qw_experts_gather_grouped_swiglu(b.tiled_x, w.gate_up, self.E, b.ws, b.ws_bytes, T, A, b.h,
+                                                          Act.F16_STAGED, math, h_f16=hf)
+            else:
+                K.stage_f16_tiles(x, b.ws, b.ws_bytes, T, A, self.E, self.d, w.gate_up.bits, b.tiled_x)
+                K.linear_qw_experts_gather_grouped_swiglu(b.tiled_x, w.gate_up, self.E, b.ws, b.ws_bytes, T, A, b.h,
+                                                          Act.F16_TILED, math, h_f16=hf)
         else:
             K.linear_qw_experts_gather_grouped_swiglu(x, w.gate_up, self.E, b.ws, b.ws_bytes, T, A, b.h, Act.BF16, math)
         if events is not None:
