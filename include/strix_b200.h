@@ -391,6 +391,49 @@ int sxb_moe_layer_ep(SxbEp *ep, const SxbMoeLayerArgs *args, sxb_stream_t stream
 int sxb_ep_set_timing(SxbEp *ep, int on);
 int sxb_ep_timing(SxbEp *ep, float ms[5], int *layers);
 
+/* ---- strixw: the converted-weights file (formats/strixw.hpp:17-50) ---------------------------------------------- */
+
+/* formats/strixw.hpp:13-16  StrixwEncoding / StrixwRole. */
+enum { SXB_STRIXW_Q4 = 1, SXB_STRIXW_Q4_CHUNK_MAJOR = 2, SXB_STRIXW_BF16 = 3, SXB_STRIXW_F32 = 4, SXB_STRIXW_I64 = 5,
+       SXB_STRIXW_Q8 = 6, SXB_STRIXW_Q8_CHUNK_MAJOR = 7, SXB_STRIXW_Q6 = 8, SXB_STRIXW_Q5 = 9 };
+enum { SXB_STRIXW_DATA = 0, SXB_STRIXW_QCODES = 1, SXB_STRIXW_SCALE = 2, SXB_STRIXW_MIN = 3 };
+/* formats/strixw.hpp:37-48  StrixwTensor, flattened (name points into the file object; parts through sxb_strixw_part). */
+typedef struct SxbStrixwTensor {
+    const char *name;
+    int encoding, ndim;
+    int64_t shape[8];
+    int64_t group_size, experts;
+    int n_parts, n_components;
+    int component_role[3];
+    uint64_t component_offset[3], component_bytes[3], component_hash[3]; /* offsets: absolute, in the file */
+} SxbStrixwTensor;
+typedef struct SxbStrixw SxbStrixw;
+/* formats/strixw.hpp:96-120  StrixwFile: maps the file and validates header, index and every record (versions 1..4). */
+int sxb_strixw_open(const char *path, SxbStrixw **out);
+int sxb_strixw_close(SxbStrixw *f);
+int64_t sxb_strixw_tensor_count(const SxbStrixw *f);
+int sxb_strixw_tensor(const SxbStrixw *f, int64_t index, SxbStrixwTensor *out);
+int sxb_strixw_find(const SxbStrixw *f, const char *name, SxbStrixwTensor *out);
+int sxb_strixw_part(const SxbStrixw *f, const char *name, int index, const char **source, int64_t *row_offset, int64_t *rows);
+const char *sxb_strixw_meta(const SxbStrixw *f, const char *key);             /* NULL if absent */
+const void *sxb_strixw_data(const SxbStrixw *f, const char *name, int role);  /* host pointer into the mapping; NULL if absent */
+/* StrixwFile::verify_hashes: recomputes every component hash on `threads` host threads. */
+int sxb_strixw_verify(const SxbStrixw *f, int threads);
+/* formats/strixw.hpp:58  strix_hash64. */
+uint64_t sxb_strix_hash64(const void *data, size_t n);
+/* runtime/strixw_loader.hpp:37-60  StrixwDevice: the whole data region as ONE device allocation (made here, once), filled
+ * through two pinned staging buffers by `read_threads` concurrent pread()s and asynchronous copies on `stream`; returns
+ * when the data is resident.  Components keep their file offsets (4096 / 256-byte alignment carries over). */
+int sxb_strixw_load(SxbStrixw *f, int read_threads, sxb_stream_t stream);
+double sxb_strixw_load_seconds(const SxbStrixw *f);
+const void *sxb_strixw_device_ptr(const SxbStrixw *f, const char *name, int role);
+/* StrixwDevice::q4 / q8 / qw: the device view of a Q4 or Q8 row-major tensor of the expected shape; *bits = 4 or 8. */
+int sxb_strixw_qview(const SxbStrixw *f, const char *name, int64_t N, int64_t K, SxbQView *view, int *bits);
+/* formats/merge_plan.cpp:33-41: "<layer>mlp.experts_gate_up" / "<layer>mlp.experts_down" stack the E routed experts and,
+ * when it shares their format, the shared expert as expert #E.  routed = the view of the E routed experts; shared (may be
+ * NULL) = the shared expert's view, or all zero when the file keeps it elsewhere. */
+int sxb_strixw_expert_views(const SxbStrixw *f, const char *name, int64_t E, SxbQView *routed, SxbQView *shared, int *bits);
+
 /* ---- Quantizers on the device ------------------------------------------------------------------------------- */
 
 /* formats/q4.hpp:32 quantize_q4 / formats/q8.hpp:32 quantize_q8, for weights already on the device: w [N, K] FP32 ->

@@ -26,6 +26,14 @@ class SxbMoeSharedAdd(C.Structure):
     _fields_ = [("s", vp), ("gate_logit", vp), ("gate_ld", i64), ("gate_index", u32), ("err", vp)]
 
 
+class SxbStrixwTensor(C.Structure):
+    """formats/strixw.hpp:37-48 StrixwTensor, flattened (include/strix_b200.h)."""
+
+    _fields_ = [("name", cp), ("encoding", C.c_int), ("ndim", C.c_int), ("shape", i64 * 8), ("group_size", i64), ("experts", i64),
+                ("n_parts", C.c_int), ("n_components", C.c_int), ("component_role", C.c_int * 3), ("component_offset", C.c_uint64 * 3),
+                ("component_bytes", C.c_uint64 * 3), ("component_hash", C.c_uint64 * 3)]
+
+
 class SxbMoeLayerArgs(C.Structure):
     """The argument block of sxb_moe_layer (include/strix_b200.h), field for field."""
 
@@ -83,6 +91,21 @@ SIGNATURES = {
     "sxb_moe_layer_ep": (C.c_int, [vp, C.POINTER(SxbMoeLayerArgs), vp]),
     "sxb_ep_set_timing": (C.c_int, [vp, C.c_int]),
     "sxb_ep_timing": (C.c_int, [vp, C.POINTER(C.c_float), C.POINTER(C.c_int)]),
+    "sxb_strixw_open": (C.c_int, [cp, C.POINTER(vp)]),
+    "sxb_strixw_close": (C.c_int, [vp]),
+    "sxb_strixw_tensor_count": (i64, [vp]),
+    "sxb_strixw_tensor": (C.c_int, [vp, i64, C.POINTER(SxbStrixwTensor)]),
+    "sxb_strixw_find": (C.c_int, [vp, cp, C.POINTER(SxbStrixwTensor)]),
+    "sxb_strixw_part": (C.c_int, [vp, cp, C.c_int, C.POINTER(cp), C.POINTER(i64), C.POINTER(i64)]),
+    "sxb_strixw_meta": (cp, [vp, cp]),
+    "sxb_strixw_data": (vp, [vp, cp, C.c_int]),
+    "sxb_strixw_verify": (C.c_int, [vp, C.c_int]),
+    "sxb_strix_hash64": (C.c_uint64, [vp, sz]),
+    "sxb_strixw_load": (C.c_int, [vp, C.c_int, vp]),
+    "sxb_strixw_load_seconds": (C.c_double, [vp]),
+    "sxb_strixw_device_ptr": (vp, [vp, cp, C.c_int]),
+    "sxb_strixw_qview": (C.c_int, [vp, cp, i64, i64, C.POINTER(SxbQView), C.POINTER(C.c_int)]),
+    "sxb_strixw_expert_views": (C.c_int, [vp, cp, i64, C.POINTER(SxbQView), C.POINTER(SxbQView), C.POINTER(C.c_int)]),
     "sxb_moe_route_small": (C.c_int, [vp, i64, i64, i64, i64, i64, i64, vp, vp, vp, sz, vp, vp, vp]),
 }
 for _b in ("q4", "q8"):

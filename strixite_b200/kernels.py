@@ -100,6 +100,21 @@ class QDeviceView:
         return QDeviceView(self.q[lo:hi], self.scale[lo:hi], self.minv[lo:hi], hi - lo, self.K, self.G, self.bits)
 
 
+class QRawView:
+    """A quantized matrix given by raw device pointers (e.g. a view into a loaded strixw file): the same interface as
+    QDeviceView for the launchers."""
+
+    def __init__(self, view: "_lib.SxbQView", bits: int, keepalive=None):
+        self.view, self.bits, self.keepalive = view, bits, keepalive
+        self.N, self.K, self.G = view.N, view.K, view.G
+
+    def c(self) -> "_lib.SxbQView":
+        return self.view
+
+    def bytes(self) -> int:
+        return self.N * self.K * self.bits // 8 + 4 * self.N * (self.K // self.G)
+
+
 def _b(w: QDeviceView) -> str:
     if w.bits not in (4, 8):
         raise Error(1, f"experts have {w.bits} bits, expected 4 or 8")
