@@ -155,6 +155,12 @@ int sxb_router_logits_wmma(const void *x, const void *planes_in, int planes, con
  * (y_act); out may be x itself.  n % 8 == 0. */
 int sxb_residual_add(const void *x, const void *y, int y_act, void *out, int64_t n, sxb_stream_t stream);
 
+/* kernels/hc.hpp:52-54  hc_inject: the residual injection that follows the block, in place:
+ * X[t, s*d + j] += w_in[t, s] * y[t, j] for the H = 4 residual streams of X [T, H*d]; one rounding per element to the
+ * activation dtype.  y must not overlap X.  (sxb_moe_shared_add_inject is this fused with the shared expert's gated add;
+ * the hyper-connection mix that PRODUCES the block's input, hc_mix_down / hc_mix_up, is not part of this library.) */
+int sxb_hc_inject(void *x, const float *w_in, const void *y, int64_t T, int64_t H, int64_t d, int act, sxb_stream_t stream);
+
 /* ---- Pack (grouping of slots by expert) --------------------------------------------------------------------- */
 
 /* kernels/moe_grouped.hpp:48  moe_route_workspace_bytes.  Returns 0 and sets the error message on bad arguments.

@@ -104,6 +104,11 @@ inline void moe_shared_add_inject(void *y, const void *s, const float *gate_logi
                                                  b200_detail::act(act), err, stream));
 }
 
+// kernels/hc.hpp:52-54
+inline void hc_inject(void *x, const float *w_in, const void *y, int64_t T, int64_t H, int64_t d, Act act, hipStream_t stream) {
+    b200_detail::check(sxb_hc_inject(x, w_in, y, T, H, d, b200_detail::act(act), stream));
+}
+
 // kernels/moe_grouped.hpp
 inline size_t moe_route_workspace_bytes(int64_t M, int64_t A, int64_t E) {
     const size_t n = sxb_moe_route_workspace_bytes(M, A, E);

@@ -106,6 +106,7 @@ SIGNATURES = {
     "sxb_strixw_device_ptr": (vp, [vp, cp, C.c_int]),
     "sxb_strixw_qview": (C.c_int, [vp, cp, i64, i64, C.POINTER(SxbQView), C.POINTER(C.c_int)]),
     "sxb_strixw_expert_views": (C.c_int, [vp, cp, i64, C.POINTER(SxbQView), C.POINTER(SxbQView), C.POINTER(C.c_int)]),
+    "sxb_hc_inject": (C.c_int, [vp, vp, vp, i64, i64, i64, C.c_int, vp]),
     "sxb_moe_route_small": (C.c_int, [vp, i64, i64, i64, i64, i64, i64, vp, vp, vp, sz, vp, vp, vp]),
 }
 for _b in ("q4", "q8"):

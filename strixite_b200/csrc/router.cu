@@ -10,6 +10,7 @@
 
 #include "router_token.cuh"
 
+#include <algorithm>
 #include <mutex>
 
 namespace sxb {
@@ -99,6 +100,21 @@ __global__ void __launch_bounds__(kAddThreads)
 #pragma unroll
         for (int st = 0; st < kStreams; ++st)
             store_from_f32(xr, st * N + n, fmaf(w_in[m * kStreams + st], v, load_as_f32(xr, st * N + n)));
+    }
+}
+
+// kernels/hc.hip:245-252 hc_inject: X[t, s*d + j] += w_in[t, s] * y[t, j] for the H = 4 residual streams, one FP32 rounding
+// (fma), then the activation dtype's.  A thread takes one column j of one token and updates its four streams: y is read once.
+template <typename T>
+__global__ void __launch_bounds__(kAddThreads)
+    hc_inject_kernel(T *__restrict__ x, const float *__restrict__ w_in, const T *__restrict__ y, int64_t tokens, int64_t d) {
+    constexpr int kStreams = 4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < tokens * d; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / d, j = i % d;
+        const float v = load_as_f32(y, i);
+        T *xr = x + t * kStreams * d;
+#pragma unroll
+        for (int st = 0; st < kStreams; ++st) store_from_f32(xr, st * d + j, fmaf(w_in[t * kStreams + st], v, load_as_f32(xr, st * d + j)));
     }
 }
 
@@ -216,6 +232,21 @@ static int shared_add_impl(const char *fn, void *y, const void *s, const float *
                                                                        gate_ld, N, gate_index, nullptr, nullptr, err);
     }
     SXB_CHECK_LAUNCH(fn, " ", act_name(act), " M=", M, " N=", N);
+    return SXB_OK;
+}
+
+int sxb_hc_inject(void *x, const float *w_in, const void *y, int64_t T, int64_t H, int64_t d, int act, sxb_stream_t stream) {
+    const char *fn = "hc_inject";
+    SXB_CHECK(x != nullptr && w_in != nullptr && y != nullptr, fn, ": null pointer (x=", x, ", w_in=", (const void *)w_in, ", y=", y, ")");
+    SXB_CHECK(H == 4, fn, ": H = ", H, " streams, expected 4");
+    SXB_CHECK(T >= 1 && d >= 1 && d <= (1 << 20) && T <= (1ll << 40) / (H * d), fn, ": T = ", T, ", d = ", d);
+    SXB_CHECK(act_ok(act), fn, ": unsupported activation dtype ", act);
+    SXB_CHECK(apart(x, T * H * d * act_bytes(act), y, T * d * act_bytes(act)), fn, ": y overlaps X");
+    const unsigned blocks = (unsigned)std::min<int64_t>((T * d + kAddThreads - 1) / kAddThreads, (int64_t)sm_count() * 16);
+    auto st = static_cast<cudaStream_t>(stream);
+    if (act == SXB_ACT_F32) hc_inject_kernel<float><<<blocks, kAddThreads, 0, st>>>((float *)x, w_in, (const float *)y, T, d);
+    else hc_inject_kernel<uint16_t><<<blocks, kAddThreads, 0, st>>>((uint16_t *)x, w_in, (const uint16_t *)y, T, d);
+    SXB_CHECK_LAUNCH(fn, " ", act_name(act), " T=", T, " d=", d);
     return SXB_OK;
 }
 

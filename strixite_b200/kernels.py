@@ -219,6 +219,11 @@ def linear_qw_wmma_swiglu(x, w: QDeviceView, h, M, act, h_f16=0, stream=None):
     _check(fn(_ptr(x), C.byref(w.c()), _ptr(h), M, int(act), int(h_f16), _stream(stream)))
 
 
+def hc_inject(x, w_in, y, T, H, d, act, stream=None):
+    """kernels/hc.hpp:52-54: X[t, s*d + j] += w_in[t, s] * y[t, j], in place."""
+    _check(_lib.load().sxb_hc_inject(_ptr(x), _ptr(w_in), _ptr(y), T, H, d, int(act), _stream(stream)))
+
+
 # ---- kernels/moe_grouped.hpp ----------------------------------------------------------------------------------
 
 def moe_route_workspace_bytes(M, A, E) -> int:

@@ -142,6 +142,28 @@ def test_residual_add(cuda, ydt):
     assert torch.equal(x, out)
 
 
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_hc_inject(cuda, oracle, dt):
+    """kernels/hc.hpp:52-54 against the oracle's injection (the one inside moe_shared_add_inject, with s = 0 and a gate that
+    does not matter), bit for bit."""
+    from strixite_b200 import kernels as Kn
+    rng = np.random.default_rng(9)
+    T, d, H = 7, 320, 4
+    y = rng.standard_normal((T, d)).astype(np.float32)
+    x = rng.standard_normal((T, H * d)).astype(np.float32)
+    w_in = (rng.random((T, H)) * 2).astype(np.float32)
+    if dt == torch.bfloat16:
+        yb, xb = oracle.f32_to_bf16(y), oracle.f32_to_bf16(x)
+        _, want = oracle.moe_shared_add_inject(yb, np.zeros_like(yb), np.zeros(T, np.float32), 0, xb, w_in)
+        xd, yd = bf16_tensor(xb, cuda), bf16_tensor(yb, cuda)
+    else:
+        _, want = oracle.moe_shared_add_inject(y, np.zeros_like(y), np.zeros(T, np.float32), 0, x, w_in)
+        xd, yd = torch.from_numpy(x).to(cuda), torch.from_numpy(y).to(cuda)
+    Kn.hc_inject(xd, torch.from_numpy(w_in).to(cuda), yd, T, H, d, Kn.Act.F32 if dt == torch.float32 else Kn.Act.BF16)
+    got = xd.cpu().numpy() if dt == torch.float32 else bits_of(xd)
+    assert np.array_equal(got, want)
+
+
 @pytest.mark.parametrize("bits,G,M,N,K", [(8, 64, 300, 2048, 1024), (4, 128, 129, 512, 2048), (8, 64, 5, 256, 256)])
 def test_dense_tcgen05_projections(cuda, oracle, bits, G, M, N, K):
     """linear_q*_wmma: y = x W^T with the matrix-unit numerics, against oracle.linear_q(w_f16); then the fused SwiGLU form
