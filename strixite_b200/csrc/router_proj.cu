@@ -25,9 +25,11 @@ namespace {
 
 // ---- streaming form ------------------------------------------------------------------------------------------
 
-constexpr int kStreamWarps = 8;   // warps of a CTA = weight rows it takes at a time
+constexpr int kStreamRows = 8;    // weight rows a CTA takes at a time
+constexpr int kStreamWarps = 2 * kStreamRows;  // two warps per row, each streaming half of the staged k range
 constexpr int kTokChunk = 16;     // tokens whose activations sit in shared memory (and whose sums a lane keeps)
 constexpr int kStreamKTile = 4096;  // k range staged at a time: 16 tokens x 4096 x 2 bytes = 128 KB of shared memory
+constexpr int kRunsPerLane = kStreamKTile / 2 / 8 / 32;  // runs of eight k a lane takes from its half of a full tile: 8
 
 __device__ inline void load_w8(const float *p, float (&w)[8]) {
     const float4 a = __ldg(reinterpret_cast<const float4 *>(p)), b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
@@ -40,18 +42,20 @@ __device__ inline void load_w8(const uint16_t *p, float (&w)[8]) {
     for (int i = 0; i < 4; ++i) w[2 * i] = __uint_as_float(u[i] << 16), w[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
 }
 
-// y[m, n] = sum_k x[m, k] * w[n, k] (+ bias[n]).  A CTA stages the activations of 16 tokens in shared memory once and its
-// eight warps then stream one weight row each against them (lanes strided over k in runs of eight: a row's bytes are
-// read once, by 16-byte loads that are independent of one another), so the activations cross L2 once per eight rows.
-// The sum of a (token, row) pair is formed in a fixed order: per lane ascending k, then an xor butterfly.
+// y[m, n] = sum_k x[m, k] * w[n, k] (+ bias[n]).  A CTA stages the activations of 16 tokens in shared memory once and
+// streams eight weight rows against them, two warps a row (one per half of the staged k range).  A lane issues ALL the
+// loads of its part of the row before it consumes any of them - with a few dozen tokens the kernel is one memory round
+// trip plus arithmetic, so what counts is how many bytes are in flight.  The sum of a (token, row) pair is formed in a
+// fixed order: per lane ascending k, an xor butterfly in the warp, then the row's two halves in order.
 template <typename TW, typename TOUT>
 __global__ void __launch_bounds__(32 * kStreamWarps)
     logits_stream_kernel(const uint16_t *__restrict__ x, const TW *__restrict__ w, const float *__restrict__ bias, int64_t M,
                          int64_t N, int64_t K, TOUT *__restrict__ y, int64_t ld) {
     extern __shared__ __align__(16) unsigned char xs_raw[];
     uint4 *xs = reinterpret_cast<uint4 *>(xs_raw);  // [kTokChunk][kt / 8] chunks of eight BF16
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int64_t n = (int64_t)blockIdx.x * kStreamWarps + warp;
+    __shared__ float part[kStreamWarps][kTokChunk];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, half = warp & 1;
+    const int64_t n = (int64_t)blockIdx.x * kStreamRows + (warp >> 1);
     const bool row_ok = n < N;
     const TW *wr = w + (row_ok ? n : 0) * K;
     const float b = (row_ok && bias) ? bias[n] : 0.f;
@@ -62,6 +66,14 @@ __global__ void __launch_bounds__(32 * kStreamWarps)
         for (int t = 0; t < kTokChunk; ++t) acc[t] = 0.f;
         for (int64_t k0 = 0; k0 < K; k0 += kStreamKTile) {
             const int kt = (int)min((int64_t)kStreamKTile, K - k0), chunks = kt / 8;
+            // this warp's half of the tile, in runs of eight k: [c_lo, c_hi)
+            const int c_lo = half * ((chunks + 1) / 2), c_hi = half ? chunks : (chunks + 1) / 2;
+            float wv[kRunsPerLane][8];
+#pragma unroll
+            for (int j = 0; j < kRunsPerLane; ++j) {  // the row's bytes first: they come from HBM
+                const int c = c_lo + lane + 32 * j;
+                if (row_ok && c < c_hi) load_w8(wr + k0 + (int64_t)c * 8, wv[j]);
+            }
             __syncthreads();  // every warp is done with the previous tile
             for (int i = threadIdx.x; i < kTokChunk * chunks; i += 32 * kStreamWarps) {
                 const int t = i / chunks, c = i % chunks;
@@ -69,27 +81,18 @@ __global__ void __launch_bounds__(32 * kStreamWarps)
             }
             __syncthreads();
             if (row_ok) {
-                // four runs of the row in flight at a time: their loads are issued before any of them is consumed
-                for (int c0 = lane; c0 < chunks; c0 += 4 * 32) {
-                    float wv[4][8];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int c = c0 + 32 * j;
-                        if (c < chunks) load_w8(wr + k0 + (int64_t)c * 8, wv[j]);
-                    }
+                for (int j = 0; j < kRunsPerLane; ++j) {
+                    const int c = c_lo + lane + 32 * j;
+                    if (c >= c_hi) break;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int c = c0 + 32 * j;
-                        if (c >= chunks) break;
+                    for (int t = 0; t < kTokChunk; ++t) {
+                        const uint4 xv = xs[t * chunks + c];
+                        const uint32_t u[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
-                        for (int t = 0; t < kTokChunk; ++t) {
-                            const uint4 xv = xs[t * chunks + c];
-                            const uint32_t u[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                acc[t] = fmaf(__uint_as_float(u[i] << 16), wv[j][2 * i], acc[t]);
-                                acc[t] = fmaf(__uint_as_float(u[i] & 0xffff0000u), wv[j][2 * i + 1], acc[t]);
-                            }
+                        for (int i = 0; i < 4; ++i) {
+                            acc[t] = fmaf(__uint_as_float(u[i] << 16), wv[j][2 * i], acc[t]);
+                            acc[t] = fmaf(__uint_as_float(u[i] & 0xffff0000u), wv[j][2 * i + 1], acc[t]);
                         }
                     }
                 }
@@ -99,8 +102,11 @@ __global__ void __launch_bounds__(32 * kStreamWarps)
         for (int t = 0; t < kTokChunk; ++t) {
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], off);
-            if (lane == 0 && row_ok && t < live) store_from_f32(y, (m0 + t) * ld + n, acc[t] + b);
+            if (lane == 0) part[warp][t] = acc[t];
         }
+        __syncthreads();
+        if (half == 0 && lane < live && row_ok) store_from_f32(y, (m0 + lane) * ld + n, part[warp][lane] + part[warp + 1][lane] + b);
+        __syncthreads();
     }
 }
 
@@ -350,7 +356,7 @@ int check_proj(const char *fn, const void *x, const void *w, const void *y, int6
 template <typename TOUT>
 int launch_stream_logits(const char *fn, const void *x, const void *w, int w_act, const float *bias, int64_t M, int64_t N, int64_t K,
                          TOUT *y, int64_t ld, cudaStream_t st) {
-    const unsigned blocks = (unsigned)((N + kStreamWarps - 1) / kStreamWarps);
+    const unsigned blocks = (unsigned)((N + kStreamRows - 1) / kStreamRows);
     const size_t smem = (size_t)kTokChunk * std::min<int64_t>(K, kStreamKTile) * 2;
     if (w_act == SXB_ACT_F32) {
         auto kern = logits_stream_kernel<float, TOUT>;
