@@ -53,35 +53,42 @@ __device__ inline int cta_exclusive_scan(int v, int *buf, int *total) {
     return excl;
 }
 
-// Writes offsets, the header and both tile lists from per-bucket counts (thread b owns bucket b).
-// tile_first: 2 * 1025 ints of shared memory.
+// Writes offsets, the header and the four tile lists from per-bucket counts (thread b owns bucket b).
+// tile_first: 4 * 1025 ints of shared memory.
 __device__ void emit_layout(int count, const RouteWords &L, int32_t *ws, int *scanbuf, int *tile_first, bool ep) {
     const int b = threadIdx.x, E = (int)L.E;
     const bool owner = b <= E;
     // Tiles are cut for buckets 0..E-1, and for the overflow bucket E only outside expert-parallel mode (there its
     // slots are invalid ids whose outputs must become NaN; in EP mode they belong to other ranks and are skipped).
     const bool tiled = owner && (b < E || !ep);
-    int total_slots, n8, n128;
+    int total_slots, n8, n128, nta, ntb;
     const int start = cta_exclusive_scan(owner ? count : 0, scanbuf, &total_slots);
     const int t8 = tiled ? (count + 7) / 8 : 0, t128 = tiled ? (count + 127) / 128 : 0;
     const int first8 = cta_exclusive_scan(t8, scanbuf, &n8);
     const int first128 = cta_exclusive_scan(t128, scanbuf, &n128);
+    const int firstta = cta_exclusive_scan(tiled ? (count + kTcTileA - 1) / kTcTileA : 0, scanbuf, &nta);
+    const int firsttb = cta_exclusive_scan(tiled ? (count + kTcTileB - 1) / kTcTileB : 0, scanbuf, &ntb);
     int32_t *offsets = ws + L.offsets;
     if (owner) offsets[b] = start;
     if (b <= E + 1) {  // first tile of each bucket; entry E + 1 = the total
         tile_first[b] = b <= E ? first8 : n8;
         tile_first[1025 + b] = b <= E ? first128 : n128;
+        tile_first[2050 + b] = b <= E ? firstta : nta;
+        tile_first[3075 + b] = b <= E ? firsttb : ntb;
     }
     if (b == 0) {
         offsets[E + 1] = total_slots;
         ws[0] = n8, ws[1] = (int32_t)L.S, ws[2] = E, ws[3] = n128, ws[4] = ep ? 1 : 0, ws[5] = 0, ws[6] = 0, ws[7] = 0;
+        ws[L.tta_n] = nta, ws[L.ttb_n] = ntb;
     }
     __syncthreads();
     // Tiles in parallel: tile t belongs to the last bucket whose first tile is <= t.
-    for (int pass = 0; pass < 2; ++pass) {
+    for (int pass = 0; pass < 4; ++pass) {
         const int *first = tile_first + pass * 1025;
-        const int n = pass ? n128 : n8, rows = pass ? 128 : 8;
-        int32_t *tb = ws + (pass ? L.t128_bucket : L.t8_bucket), *ts = ws + (pass ? L.t128_start : L.t8_start);
+        const int n = pass == 0 ? n8 : pass == 1 ? n128 : pass == 2 ? nta : ntb;
+        const int rows = pass == 0 ? 8 : pass == 1 ? 128 : pass == 2 ? kTcTileA : kTcTileB;
+        int32_t *tb = ws + (pass == 0 ? L.t8_bucket : pass == 1 ? L.t128_bucket : pass == 2 ? L.tta_bucket : L.ttb_bucket);
+        int32_t *ts = ws + (pass == 0 ? L.t8_start : pass == 1 ? L.t128_start : pass == 2 ? L.tta_start : L.ttb_start);
         for (int t = threadIdx.x; t < n; t += kPackThreads) {
             int lo = 0, hi = E + 1;  // invariant: first[lo] <= t < first[hi]
             while (hi - lo > 1) {
@@ -118,7 +125,7 @@ __device__ inline void warp_place(const int32_t *ids, int s0, int s1, int e_lo, 
 // The whole pack of a small batch by one CTA of kPackThreads threads.
 __device__ void pack_small_body(const int32_t *__restrict__ ids, const RouteWords &L, int E_total, int e_lo, bool ep, int32_t *ws,
                                 uint32_t *err) {
-    __shared__ int cnt[kPackThreads], scanbuf[33], tile_first[2 * 1025];
+    __shared__ int cnt[kPackThreads], scanbuf[33], tile_first[4 * 1025];
     __shared__ int first_bad;
     const int t = threadIdx.x, S = (int)L.S, E = (int)L.E;
     cnt[t] = 0;
@@ -189,7 +196,7 @@ __global__ void __launch_bounds__(32 * kSegWarps)
 // the bucket); totals -> offsets, header, tile lists; the first invalid slot -> err.
 __global__ void __launch_bounds__(kPackThreads)
     pack_scan_kernel(const int32_t *__restrict__ ids, RouteWords L, bool ep, int32_t *ws, uint32_t *err) {
-    __shared__ int scanbuf[33], tile_first[2 * 1025];
+    __shared__ int scanbuf[33], tile_first[4 * 1025];
     const int b = threadIdx.x, E = (int)L.E;
     int total = 0;
     if (b <= E) {
@@ -275,7 +282,14 @@ RouteWords route_words(int64_t M, int64_t A, int64_t E) {
     L.t128_start = L.t128_bucket + L.T128max;
     L.segbad = L.t128_start + L.T128max;
     L.scratch = L.segbad + L.nseg;
-    L.total = L.scratch + L.nseg * (E + 1);
+    L.TtAmax = L.S / kTcTileA + E + 2, L.TtBmax = L.S / kTcTileB + E + 2;
+    L.tta_n = L.scratch + L.nseg * (E + 1);
+    L.tta_bucket = L.tta_n + 1;
+    L.tta_start = L.tta_bucket + L.TtAmax;
+    L.ttb_n = L.tta_start + L.TtAmax;
+    L.ttb_bucket = L.ttb_n + 1;
+    L.ttb_start = L.ttb_bucket + L.TtBmax;
+    L.total = L.ttb_start + L.TtBmax;
     return L;
 }
 

@@ -233,11 +233,21 @@ def moe_route_workspace_bytes(M, A, E) -> int:
     return n
 
 
+TC_TILES = (192, 256)  # tokens per work item of the tcgen05 kernel for tile-blocked activations (route_pack.cuh)
+
+
 def route_layout(M, A, E) -> dict:
     out = (C.c_int64 * 8)()
     _check(_lib.load().sxb_route_layout(M, A, E, out))
     keys = ["header", "offsets", "slots", "tile8_bucket", "tile8_start", "tile128_bucket", "tile128_start", "total"]
-    return dict(zip(keys, list(out)))
+    L = dict(zip(keys, list(out)))
+    # two more tile lists close the workspace, each a count followed by bucket and start of up to S / rows + E + 2 tiles
+    at = L["total"]
+    for rows in reversed(TC_TILES):
+        tmax = M * A // rows + E + 2
+        at -= 1 + 2 * tmax
+        L[f"tile{rows}_n"], L[f"tile{rows}_bucket"], L[f"tile{rows}_start"] = at, at + 1, at + 1 + tmax
+    return L
 
 
 def moe_group_routes(ids, M, A, E, ws, ws_bytes, err, stream=None):

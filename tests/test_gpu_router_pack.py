@@ -163,7 +163,7 @@ def check_tiles(ws, L, offsets, E, rows, n_key, b_key, s_key, skip_last_bucket=F
 @pytest.mark.parametrize("M,A,E", [(1, 10, 512), (16, 10, 512), (37, 10, 512), (64, 11, 513), (200, 10, 512),
                                    (205, 10, 512), (4096, 10, 512), (16384, 10, 512), (5, 64, 1023), (3000, 1, 1)])
 def test_pack_bit_exact(cuda, oracle, M, A, E):
-    """offsets and, thanks to the stable order, slots and both tile lists equal the CPU counting sort word for word -
+    """offsets and, thanks to the stable order, slots and the four tile lists equal the CPU counting sort word for word -
     through both the single-CTA path (S <= 2048) and the three-launch path."""
     from strixite_b200 import kernels as K
     rng = np.random.default_rng(M * 31 + A)
@@ -181,6 +181,8 @@ def test_pack_bit_exact(cuda, oracle, M, A, E):
     assert ws[1] == M * A and ws[2] == E and ws[4] == 0
     check_tiles(ws, L, offsets, E, 8, 0, "tile8_bucket", "tile8_start")
     check_tiles(ws, L, offsets, E, 128, 3, "tile128_bucket", "tile128_start")
+    for rows in K.TC_TILES:
+        check_tiles(ws, L, offsets, E, rows, L[f"tile{rows}_n"], f"tile{rows}_bucket", f"tile{rows}_start")
 
 
 def test_pack_golden(cuda, golden):
@@ -207,3 +209,5 @@ def test_pack_expert_parallel(cuda, oracle, M):
     assert list(err) == [1, 600, (M // 2) * A + 3] and ws[4] == 1
     check_tiles(ws, L, offsets, E_local, 8, 0, "tile8_bucket", "tile8_start", skip_last_bucket=True)
     check_tiles(ws, L, offsets, E_local, 128, 3, "tile128_bucket", "tile128_start", skip_last_bucket=True)
+    for rows in K.TC_TILES:
+        check_tiles(ws, L, offsets, E_local, rows, L[f"tile{rows}_n"], f"tile{rows}_bucket", f"tile{rows}_start", skip_last_bucket=True)
