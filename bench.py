@@ -56,8 +56,9 @@ def parse():
     ap.add_argument("--planes", type=int, default=3, help="BF16 planes of the FP32 router weight on the tensor-core projection (2 or 3)")
     ap.add_argument("--ep", default="native", choices=["native", "torch"],
                     help="expert-parallel driver: the library's C entry point sxb_moe_layer_ep, or torch.distributed (strixite_b200/ep.py)")
-    ap.add_argument("--return-path", dest="return_path", type=int, default=1,
-                    help="native driver, rows back to their owners: 0 NCCL reduce-scatter, 1 peer stores of FP32 pieces, 2 of BF16 pieces")
+    ap.add_argument("--return-path", dest="return_path", type=int, default=None,
+                    help="native driver, rows back to their owners: 0 NCCL reduce-scatter, 1 peer stores of FP32 pieces, 2 of BF16 pieces "
+                         "(default: 1 up to four GPUs, 0 beyond - measured on C4: 37.1 vs 39.5 ms at two, 14.6 vs 17.5 ms at eight)")
     ap.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
                     help="expert-parallel runs: experts dealt to ranks by calibrated load, or expert e on rank e // (E / N)")
     ap.add_argument("--stage", default="tiles", choices=["tiles", "rows"],
@@ -706,6 +707,8 @@ def main():
         cfg = replace(cfg, E=args.experts or cfg.E, T=args.tokens or cfg.T, name=cfg.name + "_reduced")
     decode = cfg.T <= 64
 
+    if args.return_path is None:
+        args.return_path = 1 if world <= 4 else 0
     if cfg.shared and world > 1:
         raise SystemExit(f"{cfg.name} has a shared expert, which is not sharded: run it on one GPU (the expert-parallel workload is c4)")
     res = run_stack(cfg, args, dev, rank, world, peaks, layers=(8 if decode else None), rotate=decode)

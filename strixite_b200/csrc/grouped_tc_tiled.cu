@@ -9,7 +9,8 @@
 // rows x up to 128 tokens.  Here an item is 128 weight rows (ONE accumulator, a row per tensor-memory lane) x up to 192
 // or 256 tokens, so an expert with many tokens has its weights dequantized once per 192 / 256 of them, and the tensor
 // memory that the second row half would take holds more pipeline stages or a second accumulator instead:
-//   TILE = 256 (long contractions, K >= 2048: gate/up): one accumulator, six stages, three producer warps a quadrant;
+//   TILE = 256 (long contractions, K >= 2048: gate/up): one accumulator, six stages, three producer warps and two
+//              epilogue warps a quadrant;
 //   TILE = 192 (short contractions: a down projection is 16 k-blocks): two accumulators - the epilogue of one item runs
 //              under the mainloop of the next, which matters most when the mainloop is short - four stages, two
 //              producer warps a quadrant.
@@ -26,8 +27,10 @@
 // tile, packed codes by 2-D tensor copies (64 bytes x 64 rows a box, two boxes a ring slot).  Tensor memory: the
 // accumulator(s) first, then one 32-column A stage per pipeline stage.
 //
-// One persistent CTA per SM: warps 0-3 epilogue, 4 MMA issue, 5 activation copies, 6 the ring of weight codes, 7 idle,
-// 8.. weight producers (a lane quadrant's warps take every second or third k-block each).  A producer hands its k-block
+// One persistent CTA per SM.  Warps: the epilogue first (one per lane quadrant; two per quadrant, each taking half of the
+// columns, where there is a single accumulator whose epilogue the MMA warp has to wait for), then MMA issue, activation
+// copies, the ring of weight codes and one idle warp, then the
+// weight producers (a lane quadrant's warps take every second or third k-block each).  A producer hands its k-block
 // over before it waits for anything its next one needs.  Every wait is bounded: past the limit the CTA raises its abort
 // flag, records {2, item, role} in the status words, drains the tensor pipe and frees its tensor memory before
 // returning.  The tensor copies read this GPU's own weight array only, each into the shared memory of the one CTA that
@@ -38,7 +41,6 @@
 namespace sxb {
 namespace {
 
-constexpr int kEpiWarps = 4, kMmaWarp = 4, kBCopyWarp = 5, kWCopyWarp = 6, kFirstAWarp = 8;
 constexpr int kBK = 64;              // k per stage: one 128-byte swizzle line of F16
 constexpr int kRows = 128;           // weight rows per item = tensor-memory lanes
 constexpr int kAStageCols = kBK / 2; // 64 F16 of one weight row per lane
@@ -55,7 +57,14 @@ struct Shape {
     static constexpr int kWSlots = TILE > 192 ? 4 : 8;  // ring slots of packed codes (8 KB each)
     // Producer warps per lane quadrant: they take every kWays-th k-block each.
     static constexpr int kWays = TILE > 192 ? 3 : 2;
+    // Epilogue warps per lane quadrant: a single accumulator's epilogue is exposed (the MMA warp waits for it), so its
+    // columns are split between two sets of warps; with two accumulators one set keeps up.
+    static constexpr int kEpiSets = kAccs == 1 ? 2 : 1;
+    // warps: epilogue | MMA issue, activation copies, ring of weight codes, one idle | producers
+    static constexpr int kEpiWarps = 4 * kEpiSets, kMmaWarp = kEpiWarps, kBCopyWarp = kEpiWarps + 1, kWCopyWarp = kEpiWarps + 2,
+                         kFirstAWarp = kEpiWarps + 4;
     static constexpr int kThreads = 32 * (kFirstAWarp + 4 * kWays);
+    static_assert(TILE % (32 * kEpiSets) == 0 || kEpiSets == 1, "an epilogue set takes whole passes of 32 columns");
     static_assert(TILE % 16 == 0 && TILE <= 256 && kStages > kWays && kStages >= 3, "tile size / pipeline depth");
     static_assert(kStageBytes % 1024 == 0, "operand tiles start on the swizzle pattern's 1024-byte period");
 };
@@ -104,7 +113,9 @@ __device__ inline int next_valid_item(const TcArgs &a, int item, int n_items, in
 template <int BITS, int G, int MODE, int TILE>
 __global__ void __launch_bounds__(Shape<TILE>::kThreads, 1) tiled_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap wmap) {
     constexpr int kTile = TILE, kAccs = Shape<TILE>::kAccs, kStages = Shape<TILE>::kStages, kStageBytes = Shape<TILE>::kStageBytes,
-                  kWSlots = Shape<TILE>::kWSlots, kWays = Shape<TILE>::kWays;
+                  kWSlots = Shape<TILE>::kWSlots, kWays = Shape<TILE>::kWays, kEpiSets = Shape<TILE>::kEpiSets,
+                  kEpiWarps = Shape<TILE>::kEpiWarps, kMmaWarp = Shape<TILE>::kMmaWarp, kBCopyWarp = Shape<TILE>::kBCopyWarp,
+                  kWCopyWarp = Shape<TILE>::kWCopyWarp, kFirstAWarp = Shape<TILE>::kFirstAWarp;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment of the operand tiles (the swizzle pattern repeats every 1024 bytes).
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -419,7 +430,9 @@ __global__ void __launch_bounds__(Shape<TILE>::kThreads, 1) tiled_tc_kernel(cons
         const int64_t I = a.N / 2;
         const bool tiled_out = MODE == kTcSwiglu && a.out_f16 >= 3;
         const bool h_as_f16 = a.out_f16 != 0, q4_order = a.out_f16 == 2 || a.out_f16 == 3;
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+        const int quad = warp & 3;                         // the lane quadrant this warp may read
+        const int col_lo = (warp >> 2) * (kTile / kEpiSets);  // this warp's set takes the columns [col_lo, col_lo + kTile / kEpiSets)
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
         const int up_lane = lane >> 4;  // SwiGLU: lanes 16-31 hold the up rows of the h columns of lanes 0-15
         for (int item = blockIdx.x; item < n_items && !*abort_v; item += gridDim.x) {
             const Item it = item_info<TILE>(a, item, rbs);
@@ -429,13 +442,13 @@ __global__ void __launch_bounds__(Shape<TILE>::kThreads, 1) tiled_tc_kernel(cons
             uint32_t xor_chunk = 0;  // tile-blocked h: 16-byte chunk of the line, before the per-token swizzle
             bool row_ok;
             if (MODE == kTcSwiglu) {
-                const int64_t j = (int64_t)it.rb * (kRows / 2) + warp * 16 + (lane & 15);  // h column
+                const int64_t j = (int64_t)it.rb * (kRows / 2) + quad * 16 + (lane & 15);  // h column
                 const int j7 = (int)(j & 7), pos = q4_order ? (((j7 & 3) << 1) | (j7 >> 2)) : j7;  // [0 4 1 5 2 6 3 7]
                 row_ok = j < I;
                 if (tiled_out) elem_off = (j >> 6) * a.L.S * 128 + pos * 2, xor_chunk = (uint32_t)((j & 63) >> 3);
                 else elem_off = ((j & ~(int64_t)7) + pos) * 2;
             } else {
-                const int64_t r = (int64_t)it.rb * kRows + warp * 32 + lane;
+                const int64_t r = (int64_t)it.rb * kRows + quad * 32 + lane;
                 row_ok = r < a.N;
                 elem_off = r * (MODE == kTcPartial ? 4 : 2);
             }
@@ -447,7 +460,8 @@ __global__ void __launch_bounds__(Shape<TILE>::kThreads, 1) tiled_tc_kernel(cons
                 if (tiled_out) return (uint32_t)(it.start + n) * 8u;
                 return (uint32_t)(((int64_t)slot * (MODE == kTcSwiglu ? I * 2 : a.N * (MODE == kTcPartial ? 4 : 2))) >> 4);
             };
-            int slot_nxt = token_slot(lane);
+            const int col_hi = min(it.cnt, col_lo + kTile / kEpiSets);  // this set's tokens: [col_lo, col_hi)
+            int slot_nxt = token_slot(col_lo + lane);
             uint32_t half = 0;
             if (valid) {
                 half = acc_count % kAccs;
@@ -457,14 +471,15 @@ __global__ void __launch_bounds__(Shape<TILE>::kThreads, 1) tiled_tc_kernel(cons
                 __syncwarp();
                 if (*abort_v) break;
                 tc_fence_after();
+                if (col_lo >= col_hi && lane == 0) mbar_arrive(&acc_empty[half]);  // none of the item's tokens are this set's
             }
             unsigned char *out = static_cast<unsigned char *>(a.out) + elem_off;
-            for (int c0 = 0; c0 < it.cnt; c0 += 32) {
+            for (int c0 = col_lo; c0 < col_hi; c0 += 32) {
                 float va[16], vb[16];  // this row's accumulators of tokens c0 .. c0 + 15 and c0 + 16 .. c0 + 31
                 if (valid) {
                     const uint32_t col = lane_addr + half * (uint32_t)kTile + (uint32_t)c0;
                     tc_ld16x2(col, col + 16u, va, vb);
-                    if (c0 + 32 >= it.cnt) {  // the last columns are out: the accumulator is free for a later item
+                    if (c0 + 32 >= col_hi) {  // this set's last columns are out: its share of the accumulator is free
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&acc_empty[half]);
@@ -474,7 +489,7 @@ __global__ void __launch_bounds__(Shape<TILE>::kThreads, 1) tiled_tc_kernel(cons
                     for (int t = 0; t < 16; ++t) va[t] = vb[t] = qnan_f32();
                 }
                 const uint32_t off_cur = token_off(c0 + lane, slot_nxt);
-                if (c0 + 32 < it.cnt) slot_nxt = token_slot(c0 + 32 + lane);
+                if (c0 + 32 < col_hi) slot_nxt = token_slot(c0 + 32 + lane);
                 const int live = it.cnt - c0;  // tokens of this pass; the columns past them are computed and dropped
 #pragma unroll
                 for (int t = 0; t < 16; ++t) {

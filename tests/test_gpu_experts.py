@@ -206,7 +206,8 @@ def test_grouped_experts_exact_math(cuda, oracle, bits, G, M, A, E, I, d):
 
 
 @pytest.mark.parametrize("bits,G", [(4, 128), (8, 64), (4, 32)])
-@pytest.mark.parametrize("M,A,E,I,d", [(40, 2, 4, 128, 256), (300, 2, 8, 128, 256), (700, 4, 8, 256, 384)])
+@pytest.mark.parametrize("M,A,E,I,d", [(40, 2, 4, 128, 256), (300, 2, 8, 128, 256), (700, 4, 8, 256, 384),
+                                       (700, 2, 4, 128, 2048)])  # the last: a long contraction over well-filled experts
 def test_grouped_experts_tcgen05(cuda, oracle, bits, G, M, A, E, I, d):
     """MoeMath.WmmaF16: tcgen05 grouped GEMMs (F16 operands, FP32 accumulation in tensor memory) against the oracle's
     matrix-unit semantics: weights as the F16 operand f16(code * scale + min), h = silu(g) * u rounded once.  Both
@@ -341,4 +342,6 @@ def test_grouped_experts_tcgen05(cuda, oracle, bits, G, M, A, E, I, d):
         y_from_stored = np.einsum("ma,mad->md", coef.astype(np.float64), np.where(np.isnan(stored), 0, stored))
         assert max_abs_over_rms(yb.cpu().numpy()[rows], y_from_stored[rows]) < 3e-6
         y_ref_b = oracle.experts_combine(h_ref.reshape(M, A, I), dn, E, ids, coef, out_act=oracle.F32, w_f16=True, partial_bf16=True)
-        assert max_abs_over_rms(yb.cpu().numpy()[rows], y_ref_b[rows]) < 1e-2
+        # a dot on a BF16 rounding boundary falls either way (one ulp = 2^-8 of the dot, times its coefficient): over M * d
+        # outputs the largest such flip reaches ~1e-2 of the RMS, which is why this library's default keeps the dots in FP32
+        assert max_abs_over_rms(yb.cpu().numpy()[rows], y_ref_b[rows]) < 2e-2

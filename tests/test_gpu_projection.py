@@ -298,8 +298,9 @@ def test_cxx_host_runs_the_call_block(cuda, oracle, tmp_path):
     assert np.array_equal(ref["ids"], ids_c)
 
 
-def test_a_wait_that_runs_out_ends_the_kernel_with_a_status(cuda, oracle, lib):
-    """The tcgen05 kernels bound every device-side wait.  With the limit set to 2 ms and CTA 0 told to leave one fill of its
+@pytest.mark.parametrize("tiled", [False, True])
+def test_a_wait_that_runs_out_ends_the_kernel_with_a_status(cuda, oracle, lib, tiled):
+    """The tcgen05 kernels (tiled: the one for tile-blocked activations) bound every device-side wait.  With the limit set to 2 ms and CTA 0 told to leave one fill of its
     weight-code ring out (nothing is issued for it, so nothing can fault), the producers' wait for those codes runs out:
     the kernel returns, the status words name the work item and the role, tensor memory is released - a normal launch on
     the same context right after gives the right answer."""
@@ -310,13 +311,18 @@ def test_a_wait_that_runs_out_ends_the_kernel_with_a_status(cuda, oracle, lib):
     xb = oracle.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
     w, x = upload(wq, cuda), bf16_tensor(xb, cuda)
     y = torch.empty((M, N), dtype=torch.float32, device=cuda)
-    Kn.linear_qw_wmma(x, w, y, M, Kn.Act.BF16, Kn.Act.F32)  # warm: module loaded, attributes set
+    act = Kn.Act.BF16
+    if tiled:
+        xs = torch.empty((M, K), dtype=torch.float16, device=cuda)
+        Kn.stage_f16_tiles(x, None, 0, M, 1, 1, K, 8, xs)
+        x, act = xs, Kn.Act.F16_TILED
+    Kn.linear_qw_wmma(x, w, y, M, act, Kn.Act.F32)  # warm: module loaded, attributes set
     torch.cuda.synchronize()
     Kn.check_dense_status("warm-up")
     try:
         Kn.set_wait_limit(2_000_000)
         assert lib.sxb_test_skip_ring_slot(3) == 0
-        Kn.linear_qw_wmma(x, w, y, M, Kn.Act.BF16, Kn.Act.F32)
+        Kn.linear_qw_wmma(x, w, y, M, act, Kn.Act.F32)
         torch.cuda.synchronize()
     finally:
         lib.sxb_test_skip_ring_slot(-1)
@@ -326,7 +332,7 @@ def test_a_wait_that_runs_out_ends_the_kernel_with_a_status(cuda, oracle, lib):
         Kn.check_dense_status("skipped fill")
     Kn.check_dense_status("cleared by the read")  # the words are cleared by the failing check
     y2 = torch.empty_like(y)
-    Kn.linear_qw_wmma(x, w, y2, M, Kn.Act.BF16, Kn.Act.F32)
+    Kn.linear_qw_wmma(x, w, y2, M, act, Kn.Act.F32)
     torch.cuda.synchronize()
     Kn.check_dense_status("after")
     want = oracle.linear_q(xb, wq, out_act=oracle.F32, w_f16=True)
