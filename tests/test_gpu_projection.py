@@ -204,6 +204,30 @@ def test_dense_tcgen05_projections(cuda, oracle, bits, G, M, N, K):
     assert max_abs_over_rms(s32.cpu().numpy(), want_s) <= 1e-2
 
 
+@pytest.mark.parametrize("bits,G,M,N,K", [(8, 64, 300, 400, 256), (4, 128, 300, 400, 2048), (4, 32, 193, 144, 2048)])
+def test_dense_tcgen05_partial_row_blocks(cuda, oracle, bits, G, M, N, K):
+    """Tile-blocked activations into a weight whose row count is not a multiple of the 128-row work item, with token counts
+    that leave a partly filled last tile - on both shapes of the kernel for tile-blocked activations (K below and from 2048).
+    A store for a row past N would land in the next token's output row, so the comparison sees it."""
+    from strixite_b200 import kernels as Kn
+    rng = np.random.default_rng(bits + M + N)
+    wq = oracle.quantize(random_weights(rng, N, K), G, bits)
+    xb = oracle.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+    w, x = upload(wq, cuda), bf16_tensor(xb, cuda)
+    xs = torch.empty((M, K), dtype=torch.float16, device=cuda)
+    Kn.stage_f16_tiles(x, None, 0, M, 1, 1, K, bits, xs)
+    y32 = torch.full((M + 1, N), 7.0, dtype=torch.float32, device=cuda)
+    ybf = torch.empty((M, N), dtype=torch.bfloat16, device=cuda)
+    Kn.linear_qw_wmma(xs, w, y32, M, Kn.Act.F16_TILED, Kn.Act.F32)
+    Kn.linear_qw_wmma(xs, w, ybf, M, Kn.Act.F16_TILED, Kn.Act.BF16)
+    torch.cuda.synchronize()
+    Kn.check_dense_status("partial row blocks")
+    want = oracle.linear_q(xb, wq, out_act=oracle.F32, w_f16=True)
+    assert max_abs_over_rms(y32[:M].cpu().numpy(), want) <= 2e-5
+    assert torch.all(y32[M] == 7.0)  # nothing past the last token's row
+    assert torch.equal(ybf, y32[:M].to(torch.bfloat16))
+
+
 @pytest.mark.parametrize("bits,G", [(4, 128), (8, 64)])
 def test_fp32_activations(cuda, oracle, bits, G):
     """Act::F32 into the dense, per-slot and grouped entry points (kernels/linear_q4.hpp:26-30): FP32 in, FP32 out,
