@@ -57,8 +57,8 @@ def parse():
     ap.add_argument("--ep", default="native", choices=["native", "torch"],
                     help="expert-parallel driver: the library's C entry point sxb_moe_layer_ep, or torch.distributed (strixite_b200/ep.py)")
     ap.add_argument("--return-path", dest="return_path", type=int, default=None,
-                    help="native driver, rows back to their owners: 0 NCCL reduce-scatter, 1 peer stores of FP32 pieces, 2 of BF16 pieces "
-                         "(default: 1 up to four GPUs, 0 beyond - measured on C4: 37.1 vs 39.5 ms at two, 14.6 vs 17.5 ms at eight)")
+                    help="native driver, rows back to their owners: 0 NCCL reduce-scatter, 1 peer stores of FP32 pieces, 2 of F16 pieces "
+                         "(default: 1 up to four GPUs, 2 beyond - measured on C4 at eight: F16 pieces 13.0 ms, reduce-scatter 14.3, FP32 pieces 17.5)")
     ap.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
                     help="expert-parallel runs: experts dealt to ranks by calibrated load, or expert e on rank e // (E / N)")
     ap.add_argument("--stage", default="tiles", choices=["tiles", "rows"],
@@ -708,7 +708,7 @@ def main():
     decode = cfg.T <= 64
 
     if args.return_path is None:
-        args.return_path = 1 if world <= 4 else 0
+        args.return_path = 1 if world <= 4 else 2
     if cfg.shared and world > 1:
         raise SystemExit(f"{cfg.name} has a shared expert, which is not sharded: run it on one GPU (the expert-parallel workload is c4)")
     res = run_stack(cfg, args, dev, rank, world, peaks, layers=(8 if decode else None), rotate=decode)
@@ -731,7 +731,7 @@ def main():
     }
     if res.get("ep_info"):
         line["expert_parallel"] = {"driver": "sxb_moe_layer_ep" if st.native is not None else "torch.distributed (ep.py)",
-                                   "return_path": {0: "nccl reduce-scatter (fp32)", 1: "peer stores, fp32 pieces", 2: "peer stores, bf16 pieces"}[args.return_path]
+                                   "return_path": {0: "nccl reduce-scatter (fp32)", 1: "peer stores, fp32 pieces", 2: "peer stores, f16 pieces"}[args.return_path]
                                    if st.native is not None else st.ep.exchange, "placement": args.placement, "per_rank": res["ep_info"]}
     if args.parity_rows > 0:
         try:

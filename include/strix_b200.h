@@ -377,7 +377,7 @@ int sxb_moe_layer(const SxbMoeLayerArgs *args, sxb_stream_t stream);
  *   return_path 0  the partial rows [T, d] FP32 through ncclReduceScatter (sum);
  *   return_path 1  every row stored, as the rank's piece, straight into its owner's receive buffer through peer-mapped
  *                  pointers (plain stores from the combine kernel), the owner adds its `world` pieces in rank order (FP32);
- *   return_path 2  the same with BF16 pieces (half the bytes on the links; one more rounding per piece).
+ *   return_path 2  the same with F16 pieces (half the bytes on the links; one rounding to 11 bits per piece; |piece| < 65504).
  * libnccl.so.2 is opened at run time, not linked.  sxb_ep_unique_id: rank 0 makes the communicator's id and the host sends
  * the 128 bytes to the other ranks by its own means.  sxb_ep_create (collective, synchronizes) builds the communicator,
  * allocates the rank's exchange buffers ONCE (device memory: T*d*2 bytes of gathered activations, plus T*d*4 (paths 0, 1) or

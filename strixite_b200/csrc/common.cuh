@@ -4,6 +4,7 @@
 
 #include "strix_b200.h"
 
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -99,6 +100,7 @@ __device__ inline void raise_error(uint32_t *err, uint32_t a, uint32_t b) {
 template <typename T> __device__ inline float load_as_f32(const T *p, int64_t i);
 template <> __device__ inline float load_as_f32<float>(const float *p, int64_t i) { return p[i]; }
 template <> __device__ inline float load_as_f32<uint16_t>(const uint16_t *p, int64_t i) { return bf16_bits_to_f32(p[i]); }
+template <> __device__ inline float load_as_f32<__half>(const __half *p, int64_t i) { return __half2float(p[i]); }
 template <typename T> __device__ inline void store_from_f32(T *p, int64_t i, float v);
 template <> __device__ inline void store_from_f32<float>(float *p, int64_t i, float v) { p[i] = v; }
 template <> __device__ inline void store_from_f32<uint16_t>(uint16_t *p, int64_t i, float v) { p[i] = f32_to_bf16_bits(v); }

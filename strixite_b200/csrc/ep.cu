@@ -8,7 +8,7 @@
 //     4. the way back, one of
 //          reduce-scatter: the rank's partial rows [T, d] FP32 -> ncclReduceScatter (sum) -> its own rows
 //          peer stores:    the combine writes every row, as this rank's piece, straight into the row owner's receive
-//                          buffer [N][t][d] (FP32 or BF16) through peer-mapped pointers - plain stores, nothing
+//                          buffer [N][t][d] (FP32 or F16) through peer-mapped pointers - plain stores, nothing
 //                          multicast, no copy engine; a one-word NCCL all-reduce then tells every rank that all pieces
 //                          have landed, and the owner adds its N pieces in rank order (FP32, deterministic)
 //   The caller adds the residual (sxb_residual_add) or whatever follows.
@@ -111,7 +111,7 @@ struct SxbEp {
 namespace sxb {
 namespace {
 
-// out[m, n] = sum over ranks r, in rank order, of this rank's received pieces [world][t][N] (FP32 or BF16) -> FP32 or BF16.
+// out[m, n] = sum over ranks r, in rank order, of this rank's received pieces [world][t][N] (FP32 or F16) -> FP32 or BF16.
 template <typename TP, typename TOUT>
 __global__ void __launch_bounds__(256) sum_pieces_kernel(const TP *__restrict__ recv, int world, int64_t per_rank, TOUT *__restrict__ out) {
     const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
@@ -151,7 +151,7 @@ int sxb_ep_create(const uint8_t id[128], int world, int rank, int64_t T, int64_t
     SXB_CHECK(world >= 1 && world <= kMaxRanks && rank >= 0 && rank < world, fn, ": rank ", rank, " of ", world, " (1..", kMaxRanks, " ranks)");
     SXB_CHECK(T >= world && T % world == 0 && d >= 8 && d % 8 == 0 && A >= 1 && A <= 64, fn, ": T = ", T, " tokens over ", world,
               " ranks, d = ", d, ", A = ", A);
-    SXB_CHECK(return_path >= 0 && return_path <= 2, fn, ": return path ", return_path, " (0 reduce-scatter, 1 FP32 peer stores, 2 BF16 peer stores)");
+    SXB_CHECK(return_path >= 0 && return_path <= 2, fn, ": return path ", return_path, " (0 reduce-scatter, 1 FP32 peer stores, 2 F16 peer stores)");
     auto *ep = new SxbEp;
     ep->world = world, ep->rank = rank, ep->return_path = return_path, ep->T = T, ep->t = T / world, ep->d = d, ep->A = A;
     *out = ep;
@@ -291,7 +291,7 @@ int sxb_moe_layer_ep(SxbEp *ep, const SxbMoeLayerArgs *a, sxb_stream_t stream) {
         mark(ep, 5, st);
     } else {
         for (int r = 0; r < ep->world; ++r) peer.base[r] = ep->peer_recv[r];
-        peer.world = ep->world, peer.rank = ep->rank, peer.t = t, peer.bf16 = ep->return_path == 2;
+        peer.world = ep->world, peer.rank = ep->rank, peer.t = t, peer.f16 = ep->return_path == 2;
         b.y = nullptr, b.out_act = SXB_ACT_F32;
         if (int rc = moe_layer_impl(&b, stream, &peer)) return rc;
         mark(ep, 3, st);
@@ -299,9 +299,9 @@ int sxb_moe_layer_ep(SxbEp *ep, const SxbMoeLayerArgs *a, sxb_stream_t stream) {
         SXB_NCCL(nc.AllReduce(ep->flag, ep->flag + 32, 1, kNcclInt32, kNcclSum, ep->comm, st), "all-reduce after the peer stores");
         mark(ep, 4, st);
         const unsigned blocks = (unsigned)((t * d / 4 + 255) / 256);
-        if (peer.bf16) {
-            if (a->out_act == SXB_ACT_F32) sum_pieces_kernel<uint16_t, float><<<blocks, 256, 0, st>>>((const uint16_t *)ep->recv, ep->world, t * d, (float *)a->y);
-            else sum_pieces_kernel<uint16_t, uint16_t><<<blocks, 256, 0, st>>>((const uint16_t *)ep->recv, ep->world, t * d, (uint16_t *)a->y);
+        if (peer.f16) {
+            if (a->out_act == SXB_ACT_F32) sum_pieces_kernel<__half, float><<<blocks, 256, 0, st>>>((const __half *)ep->recv, ep->world, t * d, (float *)a->y);
+            else sum_pieces_kernel<__half, uint16_t><<<blocks, 256, 0, st>>>((const __half *)ep->recv, ep->world, t * d, (uint16_t *)a->y);
         } else {
             if (a->out_act == SXB_ACT_F32) sum_pieces_kernel<float, float><<<blocks, 256, 0, st>>>((const float *)ep->recv, ep->world, t * d, (float *)a->y);
             else sum_pieces_kernel<float, uint16_t><<<blocks, 256, 0, st>>>((const float *)ep->recv, ep->world, t * d, (uint16_t *)a->y);

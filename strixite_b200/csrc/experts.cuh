@@ -12,7 +12,7 @@ struct PeerOut {
     void *base[8];
     int world, rank;
     int64_t t;
-    int bf16;  // pieces stored as BF16 instead of FP32
+    int f16;  // pieces stored as F16 instead of FP32
 };
 
 // stream_mma.cu - exact-product kernels (mma.sync on integer codes, FP32 scale / min per group).

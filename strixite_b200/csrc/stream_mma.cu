@@ -27,6 +27,7 @@
 #include "experts.cuh"
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 namespace sxb {
 namespace {
@@ -551,7 +552,7 @@ __global__ void __launch_bounds__(256)
 
 // The same reduce for an expert-parallel rank whose rows go to their owners: no shared add, FP32 sums; the four columns
 // are stored, as this rank's piece, into the owner's receive buffer through its peer mapping (16 or 8 bytes a store).
-template <bool PBF16, bool OUT_BF16>
+template <bool PBF16, bool OUT_F16>
 __global__ void __launch_bounds__(256)
     combine_reduce_peer_kernel(const float *__restrict__ partial, const int32_t *__restrict__ ids, const float *__restrict__ coef,
                                int64_t M, int64_t A, int64_t E_total, int64_t e_lo, int64_t E_local, int64_t N, const PeerOut peer) {
@@ -578,10 +579,12 @@ __global__ void __launch_bounds__(256)
     if (!ok) v[0] = v[1] = v[2] = v[3] = qnan_f32();
     const int owner = (int)(m / peer.t);
     const int64_t at = (((int64_t)peer.rank * peer.t + m % peer.t) * N + n);
-    if constexpr (OUT_BF16) {
+    if constexpr (OUT_F16) {
+        // F16, not BF16: eleven significant bits keep the sum of a row's pieces inside the layer's tolerance (BF16 pieces
+        // measured 3.4e-2 of the RMS); a piece beyond F16's range (|v| > 65504) would become infinite
+        const __half2 lo = __floats2half2_rn(v[0], v[1]), hi = __floats2half2_rn(v[2], v[3]);
         uint2 o;
-        o.x = (uint32_t)f32_to_bf16_bits(v[0]) | ((uint32_t)f32_to_bf16_bits(v[1]) << 16);
-        o.y = (uint32_t)f32_to_bf16_bits(v[2]) | ((uint32_t)f32_to_bf16_bits(v[3]) << 16);
+        o.x = *reinterpret_cast<const uint32_t *>(&lo), o.y = *reinterpret_cast<const uint32_t *>(&hi);
         *reinterpret_cast<uint2 *>(static_cast<uint16_t *>(peer.base[owner]) + at) = o;
     } else {
         *reinterpret_cast<float4 *>(static_cast<float *>(peer.base[owner]) + at) = make_float4(v[0], v[1], v[2], v[3]);
@@ -819,10 +822,10 @@ int combine_reduce(const char *fn, const float *partial, const int32_t *ids, con
         auto st = static_cast<cudaStream_t>(stream);
 #define SXB_PEER(PB, OB) combine_reduce_peer_kernel<PB, OB><<<blocks, 256, 0, st>>>(partial, ids, coef, M, A, E_total, e_lo, E_local, N, *peer)
         if (partial_bf16) {
-            if (peer->bf16) SXB_PEER(true, true);
+            if (peer->f16) SXB_PEER(true, true);
             else SXB_PEER(true, false);
         } else {
-            if (peer->bf16) SXB_PEER(false, true);
+            if (peer->f16) SXB_PEER(false, true);
             else SXB_PEER(false, false);
         }
 #undef SXB_PEER

@@ -434,7 +434,7 @@ def ep_unique_id() -> bytes:
 
 class EpContext:
     """A rank's expert-parallel context (sxb_ep_create): NCCL communicator, exchange buffers, peer mappings.
-    return_path: 0 reduce-scatter, 1 peer stores of FP32 pieces, 2 of BF16 pieces."""
+    return_path: 0 reduce-scatter, 1 peer stores of FP32 pieces, 2 of F16 pieces."""
 
     def __init__(self, unique_id: bytes, world: int, rank: int, T: int, d: int, A: int, return_path: int = 1):
         self.handle = C.c_void_p()
