@@ -39,7 +39,7 @@ def test_one_rank_equals_the_plain_layer(cuda, T, tc):
             K.check_router_error(buf.router_err, cfg.name)
             K.check_expert_error(buf.expert_err, cfg.name)
             assert torch.equal(buf.ids, layer.buf.ids)
-            piece = want if rp != 2 else want.to(torch.bfloat16).float()  # one rank: its piece is the whole sum
+            piece = want if rp != 2 else want.to(torch.float16).float()  # one rank: its piece is the whole sum, sent as F16
             assert torch.equal(y, piece.to(dt)), f"return path {rp}, {dt}"
             tm = ctx.timing()
             assert tm["layers"] >= 1 and tm["experts"] > 0
