@@ -157,9 +157,29 @@ int sxb_residual_add(const void *x, const void *y, int y_act, void *out, int64_t
 
 /* kernels/hc.hpp:52-54  hc_inject: the residual injection that follows the block, in place:
  * X[t, s*d + j] += w_in[t, s] * y[t, j] for the H = 4 residual streams of X [T, H*d]; one rounding per element to the
- * activation dtype.  y must not overlap X.  (sxb_moe_shared_add_inject is this fused with the shared expert's gated add;
- * the hyper-connection mix that PRODUCES the block's input, hc_mix_down / hc_mix_up, is not part of this library.) */
+ * activation dtype.  y must not overlap X.  (sxb_moe_shared_add_inject is this fused with the shared expert's gated add.) */
 int sxb_hc_inject(void *x, const float *w_in, const void *y, int64_t T, int64_t H, int64_t d, int act, sxb_stream_t stream);
+
+/* kernels/hc.hpp:36-42  hc_mix_down (Q4DeviceView / Q8DeviceView overloads): the first half of the hyper-connection mix that
+ * produces the block's input.  X [T, H*d] (F32 or BF16, 16-byte aligned) -> h [T, r] = silu(a / H) for the first r rows of w,
+ * w_in [T, H] = 2 sigmoid(a / H) for the next H rows (inject != 0; w_in must be NULL otherwise), inv [T, H] = the
+ * per-stream inverse RMS.  w: [r (+ H), H*d], the hc_norm weight folded in; H == 4; d % 32 == 0; r <= 1024; T <= 65535.
+ * All arithmetic FP32. */
+int sxb_hc_mix_down_q4(const void *x, const SxbQView *w, int64_t T, int64_t H, int64_t d, int64_t r, int inject, float eps, float *h,
+                       float *w_in, float *inv, int act, sxb_stream_t stream);
+int sxb_hc_mix_down_q8(const void *x, const SxbQView *w, int64_t T, int64_t H, int64_t d, int64_t r, int inject, float eps, float *h,
+                       float *w_in, float *inv, int act, sxb_stream_t stream);
+/* kernels/hc.hpp:44-50  hc_mix_up (Q4ChunkMajorView / Q8ChunkMajorView overloads):
+ * u[t, j] = (1/H) sum_s sigmoid(W_up[s*d + j] . h[t]) * X[t, s*d + j] * inv[t, s] * (1 + norm_w[s*d + j]), rounded once to the
+ * activation dtype.  w_up: [H*d, r] in the CHUNK-MAJOR layout (formats/q4.hpp:41-55: 32-code chunk c of row n at
+ * q[(c * N + n) * 16 or 32 bytes], group g's scale / min at [g * N + n]); r % 32 == 0, r <= 1024.  u must not overlap x. */
+int sxb_hc_mix_up_q4(const float *h, const SxbQView *w_up, const void *x, const float *norm_w, const float *inv, int64_t T, int64_t H,
+                     int64_t d, void *u, int act, sxb_stream_t stream);
+int sxb_hc_mix_up_q8(const float *h, const SxbQView *w_up, const void *x, const float *norm_w, const float *inv, int64_t T, int64_t H,
+                     int64_t d, void *u, int act, sxb_stream_t stream);
+/* formats/q4.hpp:55 / formats/q8.hpp:46  to_chunk_major, for a weight already on the device: the codes, scales and mins of the
+ * row-major view w re-laid out chunk-major into q / scale / minv (same sizes as the source arrays; K % 32 == 0). */
+int sxb_to_chunk_major(const SxbQView *w, int bits, uint8_t *q, uint16_t *scale, uint16_t *minv, sxb_stream_t stream);
 
 /* ---- Pack (grouping of slots by expert) --------------------------------------------------------------------- */
 

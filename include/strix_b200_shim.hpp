@@ -108,6 +108,39 @@ inline void moe_shared_add_inject(void *y, const void *s, const float *gate_logi
 inline void hc_inject(void *x, const float *w_in, const void *y, int64_t T, int64_t H, int64_t d, Act act, hipStream_t stream) {
     b200_detail::check(sxb_hc_inject(x, w_in, y, T, H, d, b200_detail::act(act), stream));
 }
+// kernels/hc.hpp:36-50  hc_mix_down / hc_mix_up.  The chunk-major views (runtime/q4_device.hpp:37-43,
+// runtime/q8_device.hpp:36-42) have the row-major views' fields; they stay separate types so that a kernel cannot be handed
+// the wrong layout.
+struct Q4ChunkMajorView {
+    const uint8_t *q;
+    const uint16_t *scale, *minv;
+    int64_t N, K, G;
+};
+struct Q8ChunkMajorView {
+    const uint8_t *q;
+    const uint16_t *scale, *minv;
+    int64_t N, K, G;
+};
+inline void hc_mix_down(const void *x, const Q4DeviceView &w, int64_t T, int64_t H, int64_t d, int64_t r, bool inject, float eps,
+                        float *h, float *w_in, float *inv, Act act, hipStream_t stream) {
+    b200_detail::check(sxb_hc_mix_down_q4(x, reinterpret_cast<const SxbQView *>(&w), T, H, d, r, inject ? 1 : 0, eps, h, w_in, inv,
+                                          b200_detail::act(act), stream));
+}
+inline void hc_mix_down(const void *x, const Q8DeviceView &w, int64_t T, int64_t H, int64_t d, int64_t r, bool inject, float eps,
+                        float *h, float *w_in, float *inv, Act act, hipStream_t stream) {
+    b200_detail::check(sxb_hc_mix_down_q8(x, reinterpret_cast<const SxbQView *>(&w), T, H, d, r, inject ? 1 : 0, eps, h, w_in, inv,
+                                          b200_detail::act(act), stream));
+}
+inline void hc_mix_up(const float *h, const Q4ChunkMajorView &w_up, const void *x, const float *norm_w, const float *inv, int64_t T,
+                      int64_t H, int64_t d, void *u, Act act, hipStream_t stream) {
+    static_assert(sizeof(Q4ChunkMajorView) == sizeof(SxbQView), "view layouts");
+    b200_detail::check(sxb_hc_mix_up_q4(h, reinterpret_cast<const SxbQView *>(&w_up), x, norm_w, inv, T, H, d, u, b200_detail::act(act), stream));
+}
+inline void hc_mix_up(const float *h, const Q8ChunkMajorView &w_up, const void *x, const float *norm_w, const float *inv, int64_t T,
+                      int64_t H, int64_t d, void *u, Act act, hipStream_t stream) {
+    static_assert(sizeof(Q8ChunkMajorView) == sizeof(SxbQView), "view layouts");
+    b200_detail::check(sxb_hc_mix_up_q8(h, reinterpret_cast<const SxbQView *>(&w_up), x, norm_w, inv, T, H, d, u, b200_detail::act(act), stream));
+}
 
 // kernels/moe_grouped.hpp
 inline size_t moe_route_workspace_bytes(int64_t M, int64_t A, int64_t E) {

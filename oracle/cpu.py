@@ -252,6 +252,65 @@ def moe_shared_add_inject(y, s, gate_logit, gate_index, x, w_in, err=None):
     return y, x
 
 
+def codes_of(w: QWeight) -> np.ndarray:
+    """The integer codes [N, K] of a row-major weight (Q4: low nibble = even k, formats/q4.hpp:15-24)."""
+    if w.bits == 8:
+        return w.q.astype(np.float64)
+    out = np.empty((w.N, w.K), dtype=np.float64)
+    out[:, 0::2], out[:, 1::2] = (w.q & 0xF), (w.q >> 4)
+    return out
+
+
+def affine_weights(w: QWeight) -> np.ndarray:
+    """code * scale + min in float64, NOT rounded to a dequantized value: what a row's dot with a 32-code chunk amounts to
+    in the hyper-connection kernels, scale * sum(x * code) + min * sum(x) (kernels/hc.hip:117-123, 206-211)."""
+    sc = np.repeat(bf16_to_f32(w.scale).astype(np.float64), w.G, axis=1)
+    mn = np.repeat(bf16_to_f32(w.minv).astype(np.float64), w.G, axis=1)
+    return codes_of(w) * sc + mn
+
+
+def to_chunk_major(w: QWeight) -> QWeight:
+    """formats/q4.hpp:41-55 / formats/q8.hpp: 32-code chunk c of row n at q[(c * N + n) * chunk bytes], group g's scale / min
+    at [g * N + n].  Returned as a QWeight whose arrays hold that layout (q [K/32, N, chunk bytes], scale / min [K/G, N])."""
+    cb = 16 if w.bits == 4 else 32
+    q = np.ascontiguousarray(w.q.reshape(w.N, w.K // 32, cb).transpose(1, 0, 2))
+    return QWeight(q, np.ascontiguousarray(w.scale.T), np.ascontiguousarray(w.minv.T), w.N, w.K, w.G, w.bits)
+
+
+def ref_to_chunk_major(w: QWeight) -> QWeight:
+    """The reference's own to_chunk_major (compiled from its sources)."""
+    cb = 16 if w.bits == 4 else 32
+    q = np.zeros((w.K // 32, w.N, cb), dtype=np.uint8)
+    scale, minv = np.zeros((w.K // w.G, w.N), dtype=np.uint16), np.zeros((w.K // w.G, w.N), dtype=np.uint16)
+    rc = ref_lib().ref_to_chunk_major(_p(np.ascontiguousarray(w.q)), _p(np.ascontiguousarray(w.scale)), _p(np.ascontiguousarray(w.minv)),
+                                      i64(w.N), i64(w.K), i64(w.G), C.c_int(w.bits), _p(q), _p(scale), _p(minv))
+    if rc != 0:
+        raise ValueError("ref_to_chunk_major: the reference rejected the arrays")
+    return QWeight(q, scale, minv, w.N, w.K, w.G, w.bits)
+
+
+def hc_mix_down(x: np.ndarray, w: QWeight, H: int, d: int, r: int, inject: bool, eps: float):
+    """kernels/hc.hip:82-165 hc_mix_down in float64: X [T, H*d] (float32 values) -> h [T, r], w_in [T, H] or None, inv [T, H].
+    a = sum_s inv_s * (W'_s . X_s) over the folded weight's rows, z = a / H, h = silu(z), w_in = 2 sigmoid(z),
+    inv_s = 1 / sqrt(mean(X_s^2) + eps)."""
+    X = np.asarray(x, dtype=np.float64).reshape(x.shape[0], H, d)
+    W = affine_weights(w).reshape(w.N, H, d)
+    inv = 1.0 / np.sqrt((X * X).mean(axis=2) + eps)            # [T, H]
+    per_stream = np.einsum("tsk,nsk->tns", X, W)                  # [T, R, H]
+    z = (per_stream * inv[:, None, :]).sum(axis=2) / H
+    sig = 1.0 / (1.0 + np.exp(-z))
+    return z[:, :r] * sig[:, :r], (2.0 * sig[:, r:r + H] if inject else None), inv
+
+
+def hc_mix_up(h: np.ndarray, w_up: QWeight, x: np.ndarray, norm_w: np.ndarray, inv: np.ndarray, H: int, d: int) -> np.ndarray:
+    """kernels/hc.hip:176-243 hc_mix_up in float64 (w_up ROW-major [H*d, r]): u [T, d], not yet rounded to the activation dtype."""
+    T = h.shape[0]
+    logits = np.asarray(h, dtype=np.float64) @ affine_weights(w_up).T     # [T, H*d]
+    z = 1.0 / (1.0 + np.exp(-logits))
+    n = np.asarray(x, dtype=np.float64) * np.repeat(np.asarray(inv, dtype=np.float64), d, axis=1) * (1.0 + np.asarray(norm_w, dtype=np.float64))[None, :]
+    return (z * n).reshape(T, H, d).sum(axis=1) / H
+
+
 def hardware_threads() -> int:
     return int(lib().orc_hardware_threads())
 

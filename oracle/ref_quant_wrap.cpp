@@ -58,4 +58,28 @@ int ref_dequantize(const uint8_t *q, const uint16_t *scale, const uint16_t *minv
     return 0;
 }
 
+// formats/q4.hpp:55 / formats/q8.hpp:46 to_chunk_major: q holds the same number of bytes as the source, scale / minv N * (K / G).
+int ref_to_chunk_major(const uint8_t *q, const uint16_t *scale, const uint16_t *minv, int64_t N, int64_t K, int64_t G, int bits,
+                       uint8_t *qo, uint16_t *so, uint16_t *mo) {
+    try {
+        const size_t groups = (size_t)(N * (K / G));
+        if (bits == 4) {
+            strix::Q4Weight r;
+            r.N = N, r.K = K, r.G = G;
+            r.q.assign(q, q + N * K / 2), r.scale.assign(scale, scale + groups), r.minv.assign(minv, minv + groups);
+            const strix::Q4ChunkMajor c = strix::to_chunk_major(r, "ref_to_chunk_major");
+            std::memcpy(qo, c.q.data(), c.q.size()), std::memcpy(so, c.scale.data(), 2 * c.scale.size()), std::memcpy(mo, c.minv.data(), 2 * c.minv.size());
+        } else {
+            strix::Q8Weight r;
+            r.N = N, r.K = K, r.G = G;
+            r.q.assign(q, q + N * K), r.scale.assign(scale, scale + groups), r.minv.assign(minv, minv + groups);
+            const strix::Q8ChunkMajor c = strix::to_chunk_major(r, "ref_to_chunk_major");
+            std::memcpy(qo, c.q.data(), c.q.size()), std::memcpy(so, c.scale.data(), 2 * c.scale.size()), std::memcpy(mo, c.minv.data(), 2 * c.minv.size());
+        }
+    } catch (const std::exception &) {
+        return 1;
+    }
+    return 0;
+}
+
 }  // extern "C"

@@ -107,6 +107,11 @@ SIGNATURES = {
     "sxb_strixw_qview": (C.c_int, [vp, cp, i64, i64, C.POINTER(SxbQView), C.POINTER(C.c_int)]),
     "sxb_strixw_expert_views": (C.c_int, [vp, cp, i64, C.POINTER(SxbQView), C.POINTER(SxbQView), C.POINTER(C.c_int)]),
     "sxb_hc_inject": (C.c_int, [vp, vp, vp, i64, i64, i64, C.c_int, vp]),
+    "sxb_hc_mix_down_q4": (C.c_int, [vp, QV, i64, i64, i64, i64, C.c_int, C.c_float, vp, vp, vp, C.c_int, vp]),
+    "sxb_hc_mix_down_q8": (C.c_int, [vp, QV, i64, i64, i64, i64, C.c_int, C.c_float, vp, vp, vp, C.c_int, vp]),
+    "sxb_hc_mix_up_q4": (C.c_int, [vp, QV, vp, vp, vp, i64, i64, i64, vp, C.c_int, vp]),
+    "sxb_hc_mix_up_q8": (C.c_int, [vp, QV, vp, vp, vp, i64, i64, i64, vp, C.c_int, vp]),
+    "sxb_to_chunk_major": (C.c_int, [QV, C.c_int, vp, vp, vp, vp]),
     "sxb_moe_route_small": (C.c_int, [vp, i64, i64, i64, i64, i64, i64, vp, vp, vp, sz, vp, vp, vp]),
 }
 for _b in ("q4", "q8"):

@@ -224,6 +224,26 @@ def hc_inject(x, w_in, y, T, H, d, act, stream=None):
     _check(_lib.load().sxb_hc_inject(_ptr(x), _ptr(w_in), _ptr(y), T, H, d, int(act), _stream(stream)))
 
 
+def hc_mix_down(x, w: QDeviceView, T, H, d, r, inject, eps, h, w_in, inv, act, stream=None):
+    """kernels/hc.hpp:36-42: X [T, H*d] -> h [T, r], w_in [T, H] (inject), inv [T, H]; w [r (+ H), H*d] Q4 or Q8."""
+    fn = getattr(_lib.load(), f"sxb_hc_mix_down_{_b(w)}")
+    _check(fn(_ptr(x), C.byref(w.c()), T, H, d, r, int(bool(inject)), C.c_float(eps), _ptr(h), _ptr(w_in), _ptr(inv), int(act),
+              _stream(stream)))
+
+
+def hc_mix_up(h, w_up: QDeviceView, x, norm_w, inv, T, H, d, u, act, stream=None):
+    """kernels/hc.hpp:44-50: u [T, d] from h [T, r], the streams X, the hc_norm weight and inv; w_up [H*d, r] CHUNK-MAJOR."""
+    fn = getattr(_lib.load(), f"sxb_hc_mix_up_{_b(w_up)}")
+    _check(fn(_ptr(h), C.byref(w_up.c()), _ptr(x), _ptr(norm_w), _ptr(inv), T, H, d, _ptr(u), int(act), _stream(stream)))
+
+
+def to_chunk_major(w: QDeviceView, stream=None) -> QDeviceView:
+    """formats/q4.hpp:55 to_chunk_major on the device: a new view with the same codes, scales and mins chunk-major."""
+    q, sc, mn = torch.empty_like(w.q), torch.empty_like(w.scale), torch.empty_like(w.minv)
+    _check(_lib.load().sxb_to_chunk_major(C.byref(w.c()), w.bits, _ptr(q), _ptr(sc), _ptr(mn), _stream(stream)))
+    return QDeviceView(q, sc, mn, w.N, w.K, w.G, w.bits)
+
+
 # ---- kernels/moe_grouped.hpp ----------------------------------------------------------------------------------
 
 def moe_route_workspace_bytes(M, A, E) -> int:

@@ -1,0 +1,80 @@
+"""The hyper-connection mix either side of the MoE block (kernels/hc.hpp:36-54) against the float64 oracle, through the
+C ABI: hc_mix_down, hc_mix_up (chunk-major weight) and the device-side chunk-major re-layout."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import bf16_tensor, bits_of, max_abs_over_rms, random_weights, upload
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("bits,G", [(4, 64), (8, 128), (4, 32)])
+def test_to_chunk_major_on_the_device(cuda, oracle, bits, G):
+    """sxb_to_chunk_major equals the host re-layout, which test_oracle pins to the reference's own to_chunk_major."""
+    from strixite_b200 import kernels as K
+    rng = np.random.default_rng(bits + G)
+    wq = oracle.quantize(random_weights(rng, 1300, 320), G if 320 % G == 0 else 64, bits)
+    cm = K.to_chunk_major(upload(wq, cuda))
+    want = oracle.to_chunk_major(wq)
+    assert np.array_equal(cm.q.cpu().numpy().reshape(-1), want.q.reshape(-1))
+    assert np.array_equal(cm.scale.cpu().numpy().view(np.uint16).reshape(-1), want.scale.reshape(-1))
+    assert np.array_equal(cm.minv.cpu().numpy().view(np.uint16).reshape(-1), want.minv.reshape(-1))
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("bits,G,T,d,r,inject", [(4, 64, 1, 256, 64, True), (8, 128, 5, 512, 96, True), (4, 128, 16, 1024, 320, True),
+                                                  (8, 64, 37, 256, 32, False), (4, 32, 300, 128, 64, True)])
+def test_hc_mix(cuda, oracle, dt, bits, G, T, d, r, inject):
+    """hc_mix_down then hc_mix_up, each against the oracle on the same inputs: h, w_in and inv within FP32 summation noise of the
+    float64 values, u within it (F32 streams) or within one BF16 rounding of it (BF16 streams)."""
+    from strixite_b200 import kernels as K
+    H, eps = 4, 1e-6
+    rng = np.random.default_rng(T * 7 + d + bits)
+    R = r + (H if inject else 0)
+    wd = oracle.quantize(random_weights(rng, R, H * d, std=0.05), G, bits)
+    wu = oracle.quantize(random_weights(rng, H * d, r, std=0.2), 32 if r % G else G, bits)
+    norm_w = (rng.standard_normal(H * d) * 0.1).astype(np.float32)
+    x = (rng.standard_normal((T, H * d)) * np.repeat(rng.random((T, H)) * 3 + 0.2, d, axis=1)).astype(np.float32)  # streams of different RMS
+    if dt == torch.bfloat16:
+        xb = oracle.f32_to_bf16(x)
+        x = oracle.bf16_to_f32(xb)
+        xd, act = bf16_tensor(xb, cuda), K.Act.BF16
+    else:
+        xd, act = torch.from_numpy(x).to(cuda), K.Act.F32
+    h = torch.full((T, r), float("nan"), dtype=torch.float32, device=cuda)
+    w_in = torch.full((T, H), float("nan"), dtype=torch.float32, device=cuda) if inject else None
+    inv = torch.full((T, H), float("nan"), dtype=torch.float32, device=cuda)
+    K.hc_mix_down(xd, upload(wd, cuda), T, H, d, r, inject, eps, h, w_in, inv, act)
+    h_ref, w_in_ref, inv_ref = oracle.hc_mix_down(x, wd, H, d, r, inject, eps)
+    assert max_abs_over_rms(inv.cpu().numpy(), inv_ref) <= 1e-5
+    assert max_abs_over_rms(h.cpu().numpy(), h_ref) <= 1e-4
+    if inject:
+        assert max_abs_over_rms(w_in.cpu().numpy(), w_in_ref) <= 1e-4
+    # the up half on the GPU's own h and inv (so that its error is its own)
+    u = torch.empty((T, d), dtype=dt, device=cuda)
+    K.hc_mix_up(h, K.to_chunk_major(upload(wu, cuda)), xd, torch.from_numpy(norm_w).to(cuda), inv, T, H, d, u, act)
+    torch.cuda.synchronize()
+    u_ref = oracle.hc_mix_up(h.cpu().numpy(), wu, x, norm_w, inv.cpu().numpy(), H, d)
+    if dt == torch.float32:
+        assert max_abs_over_rms(u.cpu().numpy(), u_ref) <= 1e-4
+    else:
+        got = oracle.bf16_to_f32(bits_of(u)).astype(np.float64)
+        assert np.all(np.abs(got - u_ref) <= 2.0 ** -8 * np.abs(u_ref) + 1e-5 * np.sqrt(np.mean(u_ref ** 2)))  # one BF16 rounding
+
+
+def test_hc_mix_argument_checks(cuda, oracle):
+    from strixite_b200 import kernels as K
+    rng = np.random.default_rng(1)
+    H, d, r, T = 4, 64, 32, 3
+    wd = upload(oracle.quantize(random_weights(rng, r + H, H * d), 64, 4), cuda)
+    x = torch.zeros((T, H * d), dtype=torch.bfloat16, device=cuda)
+    h, w_in, inv = (torch.zeros((T, n), dtype=torch.float32, device=cuda) for n in (r, H, H))
+    with pytest.raises(K.Error, match="w_in must be given exactly when inject"):
+        K.hc_mix_down(x, wd, T, H, d, r, True, 1e-6, h, None, inv, K.Act.BF16)
+    with pytest.raises(K.Error, match="rows, expected r"):
+        K.hc_mix_down(x, wd, T, H, d, r, False, 1e-6, h, None, inv, K.Act.BF16)
+    with pytest.raises(K.Error, match="streams, only 4"):
+        K.hc_mix_down(x, wd, T, 2, 2 * d, r, True, 1e-6, h, w_in, inv, K.Act.BF16)
+    with pytest.raises(K.Error, match="eps must be finite"):
+        K.hc_mix_down(x, wd, T, H, d, r, True, 0.0, h, w_in, inv, K.Act.BF16)

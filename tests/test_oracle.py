@@ -139,3 +139,46 @@ def test_invalid_ids_poison_outputs(oracle):
     h = oracle.f32_to_bf16(rng.standard_normal((3, 2, K)).astype(np.float32))
     yc = oracle.experts_combine(h, w, E, ids, np.ones((3, 2), np.float32), out_act=oracle.F32)
     assert np.all(np.isnan(yc[1])) and not np.any(np.isnan(yc[[0, 2]]))
+
+
+@pytest.mark.parametrize("bits,G", [(4, 64), (8, 32), (4, 128)])
+def test_chunk_major_matches_compiled_reference(oracle, bits, G):
+    """The chunk-major re-layout the hyper-connection up projection reads (formats/q4.hpp:41-55) against the reference's own
+    to_chunk_major, byte for byte."""
+    if oracle.ref_lib() is None:
+        pytest.skip("the reference checkout is not available here")
+    rng = np.random.default_rng(bits * G)
+    w = oracle.quantize((rng.standard_normal((37, 256)) * 0.02).astype(np.float32), G, bits)
+    a, b = oracle.to_chunk_major(w), oracle.ref_to_chunk_major(w)
+    assert np.array_equal(a.q, b.q) and np.array_equal(a.scale, b.scale) and np.array_equal(a.minv, b.minv)
+
+
+def test_hc_mix_oracle_against_plain_loops(oracle):
+    """The vectorised float64 hc_mix oracle against the definition written out element by element on a tiny case."""
+    rng = np.random.default_rng(3)
+    H, d, r, T, eps = 4, 32, 32, 2, 1e-6
+    wd = oracle.quantize((rng.standard_normal((r + H, H * d)) * 0.05).astype(np.float32), 32, 4)
+    x = rng.standard_normal((T, H * d)).astype(np.float32)
+    h, w_in, inv = oracle.hc_mix_down(x, wd, H, d, r, True, eps)
+    W = oracle.affine_weights(wd)
+    for t in range(T):
+        iv = [1.0 / np.sqrt(np.mean(x[t, s * d:(s + 1) * d].astype(np.float64) ** 2) + eps) for s in range(H)]
+        assert np.allclose(inv[t], iv, rtol=1e-12)
+        for n in range(r + H):
+            a = sum(iv[s] * float(np.dot(x[t, s * d:(s + 1) * d].astype(np.float64), W[n, s * d:(s + 1) * d])) for s in range(H))
+            z = a / H
+            if n < r:
+                assert np.isclose(h[t, n], z / (1 + np.exp(-z)), rtol=1e-10, atol=1e-12)
+            else:
+                assert np.isclose(w_in[t, n - r], 2 / (1 + np.exp(-z)), rtol=1e-10)
+    wu = oracle.quantize((rng.standard_normal((H * d, r)) * 0.2).astype(np.float32), 32, 8)
+    nw = (rng.standard_normal(H * d) * 0.1).astype(np.float32)
+    u = oracle.hc_mix_up(h, wu, x, nw, inv, H, d)
+    Wu = oracle.affine_weights(wu)
+    for t in range(T):
+        for j in range(d):
+            tot = 0.0
+            for s in range(H):
+                row = s * d + j
+                tot += 1 / (1 + np.exp(-float(np.dot(Wu[row], h[t])))) * float(x[t, row]) * inv[t, s] * (1 + float(nw[row]))
+            assert np.isclose(u[t, j], tot / H, rtol=1e-10, atol=1e-12)
