@@ -680,6 +680,44 @@ def run_reference(args):
     }))
 
 
+def hc_mix_measure(dev, peaks, seed, T=16, d=4096, r=320, H=4, iters=50):
+    """The hyper-connection mix that produces the block's input (hc_mix_down + hc_mix_up, Q8 g64 weights) at the decode
+    configuration's T and d: microseconds a mix (CUDA events, the 10.6 MB of weights rotated through eight copies so that
+    every mix reads them from HBM) and the bandwidth that is of the measured peak."""
+    from strixite_b200 import kernels as K
+    g = torch.Generator(device=dev).manual_seed(seed + 77)
+    copies = []
+    for _ in range(8):
+        wd_f = torch.randn((r + H, H * d), device=dev, generator=g) * 0.05
+        wu_f = torch.randn((H * d, r), device=dev, generator=g) * 0.2
+        copies.append((K.quantize(wd_f, 64, 8), K.to_chunk_major(K.quantize(wu_f, 64, 8))))
+    x = torch.randn((T, H * d), device=dev, generator=g).to(torch.bfloat16)
+    norm_w = torch.randn(H * d, device=dev, generator=g) * 0.1
+    h = torch.empty((T, r), dtype=torch.float32, device=dev)
+    w_in, inv = torch.empty((T, H), dtype=torch.float32, device=dev), torch.empty((T, H), dtype=torch.float32, device=dev)
+    u = torch.empty((T, d), dtype=torch.bfloat16, device=dev)
+
+    def mix(i):
+        wd, wu = copies[i % len(copies)]
+        K.hc_mix_down(x, wd, T, H, d, r, True, 1e-6, h, w_in, inv, K.Act.BF16)
+        K.hc_mix_up(h, wu, x, norm_w, inv, T, H, d, u, K.Act.BF16)
+
+    for i in range(8):
+        mix(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        mix(i)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / iters
+    nbytes = copies[0][0].bytes() + copies[0][1].bytes() + 2 * x.numel() * 2 + u.numel() * 2
+    gbs = nbytes / (us * 1e-6) / 1e9
+    return {"T": T, "d": d, "r": r, "weights": "q8g64", "us_per_mix": us, "bytes_per_mix": nbytes, "launches_per_mix": 2,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"]}}
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -789,6 +827,10 @@ def main():
             extra[c.name] = e
             del r
             torch.cuda.empty_cache()
+        try:
+            extra["hc_mix_decode"] = hc_mix_measure(dev, peaks, args.seed)
+        except Exception as ex:
+            extra["hc_mix_decode"] = {"error": f"{type(ex).__name__}: {ex}"}
         line["other_workloads"] = extra
 
     if rank == 0:
