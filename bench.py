@@ -684,6 +684,7 @@ def hc_mix_measure(dev, peaks, seed, T=16, d=4096, r=320, H=4, iters=50):
     """The hyper-connection mix that produces the block's input (hc_mix_down + hc_mix_up, Q8 g64 weights) at the decode
     configuration's T and d: microseconds a mix (CUDA events, the 10.6 MB of weights rotated through eight copies so that
     every mix reads them from HBM) and the bandwidth that is of the measured peak."""
+    import torch
     from strixite_b200 import kernels as K
     g = torch.Generator(device=dev).manual_seed(seed + 77)
     copies = []

@@ -32,8 +32,8 @@
 namespace sxb {
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kWarps = kThreads / 32;
+constexpr int kThreads = 256;      // small launches: two CTAs of eight warps an SM
+constexpr int kBigThreads = 512;   // launches with work for every SM: one CTA of sixteen warps, units handed out on demand
 constexpr int kTileTokens = 8;
 constexpr int kPrefetch = 4;  // steps of weights in flight per warp beyond the one being consumed
 constexpr int64_t kMaxK = 1 << 24;
@@ -130,7 +130,7 @@ __device__ inline void stage_tile(const uint16_t *__restrict__ x, int K, const i
     constexpr int UNITS = geo::kUnits, KI = geo::kStepCodes, CPL = geo::kCodesPerLane;
     const int units_per_row = K / 8, steps = K / KI;
     // 8 consecutive k of token n (16 bytes) -> one unit, permuted to match the nibble pairs of the weights.
-    for (int idx = threadIdx.x; idx < kTileTokens * units_per_row; idx += kThreads) {
+    for (int idx = threadIdx.x; idx < kTileTokens * units_per_row; idx += blockDim.x) {
         const int n = idx / units_per_row, k8 = idx % units_per_row;
         const int k = k8 * 8, step = k / KI, rem = k % KI, cc = rem / CPL, v = (rem % CPL) / 8;
         uint4 src = make_uint4(0u, 0u, 0u, 0u);
@@ -147,17 +147,25 @@ __device__ inline void stage_tile(const uint16_t *__restrict__ x, int K, const i
         xs[(step * UNITS + v) * 32 + n * 4 + cc] = dst;
     }
     // sum(x) of every (step, token), in a fixed order.
-    for (int idx = threadIdx.x; idx < steps * kTileTokens; idx += kThreads) {
+    for (int idx = threadIdx.x; idx < steps * kTileTokens; idx += blockDim.x) {
         const int step = idx / kTileTokens, n = idx % kTileTokens;
         const int64_t row = rows[n];
         float sum = 0.f;
         if (row >= 0) {
+            // the loads of a batch are independent of one another: under a streaming kernel's load an L2 round trip is
+            // thousands of cycles, and one load at a time made staging a tenth of a decode kernel's time
             const uint4 *p = reinterpret_cast<const uint4 *>(x + row * K + (int64_t)step * KI);
-            for (int i = 0; i < KI / 8; ++i) {
-                const uint4 u = p[i];
-                const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+            constexpr int kBatch = KI / 8 < 8 ? KI / 8 : 8;
+            for (int i0 = 0; i0 < KI / 8; i0 += kBatch) {
+                uint4 u[kBatch];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) sum += __uint_as_float(w4[j] << 16), sum += __uint_as_float(w4[j] & 0xffff0000u);
+                for (int i = 0; i < kBatch; ++i) u[i] = p[i0 + i];
+#pragma unroll
+                for (int i = 0; i < kBatch; ++i) {
+                    const uint32_t w4[4] = {u[i].x, u[i].y, u[i].z, u[i].w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) sum += __uint_as_float(w4[j] << 16), sum += __uint_as_float(w4[j] & 0xffff0000u);
+                }
             }
         }
         xsum[idx] = sum;
@@ -357,14 +365,16 @@ __device__ inline void rows_dot(float (&acc)[4], const StreamArgs &a, int64_t ro
 }
 
 template <int BITS, int G, int MODE, int SRC, typename TOUT>
-__global__ void __launch_bounds__(kThreads, 2) stream_kernel(const StreamArgs a) {
+__global__ void __launch_bounds__(kBigThreads, 1) stream_kernel(const StreamArgs a) {
     using geo = Geo<BITS, G>;
+    const int kWarps = (int)blockDim.x >> 5;
     extern __shared__ __align__(16) unsigned char smem[];
     const int K = (int)a.K, steps = K / geo::kStepCodes;
     const size_t pass_bytes = (size_t)steps * geo::kUnits * 512 + (size_t)steps * kTileTokens * 4;
     __shared__ int64_t s_row[kTileTokens];  // activation row of each token of the tile, -1 = none
     __shared__ int64_t s_out[kTileTokens];  // output row (slot, or token for dense)
     __shared__ int s_bucket, s_cnt;
+    __shared__ int s_next;  // the next unit of the CTA's run that no warp has taken yet
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c = lane & 3;
     const int64_t I = a.N / 2;
@@ -374,9 +384,25 @@ __global__ void __launch_bounds__(kThreads, 2) stream_kernel(const StreamArgs a)
                             : SRC == kDense     ? (a.M + kTileTokens - 1) / kTileTokens
                                                 : a.M;
     const int64_t total = n_tiles * units_per_tile;
-    const int64_t u_begin = total * blockIdx.x / gridDim.x, u_end = total * (blockIdx.x + 1) / gridDim.x;
     TOUT *out = static_cast<TOUT *>(a.out);
-
+    // How the units are dealt to the CTAs.  Even split: CTA b takes units [total b / n, total (b + 1) / n) - every CTA busy,
+    // but a CTA whose range crosses a tile boundary stages activations twice.  Tile-aligned: every tile's units are cut into
+    // `cpt` equal runs and a CTA takes whole runs, one staging each.  The aligned cut is taken when it leaves (almost) no CTA
+    // idle; inside a run the warps take units on demand either way.
+    const int64_t nb = gridDim.x;
+    int64_t cpt = max((int64_t)1, nb / max(n_tiles, (int64_t)1));
+    const int64_t chunk = ((units_per_tile + cpt - 1) / cpt + kWarps - 1) / kWarps * kWarps;
+    cpt = (units_per_tile + chunk - 1) / chunk;
+    const int64_t n_chunks = n_tiles * cpt;
+    const bool aligned = ((n_chunks + nb - 1) / nb) * chunk * 100 <= ((total + nb - 1) / nb) * 103;
+    for (int64_t ci = blockIdx.x; ci < (aligned ? n_chunks : nb); ci += nb) {
+    int64_t u_begin, u_end;
+    if (aligned) {
+        u_begin = (ci / cpt) * units_per_tile + (ci % cpt) * chunk;
+        u_end = min((ci / cpt + 1) * units_per_tile, u_begin + chunk);
+    } else {
+        u_begin = total * ci / nb, u_end = total * (ci + 1) / nb;
+    }
     for (int64_t tile = u_begin / units_per_tile; tile * units_per_tile < u_end; ++tile) {
         const int64_t lo = max(u_begin, tile * units_per_tile), hi = min(u_end, (tile + 1) * units_per_tile);
 
@@ -469,9 +495,18 @@ __global__ void __launch_bounds__(kThreads, 2) stream_kernel(const StreamArgs a)
         uint4 *xs = reinterpret_cast<uint4 *>(smem);
         float *xsum = reinterpret_cast<float *>(smem + (size_t)steps * geo::kUnits * 512);
         if (valid) stage_tile<BITS, G>(a.x, K, s_row, xs, xsum);
+        if (threadIdx.x == 0) s_next = 0;
         __syncthreads();
 
-        for (int64_t unit = lo + warp; unit < hi; unit += kWarps) {
+        // Warps take units on demand: two warps of an SM do not stream at the same rate (measured: the units of one of two
+        // co-resident CTAs took 2.5 times as long as the other's while both were alive), and a fixed deal leaves the fast ones
+        // idle at the end.  A unit's result does not depend on which warp computes it.
+        for (;;) {
+            int taken = 0;
+            if (lane == 0) taken = atomicAdd(&s_next, 1);
+            taken = __shfl_sync(0xffffffffu, taken, 0);
+            const int64_t unit = lo + taken;
+            if (unit >= hi) break;
             const int64_t u = unit - tile * units_per_tile;
             // The two weight rows this lane streams, as rows inside the expert, and where their results go.
             int64_t ra, rb;
@@ -503,6 +538,7 @@ __global__ void __launch_bounds__(kThreads, 2) stream_kernel(const StreamArgs a)
                 }
             }
         }
+    }
     }
 }
 
@@ -619,11 +655,14 @@ int launch_stream(const char *fn, const StreamArgs &a, int64_t est_units, cudaSt
     auto kern = stream_kernel<BITS, G, MODE, SRC, TOUT>;
     SXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn,
              ": reserving shared memory");
-    const int per_sm = smem > 100 * 1024 ? 1 : 2;
-    // Enough CTAs to fill the machine, never more than one per 8 units (a CTA's warps each want a unit).
+    // One CTA of sixteen warps an SM when there are several units for every warp of the machine; otherwise CTAs of eight
+    // warps, two an SM where their shared memory allows, and never more CTAs than one per unit and warp.
+    const bool big = est_units >= (int64_t)sm_count() * (kBigThreads / 32) * 2;
+    const int threads = big ? kBigThreads : kThreads, warps = threads / 32;
+    const int per_sm = big || smem > 100 * 1024 ? 1 : 2;
     int64_t grid = (int64_t)sm_count() * per_sm;
-    grid = std::max<int64_t>(1, std::min<int64_t>(grid, (est_units + kWarps - 1) / kWarps));
-    kern<<<(unsigned)grid, kThreads, smem, st>>>(a);
+    grid = std::max<int64_t>(1, std::min<int64_t>(grid, (est_units + warps - 1) / warps));
+    kern<<<(unsigned)grid, threads, smem, st>>>(a);
     return SXB_OK;
 }
 
