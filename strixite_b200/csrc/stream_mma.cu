@@ -129,22 +129,36 @@ __device__ inline void stage_tile(const uint16_t *__restrict__ x, int K, const i
     using geo = Geo<BITS, G>;
     constexpr int UNITS = geo::kUnits, KI = geo::kStepCodes, CPL = geo::kCodesPerLane;
     const int units_per_row = K / 8, steps = K / KI;
-    // 8 consecutive k of token n (16 bytes) -> one unit, permuted to match the nibble pairs of the weights.
-    for (int idx = threadIdx.x; idx < kTileTokens * units_per_row; idx += blockDim.x) {
-        const int n = idx / units_per_row, k8 = idx % units_per_row;
-        const int k = k8 * 8, step = k / KI, rem = k % KI, cc = rem / CPL, v = (rem % CPL) / 8;
-        uint4 src = make_uint4(0u, 0u, 0u, 0u);
-        const int64_t row = rows[n];
-        if (row >= 0) src = *reinterpret_cast<const uint4 *>(x + row * K + k);
-        uint4 dst;
-        if (BITS == 4) {  // [x0 x4 | x1 x5 | x2 x6 | x3 x7]
-            dst.x = __byte_perm(src.x, src.z, 0x5410), dst.y = __byte_perm(src.x, src.z, 0x7632);
-            dst.z = __byte_perm(src.y, src.w, 0x5410), dst.w = __byte_perm(src.y, src.w, 0x7632);
-        } else {  // [x0 x2 | x1 x3 | x4 x6 | x5 x7]
-            dst.x = __byte_perm(src.x, src.y, 0x5410), dst.y = __byte_perm(src.x, src.y, 0x7632);
-            dst.z = __byte_perm(src.z, src.w, 0x5410), dst.w = __byte_perm(src.z, src.w, 0x7632);
+    // 8 consecutive k of token n (16 bytes) -> one unit, permuted to match the nibble pairs of the weights.  Four loads a
+    // thread are issued before the first is used (see the note on batches below).
+    const int n_units = kTileTokens * units_per_row, stride = (int)blockDim.x;
+    for (int base = threadIdx.x; base < n_units; base += 4 * stride) {
+        uint4 src[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int idx = base + j * stride;
+            src[j] = make_uint4(0u, 0u, 0u, 0u);
+            if (idx < n_units) {
+                const int64_t row = rows[idx / units_per_row];
+                if (row >= 0) src[j] = *reinterpret_cast<const uint4 *>(x + row * K + (idx % units_per_row) * 8);
+            }
         }
-        xs[(step * UNITS + v) * 32 + n * 4 + cc] = dst;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int idx = base + j * stride;
+            if (idx >= n_units) break;
+            const int n = idx / units_per_row, k = (idx % units_per_row) * 8;
+            const int step = k / KI, rem = k % KI, cc = rem / CPL, v = (rem % CPL) / 8;
+            uint4 dst;
+            if (BITS == 4) {  // [x0 x4 | x1 x5 | x2 x6 | x3 x7]
+                dst.x = __byte_perm(src[j].x, src[j].z, 0x5410), dst.y = __byte_perm(src[j].x, src[j].z, 0x7632);
+                dst.z = __byte_perm(src[j].y, src[j].w, 0x5410), dst.w = __byte_perm(src[j].y, src[j].w, 0x7632);
+            } else {  // [x0 x2 | x1 x3 | x4 x6 | x5 x7]
+                dst.x = __byte_perm(src[j].x, src[j].y, 0x5410), dst.y = __byte_perm(src[j].x, src[j].y, 0x7632);
+                dst.z = __byte_perm(src[j].z, src[j].w, 0x5410), dst.w = __byte_perm(src[j].z, src[j].w, 0x7632);
+            }
+            xs[(step * UNITS + v) * 32 + n * 4 + cc] = dst;
+        }
     }
     // sum(x) of every (step, token), in a fixed order.
     for (int idx = threadIdx.x; idx < steps * kTileTokens; idx += blockDim.x) {
@@ -394,7 +408,7 @@ __global__ void __launch_bounds__(kBigThreads, 1) stream_kernel(const StreamArgs
     const int64_t chunk = ((units_per_tile + cpt - 1) / cpt + kWarps - 1) / kWarps * kWarps;
     cpt = (units_per_tile + chunk - 1) / chunk;
     const int64_t n_chunks = n_tiles * cpt;
-    const bool aligned = ((n_chunks + nb - 1) / nb) * chunk * 100 <= ((total + nb - 1) / nb) * 103;
+    const bool aligned = ((n_chunks + nb - 1) / nb) * chunk * 100 <= ((total + nb - 1) / nb) * 115;
     for (int64_t ci = blockIdx.x; ci < (aligned ? n_chunks : nb); ci += nb) {
     int64_t u_begin, u_end;
     if (aligned) {
