@@ -9,9 +9,8 @@
 //
 // Both are small-matrix, many-launch kernels (a few MB of weights, ~97 mixes per decoded token upstream): what matters is
 // that the weight matrix is read once per group of tokens and that enough CTAs exist to cover the SMs at T = 1..64.
-//   down: a warp owns RW weight rows and TT tokens; its lanes take the 32-code chunks of the row in turn (a chunk lies in
-//         one stream since d % 32 == 0), keep per-stream partial dots in registers, and meet by shuffles.  Each chunk's
-//         sum(x) and sum(x^2) are the same for every row: computed once per CTA into shared memory.
+//   down: a CTA owns a group of weight rows and up to four tokens, whose streams it holds in shared memory; its sixteen warps
+//         take (row, eighth of the row) items, an eighth lying in one stream, and the parts meet in shared memory.
 //   up:   a thread owns one row s*d + j of W_up (consecutive threads' rows are adjacent in the chunk-major layout, so a
 //         warp's 16-byte loads are one contiguous run), dots it with the h of MT tokens held in shared memory, and the
 //         H streams of a column meet in shared memory.
@@ -29,141 +28,195 @@ constexpr int kStreams = 4;
 constexpr int kChunk = 32;  // codes per chunk: 16 bytes of Q4, 32 of Q8
 constexpr int64_t kMaxRank = 1024;
 
-// 32 activations of one chunk as FP32.
-__device__ inline void load_chunk_x(const float *x, float (&v)[kChunk]) {
-#pragma unroll
-    for (int i = 0; i < kChunk / 4; ++i) {
-        const float4 f = __ldg(reinterpret_cast<const float4 *>(x) + i);
-        v[4 * i] = f.x, v[4 * i + 1] = f.y, v[4 * i + 2] = f.z, v[4 * i + 3] = f.w;
-    }
+__device__ inline float sigmoid_f32(float z) { return 1.0f / (1.0f + expf(-z)); }
+// 16 bytes of activations as FP32: four (FP32) or eight (BF16) values.
+__device__ inline void unpack16(const uint4 &u, float (&f)[4], const float *) {
+    f[0] = __uint_as_float(u.x), f[1] = __uint_as_float(u.y), f[2] = __uint_as_float(u.z), f[3] = __uint_as_float(u.w);
 }
-__device__ inline void load_chunk_x(const uint16_t *x, float (&v)[kChunk]) {
+__device__ inline void unpack16(const uint4 &u, float (&f)[8], const uint16_t *) {
+    const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-    for (int i = 0; i < kChunk / 8; ++i) {
-        const uint4 u = __ldg(reinterpret_cast<const uint4 *>(x) + i);
-        const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) v[8 * i + 2 * j] = __uint_as_float(w4[j] << 16), v[8 * i + 2 * j + 1] = __uint_as_float(w4[j] & 0xffff0000u);
-    }
+    for (int j = 0; j < 4; ++j) f[2 * j] = __uint_as_float(w4[j] << 16), f[2 * j + 1] = __uint_as_float(w4[j] & 0xffff0000u);
 }
-// The 32 codes of a chunk as FP32 (Q4: low nibble = even code).
+
+// Eight consecutive codes of a chunk (k = 8 j .. 8 j + 7) as FP32, from the chunk's packed words.
 template <int BITS>
-__device__ inline void load_chunk_codes(const uint8_t *p, float (&c)[kChunk]) {
-    constexpr int WORDS = BITS;  // 4 words of Q4, 8 of Q8
-    uint32_t w[WORDS];
+__device__ inline void codes8(const uint32_t *w, int j, float (&c)[8]) {
+    if (BITS == 8) {
 #pragma unroll
-    for (int i = 0; i < WORDS / 4; ++i) {
+        for (int i = 0; i < 8; ++i) c[i] = (float)((w[2 * j + (i >> 2)] >> (8 * (i & 3))) & 0xFFu);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) c[i] = (float)((w[j] >> (4 * i)) & 0xFu);
+    }
+}
+template <int BITS>
+__device__ inline void load_chunk_words(const uint8_t *p, uint32_t (&w)[BITS]) {
+#pragma unroll
+    for (int i = 0; i < BITS / 4; ++i) {
         const uint4 u = __ldg(reinterpret_cast<const uint4 *>(p) + i);
         w[4 * i] = u.x, w[4 * i + 1] = u.y, w[4 * i + 2] = u.z, w[4 * i + 3] = u.w;
     }
-    constexpr int per = 32 / BITS;
-#pragma unroll
-    for (int i = 0; i < kChunk; ++i) c[i] = (float)((w[i / per] >> (BITS * (i % per))) & ((1u << BITS) - 1u));
 }
-__device__ inline float sigmoid_f32(float z) { return 1.0f / (1.0f + expf(-z)); }
 
-// hc_mix_down.  grid = (row groups, token groups); a warp: rows n0 .. n0 + RW - 1, tokens t0 .. t0 + TT - 1.
-template <typename T, int BITS, int RW, int TT>
-__global__ void __launch_bounds__(kHcThreads) hc_down_kernel(const T *__restrict__ x, const uint8_t *__restrict__ q,
-                                                             const uint16_t *__restrict__ scale, const uint16_t *__restrict__ minv, int64_t R,
-                                                             int64_t K, int64_t G, int64_t d, int r, float eps, int64_t Tn,
-                                                             float *__restrict__ h, float *__restrict__ w_in, float *__restrict__ inv) {
-    extern __shared__ float2 sums[];  // [TT][K / 32]: each chunk's sum(x) and sum(x^2)
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = kHcThreads / 32;
-    const int64_t nc = K / kChunk, t0 = (int64_t)blockIdx.y * TT;
-    const int nt = (int)min((int64_t)TT, Tn - t0);
-    for (int64_t i = threadIdx.x; i < nt * nc; i += kHcThreads) {
-        const int tt = (int)(i / nc);
-        const int64_t c = i % nc;
-        float xv[kChunk];
-        load_chunk_x(x + (t0 + tt) * K + c * kChunk, xv);
-        float s = 0.f, sq = 0.f;
+// hc_mix_down.  grid = (row groups of RG rows, token groups of TT); one CTA of sixteen warps an SM.
+//   1. The TT tokens' streams go to shared memory once (chunk-interleaved: 16-byte piece p of chunk c of token tt at
+//      ((tt * P + p) * nc + c) * 16, so that lanes with consecutive chunks read consecutive 16 bytes), and each chunk's
+//      sum(x) and sum(x^2) - the same for every weight row - are computed once.
+//   2. The work items are (row, eighth of the row's chunks): an eighth lies in one stream (H = 4).  The warps take items in
+//      turn; a lane has only a few chunks of an item and all their loads are in flight together - with a warp walking a whole
+//      row, sixteen dependent rounds of loads made this kernel 57 us at T = 16.  An item's partial dot per token goes to
+//      shared memory.
+//   3. One thread per (row, token) adds the parts in order, applies the per-stream inverse RMS and the activation.
+constexpr int kDownThreads = 512, kParts = 8;
+constexpr int kMaxRowGroup = 32;
+
+template <typename T, int BITS, int TT>
+__global__ void __launch_bounds__(kDownThreads, 1) hc_down_kernel(const T *__restrict__ x, const uint8_t *__restrict__ q,
+                                                                  const uint16_t *__restrict__ scale, const uint16_t *__restrict__ minv,
+                                                                  int64_t R, int64_t K, int64_t G, int64_t d, int r, float eps, int64_t Tn,
+                                                                  int RG, float *__restrict__ h, float *__restrict__ w_in,
+                                                                  float *__restrict__ inv) {
+    constexpr int P = kChunk * (int)sizeof(T) / 16;  // 16-byte pieces of a chunk of activations: 4 (BF16) or 8 (FP32)
+    constexpr int kWarps = kDownThreads / 32;
+    extern __shared__ __align__(16) unsigned char down_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nc = (int)(K / kChunk);
+    uint4 *xs = reinterpret_cast<uint4 *>(down_smem);                                 // [TT][P][nc]
+    float2 *sums = reinterpret_cast<float2 *>(down_smem + (size_t)TT * P * nc * 16);  // [TT][nc]
+    float *part = reinterpret_cast<float *>(sums + (size_t)TT * nc);                  // [RG][kParts][TT]
+    float *ssq = part + (size_t)kMaxRowGroup * kParts * TT;                            // [TT][H]
+    const int64_t t0 = (int64_t)blockIdx.y * TT, n0 = (int64_t)blockIdx.x * RG;
+    const int nt = (int)min((int64_t)TT, Tn - t0), rows = (int)min((int64_t)RG, R - n0);
+    // 1. the activations, all loads of a thread in flight at once (batches of eight)
+    const int pieces_per_token = nc * P;
+    for (int base = threadIdx.x; base < nt * pieces_per_token; base += 8 * kDownThreads) {
+        uint4 v[8];
 #pragma unroll
-        for (int k = 0; k < kChunk; ++k) s += xv[k], sq = fmaf(xv[k], xv[k], sq);
-        sums[tt * nc + c] = make_float2(s, sq);
+        for (int j = 0; j < 8; ++j) {
+            const int i = base + j * kDownThreads;
+            if (i < nt * pieces_per_token) {
+                const int tt = i / pieces_per_token, jj = i % pieces_per_token;
+                v[j] = __ldg(reinterpret_cast<const uint4 *>(x + (t0 + tt) * K) + jj);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = base + j * kDownThreads;
+            if (i < nt * pieces_per_token) {
+                const int tt = i / pieces_per_token, jj = i % pieces_per_token;
+                xs[(tt * P + jj % P) * nc + jj / P] = v[j];
+            }
+        }
     }
     __syncthreads();
-    const int64_t n0 = ((int64_t)blockIdx.x * warps + warp) * RW;
-    if (n0 >= R) return;
-    float dot[RW][TT][kStreams], sq[TT][kStreams];
+    for (int i = threadIdx.x; i < nt * nc; i += kDownThreads) {
+        const int tt = i / nc, c = i % nc;
+        float sx = 0.f, sq = 0.f;
 #pragma unroll
-    for (int tt = 0; tt < TT; ++tt)
+        for (int p = 0; p < P; ++p) {
+            const uint4 u = xs[(tt * P + p) * nc + c];
+            float f[16 / sizeof(T)];
+            unpack16(u, f, static_cast<const T *>(nullptr));
 #pragma unroll
-        for (int s = 0; s < kStreams; ++s) {
-            sq[tt][s] = 0.f;
-#pragma unroll
-            for (int rw = 0; rw < RW; ++rw) dot[rw][tt][s] = 0.f;
+            for (int k = 0; k < (int)(16 / sizeof(T)); ++k) sx += f[k], sq = fmaf(f[k], f[k], sq);
         }
+        sums[i] = make_float2(sx, sq);
+    }
+    __syncthreads();
+    // the sum of squares of every (token, stream): one thread each, chunks in order
+    if (threadIdx.x < nt * kStreams) {
+        const int tt = threadIdx.x / kStreams, st = threadIdx.x % kStreams, per = nc / kStreams;
+        float sq = 0.f;
+        for (int c = st * per; c < (st + 1) * per; ++c) sq += sums[tt * nc + c].y;
+        ssq[threadIdx.x] = sq;
+    }
+    // 2. items (row, part): chunks [part * nc / 8, (part + 1) * nc / 8) of row n0 + row
     const int64_t row_bytes = K * BITS / 8, groups = K / G;
-    for (int64_t c = lane; c < nc; c += 32) {
-        const int g = (int)(c * kChunk / d);  // the chunk's stream
-        float code[RW][kChunk], sc[RW], mn[RW];
+    const int per_part = nc / kParts;
+    for (int item = warp; item < rows * kParts; item += kWarps) {
+        const int row = item / kParts, pt = item % kParts;
+        const int64_t n = n0 + row;
+        float acc[TT];
 #pragma unroll
-        for (int rw = 0; rw < RW; ++rw) {
-            const int64_t n = min(n0 + rw, R - 1);  // a row past the end repeats the last one; its sums are dropped
-            load_chunk_codes<BITS>(q + n * row_bytes + c * (kChunk * BITS / 8), code[rw]);
-            sc[rw] = bf16_bits_to_f32(__ldg(scale + n * groups + c * kChunk / G));
-            mn[rw] = bf16_bits_to_f32(__ldg(minv + n * groups + c * kChunk / G));
+        for (int tt = 0; tt < TT; ++tt) acc[tt] = 0.f;
+        // a lane's chunks of the item two at a time, both chunks' loads issued before either is used
+        for (int c0 = pt * per_part + lane; c0 < (pt + 1) * per_part; c0 += 64) {
+            uint32_t w[2][BITS];
+            float sc[2], mn[2];
+            const bool two = c0 + 32 < (pt + 1) * per_part;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int c = e == 0 || two ? c0 + 32 * e : c0;
+                load_chunk_words<BITS>(q + n * row_bytes + (int64_t)c * (kChunk * BITS / 8), w[e]);
+                sc[e] = bf16_bits_to_f32(__ldg(scale + n * groups + c * kChunk / G));
+                mn[e] = bf16_bits_to_f32(__ldg(minv + n * groups + c * kChunk / G));
+            }
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                if (e == 1 && !two) break;
+                const int c = c0 + 32 * e;
+                float dsum[TT];
+#pragma unroll
+                for (int tt = 0; tt < TT; ++tt) dsum[tt] = 0.f;
+#pragma unroll
+                for (int j = 0; j < kChunk / 8; ++j) {  // eight codes at a time: converted once, met by every token
+                    float cf[8];
+                    codes8<BITS>(w[e], j, cf);
+#pragma unroll
+                    for (int tt = 0; tt < TT; ++tt) {
+                        if (tt >= nt) break;
+                        float f[8];
+                        if constexpr (sizeof(T) == 2) {
+                            unpack16(xs[(tt * P + j) * nc + c], f, static_cast<const T *>(nullptr));
+                        } else {
+                            float g4[4];
+                            unpack16(xs[(tt * P + 2 * j) * nc + c], g4, static_cast<const T *>(nullptr));
+                            f[0] = g4[0], f[1] = g4[1], f[2] = g4[2], f[3] = g4[3];
+                            unpack16(xs[(tt * P + 2 * j + 1) * nc + c], g4, static_cast<const T *>(nullptr));
+                            f[4] = g4[0], f[5] = g4[1], f[6] = g4[2], f[7] = g4[3];
+                        }
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) dsum[tt] = fmaf(f[k], cf[k], dsum[tt]);
+                    }
+                }
+#pragma unroll
+                for (int tt = 0; tt < TT; ++tt)
+                    if (tt < nt) acc[tt] += fmaf(sc[e], dsum[tt], mn[e] * sums[tt * nc + c].x);
+            }
         }
 #pragma unroll
         for (int tt = 0; tt < TT; ++tt) {
-            if (tt >= nt) break;
-            float xv[kChunk];
-            load_chunk_x(x + (t0 + tt) * K + c * kChunk, xv);
-            const float2 ss = sums[tt * nc + c];
 #pragma unroll
-            for (int rw = 0; rw < RW; ++rw) {
-                float dsum = 0.f;
-#pragma unroll
-                for (int k = 0; k < kChunk; ++k) dsum = fmaf(xv[k], code[rw][k], dsum);
-                const float pv = fmaf(sc[rw], dsum, mn[rw] * ss.x);
-#pragma unroll
-                for (int s = 0; s < kStreams; ++s)  // static indices keep the sums in registers
-                    if (s == g) dot[rw][tt][s] += pv;
-            }
-#pragma unroll
-            for (int s = 0; s < kStreams; ++s)
-                if (s == g) sq[tt][s] += ss.y;
+            for (int off = 16; off > 0; off >>= 1) acc[tt] += __shfl_xor_sync(0xffffffffu, acc[tt], off);
+            if (lane == 0) part[(row * kParts + pt) * TT + tt] = acc[tt];
         }
     }
+    __syncthreads();
+    // 3. one thread per (row, token)
+    for (int i = threadIdx.x; i < rows * nt; i += kDownThreads) {
+        const int row = i / nt, tt = i % nt;
+        const int64_t n = n0 + row, t = t0 + tt;
+        float a = 0.f;
 #pragma unroll
-    for (int tt = 0; tt < TT; ++tt)
+        for (int st = 0; st < kStreams; ++st) {
+            float dot = 0.f;
 #pragma unroll
-        for (int s = 0; s < kStreams; ++s) {
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) sq[tt][s] += __shfl_xor_sync(0xffffffffu, sq[tt][s], off);
-#pragma unroll
-            for (int rw = 0; rw < RW; ++rw)
-#pragma unroll
-                for (int off = 16; off > 0; off >>= 1) dot[rw][tt][s] += __shfl_xor_sync(0xffffffffu, dot[rw][tt][s], off);
+            for (int k = 0; k < kParts / kStreams; ++k) dot += part[(row * kParts + st * (kParts / kStreams) + k) * TT + tt];
+            a = fmaf(1.0f / sqrtf(ssq[tt * kStreams + st] / (float)d + eps), dot, a);
         }
-    if (lane != 0) return;
-#pragma unroll
-    for (int tt = 0; tt < TT; ++tt) {
-        if (tt >= nt) break;
-        const int64_t t = t0 + tt;
-        float iv[kStreams];
-#pragma unroll
-        for (int s = 0; s < kStreams; ++s) iv[s] = 1.0f / sqrtf(sq[tt][s] / (float)d + eps);
-#pragma unroll
-        for (int rw = 0; rw < RW; ++rw) {
-            const int64_t n = n0 + rw;
-            if (n >= R) break;
-            float a = 0.f;
-#pragma unroll
-            for (int s = 0; s < kStreams; ++s) a = fmaf(iv[s], dot[rw][tt][s], a);
-            const float z = a / (float)kStreams;
-            if (n < r) h[t * r + n] = z * sigmoid_f32(z);
-            else w_in[t * kStreams + (n - r)] = 2.0f * sigmoid_f32(z);
-        }
-        if (n0 == 0)
-#pragma unroll
-            for (int s = 0; s < kStreams; ++s) inv[t * kStreams + s] = iv[s];
+        const float z = a / (float)kStreams;
+        if (n < r) h[t * r + n] = z * sigmoid_f32(z);
+        else w_in[t * kStreams + (n - r)] = 2.0f * sigmoid_f32(z);
     }
+    if (n0 == 0 && threadIdx.x < nt * kStreams)
+        inv[(t0 + threadIdx.x / kStreams) * kStreams + threadIdx.x % kStreams] = 1.0f / sqrtf(ssq[threadIdx.x] / (float)d + eps);
 }
 
-// hc_mix_up.  grid = (d / 64, token groups of MT); thread (s, jl) owns row s*d + j of W_up.
+// hc_mix_up.  grid = (d / 64, token groups of MT); thread (s, jl) owns row s*d + j of W_up.  Four chunks of packed codes are
+// in flight per thread (a thread has only r / 32 chunks, and one at a time made this kernel ten rounds of load latency).
 constexpr int kUpCols = kHcThreads / kStreams;  // 64 output columns per CTA
+constexpr int kUpAhead = 4;
 
 template <typename T, int BITS, int MT>
 __global__ void __launch_bounds__(kHcThreads) hc_up_kernel(const float *__restrict__ h, const uint8_t *__restrict__ q,
@@ -174,36 +227,60 @@ __global__ void __launch_bounds__(kHcThreads) hc_up_kernel(const float *__restri
     float *hs = up_smem, *hsum = hs + (size_t)MT * r, *part = hsum + (size_t)MT * (r / kChunk);
     const int64_t t0 = (int64_t)blockIdx.y * MT, N = kStreams * d;
     const int nt = (int)min((int64_t)MT, Tn - t0), chunks = r / kChunk;
+    const int s = threadIdx.x / kUpCols, jl = threadIdx.x % kUpCols;
+    const int64_t j = (int64_t)blockIdx.x * kUpCols + jl, row = s * d + min(j, d - 1);
+    // the first chunks' codes are asked for before anything else
+    uint32_t wq[kUpAhead][BITS];
+    float sc[kUpAhead], mn[kUpAhead];
+    auto fetch = [&](int slot, int c) {
+        load_chunk_words<BITS>(q + ((int64_t)c * N + row) * (kChunk * BITS / 8), wq[slot]);
+        const int64_t gi = (int64_t)(c * kChunk / G) * N + row;
+        sc[slot] = bf16_bits_to_f32(__ldg(scale + gi)), mn[slot] = bf16_bits_to_f32(__ldg(minv + gi));
+    };
+#pragma unroll
+    for (int a = 0; a < kUpAhead; ++a)
+        if (a < chunks) fetch(a, a);
     for (int i = threadIdx.x; i < nt * r; i += kHcThreads) hs[i] = h[t0 * r + i];
     __syncthreads();
     for (int i = threadIdx.x; i < nt * chunks; i += kHcThreads) {
-        float s = 0.f;
-        for (int k = 0; k < kChunk; ++k) s += hs[(i / chunks) * r + (i % chunks) * kChunk + k];
-        hsum[i] = s;
+        float sum = 0.f;
+        for (int k = 0; k < kChunk; ++k) sum += hs[(i / chunks) * r + (i % chunks) * kChunk + k];
+        hsum[i] = sum;
     }
     __syncthreads();
-    const int s = threadIdx.x / kUpCols, jl = threadIdx.x % kUpCols;
-    const int64_t j = (int64_t)blockIdx.x * kUpCols + jl;
-    if (j < d) {
-        const int64_t row = s * d + j;
-        float acc[MT];
+    float acc[MT];
 #pragma unroll
-        for (int tt = 0; tt < MT; ++tt) acc[tt] = 0.f;
-        for (int c = 0; c < chunks; ++c) {
-            float code[kChunk];
-            load_chunk_codes<BITS>(q + ((int64_t)c * N + row) * (kChunk * BITS / 8), code);
-            const int64_t gi = (int64_t)(c * kChunk / G) * N + row;
-            const float sc = bf16_bits_to_f32(__ldg(scale + gi)), mn = bf16_bits_to_f32(__ldg(minv + gi));
+    for (int tt = 0; tt < MT; ++tt) acc[tt] = 0.f;
+    for (int c0 = 0; c0 < chunks; c0 += kUpAhead) {
 #pragma unroll
-            for (int tt = 0; tt < MT; ++tt) {
-                if (tt >= nt) break;
-                const float *hv = hs + tt * r + c * kChunk;
-                float dsum = 0.f;
+        for (int a = 0; a < kUpAhead; ++a) {
+            const int c = c0 + a;
+            if (c >= chunks) break;
+            float dsum[MT];
 #pragma unroll
-                for (int k = 0; k < kChunk; ++k) dsum = fmaf(hv[k], code[k], dsum);
-                acc[tt] = fmaf(sc, dsum, fmaf(mn, hsum[tt * chunks + c], acc[tt]));
+            for (int tt = 0; tt < MT; ++tt) dsum[tt] = 0.f;
+#pragma unroll
+            for (int jj = 0; jj < kChunk / 8; ++jj) {
+                float cf[8];
+                codes8<BITS>(wq[a], jj, cf);
+#pragma unroll
+                for (int tt = 0; tt < MT; ++tt) {
+                    if (tt >= nt) break;
+                    // two 16-byte broadcasts instead of eight scalar ones: the shared-memory pipe was this kernel's limit
+                    const float4 *hv = reinterpret_cast<const float4 *>(hs + tt * r + c * kChunk + jj * 8);
+                    const float4 h0 = hv[0], h1 = hv[1];
+                    const float hf[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) dsum[tt] = fmaf(hf[k], cf[k], dsum[tt]);
+                }
             }
+#pragma unroll
+            for (int tt = 0; tt < MT; ++tt)
+                if (tt < nt) acc[tt] = fmaf(sc[a], dsum[tt], fmaf(mn[a], hsum[tt * chunks + c], acc[tt]));
+            if (c + kUpAhead < chunks) fetch(a, c + kUpAhead);  // the slot's codes are spent: the chunk four ahead
         }
+    }
+    if (j < d) {
         const float nw = 1.0f + norm_w[row];
 #pragma unroll
         for (int tt = 0; tt < MT; ++tt) {
@@ -267,29 +344,32 @@ int mix_down(const void *x, const SxbQView *w, int64_t T, int64_t H, int64_t d, 
     SXB_CHECK(w->N == R, fn, ": weight has ", w->N, " rows, expected r", inject ? " + H" : "", " = ", R);
     SXB_CHECK(aligned16(x), fn, ": x ", x, " must be 16-byte aligned");
     SXB_CHECK(std::isfinite(eps) && eps > 0.f, fn, ": eps must be finite and > 0, got ", eps);
-    // Tokens per warp: as many as keeps at least one CTA per SM in the grid (every token group re-reads the weight from L2).
-    const int64_t row_groups1 = (R + 7) / 8;
+    SXB_CHECK((w->K / kChunk) % kParts == 0, fn, ": H*d = ", w->K, " must be a multiple of ", kChunk * kParts, " (eight parts of whole chunks a row)");
+    // Tokens per CTA: as many as shared memory holds (up to four); rows per CTA: so that the grid is one wave of CTAs.
+    const size_t es = act == SXB_ACT_F32 ? 4 : 2, per_token = (size_t)w->K * es + (size_t)(w->K / kChunk) * sizeof(float2);
+    const size_t fixed = (size_t)kMaxRowGroup * kParts * 4 * sizeof(float) + 64 * sizeof(float);
     int TT = 4;
-    while (TT > 1 && row_groups1 * ((T + TT - 1) / TT) < sm_count()) TT >>= 1;
-    const size_t smem = (size_t)TT * (size_t)(w->K / kChunk) * sizeof(float2);
-    SXB_CHECK(smem <= 160 * 1024, fn, ": H*d = ", w->K, " needs ", smem, " bytes of shared memory for its chunk sums");
+    while (TT > 1 && (TT * per_token + fixed > 200 * 1024 || TT > T)) TT >>= 1;
+    SXB_CHECK(TT * per_token + fixed <= 200 * 1024, fn, ": H*d = ", w->K, " needs ", per_token, " bytes of shared memory a token");
+    const int64_t token_groups = (T + TT - 1) / TT;
+    int64_t row_groups = std::max<int64_t>(1, std::min<int64_t>(R, sm_count() / token_groups));
+    int RG = (int)std::min<int64_t>(kMaxRowGroup, (R + row_groups - 1) / row_groups);
+    row_groups = (R + RG - 1) / RG;
+    const size_t smem = TT * per_token + fixed;
     auto st = static_cast<cudaStream_t>(stream);
-    // two rows a warp once the grid is large anyway (each activation load then meets two rows)
-    const bool two = (R + 15) / 16 * ((T + TT - 1) / TT) >= 2 * sm_count();
-#define SXB_HC_DOWN(TYPE, RW, TTV)                                                                                                     \
+#define SXB_HC_DOWN(TYPE, TTV)                                                                                                         \
     do {                                                                                                                               \
-        auto kern = hc_down_kernel<TYPE, BITS, RW, TTV>;                                                                               \
+        auto kern = hc_down_kernel<TYPE, BITS, TTV>;                                                                                   \
         SXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn, ": reserving shared memory"); \
-        const dim3 grid((unsigned)((R + 8 * RW - 1) / (8 * RW)), (unsigned)((T + TTV - 1) / TTV));                                     \
-        kern<<<grid, kHcThreads, smem, st>>>(static_cast<const TYPE *>(x), w->q, w->scale, w->minv, R, w->K, w->G, d, (int)r, eps, T, h, \
-                                             w_in, inv);                                                                               \
+        const dim3 grid((unsigned)row_groups, (unsigned)token_groups);                                                                 \
+        kern<<<grid, kDownThreads, smem, st>>>(static_cast<const TYPE *>(x), w->q, w->scale, w->minv, R, w->K, w->G, d, (int)r, eps, T, RG, h, \
+                                               w_in, inv);                                                                             \
     } while (0)
-#define SXB_HC_DOWN_T(TYPE)                             \
-    do {                                                \
-        if (TT == 4 && two) SXB_HC_DOWN(TYPE, 2, 4);    \
-        else if (TT == 4) SXB_HC_DOWN(TYPE, 1, 4);      \
-        else if (TT == 2) SXB_HC_DOWN(TYPE, 1, 2);      \
-        else SXB_HC_DOWN(TYPE, 1, 1);                   \
+#define SXB_HC_DOWN_T(TYPE)                     \
+    do {                                        \
+        if (TT == 4) SXB_HC_DOWN(TYPE, 4);      \
+        else if (TT == 2) SXB_HC_DOWN(TYPE, 2); \
+        else SXB_HC_DOWN(TYPE, 1);              \
     } while (0)
     if (act == SXB_ACT_F32) SXB_HC_DOWN_T(float);
     else SXB_HC_DOWN_T(uint16_t);
