@@ -728,6 +728,54 @@ def hc_mix_measure(dev, peaks, seed, T=16, d=4096, r=320, H=4, iters=50):
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"]}}
 
 
+def hc_mix_prefill_measure(dev, peaks, seed, T=4096, d=4096, r=320, H=4, iters=10):
+    """The same mix for a multi-token forward on the tensor cores (hc_mix_down_wmma + hc_mix_up_wmma, Q8 g64 weights):
+    milliseconds a mix by CUDA events, each half on its own as well, and the products' 2 T H d (R + r) flops against the
+    measured bf16 peak.  The streams X (T H d BF16, 134 MB at the default) are larger than L2."""
+    import torch
+    from strixite_b200 import kernels as K
+    g = torch.Generator(device=dev).manual_seed(seed + 78)
+    R = r + H
+    wd = K.quantize(torch.randn((R, H * d), device=dev, generator=g) * 0.05, 64, 8)
+    wu = K.to_chunk_major(K.quantize(torch.randn((H * d, r), device=dev, generator=g) * 0.2, 64, 8))
+    x = torch.randn((T, H * d), device=dev, generator=g).to(torch.bfloat16)
+    norm_w = torch.randn(H * d, device=dev, generator=g) * 0.1
+    h = torch.empty((T, r), dtype=torch.float32, device=dev)
+    w_in, inv = torch.empty((T, H), dtype=torch.float32, device=dev), torch.empty((T, H), dtype=torch.float32, device=dev)
+    u = torch.empty((T, d), dtype=torch.bfloat16, device=dev)
+    ws_d = torch.empty(K.hc_wmma_workspace_bytes(T, H, d, R, 8, 64), dtype=torch.uint8, device=dev)
+    ws_u = torch.empty(K.hc_mix_up_wmma_workspace_bytes(T, H, d, r, 8, 64), dtype=torch.uint8, device=dev)
+
+    def down():
+        K.hc_mix_down_wmma(x, wd, T, H, d, r, True, 1e-6, h, w_in, inv, ws_d, K.Act.BF16)
+
+    def up():
+        K.hc_mix_up_wmma(h, wu, x, norm_w, inv, T, H, d, u, ws_u, K.Act.BF16)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    ms_down, ms_up = timed(down), timed(up)
+    ms = timed(lambda: (down(), up()))
+    K.check_grouped_status(ws_d, "hc_mix_down_wmma")
+    K.check_dense_status("hc_mix_up_wmma")
+    flops = 2.0 * T * H * d * (R + r)
+    tf = flops / (ms * 1e-3) / 1e12
+    return {"T": T, "d": d, "r": r, "weights": "q8g64", "ms_per_mix": ms, "ms_down": ms_down, "ms_up": ms_up,
+            "launches_per_mix": 5 + 1 + 3 * ((T + 1023) // 1024),
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["tflops_burst"], "unit": "TFLOP/s", "frac": tf / peaks["tflops_burst"]},
+            "hbm_bytes_floor": 2 * x.numel() * 2 + u.numel() * 2}
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -841,6 +889,10 @@ def main():
             extra["hc_mix_decode"] = hc_mix_measure(dev, peaks, args.seed)
         except Exception as ex:
             extra["hc_mix_decode"] = {"error": f"{type(ex).__name__}: {ex}"}
+        try:
+            extra["hc_mix_prefill"] = hc_mix_prefill_measure(dev, peaks, args.seed)
+        except Exception as ex:
+            extra["hc_mix_prefill"] = {"error": f"{type(ex).__name__}: {ex}"}
         line["other_workloads"] = extra
 
     if rank == 0:

@@ -177,6 +177,34 @@ int sxb_hc_mix_up_q4(const float *h, const SxbQView *w_up, const void *x, const 
                      int64_t d, void *u, int act, sxb_stream_t stream);
 int sxb_hc_mix_up_q8(const float *h, const SxbQView *w_up, const void *x, const float *norm_w, const float *inv, int64_t T, int64_t H,
                      int64_t d, void *u, int act, sxb_stream_t stream);
+/* kernels/hc_wmma.hpp:29-38  hc_wmma_workspace_bytes + hc_mix_down_wmma (Q4DeviceView / Q8DeviceView overloads): hc_mix_down for
+ * multi-token forwards on the tensor cores - x rounded once to F16, weights f16(code * scale + min), FP32 accumulation over
+ * each stream's d inputs; inv, the stream sum, silu and sigmoid in FP32.  Same arguments as sxb_hc_mix_down_q*, plus the
+ * workspace (device, 256-byte aligned) and inv_ready (inv already holds X's inverse RMS, as sxb_hc_inject_inv leaves it).
+ * Here the H streams run as H experts of the tcgen05 grouped kernel, so the workspace holds more than the reference's FP32
+ * partials (kernels/hc_wmma.hip:296-331): the grouping workspace (first, so sxb_check_grouped_status(ws, ..) reports a
+ * device-side wait that ran out), the restacked weight, X as tile-blocked F16 and the per-slot dots.  R = r (+ H).
+ * d % 128 == 0, d % G == 0, T <= 65535.  Returns 0 and sets the error message on bad arguments. */
+size_t sxb_hc_mix_down_wmma_workspace_bytes(int64_t T, int64_t H, int64_t d, int64_t R, int bits, int64_t G);
+int sxb_hc_mix_down_wmma_q4(const void *x, const SxbQView *w, int64_t T, int64_t H, int64_t d, int64_t r, int inject, float eps, float *h,
+                            float *w_in, float *inv, void *ws, size_t ws_bytes, int act, int inv_ready, sxb_stream_t stream);
+int sxb_hc_mix_down_wmma_q8(const void *x, const SxbQView *w, int64_t T, int64_t H, int64_t d, int64_t r, int inject, float eps, float *h,
+                            float *w_in, float *inv, void *ws, size_t ws_bytes, int act, int inv_ready, sxb_stream_t stream);
+/* kernels/hc_wmma.hpp:40-43  hc_inject_inv: sxb_hc_inject fused with the next mix's inverse RMS of the updated X into
+ * inv [T, H] - the stored (rounded) values are the ones squared - in one pass over X.  H == 4. */
+int sxb_hc_inject_inv(void *x, const float *w_in, const void *y, int64_t T, int64_t H, int64_t d, float eps, float *inv, int act,
+                      sxb_stream_t stream);
+/* kernels/hc_wmma.hpp:45-49  hc_mix_up_wmma (Q4ChunkMajorView / Q8ChunkMajorView overloads): hc_mix_up on the tensor cores -
+ * h rounded once to F16, weights f16(code * scale + min), FP32 accumulation; sigmoid and the stream combine in FP32.
+ * Same arguments as sxb_hc_mix_up_q*, plus a workspace (the reference's launcher needs none; this one un-chunks W_up to
+ * row-major and keeps the FP32 logits z of one block of 1024 tokens there): sxb_hc_mix_up_wmma_workspace_bytes, device,
+ * 256-byte aligned.  h, x, norm_w, u 16-byte aligned; d % 128 == 0.  A device-side wait that ran out is reported by
+ * sxb_check_dense_status. */
+size_t sxb_hc_mix_up_wmma_workspace_bytes(int64_t T, int64_t H, int64_t d, int64_t r, int bits, int64_t G);
+int sxb_hc_mix_up_wmma_q4(const float *h, const SxbQView *w_up, const void *x, const float *norm_w, const float *inv, int64_t T, int64_t H,
+                          int64_t d, void *u, void *ws, size_t ws_bytes, int act, sxb_stream_t stream);
+int sxb_hc_mix_up_wmma_q8(const float *h, const SxbQView *w_up, const void *x, const float *norm_w, const float *inv, int64_t T, int64_t H,
+                          int64_t d, void *u, void *ws, size_t ws_bytes, int act, sxb_stream_t stream);
 /* formats/q4.hpp:55 / formats/q8.hpp:46  to_chunk_major, for a weight already on the device: the codes, scales and mins of the
  * row-major view w re-laid out chunk-major into q / scale / minv (same sizes as the source arrays; K % 32 == 0). */
 int sxb_to_chunk_major(const SxbQView *w, int bits, uint8_t *q, uint16_t *scale, uint16_t *minv, sxb_stream_t stream);

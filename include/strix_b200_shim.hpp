@@ -142,6 +142,47 @@ inline void hc_mix_up(const float *h, const Q8ChunkMajorView &w_up, const void *
     b200_detail::check(sxb_hc_mix_up_q8(h, reinterpret_cast<const SxbQView *>(&w_up), x, norm_w, inv, T, H, d, u, b200_detail::act(act), stream));
 }
 
+// kernels/hc_wmma.hpp:29-49, the mixes for multi-token forwards.  Two differences from the reference's declarations, both
+// about scratch memory: hc_wmma_workspace_bytes also needs d, the code width and the group size (the workspace holds the
+// restacked weight and the F16 operand besides the FP32 partials), and hc_mix_up_wmma takes a workspace of its own
+// (hc_up_wmma_workspace_bytes) where the reference's launcher needs none.  `ws` is a void pointer, 256-byte aligned.
+inline size_t hc_wmma_workspace_bytes(int64_t T, int64_t H, int64_t R, int64_t d, int bits, int64_t G) {
+    const size_t n = sxb_hc_mix_down_wmma_workspace_bytes(T, H, d, R, bits, G);
+    if (n == 0) throw Error(sxb_last_error());
+    return n;
+}
+inline size_t hc_up_wmma_workspace_bytes(int64_t T, int64_t H, int64_t d, int64_t r, int bits, int64_t G) {
+    const size_t n = sxb_hc_mix_up_wmma_workspace_bytes(T, H, d, r, bits, G);
+    if (n == 0) throw Error(sxb_last_error());
+    return n;
+}
+inline void hc_mix_down_wmma(const void *x, const Q4DeviceView &w, int64_t T, int64_t H, int64_t d, int64_t r, bool inject, float eps,
+                             float *h, float *w_in, float *inv, void *ws, size_t ws_bytes, Act act, hipStream_t stream,
+                             bool inv_ready = false) {
+    b200_detail::check(sxb_hc_mix_down_wmma_q4(x, reinterpret_cast<const SxbQView *>(&w), T, H, d, r, inject ? 1 : 0, eps, h, w_in, inv, ws,
+                                               ws_bytes, b200_detail::act(act), inv_ready ? 1 : 0, stream));
+}
+inline void hc_mix_down_wmma(const void *x, const Q8DeviceView &w, int64_t T, int64_t H, int64_t d, int64_t r, bool inject, float eps,
+                             float *h, float *w_in, float *inv, void *ws, size_t ws_bytes, Act act, hipStream_t stream,
+                             bool inv_ready = false) {
+    b200_detail::check(sxb_hc_mix_down_wmma_q8(x, reinterpret_cast<const SxbQView *>(&w), T, H, d, r, inject ? 1 : 0, eps, h, w_in, inv, ws,
+                                               ws_bytes, b200_detail::act(act), inv_ready ? 1 : 0, stream));
+}
+inline void hc_inject_inv(void *x, const float *w_in, const void *y, int64_t T, int64_t H, int64_t d, float eps, float *inv, Act act,
+                          hipStream_t stream) {
+    b200_detail::check(sxb_hc_inject_inv(x, w_in, y, T, H, d, eps, inv, b200_detail::act(act), stream));
+}
+inline void hc_mix_up_wmma(const float *h, const Q4ChunkMajorView &w_up, const void *x, const float *norm_w, const float *inv, int64_t T,
+                           int64_t H, int64_t d, void *u, void *ws, size_t ws_bytes, Act act, hipStream_t stream) {
+    b200_detail::check(sxb_hc_mix_up_wmma_q4(h, reinterpret_cast<const SxbQView *>(&w_up), x, norm_w, inv, T, H, d, u, ws, ws_bytes,
+                                             b200_detail::act(act), stream));
+}
+inline void hc_mix_up_wmma(const float *h, const Q8ChunkMajorView &w_up, const void *x, const float *norm_w, const float *inv, int64_t T,
+                           int64_t H, int64_t d, void *u, void *ws, size_t ws_bytes, Act act, hipStream_t stream) {
+    b200_detail::check(sxb_hc_mix_up_wmma_q8(h, reinterpret_cast<const SxbQView *>(&w_up), x, norm_w, inv, T, H, d, u, ws, ws_bytes,
+                                             b200_detail::act(act), stream));
+}
+
 // kernels/moe_grouped.hpp
 inline size_t moe_route_workspace_bytes(int64_t M, int64_t A, int64_t E) {
     const size_t n = sxb_moe_route_workspace_bytes(M, A, E);

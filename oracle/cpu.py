@@ -289,23 +289,38 @@ def ref_to_chunk_major(w: QWeight) -> QWeight:
     return QWeight(q, scale, minv, w.N, w.K, w.G, w.bits)
 
 
-def hc_mix_down(x: np.ndarray, w: QWeight, H: int, d: int, r: int, inject: bool, eps: float):
+def _as_f16(v: np.ndarray) -> np.ndarray:
+    """float64 values rounded once to IEEE half precision (to nearest even), back as float64."""
+    with np.errstate(over="ignore"):
+        return np.asarray(v, dtype=np.float64).astype(np.float16).astype(np.float64)
+
+
+def hc_mix_down(x: np.ndarray, w: QWeight, H: int, d: int, r: int, inject: bool, eps: float, f16_operands: bool = False):
     """kernels/hc.hip:82-165 hc_mix_down in float64: X [T, H*d] (float32 values) -> h [T, r], w_in [T, H] or None, inv [T, H].
     a = sum_s inv_s * (W'_s . X_s) over the folded weight's rows, z = a / H, h = silu(z), w_in = 2 sigmoid(z),
-    inv_s = 1 / sqrt(mean(X_s^2) + eps)."""
+    inv_s = 1 / sqrt(mean(X_s^2) + eps).
+    f16_operands: the matrix-unit form's numerics (kernels/hc_wmma.hpp:3-8, kernels/hc_wmma.hip:75-134) - the products take
+    x rounded once to F16 and the weights as f16(code * scale + min); inv still comes from the unrounded x."""
     X = np.asarray(x, dtype=np.float64).reshape(x.shape[0], H, d)
     W = affine_weights(w).reshape(w.N, H, d)
     inv = 1.0 / np.sqrt((X * X).mean(axis=2) + eps)            # [T, H]
+    if f16_operands:
+        X, W = _as_f16(X), _as_f16(W)
     per_stream = np.einsum("tsk,nsk->tns", X, W)                  # [T, R, H]
     z = (per_stream * inv[:, None, :]).sum(axis=2) / H
     sig = 1.0 / (1.0 + np.exp(-z))
     return z[:, :r] * sig[:, :r], (2.0 * sig[:, r:r + H] if inject else None), inv
 
 
-def hc_mix_up(h: np.ndarray, w_up: QWeight, x: np.ndarray, norm_w: np.ndarray, inv: np.ndarray, H: int, d: int) -> np.ndarray:
-    """kernels/hc.hip:176-243 hc_mix_up in float64 (w_up ROW-major [H*d, r]): u [T, d], not yet rounded to the activation dtype."""
+def hc_mix_up(h: np.ndarray, w_up: QWeight, x: np.ndarray, norm_w: np.ndarray, inv: np.ndarray, H: int, d: int,
+              f16_operands: bool = False) -> np.ndarray:
+    """kernels/hc.hip:176-243 hc_mix_up in float64 (w_up ROW-major [H*d, r]): u [T, d], not yet rounded to the activation dtype.
+    f16_operands: the matrix-unit form (kernels/hc_wmma.hip:203-272) - h rounded once to F16, weights f16(code * scale + min)."""
     T = h.shape[0]
-    logits = np.asarray(h, dtype=np.float64) @ affine_weights(w_up).T     # [T, H*d]
+    hh, ww = np.asarray(h, dtype=np.float64), affine_weights(w_up)
+    if f16_operands:
+        hh, ww = _as_f16(hh), _as_f16(ww)
+    logits = hh @ ww.T                                                    # [T, H*d]
     z = 1.0 / (1.0 + np.exp(-logits))
     n = np.asarray(x, dtype=np.float64) * np.repeat(np.asarray(inv, dtype=np.float64), d, axis=1) * (1.0 + np.asarray(norm_w, dtype=np.float64))[None, :]
     return (z * n).reshape(T, H, d).sum(axis=1) / H

@@ -112,6 +112,13 @@ SIGNATURES = {
     "sxb_hc_mix_up_q4": (C.c_int, [vp, QV, vp, vp, vp, i64, i64, i64, vp, C.c_int, vp]),
     "sxb_hc_mix_up_q8": (C.c_int, [vp, QV, vp, vp, vp, i64, i64, i64, vp, C.c_int, vp]),
     "sxb_to_chunk_major": (C.c_int, [QV, C.c_int, vp, vp, vp, vp]),
+    "sxb_hc_mix_down_wmma_workspace_bytes": (sz, [i64, i64, i64, i64, C.c_int, i64]),
+    "sxb_hc_mix_down_wmma_q4": (C.c_int, [vp, QV, i64, i64, i64, i64, C.c_int, C.c_float, vp, vp, vp, vp, sz, C.c_int, C.c_int, vp]),
+    "sxb_hc_mix_down_wmma_q8": (C.c_int, [vp, QV, i64, i64, i64, i64, C.c_int, C.c_float, vp, vp, vp, vp, sz, C.c_int, C.c_int, vp]),
+    "sxb_hc_inject_inv": (C.c_int, [vp, vp, vp, i64, i64, i64, C.c_float, vp, C.c_int, vp]),
+    "sxb_hc_mix_up_wmma_workspace_bytes": (sz, [i64, i64, i64, i64, C.c_int, i64]),
+    "sxb_hc_mix_up_wmma_q4": (C.c_int, [vp, QV, vp, vp, vp, i64, i64, i64, vp, vp, sz, C.c_int, vp]),
+    "sxb_hc_mix_up_wmma_q8": (C.c_int, [vp, QV, vp, vp, vp, i64, i64, i64, vp, vp, sz, C.c_int, vp]),
     "sxb_moe_route_small": (C.c_int, [vp, i64, i64, i64, i64, i64, i64, vp, vp, vp, sz, vp, vp, vp]),
 }
 for _b in ("q4", "q8"):

@@ -237,6 +237,42 @@ def hc_mix_up(h, w_up: QDeviceView, x, norm_w, inv, T, H, d, u, act, stream=None
     _check(fn(_ptr(h), C.byref(w_up.c()), _ptr(x), _ptr(norm_w), _ptr(inv), T, H, d, _ptr(u), int(act), _stream(stream)))
 
 
+def hc_wmma_workspace_bytes(T, H, d, R, bits, G) -> int:
+    """kernels/hc_wmma.hpp:29-30: bytes of device workspace hc_mix_down_wmma needs for T tokens and R = r (+ H) weight rows."""
+    n = _lib.load().sxb_hc_mix_down_wmma_workspace_bytes(T, H, d, R, int(bits), G)
+    if n == 0:
+        _check(1)
+    return n
+
+
+def hc_mix_down_wmma(x, w: QDeviceView, T, H, d, r, inject, eps, h, w_in, inv, ws, act, stream=None, inv_ready=False):
+    """kernels/hc_wmma.hpp:34-39: hc_mix_down on the tensor cores (F16 operands, FP32 accumulation); ws: a uint8 tensor of
+    hc_wmma_workspace_bytes, 256-byte aligned."""
+    fn = getattr(_lib.load(), f"sxb_hc_mix_down_wmma_{_b(w)}")
+    _check(fn(_ptr(x), C.byref(w.c()), T, H, d, r, int(bool(inject)), C.c_float(eps), _ptr(h), _ptr(w_in), _ptr(inv), _ptr(ws),
+              ws.numel() * ws.element_size(), int(act), int(bool(inv_ready)), _stream(stream)))
+
+
+def hc_inject_inv(x, w_in, y, T, H, d, eps, inv, act, stream=None):
+    """kernels/hc_wmma.hpp:40-43: hc_inject and the next mix's inv [T, H] of the updated X, in one pass."""
+    _check(_lib.load().sxb_hc_inject_inv(_ptr(x), _ptr(w_in), _ptr(y), T, H, d, C.c_float(eps), _ptr(inv), int(act), _stream(stream)))
+
+
+def hc_mix_up_wmma_workspace_bytes(T, H, d, r, bits, G) -> int:
+    n = _lib.load().sxb_hc_mix_up_wmma_workspace_bytes(T, H, d, r, int(bits), G)
+    if n == 0:
+        _check(1)
+    return n
+
+
+def hc_mix_up_wmma(h, w_up: QDeviceView, x, norm_w, inv, T, H, d, u, ws, act, stream=None):
+    """kernels/hc_wmma.hpp:45-49: hc_mix_up on the tensor cores; w_up [H*d, r] CHUNK-MAJOR; ws: a uint8 tensor of
+    hc_mix_up_wmma_workspace_bytes."""
+    fn = getattr(_lib.load(), f"sxb_hc_mix_up_wmma_{_b(w_up)}")
+    _check(fn(_ptr(h), C.byref(w_up.c()), _ptr(x), _ptr(norm_w), _ptr(inv), T, H, d, _ptr(u), _ptr(ws), ws.numel() * ws.element_size(),
+              int(act), _stream(stream)))
+
+
 def to_chunk_major(w: QDeviceView, stream=None) -> QDeviceView:
     """formats/q4.hpp:55 to_chunk_major on the device: a new view with the same codes, scales and mins chunk-major."""
     q, sc, mn = torch.empty_like(w.q), torch.empty_like(w.scale), torch.empty_like(w.minv)
