@@ -52,6 +52,8 @@ def parse():
     ap.add_argument("--no-graph", action="store_true", help="decode workloads: launch eagerly instead of replaying CUDA graphs")
     ap.add_argument("--micro", type=int, default=0, help="micro-batches per rank in expert-parallel runs (default 1)")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--hc-mix", dest="hc_mix", type=int, default=0,
+                    help="measure only the hyper-connection mix at this many tokens (tensor-core form from 65 tokens up) and print it")
     ap.add_argument("--parity-rows", type=int, default=32, help="token rows checked against the CPU oracle after the timed region (0 = skip)")
     ap.add_argument("--planes", type=int, default=3, help="BF16 planes of the FP32 router weight on the tensor-core projection (2 or 3)")
     ap.add_argument("--ep", default="native", choices=["native", "torch"],
@@ -797,6 +799,10 @@ def main():
     if world != args.gpus and rank == 0:
         print(f"note: --gpus {args.gpus} but WORLD_SIZE={world}; using {world}", file=sys.stderr)
     peaks = measured_peaks()
+    if args.hc_mix:
+        m = hc_mix_prefill_measure(dev, peaks, args.seed, T=args.hc_mix) if args.hc_mix > 64 else hc_mix_measure(dev, peaks, args.seed, T=args.hc_mix)
+        print(json.dumps({"metric": "hyper-connection mix", "n_gpus": 1, **m}))
+        return
     cfg = W.c2_config(args.seed) if args.workload == "c2" else W.CONFIGS[args.workload]
     if args.experts or args.tokens:
         from dataclasses import replace
