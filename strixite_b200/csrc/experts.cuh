@@ -50,6 +50,10 @@ int tc_partial_grouped(const char *fn, const void *h, const SxbQView *w, int64_t
 template <int BITS>
 int tc_dense(const char *fn, const void *x, const SxbQView *w, void *y, int64_t M, int x_kind, int out_kind, int h_f16,
              uint32_t *status, sxb_stream_t stream);
+// The up half of the hyper-connection mix on the same kernel: the stream combine is the epilogue (hc_tc.cu).
+template <int BITS>
+int tc_hc_up(const char *fn, const void *hs, const SxbQView *w, const void *x, const float *inv, const float *norm_w, void *u, int64_t M,
+             int64_t d, bool f32, sxb_stream_t stream);
 // f32act.cu - Act::F32 activations: the plain FP32 correctness path.  ids / ws both null: a dense projection.
 template <int BITS>
 int f32_gather(const char *fn, const void *x, const SxbQView *w, int64_t E, const int32_t *ids, const void *ws, int64_t M, int64_t A,

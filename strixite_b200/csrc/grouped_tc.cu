@@ -875,6 +875,34 @@ int tc_dense(const char *fn, const void *x, const SxbQView *w, void *y, int64_t 
     return SXB_OK;
 }
 
+// The up half of the hyper-connection mix as a dense projection with its own epilogue (kTcHcUp): hs = h [M, K] as
+// tile-blocked F16, w = W_up's rows in the epilogue's lane order [4 d, K], u [M, d] written by the kernel.
+template <int BITS>
+int tc_hc_up(const char *fn, const void *hs, const SxbQView *w, const void *x, const float *inv, const float *norm_w, void *u, int64_t M,
+             int64_t d, bool f32, sxb_stream_t stream) {
+    SXB_CHECK(hs != nullptr && w != nullptr && x != nullptr && inv != nullptr && norm_w != nullptr && u != nullptr, fn, ": null pointer");
+    SXB_CHECK(w->G == 32 || w->G == 64 || w->G == 128, fn, ": group size ", w->G, " unsupported (32, 64 or 128)");
+    SXB_CHECK(w->K >= 128 && w->K % 128 == 0 && w->K < 2048, fn, ": K = ", w->K, ", expected a multiple of 128 below 2048");
+    SXB_CHECK(M >= 1 && M <= kMoeMaxSlots && d >= 32 && d % 32 == 0 && w->N == 4 * d, fn, ": M = ", M, ", d = ", d, ", weight rows ", w->N);
+    SXB_CHECK(aligned16(w->q) && aligned16(hs), fn, ": codes and hs must be 16-byte aligned");
+    uint32_t *status = nullptr;
+    if (int rc = library_status_words(fn, &status)) return rc;
+    TcArgs a{};
+    a.x = static_cast<const uint16_t *>(hs), a.q = w->q, a.scale = w->scale, a.minv = w->minv;
+    a.N = w->N, a.K = w->K, a.A = 1, a.E = 1, a.ws = nullptr, a.L = RouteWords{};
+    a.L.S = M, a.L.E = 1;
+    a.out = u, a.x_kind = 3, a.out_f16 = 0, a.dense_M = M, a.status = status;
+    a.wait_limit_ns = g_wait_limit_ns, a.test_skip_slot = g_test_skip_slot;
+    a.hc = TcHcUp{x, inv, norm_w, u, d, f32 ? 1 : 0};
+    if (int rc = launch_tiled_tc<BITS, kTcHcUp>(fn, a, w->G, static_cast<cudaStream_t>(stream))) return rc;
+    SXB_CHECK_LAUNCH(fn, " tcgen05 up mix M=", M, " d=", d, " K=", w->K, " G=", w->G);
+    return SXB_OK;
+}
+template int tc_hc_up<4>(const char *, const void *, const SxbQView *, const void *, const float *, const float *, void *, int64_t, int64_t, bool,
+                         sxb_stream_t);
+template int tc_hc_up<8>(const char *, const void *, const SxbQView *, const void *, const float *, const float *, void *, int64_t, int64_t, bool,
+                         sxb_stream_t);
+
 template int tc_gather_grouped<4>(const char *, const void *, const SxbQView *, int64_t, const void *, size_t, int64_t, int64_t,
                                   void *, int, bool, int, sxb_stream_t);
 template int tc_gather_grouped<8>(const char *, const void *, const SxbQView *, int64_t, const void *, size_t, int64_t, int64_t,

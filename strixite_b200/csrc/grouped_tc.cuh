@@ -10,7 +10,22 @@ namespace sxb {
 
 // kTcPartialBf16: kTcPartial with the per-slot dots stored as BF16 bits (N * 2 bytes a slot) - for the epilogue it is the
 // plain gather's store on h rows.  A mode of its own, so that the per-token store code of every mode stays one short form.
-enum TcMode { kTcGather = 0, kTcSwiglu = 1, kTcPartial = 2, kTcPartialBf16 = 3 };
+// kTcHcUp: a dense projection whose epilogue is the stream combine of the hyper-connection up mix (TcHcUp below); the
+// kernel for tile-blocked activations only.
+enum TcMode { kTcGather = 0, kTcSwiglu = 1, kTcPartial = 2, kTcPartialBf16 = 3, kTcHcUp = 4 };
+
+// kTcHcUp (kernels/hc_wmma.hip:244-272): the weight's rows are W_up's rows in the order that puts the H = 4 streams of an
+// output column into adjacent tensor-memory lanes - row rb * 128 + q * 32 + l is stream l & 3 of column
+// rb * 32 + q * 8 + (l >> 2) - so that a lane finishes z -> sigmoid(z) * x * inv * (1 + norm_w) for its stream and two
+// shuffles add the four streams: u[t, j] = (1/4) sum_s ..., rounded once to the activation dtype.  No z in memory.
+struct TcHcUp {
+    const void *x;        // the streams X [M, 4 d], FP32 or BF16
+    const float *inv;     // [M, 4]
+    const float *norm_w;  // [4 d]
+    void *u;              // [M, d] in x's dtype
+    int64_t d;
+    int f32;              // x and u are FP32 (else BF16)
+};
 
 struct TcArgs {
     const uint16_t *x;  // activations: BF16 or F16 bits, see x_kind
@@ -29,6 +44,7 @@ struct TcArgs {
     int64_t dense_M;   // > 0: a dense projection - no grouping workspace, one group holding rows 0 .. dense_M - 1 in order
     unsigned long long wait_limit_ns;  // bound of every device-side wait
     int test_skip_slot;  // >= 0: CTA 0 never issues ring slot number test_skip_slot, so a wait runs out (tests only)
+    TcHcUp hc;           // kTcHcUp only
 };
 
 // Eight weights = one 16-byte chunk of the A line, from one word of Q4 codes or two words of Q8 codes.

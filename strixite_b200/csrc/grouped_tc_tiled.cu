@@ -69,6 +69,8 @@ struct Shape {
     static_assert(kStageBytes % 1024 == 0, "operand tiles start on the swizzle pattern's 1024-byte period");
 };
 constexpr int kWSlotBytes = kRows * 64;  // 64 bytes (128 Q4 or 64 Q8 codes) of each of the item's rows
+// kTcHcUp: one buffer of an epilogue warp - a pass's 128 (token, stream) segments of X, 32 bytes each at most, then inv
+constexpr int kHcUpBufBytes = 128 * 32 + 32 * 16;
 
 struct Item {
     int bucket, start, cnt;  // expert (bucket E = invalid ids), first position in slots[], tokens of the item
@@ -419,6 +421,121 @@ __global__ void __launch_bounds__(Shape<TILE>::kThreads, 1) tiled_tc_kernel(cons
         tc_commit(&drain_bar);
         if (lane == 0) mbar_wait(&drain_bar, 0u, nullptr, a.wait_limit_ns);
         __syncwarp();
+    } else if (MODE == kTcHcUp && warp < kEpiWarps) {
+        // ===================== epilogue of the hyper-connection up mix =====================
+        // Lane = (stream s = lane & 3, output column j): per token it needs one activation X[t, s d + j] and inv[t, s].
+        // Loads into registers would stall the in-order issue once per token, so a pass's 32 tokens x 4 streams x 8 columns
+        // of X and 32 x 4 of inv come through shared memory by 16-byte asynchronous copies (no registers held), issued one
+        // pass ahead - across items too - into the warp's own double buffer.  Same hand-overs with the MMA warp as below.
+        if constexpr (MODE == kTcHcUp) {
+            const TcHcUp &hc = a.hc;
+            uint32_t acc_count = 0, pass_count = 0;
+            const int quad = warp & 3, s = lane & 3, jj = lane >> 2;
+            const int col_lo = (warp >> 2) * (kTile / kEpiSets);
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+            const int64_t HD = 4 * hc.d;
+            const bool f32 = hc.f32 != 0;
+            const int es = f32 ? 4 : 2, seg = 8 * es;  // bytes of a (token, stream) segment: this quadrant's 8 columns
+            unsigned char *my_buf = smem + kStages * kStageBytes + kWSlots * kWSlotBytes + warp * (2 * kHcUpBufBytes);
+            // the copies of the pass that starts at token c0 of item `it`, into buffer `buf`: X segments, then inv
+            auto issue = [&](const Item &it, int c0, int col_hi, unsigned char *buf) {
+                const unsigned char *xg = static_cast<const unsigned char *>(hc.x) + ((int64_t)it.rb * 32 + quad * 8) * es;
+                const int sh = f32 ? 1 : 0, pieces = 128 << sh;  // 16-byte pieces of the pass's 128 segments (one or two each)
+                for (int p = lane; p < pieces; p += 32) {
+                    const int g = p >> sh, part = p & sh, tt = g >> 2, sg = g & 3;
+                    if (c0 + tt < col_hi)
+                        cp_async16(smem_u32(buf + p * 16), xg + ((int64_t)(it.start + c0 + tt) * HD + (int64_t)sg * hc.d) * es + part * 16);
+                }
+                if (c0 + lane < col_hi) cp_async16(smem_u32(buf + 128 * 32 + lane * 16), hc.inv + (int64_t)(it.start + c0 + lane) * 4);
+                cp_async_commit();
+            };
+            auto col_hi_of = [&](const Item &it) { return min(it.cnt, col_lo + kTile / kEpiSets); };
+            if (blockIdx.x < n_items) {
+                const Item it0 = item_info<TILE>(a, blockIdx.x, rbs);
+                issue(it0, col_lo, col_hi_of(it0), my_buf);
+            }
+            for (int item = blockIdx.x; item < n_items && !*abort_v; item += gridDim.x) {
+                const Item it = item_info<TILE>(a, item, rbs);
+                const int64_t j = (int64_t)it.rb * 32 + quad * 8 + jj;
+                const float nwp = 1.0f + __ldg(hc.norm_w + (int64_t)s * hc.d + j);
+                const int col_hi = col_hi_of(it);
+                const uint32_t half = acc_count % kAccs, acc_phase = (acc_count / kAccs) & 1u;
+                ++acc_count;
+                if (lane == 0 && !mbar_wait(&acc_full[half], acc_phase, abort_v, a.wait_limit_ns)) raise_abort(item, 4);
+                __syncwarp();
+                if (*abort_v) break;
+                tc_fence_after();
+                if (col_lo >= col_hi && lane == 0) mbar_arrive(&acc_empty[half]);
+                // a pass is issued even when this set has no tokens in the item, so that every item consumes one buffer at least
+                for (int c0 = col_lo; c0 < col_hi || c0 == col_lo; c0 += 32) {
+                    unsigned char *buf = my_buf + (pass_count & 1u) * kHcUpBufBytes, *nxt = my_buf + ((pass_count + 1) & 1u) * kHcUpBufBytes;
+                    ++pass_count;
+                    __syncwarp();  // every lane has finished reading the buffer that the next copies overwrite
+                    if (c0 + 32 < col_hi) {
+                        issue(it, c0 + 32, col_hi, nxt);
+                    } else if (item + (int)gridDim.x < n_items) {
+                        const Item itn = item_info<TILE>(a, item + gridDim.x, rbs);
+                        issue(itn, col_lo, col_hi_of(itn), nxt);
+                    } else {
+                        cp_async_commit();
+                    }
+                    if (c0 >= col_hi) {  // nothing to finish: only the buffer rotation above
+                        cp_async_wait<1>();
+                        break;
+                    }
+                    float va[16], vb[16];
+                    const uint32_t tcol = lane_addr + half * (uint32_t)kTile + (uint32_t)c0;
+                    tc_ld16x2(tcol, tcol + 16u, va, vb);
+                    if (c0 + 32 >= col_hi) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&acc_empty[half]);
+                    }
+                    cp_async_wait<1>();  // this pass's copies have landed (the next pass's may still be in flight)
+                    __syncwarp();
+                    const int live = col_hi - c0;
+                    const unsigned char *xs_ = buf + s * seg + jj * es;
+                    const float *ivs = reinterpret_cast<const float *>(buf + 128 * 32) + s;
+                    // First every token's term of this lane's stream, in place of its accumulator (shared-memory reads and
+                    // arithmetic only: a store to u in between would fence the next token's reads behind it, both being
+                    // generic addresses).  Then the four streams of a column - lanes l, l ^ 1, l ^ 2, l ^ 3 - are added
+                    // four tokens at a time by a reduce-scatter: three shuffles instead of the eight of four butterflies,
+                    // and it leaves each of the four lanes with the sum of one token, which that lane stores.
+#pragma unroll
+                    for (int t = 0; t < 16; ++t) {
+#pragma unroll
+                        for (int hf = 0; hf < 2; ++hf) {
+                            const int tt = t + 16 * hf;
+                            const float z = hf ? vb[t] : va[t];
+                            const float xv = f32 ? *reinterpret_cast<const float *>(xs_ + tt * 4 * seg)
+                                                 : __uint_as_float((uint32_t) * reinterpret_cast<const uint16_t *>(xs_ + tt * 4 * seg) << 16);
+                            const float c = __fdividef(xv * ivs[tt * 4] * nwp, 1.0f + __expf(-z));
+                            if (hf) vb[t] = c;
+                            else va[t] = c;
+                        }
+                    }
+                    const bool b0 = (lane & 1) != 0, b1 = (lane & 2) != 0;
+                    const int mine = (b0 ? 2 : 0) + (b1 ? 1 : 0);  // which of a group's four tokens this lane ends up with
+                    const int64_t at0 = (int64_t)(it.start + c0 + mine) * hc.d + j;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float ta = i < 4 ? va[4 * i] : vb[4 * i - 16], tb = i < 4 ? va[4 * i + 1] : vb[4 * i - 15];
+                        const float tc = i < 4 ? va[4 * i + 2] : vb[4 * i - 14], td = i < 4 ? va[4 * i + 3] : vb[4 * i - 13];
+                        // lanes with bit 0 clear keep tokens a, b and send c, d; the others the reverse
+                        const float k0 = (b0 ? tc : ta) + __shfl_xor_sync(0xffffffffu, b0 ? ta : tc, 1);
+                        const float k1 = (b0 ? td : tb) + __shfl_xor_sync(0xffffffffu, b0 ? tb : td, 1);
+                        // lanes with bit 1 clear keep the first of the two and send the second; the others the reverse
+                        const float sum = (b1 ? k1 : k0) + __shfl_xor_sync(0xffffffffu, b1 ? k0 : k1, 2);
+                        if (4 * i + mine < live) {
+                            const int64_t at = at0 + (int64_t)(4 * i) * hc.d;
+                            if (f32) static_cast<float *>(hc.u)[at] = sum * 0.25f;
+                            else static_cast<uint16_t *>(hc.u)[at] = __bfloat16_as_ushort(__float2bfloat16_rn(sum * 0.25f));
+                        }
+                    }
+                }
+            }
+            cp_async_wait<0>();
+        }
     } else if (warp < kEpiWarps) {
         // ===================== epilogue =====================
         // Lane = weight row: 32 tokens at a time from tensor memory into registers (two loads of 16 columns), then one
@@ -556,21 +673,25 @@ int launch_tiled_tc(const char *fn, TcArgs a, int64_t G, cudaStream_t st) {
         return rc;
     // A long contraction (gate/up: d = 4096 is 64 k-blocks) takes the wider tile; a short one (down: I = 1024 is 16 k-blocks)
     // the narrower, double-buffered one: there the epilogue weighs as much as the mainloop.
-    const bool wide = a.K >= 2048;
+    // (the up mix of the hyper-connections contracts over its rank, at most 1024: it has the narrower form only)
+    const bool wide = MODE != kTcHcUp && a.K >= 2048;
     using SB = Shape<kTcTileB>;
     using SA = Shape<kTcTileA>;
     const size_t smem = (wide ? (size_t)SB::kStages * SB::kStageBytes + (size_t)SB::kWSlots * kWSlotBytes
-                              : (size_t)SA::kStages * SA::kStageBytes + (size_t)SA::kWSlots * kWSlotBytes) + 1024;
+                              : (size_t)SA::kStages * SA::kStageBytes + (size_t)SA::kWSlots * kWSlotBytes) + 1024 +
+                        (MODE == kTcHcUp ? (size_t)SA::kEpiWarps * 2 * kHcUpBufBytes : 0);
     auto go = [&](auto kern) -> int {
         SXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), fn, ": reserving shared memory");
         kern<<<(unsigned)sm_count(), wide ? SB::kThreads : SA::kThreads, smem, st>>>(a, wmap);
         return SXB_OK;
     };
-    if (wide) {
-        switch (G) {
-            case 32: return go(tiled_tc_kernel<BITS, 32, MODE, kTcTileB>);
-            case 64: return go(tiled_tc_kernel<BITS, 64, MODE, kTcTileB>);
-            default: return go(tiled_tc_kernel<BITS, 128, MODE, kTcTileB>);
+    if constexpr (MODE != kTcHcUp) {
+        if (wide) {
+            switch (G) {
+                case 32: return go(tiled_tc_kernel<BITS, 32, MODE, kTcTileB>);
+                case 64: return go(tiled_tc_kernel<BITS, 64, MODE, kTcTileB>);
+                default: return go(tiled_tc_kernel<BITS, 128, MODE, kTcTileB>);
+            }
         }
     }
     switch (G) {
@@ -588,5 +709,7 @@ template int launch_tiled_tc<8, kTcGather>(const char *, TcArgs, int64_t, cudaSt
 template int launch_tiled_tc<8, kTcSwiglu>(const char *, TcArgs, int64_t, cudaStream_t);
 template int launch_tiled_tc<8, kTcPartial>(const char *, TcArgs, int64_t, cudaStream_t);
 template int launch_tiled_tc<8, kTcPartialBf16>(const char *, TcArgs, int64_t, cudaStream_t);
+template int launch_tiled_tc<4, kTcHcUp>(const char *, TcArgs, int64_t, cudaStream_t);
+template int launch_tiled_tc<8, kTcHcUp>(const char *, TcArgs, int64_t, cudaStream_t);
 
 }  // namespace sxb

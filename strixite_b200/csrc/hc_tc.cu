@@ -10,9 +10,11 @@
 //         rows zero).  One pass over X computes inv and writes the tile-blocked F16 operand; the pack of the constant ids
 //         (t * H + s -> s) builds the tile lists; the grouped kernel leaves FP32 per-slot dots; a last pass folds them with
 //         inv, in stream order (kernels/hc_wmma.hip:136-150), into h and w_in.
-//   up    z = h W_up^T is a dense projection of h [T, r] on W_up [H*d, r] un-chunked to row-major with r padded to a
-//         multiple of 128 by zero groups; it runs per block of tokens so that z (FP32, H*d a token) stays in L2 for the
-//         pass that follows: u = (1/H) sum_s sigmoid(z_s) * X_s * inv_s * (1 + norm_w_s) (kernels/hc_wmma.hip:244-272).
+//   up    z = h W_up^T is a dense projection of h [T, r] on W_up [H*d, r], un-chunked to row-major with r padded to a
+//         multiple of 128 by zero groups and its rows put in the order that makes the four streams of an output column
+//         neighbours in tensor memory; the kernel's epilogue is the stream combine itself,
+//         u = (1/H) sum_s sigmoid(z_s) * X_s * inv_s * (1 + norm_w_s) (kernels/hc_wmma.hip:244-272), so z never exists
+//         in memory.
 // The re-layouts of the two weights (a few MB) are done per call into the caller's workspace: the views an engine holds
 // stay the reference's (row-major folded down weight, chunk-major up weight), shared with the per-token kernels.
 
@@ -29,9 +31,7 @@ namespace {
 constexpr int kStreams = 4;
 constexpr int kChunk = 32;           // codes per chunk of the chunk-major layout
 constexpr int64_t kMaxRank = 1024;
-constexpr int64_t kUpTokens = 1024;  // tokens per block of the up mix: z = 1024 * H*d * 4 bytes (64 MB at d = 4096)
 
-__device__ inline float sigmoid_f32(float z) { return 1.0f / (1.0f + expf(-z)); }
 inline int64_t up16(int64_t v) { return (v + 15) / 16 * 16; }
 inline int64_t up128(int64_t v) { return (v + 127) / 128 * 128; }
 inline size_t al256(size_t v) { return (v + 255) / 256 * 256; }
@@ -176,21 +176,28 @@ __global__ void __launch_bounds__(256) hc_inject_inv_kernel(TX *__restrict__ x, 
 
 // ---- up ------------------------------------------------------------------------------------------------------------
 
-// Chunk-major W_up [N, r] (32-code chunk c of row n at word (c N + n) * cw, group g's scale / min at [g N + n]) -> row-major
-// [N, Kp] with Kp >= r: the chunks and groups past r are zero codes, zero scale, zero min.
+// Chunk-major W_up [N = 4 d, r] (32-code chunk c of row n at word (c N + n) * cw, group g's scale / min at [g N + n]) ->
+// row-major [N, Kp] with Kp >= r: the chunks and groups past r are zero codes, zero scale, zero min.  Row
+// rb * 128 + q * 32 + l of the result is W_up's row s d + j with s = l & 3, j = rb * 32 + q * 8 + (l >> 2): the order in
+// which the up mix's epilogue wants the rows in tensor-memory lanes (TcHcUp).
+__device__ inline int64_t up_source_row(int64_t row, int64_t d) {
+    const int64_t rb = row >> 7, q = (row >> 5) & 3, l = row & 31;
+    return (l & 3) * d + rb * 32 + q * 8 + (l >> 2);
+}
 __global__ void __launch_bounds__(256) hc_unchunk_up_kernel(const uint8_t *__restrict__ q, const uint16_t *__restrict__ scale,
-                                                            const uint16_t *__restrict__ minv, int64_t N, int64_t r, int64_t Kp, int64_t G,
+                                                            const uint16_t *__restrict__ minv, int64_t d, int64_t r, int64_t Kp, int64_t G,
                                                             int bits, uint32_t *__restrict__ qo, uint16_t *__restrict__ so,
                                                             uint16_t *__restrict__ mo) {
+    const int64_t N = kStreams * d;
     const int64_t cw = bits, chunks = r / kChunk, chunks_p = Kp / kChunk, groups = r / G, groups_p = Kp / G;  // cw: words per chunk
     const int64_t stride = (int64_t)gridDim.x * blockDim.x, first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const uint32_t *qi = reinterpret_cast<const uint32_t *>(q);
     for (int64_t i = first; i < N * chunks_p * cw; i += stride) {
-        const int64_t w = i % cw, nc = i / cw, c = nc % chunks_p, n = nc / chunks_p;
+        const int64_t w = i % cw, nc = i / cw, c = nc % chunks_p, n = up_source_row(nc / chunks_p, d);
         qo[i] = c < chunks ? qi[(c * N + n) * cw + w] : 0u;
     }
     for (int64_t i = first; i < N * groups_p; i += stride) {
-        const int64_t g = i % groups_p, n = i / groups_p;
+        const int64_t g = i % groups_p, n = up_source_row(i / groups_p, d);
         so[i] = g < groups ? scale[g * N + n] : (uint16_t)0, mo[i] = g < groups ? minv[g * N + n] : (uint16_t)0;
     }
 }
@@ -206,30 +213,6 @@ __global__ void __launch_bounds__(256) hc_stage_h_kernel(const float *__restrict
         float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         if ((int64_t)kk * 8 < r) load8(h + t * r, (int64_t)kk * 8, f);
         *reinterpret_cast<uint4 *>(hs + tiled_offset(M, kk >> 3, t, (int)(t & 7), kk & 7)) = f16_chunk<BITS>(f);
-    }
-}
-
-// u[t, j] = (1/H) sum_s sigmoid(z[t, s d + j]) * (X[t, s d + j] * inv[t, s] * (1 + norm_w[s d + j])), streams in order,
-// rounded once to the activation dtype (kernels/hc_wmma.hip:244-272).  A thread takes four consecutive columns of a token.
-template <typename TX>
-__global__ void __launch_bounds__(256) hc_finish_up_kernel(const float *__restrict__ z, const TX *__restrict__ x, const float *__restrict__ norm_w,
-                                                           const float *__restrict__ inv, int64_t M, int64_t d, TX *__restrict__ u) {
-    const int64_t quads = d / 4;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < M * quads; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t t = i / quads, j = (i % quads) * 4;
-        float sum[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int s = 0; s < kStreams; ++s) {
-            const int64_t g = (int64_t)s * d + j;
-            const float4 zz = *reinterpret_cast<const float4 *>(z + t * kStreams * d + g);
-            const float4 nw = __ldg(reinterpret_cast<const float4 *>(norm_w + g));
-            const float is = inv[t * kStreams + s];
-            const float zv[4] = {zz.x, zz.y, zz.z, zz.w}, nv[4] = {nw.x, nw.y, nw.z, nw.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) sum[e] += sigmoid_f32(zv[e]) * (load_as_f32(x, t * kStreams * d + g + e) * is * (1.0f + nv[e]));
-        }
-#pragma unroll
-        for (int e = 0; e < 4; ++e) store_from_f32(u, t * d + j + e, sum[e] / (float)kStreams);
     }
 }
 
@@ -310,15 +293,15 @@ int mix_down_tc(const void *x, const SxbQView *w, int64_t T, int64_t H, int64_t 
 }
 
 struct UpWs {
-    size_t wq, wscale, wmin, hs, z, total;
+    size_t wq, wscale, wmin, hs, total;
 };
 UpWs up_ws(int64_t T, int64_t d, int64_t r, int bits, int64_t G) {
-    const int64_t Kp = up128(r), N = kStreams * d, Tb = std::min(T, kUpTokens);
+    const int64_t Kp = up128(r), N = kStreams * d;
     UpWs L{};
     size_t at = 0;
     auto take = [&](size_t bytes) { const size_t o = at; at += al256(bytes); return o; };
     L.wq = take((size_t)N * Kp * bits / 8), L.wscale = take((size_t)N * (Kp / G) * 2), L.wmin = take((size_t)N * (Kp / G) * 2);
-    L.hs = take((size_t)Tb * Kp * 2), L.z = take((size_t)Tb * N * 4);
+    L.hs = take((size_t)T * Kp * 2);
     L.total = at;
     return L;
 }
@@ -343,32 +326,16 @@ int mix_up_tc(const float *h, const SxbQView *w, const void *x, const float *nor
     auto *base = static_cast<unsigned char *>(ws);
     auto st = static_cast<cudaStream_t>(stream);
     SxbQView rows{base + L.wq, reinterpret_cast<uint16_t *>(base + L.wscale), reinterpret_cast<uint16_t *>(base + L.wmin), N, Kp, w->G};
-    auto *z = reinterpret_cast<float *>(base + L.z);
 
     const int64_t words = N * Kp * BITS / 32;
     hc_unchunk_up_kernel<<<(unsigned)std::min<int64_t>((words + 255) / 256, (int64_t)sm_count() * 8), 256, 0, st>>>(
-        w->q, w->scale, w->minv, N, r, Kp, w->G, BITS, reinterpret_cast<uint32_t *>(base + L.wq), reinterpret_cast<uint16_t *>(base + L.wscale),
+        w->q, w->scale, w->minv, d, r, Kp, w->G, BITS, reinterpret_cast<uint32_t *>(base + L.wq), reinterpret_cast<uint16_t *>(base + L.wscale),
         reinterpret_cast<uint16_t *>(base + L.wmin));
     SXB_CHECK_LAUNCH(fn, " un-chunking the weight, N=", N, " r=", r);
-    const size_t es = act_bytes(act);
-    for (int64_t t0 = 0; t0 < T; t0 += kUpTokens) {
-        const int64_t M = std::min(kUpTokens, T - t0);
-        const unsigned stage_blocks = (unsigned)std::min<int64_t>((M * (Kp / 8) + 255) / 256, (int64_t)sm_count() * 8);
-        hc_stage_h_kernel<BITS><<<stage_blocks, 256, 0, st>>>(h + t0 * r, M, r, Kp, base + L.hs);
-        SXB_CHECK_LAUNCH(fn, " staging h, rows ", t0, " .. ", t0 + M);
-        if (int rc = tc_dense<BITS>(fn, base + L.hs, &rows, z, M, 3, 1, 0, nullptr, stream)) return rc;
-        const unsigned fin_blocks = (unsigned)std::min<int64_t>((M * (d / 4) + 255) / 256, (int64_t)sm_count() * 16);
-        const auto *xb = static_cast<const unsigned char *>(x) + (size_t)t0 * N * es;
-        auto *ub = static_cast<unsigned char *>(u) + (size_t)t0 * d * es;
-        if (act == SXB_ACT_F32)
-            hc_finish_up_kernel<float><<<fin_blocks, 256, 0, st>>>(z, reinterpret_cast<const float *>(xb), norm_w, inv + t0 * kStreams, M, d,
-                                                                   reinterpret_cast<float *>(ub));
-        else
-            hc_finish_up_kernel<uint16_t><<<fin_blocks, 256, 0, st>>>(z, reinterpret_cast<const uint16_t *>(xb), norm_w, inv + t0 * kStreams, M, d,
-                                                                      reinterpret_cast<uint16_t *>(ub));
-        SXB_CHECK_LAUNCH(fn, " Q", BITS, " ", act_name(act), " rows ", t0, " .. ", t0 + M, " d=", d, " r=", r, " G=", w->G);
-    }
-    return SXB_OK;
+    const unsigned stage_blocks = (unsigned)std::min<int64_t>((T * (Kp / 8) + 255) / 256, (int64_t)sm_count() * 8);
+    hc_stage_h_kernel<BITS><<<stage_blocks, 256, 0, st>>>(h, T, r, Kp, base + L.hs);
+    SXB_CHECK_LAUNCH(fn, " staging h, T=", T, " r=", r);
+    return tc_hc_up<BITS>(fn, base + L.hs, &rows, x, inv, norm_w, u, T, d, act == SXB_ACT_F32, stream);
 }
 
 }  // namespace

@@ -191,6 +191,16 @@ __device__ inline void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, 
                  "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
                  : "memory");
 }
+// 16 bytes global -> shared without passing through registers (both addresses 16-byte aligned); complete, for the
+// issuing thread, after cp_async_wait<N> has let at most N of its later groups remain in flight.
+__device__ inline void cp_async16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ inline void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ inline void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 __device__ inline uint4 ld_shared_v4(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
