@@ -773,7 +773,7 @@ def hc_mix_prefill_measure(dev, peaks, seed, T=4096, d=4096, r=320, H=4, iters=1
     flops = 2.0 * T * H * d * (R + r)
     tf = flops / (ms * 1e-3) / 1e12
     return {"T": T, "d": d, "r": r, "weights": "q8g64", "ms_per_mix": ms, "ms_down": ms_down, "ms_up": ms_up,
-            "launches_per_mix": 10,
+            "launches_per_mix": 8,
             "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["tflops_burst"], "unit": "TFLOP/s", "frac": tf / peaks["tflops_burst"]},
             "hbm_bytes_floor": 2 * x.numel() * 2 + u.numel() * 2}
 

@@ -7,8 +7,8 @@
 //   down  a = sum_s inv[t, s] * (W'_s . X_s[t]) is a grouped projection with the H streams as H "experts": slot t * H + s
 //         holds the row X_s[t] (X [T, H*d] read as [T*H, d] IS that slot-major matrix), expert s the weight's column range
 //         [s d, (s + 1) d) restacked as rows [s Rp, (s + 1) Rp) of a [H * Rp, d] view (Rp = R rounded up to 16, the padding
-//         rows zero).  One pass over X computes inv and writes the tile-blocked F16 operand; the pack of the constant ids
-//         (t * H + s -> s) builds the tile lists; the grouped kernel leaves FP32 per-slot dots; a last pass folds them with
+//         rows zero).  One pass over X computes inv and writes the tile-blocked F16 operand; the grouping workspace of that
+//         regular pattern is written directly (no ids, no sort); the grouped kernel leaves FP32 per-slot dots; a last pass folds them with
 //         inv, in stream order (kernels/hc_wmma.hip:136-150), into h and w_in.
 //   up    z = h W_up^T is a dense projection of h [T, r] on W_up [H*d, r], un-chunked to row-major with r padded to a
 //         multiple of 128 by zero groups and its rows put in the order that makes the four streams of an output column
@@ -64,12 +64,11 @@ __device__ inline void load8(const uint16_t *p, int64_t i, float (&f)[8]) {
 // ---- down ----------------------------------------------------------------------------------------------------------
 
 // The folded down weight [R, H*d] -> per-stream stacks [H * Rp, d]: codes, scales and mins of columns [s d, (s + 1) d) of
-// row n become row s * Rp + n; rows n >= R are zero codes with zero scale and min.  Also the constant ids of the pack:
-// slot t * H + s belongs to "expert" s.
+// row n become row s * Rp + n; rows n >= R are zero codes with zero scale and min.
 __global__ void __launch_bounds__(256) hc_stack_down_kernel(const uint8_t *__restrict__ q, const uint16_t *__restrict__ scale,
                                                             const uint16_t *__restrict__ minv, int64_t R, int64_t Rp, int64_t d, int64_t G,
                                                             int bits, uint32_t *__restrict__ qo, uint16_t *__restrict__ so,
-                                                            uint16_t *__restrict__ mo, int32_t *__restrict__ ids, int64_t slots) {
+                                                            uint16_t *__restrict__ mo) {
     const int64_t row_words = d * bits / 32, row_groups = d / G, stride = (int64_t)gridDim.x * blockDim.x;
     const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const uint32_t *qi = reinterpret_cast<const uint32_t *>(q);
@@ -82,7 +81,6 @@ __global__ void __launch_bounds__(256) hc_stack_down_kernel(const uint8_t *__res
         const int64_t at = (n * kStreams + s) * row_groups + g;
         so[i] = n < R ? scale[at] : (uint16_t)0, mo[i] = n < R ? minv[at] : (uint16_t)0;
     }
-    for (int64_t i = first; i < slots; i += stride) ids[i] = (int32_t)(i % kStreams);
 }
 
 // One pass over X [T, H*d]: inv[t, s] = 1 / sqrt(mean(X_s[t]^2) + eps) (kernels/hc_wmma.hip:25-45; skipped when the caller
@@ -233,7 +231,7 @@ int check_shape(const char *fn, int64_t T, int64_t H, int64_t d, const SxbQView 
 // Parts of the down mix's workspace, in bytes from its start; the grouping workspace comes first, so that
 // sxb_check_grouped_status reads the caller's pointer as it is.
 struct DownWs {
-    size_t route, route_bytes, err, ids, wq, wscale, wmin, xs, partial, total;
+    size_t route, route_bytes, wq, wscale, wmin, xs, partial, total;
 };
 DownWs down_ws(int64_t T, int64_t d, int64_t R, int bits, int64_t G) {
     const int64_t Rp = up16(R), S = T * kStreams;
@@ -241,7 +239,7 @@ DownWs down_ws(int64_t T, int64_t d, int64_t R, int bits, int64_t G) {
     size_t at = 0;
     auto take = [&](size_t bytes) { const size_t o = at; at += al256(bytes); return o; };
     L.route_bytes = (size_t)route_words(S, 1, kStreams).total * 4;
-    L.route = take(L.route_bytes), L.err = take(64), L.ids = take((size_t)S * 4);
+    L.route = take(L.route_bytes);
     L.wq = take((size_t)kStreams * Rp * d * bits / 8), L.wscale = take((size_t)kStreams * Rp * (d / G) * 2), L.wmin = take((size_t)kStreams * Rp * (d / G) * 2);
     L.xs = take((size_t)S * d * 2), L.partial = take((size_t)S * Rp * 4);
     L.total = at;
@@ -266,18 +264,15 @@ int mix_down_tc(const void *x, const SxbQView *w, int64_t T, int64_t H, int64_t 
     SXB_CHECK(ws_bytes >= L.total, fn, ": workspace of ", ws_bytes, " bytes, needs ", L.total);
     auto *base = static_cast<unsigned char *>(ws);
     auto st = static_cast<cudaStream_t>(stream);
-    auto *ids = reinterpret_cast<int32_t *>(base + L.ids);
-    auto *err = reinterpret_cast<uint32_t *>(base + L.err);
     auto *partial = reinterpret_cast<float *>(base + L.partial);
     SxbQView stacked{base + L.wq, reinterpret_cast<uint16_t *>(base + L.wscale), reinterpret_cast<uint16_t *>(base + L.wmin), kStreams * Rp, d, w->G};
 
     const int64_t stack_words = kStreams * Rp * d * BITS / 32;
-    hc_stack_down_kernel<<<(unsigned)std::min<int64_t>((std::max(stack_words, S) + 255) / 256, (int64_t)sm_count() * 8), 256, 0, st>>>(
+    hc_stack_down_kernel<<<(unsigned)std::min<int64_t>((stack_words + 255) / 256, (int64_t)sm_count() * 8), 256, 0, st>>>(
         w->q, w->scale, w->minv, R, Rp, d, w->G, BITS, reinterpret_cast<uint32_t *>(base + L.wq), reinterpret_cast<uint16_t *>(base + L.wscale),
-        reinterpret_cast<uint16_t *>(base + L.wmin), ids, S);
+        reinterpret_cast<uint16_t *>(base + L.wmin));
     SXB_CHECK_LAUNCH(fn, " restacking the weight, R=", R, " d=", d);
-    SXB_CUDA(cudaMemsetAsync(err, 0, 64, st), fn, ": clearing the pack's error words");
-    if (int rc = sxb_moe_group_routes(ids, S, 1, kStreams, base + L.route, L.route_bytes, err, stream)) return rc;
+    if (int rc = regular_routes(fn, T, kStreams, base + L.route, L.route_bytes, stream)) return rc;
     const unsigned stage_blocks = (unsigned)std::min<int64_t>((S + 7) / 8, (int64_t)sm_count() * 8);
     if (act == SXB_ACT_F32)
         hc_stage_down_kernel<float, BITS><<<stage_blocks, 256, 0, st>>>(static_cast<const float *>(x), T, d, eps, inv_ready == 0, inv, base + L.xs);

@@ -11,6 +11,8 @@
 //   bases / tile lists, and a scatter in which every warp places its own segment in order.
 
 #include "route_pack.cuh"
+
+#include <algorithm>
 #include "router_token.cuh"
 
 namespace sxb {
@@ -267,7 +269,28 @@ int group_routes(const char *fn, const int32_t *ids, int64_t M, int64_t A, int64
     return SXB_OK;
 }
 
+// The workspace of a regular grouping, written without ids: S = M * E slots, slot m * E + b in bucket b for every m, so that
+// bucket b holds M slots in ascending order.  CTA 0 writes offsets, header and tile lists; every CTA writes slots.
+__global__ void __launch_bounds__(kPackThreads) regular_routes_kernel(RouteWords L, int per_bucket, int32_t *ws) {
+    __shared__ int scanbuf[33], tile_first[4 * 1025];
+    const int E = (int)L.E;
+    int32_t *slots = ws + L.slots;
+    for (int64_t pos = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; pos < L.S; pos += (int64_t)gridDim.x * blockDim.x)
+        slots[pos] = (int32_t)((pos % per_bucket) * E + pos / per_bucket);
+    if (blockIdx.x == 0) emit_layout((int)threadIdx.x < E ? per_bucket : 0, L, ws, scanbuf, tile_first, false);
+}
+
 }  // namespace
+
+int regular_routes(const char *fn, int64_t M, int64_t E, void *ws, size_t ws_bytes, sxb_stream_t stream) {
+    SXB_CHECK(ws != nullptr && M >= 1 && E >= 1 && E <= kMoeMaxExperts && M * E <= kMoeMaxSlots, fn, ": M = ", M, ", E = ", E, ", ws = ", ws);
+    const RouteWords L = route_words(M * E, 1, E);
+    SXB_CHECK(ws_bytes >= (size_t)L.total * 4 && reinterpret_cast<uintptr_t>(ws) % 4 == 0, fn, ": workspace of ", ws_bytes, " bytes, needs ", L.total * 4);
+    const unsigned ctas = (unsigned)std::min<int64_t>((L.S + kPackThreads - 1) / kPackThreads, (int64_t)sm_count() * 2);
+    regular_routes_kernel<<<ctas, kPackThreads, 0, static_cast<cudaStream_t>(stream)>>>(L, (int)M, static_cast<int32_t *>(ws));
+    SXB_CHECK_LAUNCH(fn, " regular grouping M=", M, " E=", E);
+    return SXB_OK;
+}
 
 RouteWords route_words(int64_t M, int64_t A, int64_t E) {
     RouteWords L;

@@ -27,5 +27,8 @@ struct RouteWords {
     int64_t offsets, slots, t8_bucket, t8_start, t128_bucket, t128_start, segbad, scratch, tta_n, tta_bucket, tta_start, ttb_n, ttb_bucket, ttb_start, total;
 };
 RouteWords route_words(int64_t M, int64_t A, int64_t E);
+// The workspace (route_words(M * E, 1, E)) of the grouping in which slot m * E + b belongs to bucket b, for all m < M: what
+// sxb_moe_group_routes writes for ids[m * E + b] = b, without the ids or the sort.
+int regular_routes(const char *fn, int64_t M, int64_t E, void *ws, size_t ws_bytes, sxb_stream_t stream);
 
 }  // namespace sxb

@@ -115,6 +115,22 @@ def test_hc_mix_wmma(cuda, oracle, dt, bits, G, T, d, r, inject):
     ws = _ws(K.hc_wmma_workspace_bytes(T, H, d, R, bits, G), cuda)
     K.hc_mix_down_wmma(xd, upload(wd, cuda), T, H, d, r, inject, eps, h, w_in, inv, ws, act)
     K.check_grouped_status(ws, "hc_mix_down_wmma")
+    # the grouping workspace the mix wrote without ids (streams as experts) is the pack's own for ids[t * H + s] = s
+    S = T * H
+    ids = (torch.arange(S, device=cuda) % H).to(torch.int32)
+    nbytes = K.moe_route_workspace_bytes(S, 1, H)
+    ws_pack, err = torch.zeros(nbytes // 4, dtype=torch.int32, device=cuda), torch.zeros(4, dtype=torch.int32, device=cuda)
+    K.moe_group_routes(ids, S, 1, H, ws_pack, nbytes, err)
+    got_ws, want_ws, lay = ws[:nbytes].view(torch.int32).cpu().numpy(), ws_pack.cpu().numpy(), K.route_layout(S, 1, H)
+    assert np.array_equal(got_ws[:5], want_ws[:5])
+    assert np.array_equal(got_ws[lay["offsets"]:lay["offsets"] + H + 2], want_ws[lay["offsets"]:lay["offsets"] + H + 2])
+    assert np.array_equal(got_ws[lay["slots"]:lay["slots"] + S], want_ws[lay["slots"]:lay["slots"] + S])
+    for rows, n_at in ((8, 0), (128, 3), (192, lay["tile192_n"]), (256, lay["tile256_n"])):
+        n = int(want_ws[n_at])
+        assert int(got_ws[n_at]) == n
+        for part in ("bucket", "start"):
+            at = lay[f"tile{rows}_{part}"]
+            assert np.array_equal(got_ws[at:at + n], want_ws[at:at + n])
     h_ref, w_in_ref, inv_ref = oracle.hc_mix_down(x, wd, H, d, r, inject, eps, f16_operands=True)
     h_exact, _, _ = oracle.hc_mix_down(x, wd, H, d, r, inject, eps)
     assert max_abs_over_rms(inv.cpu().numpy(), inv_ref) <= 1e-5
