@@ -125,7 +125,7 @@ def test_hc_mix_wmma(cuda, oracle, dt, bits, G, T, d, r, inject):
     assert np.array_equal(got_ws[:5], want_ws[:5])
     assert np.array_equal(got_ws[lay["offsets"]:lay["offsets"] + H + 2], want_ws[lay["offsets"]:lay["offsets"] + H + 2])
     assert np.array_equal(got_ws[lay["slots"]:lay["slots"] + S], want_ws[lay["slots"]:lay["slots"] + S])
-    for rows, n_at in ((8, 0), (128, 3), (192, lay["tile192_n"]), (256, lay["tile256_n"])):
+    for rows, n_at in ((8, 0), (128, 3)) + tuple((rows, lay[f"tile{rows}_n"]) for rows in K.TC_TILES):
         n = int(want_ws[n_at])
         assert int(got_ws[n_at]) == n
         for part in ("bucket", "start"):
