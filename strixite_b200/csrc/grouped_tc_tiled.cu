@@ -38,6 +38,8 @@
 
 #include "grouped_tc.cuh"
 
+#include <type_traits>
+
 namespace sxb {
 namespace {
 
@@ -428,113 +430,117 @@ __global__ void __launch_bounds__(Shape<TILE>::kThreads, 1) tiled_tc_kernel(cons
         // of X and 32 x 4 of inv come through shared memory by 16-byte asynchronous copies (no registers held), issued one
         // pass ahead - across items too - into the warp's own double buffer.  Same hand-overs with the MMA warp as below.
         if constexpr (MODE == kTcHcUp) {
-            const TcHcUp &hc = a.hc;
-            uint32_t acc_count = 0, pass_count = 0;
-            const int quad = warp & 3, s = lane & 3, jj = lane >> 2;
-            const int col_lo = (warp >> 2) * (kTile / kEpiSets);
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-            const int64_t HD = 4 * hc.d;
-            const bool f32 = hc.f32 != 0;
-            const int es = f32 ? 4 : 2, seg = 8 * es;  // bytes of a (token, stream) segment: this quadrant's 8 columns
-            unsigned char *my_buf = smem + kStages * kStageBytes + kWSlots * kWSlotBytes + warp * (2 * kHcUpBufBytes);
-            // the copies of the pass that starts at token c0 of item `it`, into buffer `buf`: X segments, then inv
-            auto issue = [&](const Item &it, int c0, int col_hi, unsigned char *buf) {
-                const unsigned char *xg = static_cast<const unsigned char *>(hc.x) + ((int64_t)it.rb * 32 + quad * 8) * es;
-                const int sh = f32 ? 1 : 0, pieces = 128 << sh;  // 16-byte pieces of the pass's 128 segments (one or two each)
-                for (int p = lane; p < pieces; p += 32) {
-                    const int g = p >> sh, part = p & sh, tt = g >> 2, sg = g & 3;
-                    if (c0 + tt < col_hi)
-                        cp_async16(smem_u32(buf + p * 16), xg + ((int64_t)(it.start + c0 + tt) * HD + (int64_t)sg * hc.d) * es + part * 16);
+            // The activation dtype is a compile-time constant of the loops (one instantiation each): a run-time choice
+            // between two loads per token would put a branch between the tokens, and their chains would not overlap.
+            auto run = [&](auto f32_tag) {
+                constexpr bool kF32 = decltype(f32_tag)::value;
+                constexpr int es = kF32 ? 4 : 2, seg = 8 * es;  // bytes of a (token, stream) segment: this quadrant's 8 columns
+                constexpr int kPieces = (128 * seg / 16) / 32;   // 16-byte copies per lane and pass
+                using TX = typename std::conditional<kF32, float, uint16_t>::type;
+                const TcHcUp &hc = a.hc;
+                uint32_t acc_count = 0, pass_count = 0;
+                const int quad = warp & 3, s = lane & 3, jj = lane >> 2;
+                const int col_lo = (warp >> 2) * (kTile / kEpiSets);
+                const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+                const int64_t row_bytes = 4 * hc.d * es;  // a token's four streams
+                unsigned char *my_buf = smem + kStages * kStageBytes + kWSlots * kWSlotBytes + warp * (2 * kHcUpBufBytes);
+                // Copy number k of a pass: piece p = 32 k + lane of the pass's [token][stream][part] order, i.e. token
+                // k * (8 / parts) + tok_l, stream str_l, part part_l with parts = seg / 16.
+                constexpr int kParts = seg / 16, kTokStep = 8 / kParts;
+                const int part_l = lane % kParts, str_l = (lane / kParts) & 3, tok_l = lane / (4 * kParts);
+                auto issue = [&](const Item &it, int c0, int col_hi, unsigned char *buf) {
+                    const unsigned char *src = static_cast<const unsigned char *>(hc.x) + ((int64_t)it.rb * 32 + quad * 8 + (int64_t)str_l * hc.d) * es +
+                                               part_l * 16 + (int64_t)(it.start + c0 + tok_l) * row_bytes;
+                    const uint32_t dst = smem_u32(buf) + (uint32_t)lane * 16u;
+#pragma unroll
+                    for (int k = 0; k < kPieces; ++k)
+                        if (c0 + k * kTokStep + tok_l < col_hi) cp_async16(dst + (uint32_t)k * 512u, src + (int64_t)(k * kTokStep) * row_bytes);
+                    if (c0 + lane < col_hi) cp_async16(smem_u32(buf) + 128 * 32 + (uint32_t)lane * 16u, hc.inv + (int64_t)(it.start + c0 + lane) * 4);
+                    cp_async_commit();
+                };
+                auto col_hi_of = [&](const Item &it) { return min(it.cnt, col_lo + kTile / kEpiSets); };
+                if (blockIdx.x < n_items) {
+                    const Item it0 = item_info<TILE>(a, blockIdx.x, rbs);
+                    issue(it0, col_lo, col_hi_of(it0), my_buf);
                 }
-                if (c0 + lane < col_hi) cp_async16(smem_u32(buf + 128 * 32 + lane * 16), hc.inv + (int64_t)(it.start + c0 + lane) * 4);
-                cp_async_commit();
-            };
-            auto col_hi_of = [&](const Item &it) { return min(it.cnt, col_lo + kTile / kEpiSets); };
-            if (blockIdx.x < n_items) {
-                const Item it0 = item_info<TILE>(a, blockIdx.x, rbs);
-                issue(it0, col_lo, col_hi_of(it0), my_buf);
-            }
-            for (int item = blockIdx.x; item < n_items && !*abort_v; item += gridDim.x) {
-                const Item it = item_info<TILE>(a, item, rbs);
-                const int64_t j = (int64_t)it.rb * 32 + quad * 8 + jj;
-                const float nwp = 1.0f + __ldg(hc.norm_w + (int64_t)s * hc.d + j);
-                const int col_hi = col_hi_of(it);
-                const uint32_t half = acc_count % kAccs, acc_phase = (acc_count / kAccs) & 1u;
-                ++acc_count;
-                if (lane == 0 && !mbar_wait(&acc_full[half], acc_phase, abort_v, a.wait_limit_ns)) raise_abort(item, 4);
-                __syncwarp();
-                if (*abort_v) break;
-                tc_fence_after();
-                if (col_lo >= col_hi && lane == 0) mbar_arrive(&acc_empty[half]);
-                // a pass is issued even when this set has no tokens in the item, so that every item consumes one buffer at least
-                for (int c0 = col_lo; c0 < col_hi || c0 == col_lo; c0 += 32) {
-                    unsigned char *buf = my_buf + (pass_count & 1u) * kHcUpBufBytes, *nxt = my_buf + ((pass_count + 1) & 1u) * kHcUpBufBytes;
-                    ++pass_count;
-                    __syncwarp();  // every lane has finished reading the buffer that the next copies overwrite
-                    if (c0 + 32 < col_hi) {
-                        issue(it, c0 + 32, col_hi, nxt);
-                    } else if (item + (int)gridDim.x < n_items) {
-                        const Item itn = item_info<TILE>(a, item + gridDim.x, rbs);
-                        issue(itn, col_lo, col_hi_of(itn), nxt);
-                    } else {
-                        cp_async_commit();
-                    }
-                    if (c0 >= col_hi) {  // nothing to finish: only the buffer rotation above
-                        cp_async_wait<1>();
-                        break;
-                    }
-                    float va[16], vb[16];
-                    const uint32_t tcol = lane_addr + half * (uint32_t)kTile + (uint32_t)c0;
-                    tc_ld16x2(tcol, tcol + 16u, va, vb);
-                    if (c0 + 32 >= col_hi) {
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&acc_empty[half]);
-                    }
-                    cp_async_wait<1>();  // this pass's copies have landed (the next pass's may still be in flight)
+                for (int item = blockIdx.x; item < n_items && !*abort_v; item += gridDim.x) {
+                    const Item it = item_info<TILE>(a, item, rbs);
+                    const int64_t j = (int64_t)it.rb * 32 + quad * 8 + jj;
+                    const float nwp = 1.0f + __ldg(hc.norm_w + (int64_t)s * hc.d + j);
+                    const int col_hi = col_hi_of(it);
+                    const uint32_t half = acc_count % kAccs, acc_phase = (acc_count / kAccs) & 1u;
+                    ++acc_count;
+                    if (lane == 0 && !mbar_wait(&acc_full[half], acc_phase, abort_v, a.wait_limit_ns)) raise_abort(item, 4);
                     __syncwarp();
-                    const int live = col_hi - c0;
-                    const unsigned char *xs_ = buf + s * seg + jj * es;
-                    const float *ivs = reinterpret_cast<const float *>(buf + 128 * 32) + s;
-                    // First every token's term of this lane's stream, in place of its accumulator (shared-memory reads and
-                    // arithmetic only: a store to u in between would fence the next token's reads behind it, both being
-                    // generic addresses).  Then the four streams of a column - lanes l, l ^ 1, l ^ 2, l ^ 3 - are added
-                    // four tokens at a time by a reduce-scatter: three shuffles instead of the eight of four butterflies,
-                    // and it leaves each of the four lanes with the sum of one token, which that lane stores.
-#pragma unroll
-                    for (int t = 0; t < 16; ++t) {
-#pragma unroll
-                        for (int hf = 0; hf < 2; ++hf) {
-                            const int tt = t + 16 * hf;
-                            const float z = hf ? vb[t] : va[t];
-                            const float xv = f32 ? *reinterpret_cast<const float *>(xs_ + tt * 4 * seg)
-                                                 : __uint_as_float((uint32_t) * reinterpret_cast<const uint16_t *>(xs_ + tt * 4 * seg) << 16);
-                            const float c = __fdividef(xv * ivs[tt * 4] * nwp, 1.0f + __expf(-z));
-                            if (hf) vb[t] = c;
-                            else va[t] = c;
+                    if (*abort_v) break;
+                    tc_fence_after();
+                    if (col_lo >= col_hi && lane == 0) mbar_arrive(&acc_empty[half]);
+                    // a pass is issued even when this set has no tokens in the item, so that every item consumes one buffer at least
+                    for (int c0 = col_lo; c0 < col_hi || c0 == col_lo; c0 += 32) {
+                        unsigned char *buf = my_buf + (pass_count & 1u) * kHcUpBufBytes, *nxt = my_buf + ((pass_count + 1) & 1u) * kHcUpBufBytes;
+                        ++pass_count;
+                        __syncwarp();  // every lane has finished reading the buffer that the next copies overwrite
+                        if (c0 + 32 < col_hi) {
+                            issue(it, c0 + 32, col_hi, nxt);
+                        } else if (item + (int)gridDim.x < n_items) {
+                            const Item itn = item_info<TILE>(a, item + gridDim.x, rbs);
+                            issue(itn, col_lo, col_hi_of(itn), nxt);
+                        } else {
+                            cp_async_commit();
                         }
-                    }
-                    const bool b0 = (lane & 1) != 0, b1 = (lane & 2) != 0;
-                    const int mine = (b0 ? 2 : 0) + (b1 ? 1 : 0);  // which of a group's four tokens this lane ends up with
-                    const int64_t at0 = (int64_t)(it.start + c0 + mine) * hc.d + j;
+                        if (c0 >= col_hi) {  // nothing to finish: only the buffer rotation above
+                            cp_async_wait<1>();
+                            break;
+                        }
+                        float va[16], vb[16];
+                        const uint32_t tcol = lane_addr + half * (uint32_t)kTile + (uint32_t)c0;
+                        tc_ld16x2(tcol, tcol + 16u, va, vb);
+                        if (c0 + 32 >= col_hi) {
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&acc_empty[half]);
+                        }
+                        cp_async_wait<1>();  // this pass's copies have landed (the next pass's may still be in flight)
+                        __syncwarp();
+                        const int live = col_hi - c0;
+                        const TX *xs_ = reinterpret_cast<const TX *>(buf + s * seg) + jj;  // token tt: + tt * 32 elements
+                        const float *ivs = reinterpret_cast<const float *>(buf + 128 * 32) + s;
+                        // First every token's term of this lane's stream, in place of its accumulator (shared-memory reads and
+                        // arithmetic only: a store to u in between would fence the next token's reads behind it, both being
+                        // generic addresses).  Then the four streams of a column - lanes l, l ^ 1, l ^ 2, l ^ 3 - are added
+                        // four tokens at a time by a reduce-scatter: three shuffles instead of the eight of four butterflies,
+                        // and it leaves each of the four lanes with the sum of one token, which that lane stores.
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float ta = i < 4 ? va[4 * i] : vb[4 * i - 16], tb = i < 4 ? va[4 * i + 1] : vb[4 * i - 15];
-                        const float tc = i < 4 ? va[4 * i + 2] : vb[4 * i - 14], td = i < 4 ? va[4 * i + 3] : vb[4 * i - 13];
-                        // lanes with bit 0 clear keep tokens a, b and send c, d; the others the reverse
-                        const float k0 = (b0 ? tc : ta) + __shfl_xor_sync(0xffffffffu, b0 ? ta : tc, 1);
-                        const float k1 = (b0 ? td : tb) + __shfl_xor_sync(0xffffffffu, b0 ? tb : td, 1);
-                        // lanes with bit 1 clear keep the first of the two and send the second; the others the reverse
-                        const float sum = (b1 ? k1 : k0) + __shfl_xor_sync(0xffffffffu, b1 ? k0 : k1, 2);
-                        if (4 * i + mine < live) {
-                            const int64_t at = at0 + (int64_t)(4 * i) * hc.d;
-                            if (f32) static_cast<float *>(hc.u)[at] = sum * 0.25f;
-                            else static_cast<uint16_t *>(hc.u)[at] = __bfloat16_as_ushort(__float2bfloat16_rn(sum * 0.25f));
+                        for (int t = 0; t < 16; ++t) {
+#pragma unroll
+                            for (int hf = 0; hf < 2; ++hf) {
+                                const int tt = t + 16 * hf;
+                                const float z = hf ? vb[t] : va[t];
+                                const float c = __fdividef(load_as_f32(xs_, tt * 32) * ivs[tt * 4] * nwp, 1.0f + __expf(-z));
+                                if (hf) vb[t] = c;
+                                else va[t] = c;
+                            }
+                        }
+                        const bool b0 = (lane & 1) != 0, b1 = (lane & 2) != 0;
+                        const int mine = (b0 ? 2 : 0) + (b1 ? 1 : 0);  // which of a group's four tokens this lane ends up with
+                        TX *up = static_cast<TX *>(hc.u) + (int64_t)(it.start + c0 + mine) * hc.d + j;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float ta = i < 4 ? va[4 * i] : vb[4 * i - 16], tb = i < 4 ? va[4 * i + 1] : vb[4 * i - 15];
+                            const float tc = i < 4 ? va[4 * i + 2] : vb[4 * i - 14], td = i < 4 ? va[4 * i + 3] : vb[4 * i - 13];
+                            // lanes with bit 0 clear keep tokens a, b and send c, d; the others the reverse
+                            const float k0 = (b0 ? tc : ta) + __shfl_xor_sync(0xffffffffu, b0 ? ta : tc, 1);
+                            const float k1 = (b0 ? td : tb) + __shfl_xor_sync(0xffffffffu, b0 ? tb : td, 1);
+                            // lanes with bit 1 clear keep the first of the two and send the second; the others the reverse
+                            const float sum = (b1 ? k1 : k0) + __shfl_xor_sync(0xffffffffu, b1 ? k0 : k1, 2);
+                            if (4 * i + mine < live) store_from_f32(up, (int64_t)(4 * i) * hc.d, sum * 0.25f);
                         }
                     }
                 }
-            }
-            cp_async_wait<0>();
+                cp_async_wait<0>();
+            };
+            if (a.hc.f32) run(std::true_type{});
+            else run(std::false_type{});
         }
     } else if (warp < kEpiWarps) {
         // ===================== epilogue =====================
