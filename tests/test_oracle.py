@@ -182,3 +182,40 @@ def test_hc_mix_oracle_against_plain_loops(oracle):
                 row = s * d + j
                 tot += 1 / (1 + np.exp(-float(np.dot(Wu[row], h[t])))) * float(x[t, row]) * inv[t, s] * (1 + float(nw[row]))
             assert np.isclose(u[t, j], tot / H, rtol=1e-10, atol=1e-12)
+
+
+def test_hc_mix_oracle_f16_operands(oracle):
+    """The matrix-unit form of the mix (kernels/hc_wmma.hpp:3-8): products of x, h and the weights each rounded once to F16,
+    written out element by element with numpy's half type; inv comes from the unrounded x.  The rounding moves the result by
+    about one part in a thousand, not more."""
+    rng = np.random.default_rng(4)
+    H, d, r, T, eps = 4, 32, 32, 2, 1e-6
+    wd = oracle.quantize((rng.standard_normal((r + H, H * d)) * 0.05).astype(np.float32), 32, 8)
+    x = (rng.standard_normal((T, H * d)) * 3).astype(np.float32)
+    h, w_in, inv = oracle.hc_mix_down(x, wd, H, d, r, True, eps, f16_operands=True)
+    h_exact, w_in_exact, inv_exact = oracle.hc_mix_down(x, wd, H, d, r, True, eps)
+    assert np.array_equal(inv, inv_exact)
+    W16 = oracle.affine_weights(wd).astype(np.float16).astype(np.float64)
+    x16 = x.astype(np.float16).astype(np.float64)
+    for t in range(T):
+        for n in range(r + H):
+            a = sum(inv[t, s] * float(np.dot(x16[t, s * d:(s + 1) * d], W16[n, s * d:(s + 1) * d])) for s in range(H))
+            z = a / H
+            got = h[t, n] if n < r else w_in[t, n - r]
+            want = z / (1 + np.exp(-z)) if n < r else 2 / (1 + np.exp(-z))
+            assert np.isclose(got, want, rtol=1e-10, atol=1e-12)
+    assert 0 < np.max(np.abs(h - h_exact)) <= 1e-2 * np.sqrt(np.mean(h_exact ** 2))
+    wu = oracle.quantize((rng.standard_normal((H * d, r)) * 0.2).astype(np.float32), 32, 4)
+    nw = (rng.standard_normal(H * d) * 0.1).astype(np.float32)
+    u = oracle.hc_mix_up(h, wu, x, nw, inv, H, d, f16_operands=True)
+    Wu16 = oracle.affine_weights(wu).astype(np.float16).astype(np.float64)
+    h16 = h.astype(np.float16).astype(np.float64)
+    for t in range(T):
+        for j in range(d):
+            tot = 0.0
+            for s in range(H):
+                row = s * d + j
+                tot += 1 / (1 + np.exp(-float(np.dot(Wu16[row], h16[t])))) * float(x[t, row]) * inv[t, s] * (1 + float(nw[row]))
+            assert np.isclose(u[t, j], tot / H, rtol=1e-10, atol=1e-12)
+    u_exact = oracle.hc_mix_up(h, wu, x, nw, inv, H, d)
+    assert 0 < np.max(np.abs(u - u_exact)) <= 1e-2 * np.sqrt(np.mean(u_exact ** 2))
