@@ -130,3 +130,32 @@ def test_layer_entry_checks_its_argument_block(lib):
     assert lib.sxb_moe_layer(C.byref(a), None) == 1 and "experts [0, 64) of 32" in lib.sxb_last_error().decode()
     a.E_total = 64
     assert lib.sxb_moe_layer(C.byref(a), None) == 1 and "null buffer" in lib.sxb_last_error().decode()
+
+
+def test_hc_wmma_workspace_sizes_and_preconditions(lib):
+    """The workspace sizes of the tensor-core hyper-connection mix are host arithmetic: they hold at least what the
+    launchers lay out (grouping workspace, restacked weight, F16 operand, per-slot dots / un-chunked weight, F16 h), grow
+    with T, and bad shapes are refused with a message, before any launch."""
+    from strixite_b200 import kernels as K
+    T, H, d, r = 300, 4, 2560, 320
+    R, Rp = r + H, 336
+    need = K.hc_wmma_workspace_bytes(T, H, d, R, 8, 64)
+    parts = K.moe_route_workspace_bytes(T * H, 1, H) + H * Rp * d + 2 * H * Rp * (d // 64) * 2 + T * H * d * 2 + T * H * Rp * 4
+    assert parts <= need <= parts + 8 * 256
+    assert K.hc_wmma_workspace_bytes(2 * T, H, d, R, 8, 64) > need
+    assert K.hc_wmma_workspace_bytes(T, H, d, R, 4, 64) < need
+    up = K.hc_mix_up_wmma_workspace_bytes(T, H, d, r, 4, 32)
+    Kp = 384
+    parts_up = H * d * Kp // 2 + 2 * H * d * (Kp // 32) * 2 + T * Kp * 2
+    assert parts_up <= up <= parts_up + 8 * 256
+    for bad in ((0, H, d, R, 8, 64), (T, 3, d, R, 8, 64), (T, H, 100, R, 8, 64), (T, H, d, R, 5, 64), (T, H, d, R, 8, 48), (70000, H, d, R, 8, 64)):
+        with pytest.raises(K.Error, match="hc_mix_down_wmma_workspace_bytes"):
+            K.hc_wmma_workspace_bytes(*bad)
+    with pytest.raises(K.Error, match="hc_mix_up_wmma_workspace_bytes"):
+        K.hc_mix_up_wmma_workspace_bytes(T, H, d, 48, 8, 32)
+    with pytest.raises(K.Error, match="null pointer"):
+        K.hc_inject_inv(0, 4096, 8192, 4, 4, 64, 1e-6, 16384, K.Act.BF16, stream=0)
+    with pytest.raises(K.Error, match="eps must be finite"):
+        K.hc_inject_inv(1 << 20, 4096, 8192, 4, 4, 64, 0.0, 16384, K.Act.BF16, stream=0)
+    with pytest.raises(K.Error, match="y overlaps the streams"):
+        K.hc_inject_inv(1 << 20, 4096, (1 << 20) + 64, 4, 4, 64, 1e-6, 16384, K.Act.BF16, stream=0)
