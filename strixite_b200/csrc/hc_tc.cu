@@ -69,12 +69,13 @@ __global__ void __launch_bounds__(256) hc_stack_down_kernel(const uint8_t *__res
                                                             const uint16_t *__restrict__ minv, int64_t R, int64_t Rp, int64_t d, int64_t G,
                                                             int bits, uint32_t *__restrict__ qo, uint16_t *__restrict__ so,
                                                             uint16_t *__restrict__ mo) {
-    const int64_t row_words = d * bits / 32, row_groups = d / G, stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t row_vecs = d * bits / 128, row_groups = d / G, stride = (int64_t)gridDim.x * blockDim.x;  // 16-byte pieces a stream's row
     const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const uint32_t *qi = reinterpret_cast<const uint32_t *>(q);
-    for (int64_t i = first; i < kStreams * Rp * row_words; i += stride) {
-        const int64_t w = i % row_words, sn = i / row_words, n = sn % Rp, s = sn / Rp;
-        qo[i] = n < R ? qi[(n * kStreams + s) * row_words + w] : 0u;
+    const uint4 *qi = reinterpret_cast<const uint4 *>(q);
+    uint4 *qv = reinterpret_cast<uint4 *>(qo);
+    for (int64_t i = first; i < kStreams * Rp * row_vecs; i += stride) {
+        const int64_t w = i % row_vecs, sn = i / row_vecs, n = sn % Rp, s = sn / Rp;
+        qv[i] = n < R ? __ldg(qi + (n * kStreams + s) * row_vecs + w) : make_uint4(0u, 0u, 0u, 0u);
     }
     for (int64_t i = first; i < kStreams * Rp * row_groups; i += stride) {
         const int64_t g = i % row_groups, sn = i / row_groups, n = sn % Rp, s = sn / Rp;
@@ -187,12 +188,13 @@ __global__ void __launch_bounds__(256) hc_unchunk_up_kernel(const uint8_t *__res
                                                             int bits, uint32_t *__restrict__ qo, uint16_t *__restrict__ so,
                                                             uint16_t *__restrict__ mo) {
     const int64_t N = kStreams * d;
-    const int64_t cw = bits, chunks = r / kChunk, chunks_p = Kp / kChunk, groups = r / G, groups_p = Kp / G;  // cw: words per chunk
+    const int64_t cv = bits / 4, chunks = r / kChunk, chunks_p = Kp / kChunk, groups = r / G, groups_p = Kp / G;  // cv: 16-byte pieces a chunk
     const int64_t stride = (int64_t)gridDim.x * blockDim.x, first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const uint32_t *qi = reinterpret_cast<const uint32_t *>(q);
-    for (int64_t i = first; i < N * chunks_p * cw; i += stride) {
-        const int64_t w = i % cw, nc = i / cw, c = nc % chunks_p, n = up_source_row(nc / chunks_p, d);
-        qo[i] = c < chunks ? qi[(c * N + n) * cw + w] : 0u;
+    const uint4 *qi = reinterpret_cast<const uint4 *>(q);
+    uint4 *qv = reinterpret_cast<uint4 *>(qo);
+    for (int64_t i = first; i < N * chunks_p * cv; i += stride) {
+        const int64_t w = i % cv, nc = i / cv, c = nc % chunks_p, n = up_source_row(nc / chunks_p, d);
+        qv[i] = c < chunks ? __ldg(qi + (c * N + n) * cv + w) : make_uint4(0u, 0u, 0u, 0u);
     }
     for (int64_t i = first; i < N * groups_p; i += stride) {
         const int64_t g = i % groups_p, n = up_source_row(i / groups_p, d);
@@ -224,7 +226,7 @@ int check_shape(const char *fn, int64_t T, int64_t H, int64_t d, const SxbQView 
     SXB_CHECK(w != nullptr && w->q != nullptr && w->scale != nullptr && w->minv != nullptr, fn, ": null weight pointer");
     SXB_CHECK(w->G == 32 || w->G == 64 || w->G == 128, fn, ": group size ", w->G, " unsupported (32, 64 or 128)");
     SXB_CHECK(w->K >= w->G && w->K % w->G == 0, fn, ": K = ", w->K, " must be a positive multiple of group size ", w->G);
-    SXB_CHECK(reinterpret_cast<uintptr_t>(w->q) % 4 == 0, fn, ": code array ", (const void *)w->q, " must be 4-byte aligned");
+    SXB_CHECK(aligned16(w->q), fn, ": code array ", (const void *)w->q, " must be 16-byte aligned");
     return SXB_OK;
 }
 
@@ -267,8 +269,8 @@ int mix_down_tc(const void *x, const SxbQView *w, int64_t T, int64_t H, int64_t 
     auto *partial = reinterpret_cast<float *>(base + L.partial);
     SxbQView stacked{base + L.wq, reinterpret_cast<uint16_t *>(base + L.wscale), reinterpret_cast<uint16_t *>(base + L.wmin), kStreams * Rp, d, w->G};
 
-    const int64_t stack_words = kStreams * Rp * d * BITS / 32;
-    hc_stack_down_kernel<<<(unsigned)std::min<int64_t>((stack_words + 255) / 256, (int64_t)sm_count() * 8), 256, 0, st>>>(
+    const int64_t stack_vecs = kStreams * Rp * d * BITS / 128;
+    hc_stack_down_kernel<<<(unsigned)std::min<int64_t>((stack_vecs + 255) / 256, (int64_t)sm_count() * 8), 256, 0, st>>>(
         w->q, w->scale, w->minv, R, Rp, d, w->G, BITS, reinterpret_cast<uint32_t *>(base + L.wq), reinterpret_cast<uint16_t *>(base + L.wscale),
         reinterpret_cast<uint16_t *>(base + L.wmin));
     SXB_CHECK_LAUNCH(fn, " restacking the weight, R=", R, " d=", d);
@@ -322,8 +324,8 @@ int mix_up_tc(const float *h, const SxbQView *w, const void *x, const float *nor
     auto st = static_cast<cudaStream_t>(stream);
     SxbQView rows{base + L.wq, reinterpret_cast<uint16_t *>(base + L.wscale), reinterpret_cast<uint16_t *>(base + L.wmin), N, Kp, w->G};
 
-    const int64_t words = N * Kp * BITS / 32;
-    hc_unchunk_up_kernel<<<(unsigned)std::min<int64_t>((words + 255) / 256, (int64_t)sm_count() * 8), 256, 0, st>>>(
+    const int64_t vecs = N * Kp * BITS / 128;
+    hc_unchunk_up_kernel<<<(unsigned)std::min<int64_t>((vecs + 255) / 256, (int64_t)sm_count() * 8), 256, 0, st>>>(
         w->q, w->scale, w->minv, d, r, Kp, w->G, BITS, reinterpret_cast<uint32_t *>(base + L.wq), reinterpret_cast<uint16_t *>(base + L.wscale),
         reinterpret_cast<uint16_t *>(base + L.wmin));
     SXB_CHECK_LAUNCH(fn, " un-chunking the weight, N=", N, " r=", r);
