@@ -491,7 +491,10 @@ def roofline_tensor(cfg, res, peaks, world):
     # codes + scales / mins + tile-blocked activations, a ratio of 1.00; the same sum for this launch, times that ratio.
     ly = res["stack"].layers[0]
     traffic = 1.003 * (ly.w.gate_up.bytes() + cfg.T * cfg.k / world / micro * cfg.d * 2)
-    return dict(bound="tensor", kernel="grouped_tc_kernel<gate_up+swiglu>", achieved=achieved, peak=peak, unit="TFLOP/s",
+    # which tcgen05 kernel serves gate/up (launch_tc in csrc/grouped_tc.cu): tile-blocked activations and >= 160 slots an expert
+    # on average go to the 128-row x 256-token kernel, fewer stay on the 256-row x 128-token one
+    name = "tiled_tc_kernel" if cfg.T * cfg.k / world / micro / (cfg.E / world) >= 160 else "grouped_tc_kernel"
+    return dict(bound="tensor", kernel=name + "<gate_up+swiglu>", achieved=achieved, peak=peak, unit="TFLOP/s",
                 frac=achieved / peak, peak_source=peaks["source"] + " (sustained bf16)",
                 frac_of_burst=achieved / peaks["tflops_burst"], peak_burst=peaks["tflops_burst"], traffic=traffic,
                 traffic_source="dram bytes of an ncu capture of a reduced case, scaled by algorithmic bytes",
