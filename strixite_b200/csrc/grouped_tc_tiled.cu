@@ -50,18 +50,21 @@ constexpr int kTmemCols = 512;
 // TILE = tokens per item at most = columns of an accumulator.  Tensor memory holds two accumulators when they fit beside at
 // least four A stages (an item's epilogue then runs under the next item's mainloop), else one; the rest is A stages, as
 // many as the activation tiles of as many k-blocks fit in shared memory.
-template <int TILE>
+// HC: the shape of the hyper-connection up mix (kTcHcUp), whose epilogue does the arithmetic of the stream combine and is
+// what its items wait for: a second set of epilogue warps, and a shorter ring of codes (its contractions are a few
+// k-blocks) to leave their staging buffers room in shared memory.
+template <int TILE, bool HC = false>
 struct Shape {
     static constexpr int kAccs = 2 * TILE + 4 * kAStageCols <= kTmemCols ? 2 : 1;
     static constexpr int kStageBytes = TILE * kBK * 2;  // the activation tile of one k-block
     static constexpr int kByTmem = (kTmemCols - kAccs * TILE) / kAStageCols, kBySmem = TILE > 192 ? 6 : 8;
     static constexpr int kStages = kByTmem < kBySmem ? kByTmem : kBySmem;
-    static constexpr int kWSlots = TILE > 192 ? 4 : 8;  // ring slots of packed codes (8 KB each)
+    static constexpr int kWSlots = TILE > 192 ? 4 : HC ? 6 : 8;  // ring slots of packed codes (8 KB each)
     // Producer warps per lane quadrant: they take every kWays-th k-block each.
     static constexpr int kWays = TILE > 192 ? 3 : 2;
     // Epilogue warps per lane quadrant: a single accumulator's epilogue is exposed (the MMA warp waits for it), so its
     // columns are split between two sets of warps; with two accumulators one set keeps up.
-    static constexpr int kEpiSets = kAccs == 1 ? 2 : 1;
+    static constexpr int kEpiSets = kAccs == 1 || HC ? 2 : 1;
     // warps: epilogue | MMA issue, activation copies, ring of weight codes, one idle | producers
     static constexpr int kEpiWarps = 4 * kEpiSets, kMmaWarp = kEpiWarps, kBCopyWarp = kEpiWarps + 1, kWCopyWarp = kEpiWarps + 2,
                          kFirstAWarp = kEpiWarps + 4;
@@ -115,11 +118,12 @@ __device__ inline int next_valid_item(const TcArgs &a, int item, int n_items, in
 }
 
 template <int BITS, int G, int MODE, int TILE>
-__global__ void __launch_bounds__(Shape<TILE>::kThreads, 1) tiled_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap wmap) {
-    constexpr int kTile = TILE, kAccs = Shape<TILE>::kAccs, kStages = Shape<TILE>::kStages, kStageBytes = Shape<TILE>::kStageBytes,
-                  kWSlots = Shape<TILE>::kWSlots, kWays = Shape<TILE>::kWays, kEpiSets = Shape<TILE>::kEpiSets,
-                  kEpiWarps = Shape<TILE>::kEpiWarps, kMmaWarp = Shape<TILE>::kMmaWarp, kBCopyWarp = Shape<TILE>::kBCopyWarp,
-                  kWCopyWarp = Shape<TILE>::kWCopyWarp, kFirstAWarp = Shape<TILE>::kFirstAWarp;
+__global__ void __launch_bounds__((Shape<TILE, MODE == kTcHcUp>::kThreads), 1)
+    tiled_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap wmap) {
+    using S = Shape<TILE, MODE == kTcHcUp>;
+    constexpr int kTile = TILE, kAccs = S::kAccs, kStages = S::kStages, kStageBytes = S::kStageBytes, kWSlots = S::kWSlots, kWays = S::kWays,
+                  kEpiSets = S::kEpiSets, kEpiWarps = S::kEpiWarps, kMmaWarp = S::kMmaWarp, kBCopyWarp = S::kBCopyWarp,
+                  kWCopyWarp = S::kWCopyWarp, kFirstAWarp = S::kFirstAWarp;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment of the operand tiles (the swizzle pattern repeats every 1024 bytes).
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -682,7 +686,7 @@ int launch_tiled_tc(const char *fn, TcArgs a, int64_t G, cudaStream_t st) {
     // (the up mix of the hyper-connections contracts over its rank, at most 1024: it has the narrower form only)
     const bool wide = MODE != kTcHcUp && a.K >= 2048;
     using SB = Shape<kTcTileB>;
-    using SA = Shape<kTcTileA>;
+    using SA = Shape<kTcTileA, MODE == kTcHcUp>;
     const size_t smem = (wide ? (size_t)SB::kStages * SB::kStageBytes + (size_t)SB::kWSlots * kWSlotBytes
                               : (size_t)SA::kStages * SA::kStageBytes + (size_t)SA::kWSlots * kWSlotBytes) + 1024 +
                         (MODE == kTcHcUp ? (size_t)SA::kEpiWarps * 2 * kHcUpBufBytes : 0);
