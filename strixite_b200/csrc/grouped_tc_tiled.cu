@@ -28,7 +28,8 @@
 // accumulator(s) first, then one 32-column A stage per pipeline stage.
 //
 // One persistent CTA per SM.  Warps: the epilogue first (one per lane quadrant; two per quadrant, each taking half of the
-// columns, where there is a single accumulator whose epilogue the MMA warp has to wait for), then MMA issue, activation
+// columns, where there is a single accumulator whose epilogue the MMA warp has to wait for, and in the hyper-connection up
+// mix, whose epilogue carries the arithmetic of the stream combine - see TcHcUp), then MMA issue, activation
 // copies, the ring of weight codes and one idle warp, then the
 // weight producers (a lane quadrant's warps take every second or third k-block each).  A producer hands its k-block
 // over before it waits for anything its next one needs.  Every wait is bounded: past the limit the CTA raises its abort
